@@ -1,0 +1,93 @@
+// Shared helpers of the kernels: element types, conversions, warp and block
+// reductions, the launch-error convention of the exported functions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers and a
+// stream, and returns 0 or a negative code; the message of the last refusal is
+// kept per thread and read with hos_last_error().  A function that cannot take
+// a size says so and launches nothing.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace hos {
+
+typedef __nv_bfloat16 bf16;
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// ---- error reporting ---------------------------------------------------------------
+inline char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+#define HOS_REFUSE(...)                                                     \
+    do {                                                                    \
+        snprintf(hos::error_buffer(), 512, __VA_ARGS__);                    \
+        return -1;                                                          \
+    } while (0)
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(error_buffer(), 512, "%s: %s", what, cudaGetErrorString(e));
+        return -2;
+    }
+    return 0;
+}
+
+// ---- conversions -------------------------------------------------------------------
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- reductions --------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  All threads
+// get the result.  Safe to call repeatedly with the same scratch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+// Soft-cap c*tanh(v/c), identity when c <= 0.  Precise tanhf: the 32-bit path
+// and the logits use this one.
+__device__ __forceinline__ float softcap_precise(float v, float c) {
+    return c > 0.f ? c * tanhf(v / c) : v;
+}
+
+// tanh-form GELU: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float c = 0.79788452f;   // sqrt(2/pi) as 32-bit arithmetic gives it: sqrtf(2.f / 3.14159274f)
+    return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+
+}  // namespace hos

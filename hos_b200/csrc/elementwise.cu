@@ -1,0 +1,279 @@
+// Memory-bound kernels around the matrix products: embedding, RMSNorm and its
+// fusions with the residual sum, rotary encoding fused with the cache write,
+// the gated activation, row gather.  Statistics, angles and the residual sum are
+// 32-bit; only what a matrix product reads next is rounded to the activation type.
+#include "common.cuh"
+#include "kv_layout.cuh"
+
+namespace hos {
+
+// ---- embedding ---------------------------------------------------------------------
+// out[n, :] = table[token[n], :] * scale   (32-bit multiply; a negative token id,
+// which marks padding, gives a zero row).
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float scale, float* __restrict__ out, int D) {
+    const int n = blockIdx.x;
+    const int tok = tokens[n];
+    float* o = out + (size_t)n * D;
+    if (tok < 0) {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = 0.f;
+        return;
+    }
+    const TW* row = table + (size_t)tok * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = to_float(row[d]) * scale;
+}
+
+// ---- RMSNorm -----------------------------------------------------------------------
+// y = x * rsqrt(mean(x^2) + eps) * (w + add_one).  One block per row; the row is
+// held in shared memory between the two passes.
+template <typename TIn, typename TOut>
+__global__ void rmsnorm_kernel(const TIn* __restrict__ x, const float* __restrict__ w, float eps,
+                               float add_one, TOut* __restrict__ out, int D) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = to_float(x[base + d]);
+        row[d] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x)
+        out[base + d] = from_float<TOut>(row[d] * r * (w[d] + add_one));
+}
+
+// x += RMSNorm(y; w_post);  optionally h = RMSNorm(x; w_next).
+// The sandwich arrangement's "post norm, residual sum, next pre norm" in one pass
+// over the row: y is read once, x is read and written once, h is written once.
+template <typename TY, typename TH>
+__global__ void norm_add_norm_kernel(const TY* __restrict__ y, const float* __restrict__ w_post,
+                                     float eps_post, float add_one_post, float* __restrict__ x,
+                                     const float* __restrict__ w_next, float eps_next,
+                                     float add_one_next, TH* __restrict__ h, int D) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = to_float(y[base + d]);
+        row[d] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps_post);
+    float ss2 = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = x[base + d] + row[d] * r * (w_post[d] + add_one_post);
+        x[base + d] = v;
+        row[d] = v;
+        ss2 += v * v;
+    }
+    if (h == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float r2 = 1.0f / sqrtf(ss2 / (float)D + eps_next);
+    for (int d = threadIdx.x; d < D; d += blockDim.x)
+        h[base + d] = from_float<TH>(row[d] * r2 * (w_next[d] + add_one_next));
+}
+
+// x += y (plain residual sum in 32-bit, for arrangements without a post norm).
+template <typename TY>
+__global__ void residual_add_kernel(const TY* __restrict__ y, float* __restrict__ x, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += to_float(y[i]);
+}
+
+// ---- rotary encoding + cache write --------------------------------------------------
+// One block per token.  q and k rows of the fused projection output are rotated in
+// place (angle = position * inv_freq[i], sincosf in 32-bit); the rotated key and the
+// value go to the token's place in the paged cache.  A token whose place in a ring
+// is overwritten by a later token of the same step is not stored.
+// style 0: pairs (i, i + rot/2) ("rotate half"); style 1: pairs (2i, 2i+1).
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int n_heads,
+                                     const int* __restrict__ token_pos,
+                                     const int* __restrict__ token_seq,
+                                     const int* __restrict__ seq_slot,
+                                     const int* __restrict__ seq_len_after,
+                                     const float* __restrict__ inv_freq, int rotary_dim, int style,
+                                     PagedKV cache, int write_cache) {
+    const int n = blockIdx.x;
+    const int seq = token_seq[n];
+    if (seq < 0) return;
+    const int pos = token_pos[n];
+    const int hd = cache.head_dim, nkv = cache.n_kv_heads;
+    const int half = rotary_dim >> 1;
+    T* row = qkv + (size_t)n * row_stride;
+    // rotate q heads and k heads: heads [0, n_heads) are q, [n_heads, n_heads+nkv) are k
+    const int n_rot_heads = n_heads + nkv;
+    for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int a = style == 0 ? i : 2 * i;
+        const int b = style == 0 ? i + half : 2 * i + 1;
+        T* hp = row + (size_t)head * hd;
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float x0 = to_float(hp[a]), x1 = to_float(hp[b]);
+        hp[a] = from_float<T>(x0 * c - x1 * s);
+        hp[b] = from_float<T>(x0 * s + x1 * c);
+    }
+    if (!write_cache) return;
+    __syncthreads();
+    if (cache.ring_pages > 0 && pos + cache.ring_pages * kPageTokens < seq_len_after[seq]) return;
+    const int slot = seq_slot[seq];
+    const int lp = pos / kPageTokens, r = pos % kPageTokens;
+    const int page = cache.page_table[(size_t)slot * cache.table_stride + kv_table_entry(cache, lp)];
+    const T* ksrc = row + (size_t)n_heads * hd;
+    const T* vsrc = ksrc + (size_t)nkv * hd;
+    T* kp = (T*)cache.k_pages;
+    T* vp = (T*)cache.v_pages;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+        const int kvh = idx / hd, d = idx - kvh * hd;
+        const size_t off = kv_tile_offset(cache, page, kvh) + kv_elem_offset(r, d, hd);
+        kp[off] = ksrc[idx];
+        vp[off] = vsrc[idx];
+    }
+}
+
+// ---- gated activation ---------------------------------------------------------------
+// out[n, f] = act(gu[n, f]) * gu[n, F + f]; act 0 = tanh-form GELU, 1 = SiLU.
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, int act) {
+    const size_t n = blockIdx.x;
+    const int f = blockIdx.y * blockDim.x + threadIdx.x;
+    if (f >= F) return;
+    const float g = to_float(gu[n * 2 * F + f]);
+    const float u = to_float(gu[n * 2 * F + F + f]);
+    const float a = act == 0 ? gelu_tanh(g) : g / (1.f + expf(-g));
+    out[n * F + f] = from_float<T>(a * u);
+}
+
+// ---- row gather ----------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
+                                   float* __restrict__ out, int D) {
+    const int i = blockIdx.x;
+    const float* src = x + (size_t)idx[i] * D;
+    float* dst = out + (size_t)i * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+}
+
+static int row_smem_ok(const void* kernel, int D) {
+    size_t bytes = (size_t)D * sizeof(float);
+    if (bytes > 200 * 1024) return -1;
+    if (bytes > 48 * 1024)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    return 0;
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
+extern "C" int hos_embed(const int* tokens, const void* table, int table_dtype, float scale,
+                         float* out, int N, int D, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (table_dtype == kBF16)
+        embed_kernel<bf16><<<N, 256, 0, stream>>>(tokens, (const bf16*)table, scale, out, D);
+    else if (table_dtype == kF32)
+        embed_kernel<float><<<N, 256, 0, stream>>>(tokens, (const float*)table, scale, out, D);
+    else
+        HOS_REFUSE("embed: unknown table dtype %d", table_dtype);
+    return check_launch("embed");
+}
+
+extern "C" int hos_rmsnorm(const void* x, int x_dtype, const float* w, float eps, int add_one,
+                           void* out, int out_dtype, int N, int D, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const size_t smem = (size_t)D * sizeof(float);
+    const float a1 = add_one ? 1.f : 0.f;
+#define HOS_LAUNCH_NORM(TI, TO)                                                              \
+    do {                                                                                     \
+        if (row_smem_ok((const void*)rmsnorm_kernel<TI, TO>, D))                             \
+            HOS_REFUSE("rmsnorm: width %d does not fit a block's shared memory", D);         \
+        rmsnorm_kernel<TI, TO><<<N, 256, smem, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D); \
+    } while (0)
+    if (x_dtype == kF32 && out_dtype == kF32) HOS_LAUNCH_NORM(float, float);
+    else if (x_dtype == kF32 && out_dtype == kBF16) HOS_LAUNCH_NORM(float, bf16);
+    else if (x_dtype == kBF16 && out_dtype == kBF16) HOS_LAUNCH_NORM(bf16, bf16);
+    else if (x_dtype == kBF16 && out_dtype == kF32) HOS_LAUNCH_NORM(bf16, float);
+    else HOS_REFUSE("rmsnorm: unknown dtypes %d -> %d", x_dtype, out_dtype);
+#undef HOS_LAUNCH_NORM
+    return check_launch("rmsnorm");
+}
+
+// x += RMSNorm(y; w_post); if h != NULL also h = RMSNorm(x; w_next).  y and h share a dtype.
+extern "C" int hos_norm_add_norm(const void* y, int y_dtype, const float* w_post, float eps_post,
+                                 int add_one_post, float* x, const float* w_next, float eps_next,
+                                 int add_one_next, void* h, int N, int D, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const size_t smem = (size_t)D * sizeof(float);
+    const float a1 = add_one_post ? 1.f : 0.f, a2 = add_one_next ? 1.f : 0.f;
+    if (y_dtype == kF32) {
+        if (row_smem_ok((const void*)norm_add_norm_kernel<float, float>, D))
+            HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);
+        norm_add_norm_kernel<float, float><<<N, 256, smem, stream>>>(
+            (const float*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (float*)h, D);
+    } else if (y_dtype == kBF16) {
+        if (row_smem_ok((const void*)norm_add_norm_kernel<bf16, bf16>, D))
+            HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);
+        norm_add_norm_kernel<bf16, bf16><<<N, 256, smem, stream>>>(
+            (const bf16*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (bf16*)h, D);
+    } else {
+        HOS_REFUSE("norm_add_norm: unknown dtype %d", y_dtype);
+    }
+    return check_launch("norm_add_norm");
+}
+
+extern "C" int hos_residual_add(const void* y, int y_dtype, float* x, long long n,
+                                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (y_dtype == kF32) residual_add_kernel<float><<<blocks, 256, 0, stream>>>((const float*)y, x, (size_t)n);
+    else if (y_dtype == kBF16) residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)y, x, (size_t)n);
+    else HOS_REFUSE("residual_add: unknown dtype %d", y_dtype);
+    return check_launch("residual_add");
+}
+
+extern "C" int hos_rope_kv_write(void* qkv, int dtype, int row_stride, int n_heads,
+                                 const int* token_pos, const int* token_seq, const int* seq_slot,
+                                 const int* seq_len_after, const float* inv_freq, int rotary_dim,
+                                 int style, void* k_pages, void* v_pages, const int* page_table,
+                                 int table_stride, int ring_pages, int n_kv_heads, int head_dim,
+                                 int write_cache, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+        HOS_REFUSE("rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    if (style != 0 && style != 1) HOS_REFUSE("rope: unknown pairing style %d", style);
+    PagedKV c{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
+    if (dtype == kF32)
+        rope_kv_write_kernel<float><<<N, 256, 0, stream>>>((float*)qkv, row_stride, n_heads, token_pos,
+            token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
+    else if (dtype == kBF16)
+        rope_kv_write_kernel<bf16><<<N, 256, 0, stream>>>((bf16*)qkv, row_stride, n_heads, token_pos,
+            token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
+    else
+        HOS_REFUSE("rope: unknown dtype %d", dtype);
+    return check_launch("rope_kv_write");
+}
+
+extern "C" int hos_gated_act(const void* gu, void* out, int dtype, int N, int F, int act,
+                             cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (act != 0 && act != 1) HOS_REFUSE("gated_act: unknown activation %d", act);
+    dim3 grid(N, (F + 255) / 256);
+    if (dtype == kF32) gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, F, act);
+    else if (dtype == kBF16) gated_act_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, act);
+    else HOS_REFUSE("gated_act: unknown dtype %d", dtype);
+    return check_launch("gated_act");
+}
+
+extern "C" int hos_gather_rows(const float* x, const int* idx, float* out, int n, int D,
+                               cudaStream_t stream) {
+    if (n <= 0) return 0;
+    gather_rows_kernel<<<n, 256, 0, stream>>>(x, idx, out, D);
+    return check_launch("gather_rows");
+}

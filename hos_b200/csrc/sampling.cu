@@ -1,0 +1,321 @@
+// Token choice on the device, one block per sequence.  The order of operations is
+// the reference sampler's (src/lib.rs:91-172): repetition penalty over the recent
+// tokens (once per occurrence, :102-118); temp <= 0 -> arg max, first maximum wins
+// (:120-128); else p_i = exp((l_i - max) / temp) (:130-135); keep the top_k most
+// probable (:142-148), then the shortest prefix of them, in falling order of
+// probability, whose mass reaches top_p (:149-160); draw r = u * (kept mass) and walk
+// the kept tokens in that same order until the running sum exceeds r (:162-171).
+// u comes from the caller's xorshift64 stream (src/lib.rs:78-85).
+//
+// The reference sorts; this kernel never does.  Everything above depends only on the
+// order "higher probability first, lower token id first among equals", so the k-th
+// token, the top_p cut and the drawn token are found by radix selection: per pass a
+// histogram (of counts or of probability mass) over one digit of an order-preserving
+// integer image of the logit, kept private per thread in shared memory so that no
+// atomics are needed, then a walk over the 32 bins.  Equal logits have equal
+// probability, so positions among equals follow by division and a selection on the id.
+#include "common.cuh"
+
+namespace hos {
+
+constexpr int kThreads = 512;
+constexpr int kDigitBits = 5;
+constexpr int kBins = 1 << kDigitBits;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // larger float -> larger key
+}
+
+struct Kept {          // the kept set: key > x, or key == x and id <= last_id
+    uint32_t x;
+    int last_id;
+};
+__device__ __forceinline__ bool in_kept(const Kept& k, uint32_t key, int id) {
+    return key > k.x || (key == k.x && id <= k.last_id);
+}
+
+struct SelectResult {
+    bool found;
+    uint32_t x;        // the selected digit string
+    float above;       // weight of everything ordered before it
+    float equal;       // weight of the elements that share it
+};
+
+// Radix selection, most significant digit first, over elements for which `filter`
+// holds, ordered by `keyfn` descending, with weights `wfn`.  Finds x with
+//   strict == false:  W(key > x) <  target <= W(key >= x)
+//   strict == true :  W(key > x) <= target <  W(key >= x)
+// hist: kBins * kThreads floats of shared memory; red: kBins floats.
+template <typename KeyFn, typename WFn, typename FilterFn>
+__device__ SelectResult radix_select(int V, int nbits, float target, bool strict, KeyFn keyfn,
+                                     WFn wfn, FilterFn filter, float* hist, float* red) {
+    const int tid = threadIdx.x;
+    uint32_t prefix = 0, prefix_mask = 0;
+    float above = 0.f, equal = 0.f;
+    const int passes = (nbits + kDigitBits - 1) / kDigitBits;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int shift = max(0, nbits - (pass + 1) * kDigitBits);
+        const int width = min(kDigitBits, nbits - pass * kDigitBits);
+        const uint32_t dmask = (1u << width) - 1u;
+        for (int b = 0; b < kBins; ++b) hist[b * kThreads + tid] = 0.f;
+        for (int i = tid; i < V; i += kThreads) {
+            if (!filter(i)) continue;
+            const uint32_t key = keyfn(i);
+            if ((key & prefix_mask) != prefix) continue;
+            hist[((key >> shift) & dmask) * kThreads + tid] += wfn(i);
+        }
+        __syncthreads();
+        // reduce each bin over the threads: 16 threads per bin, 32 columns each
+        {
+            const int bin = tid >> 4, part = tid & 15;
+            float s = 0.f;
+            for (int c = part; c < kThreads; c += 16) s += hist[bin * kThreads + c];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (part == 0) red[bin] = s;
+        }
+        __syncthreads();
+        // every thread walks the bins from the highest digit down (same result everywhere)
+        int chosen = -1, lowest = -1;
+        float acc = above, acc_lowest = above;
+        for (int b = (int)dmask; b >= 0; --b) {
+            const float next = acc + red[b];
+            const bool cross = strict ? (next > target) : (next >= target);
+            if (red[b] > 0.f) { lowest = b; acc_lowest = acc; }
+            if (cross && red[b] > 0.f) { chosen = b; break; }
+            acc = next;
+        }
+        __syncthreads();
+        if (chosen < 0 && pass > 0 && lowest >= 0) {
+            // the parent bin crossed the target but, summed in another order, its parts
+            // fall a rounding short: the crossing is in the last non-empty part
+            chosen = lowest;
+            acc = acc_lowest;
+        }
+        if (chosen < 0) return SelectResult{false, 0u, acc, 0.f};
+        above = acc;
+        equal = red[chosen];
+        prefix |= ((uint32_t)chosen) << shift;
+        prefix_mask |= dmask << shift;
+        __syncthreads();
+    }
+    return SelectResult{true, prefix, above, equal};
+}
+
+// id of the j-th (1-based) smallest token id among kept elements whose key is x
+template <typename KeyFn>
+__device__ int nth_equal_id(int V, uint32_t x, const Kept& kept, int j, int id_bits, KeyFn keyfn,
+                            float* hist, float* red) {
+    const uint32_t idmask = (1u << id_bits) - 1u;
+    SelectResult r = radix_select(
+        V, id_bits, (float)j, false,
+        [&](int i) { return (~(uint32_t)i) & idmask; },      // descending in ~id = ascending in id
+        [&](int) { return 1.f; },
+        [&](int i) { return keyfn(i) == x && in_kept(kept, x, i); }, hist, red);
+    if (!r.found) return -1;
+    return (int)((~r.x) & idmask);
+}
+
+// One block per row.  logits rows are modified in place for the penalty and restored.
+__global__ void __launch_bounds__(kThreads)
+sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict__ uniforms,
+              const int* __restrict__ recent, int recent_stride, const int* __restrict__ recent_len,
+              float temp, int top_k, float top_p, float rep_penalty, int* __restrict__ out) {
+    extern __shared__ float smem[];
+    float* hist = smem;                       // kBins * kThreads
+    float* red = hist + kBins * kThreads;     // kBins
+    float* scratch = red + kBins;             // 32
+    __shared__ float saved_val[256];
+    __shared__ int saved_id[256];
+    __shared__ int n_saved;
+    __shared__ int best_id_sh;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    float* l = logits + (size_t)row * ld;
+
+    // repetition penalty, once per occurrence, first-seen originals remembered
+    const int nrec = (recent != nullptr && rep_penalty != 1.0f) ? min(recent_len[row], 256) : 0;
+    if (tid == 0) {
+        int ns = 0;
+        for (int j = 0; j < nrec; ++j) {
+            const int t = recent[(size_t)row * recent_stride + j];
+            if (t < 0 || t >= V) continue;
+            bool seen = false;
+            for (int s = 0; s < ns; ++s) seen |= (saved_id[s] == t);
+            if (!seen) { saved_id[ns] = t; saved_val[ns] = l[t]; ++ns; }
+            const float v = l[t];
+            l[t] = v > 0.f ? v / rep_penalty : v * rep_penalty;
+        }
+        n_saved = ns;
+        __threadfence_block();
+    }
+    __syncthreads();
+
+    int result;
+    // ---- arg max (also needed for the softmax's maximum) ----
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = tid; i < V; i += kThreads) {
+        const float v = l[i];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+    const float maxv = block_max(best, scratch);
+    {
+        // lowest id among the threads that hold the maximum
+        int cand = (best == maxv) ? best_i : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+        __shared__ int warp_best[kThreads / 32];
+        if ((tid & 31) == 0) warp_best[tid >> 5] = cand;
+        __syncthreads();
+        if (tid == 0) {
+            int b = 0x7fffffff;
+            for (int w = 0; w < kThreads / 32; ++w) b = min(b, warp_best[w]);
+            best_id_sh = b;
+        }
+        __syncthreads();
+    }
+    if (temp <= 0.f) {
+        result = best_id_sh;
+    } else {
+        auto keyfn = [&](int i) { return order_key(l[i]); };
+        auto prob = [&](int i) { return expf((l[i] - maxv) / temp); };   // not normalised
+        int id_bits = 1;
+        while ((1 << id_bits) < V) ++id_bits;
+        float z = 0.f;
+        for (int i = tid; i < V; i += kThreads) z += prob(i);
+        z = block_sum(z, scratch);
+
+        Kept kept{0u, V};      // everything
+        float kept_mass = z;
+        auto all = [&](int) { return true; };
+        auto kept_filter = [&](int i) { return in_kept(kept, keyfn(i), i); };
+        // ---- top-k ----
+        if (top_k > 0 && top_k < V) {
+            SelectResult r = radix_select(V, 32, (float)top_k, false, keyfn,
+                                          [&](int) { return 1.f; }, all, hist, red);
+            // r.found always holds here: top_k < V elements exist
+            const int need = top_k - (int)r.above;          // how many of the equals stay
+            Kept whole{r.x, V};
+            const int last = nth_equal_id(V, r.x, whole, need, id_bits, keyfn, hist, red);
+            kept = Kept{r.x, last};
+            float m = 0.f;
+            for (int i = tid; i < V; i += kThreads)
+                if (kept_filter(i)) m += prob(i);
+            kept_mass = block_sum(m, scratch);
+        }
+        // ---- top-p: shortest prefix whose mass reaches top_p of the WHOLE distribution ----
+        if (top_p < 1.0f) {
+            const float target = top_p * z;
+            SelectResult r = radix_select(V, 32, target, false, keyfn, prob, kept_filter, hist, red);
+            if (r.found) {
+                // equals share one probability; the prefix needs j of them
+                int n_eq = 0;
+                float p_eq = 0.f;
+                for (int i = tid; i < V; i += kThreads)
+                    if (keyfn(i) == r.x && kept_filter(i)) { ++n_eq; p_eq = prob(i); }
+                n_eq = (int)(block_sum((float)n_eq, scratch) + 0.5f);
+                p_eq = block_max(p_eq, scratch);
+                int j = (int)ceilf((target - r.above) / p_eq);
+                j = max(1, min(j, n_eq));
+                const int last = nth_equal_id(V, r.x, kept, j, id_bits, keyfn, hist, red);
+                kept = Kept{r.x, last};
+                kept_mass = r.above + (float)j * p_eq;
+            }
+        }
+        // ---- draw ----
+        const float rr = uniforms[row] * kept_mass;
+        SelectResult r = radix_select(V, 32, rr, true, keyfn, prob, kept_filter, hist, red);
+        if (!r.found) {
+            result = kept.last_id < V ? kept.last_id : -1;
+            if (result < 0) {
+                // the kept set is everything: its last element is the least probable, highest id
+                SelectResult lo = radix_select(V, 32, (float)V, false, keyfn,
+                                               [&](int) { return 1.f; }, all, hist, red);
+                int n_eq = (int)(lo.equal + 0.5f);
+                Kept whole{lo.x, V};
+                result = nth_equal_id(V, lo.x, whole, n_eq, id_bits, keyfn, hist, red);
+            }
+        } else {
+            int n_eq = 0;
+            float p_eq = 0.f;
+            for (int i = tid; i < V; i += kThreads)
+                if (keyfn(i) == r.x && kept_filter(i)) { ++n_eq; p_eq = prob(i); }
+            n_eq = (int)(block_sum((float)n_eq, scratch) + 0.5f);
+            p_eq = block_max(p_eq, scratch);
+            int j = (int)floorf((rr - r.above) / p_eq) + 1;
+            j = max(1, min(j, n_eq));
+            result = nth_equal_id(V, r.x, kept, j, id_bits, keyfn, hist, red);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int s = 0; s < n_saved; ++s) l[saved_id[s]] = saved_val[s];
+        out[row] = result;
+    }
+}
+
+// Arg max alone (first maximum wins), for the greedy loop: reads, never writes, the logits.
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* l = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = l[i];
+        if (v > best) { best = v; best_i = i; }     // ids rise within a thread: first maximum kept
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+        best_i = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" int hos_argmax(const float* logits, int ld, int B, int V, int* out, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) HOS_REFUSE("argmax: empty vocabulary");
+    argmax_kernel<<<B, 1024, 0, stream>>>(logits, ld, V, out);
+    return check_launch("argmax");
+}
+
+// recent: [B, recent_stride] token ids with recent_len[b] valid entries per row (may be NULL).
+extern "C" int hos_sample(float* logits, int ld, int B, int V, const float* uniforms,
+                          const int* recent, int recent_stride, const int* recent_len, float temp,
+                          int top_k, float top_p, float rep_penalty, int* out, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) HOS_REFUSE("sample: empty vocabulary");
+    if (V > (1 << 24)) HOS_REFUSE("sample: vocabulary %d is beyond 2^24 (counts are kept in float)", V);
+    if (top_k < 0) HOS_REFUSE("sample: top_k %d is negative", top_k);
+    if (!(rep_penalty > 0.f)) HOS_REFUSE("sample: repetition penalty must be positive");
+    const size_t smem = (size_t)(kBins * kThreads + kBins + 32) * sizeof(float);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    sample_kernel<<<B, kThreads, smem, stream>>>(logits, ld, V, uniforms, recent, recent_stride,
+                                                 recent_len, temp, top_k, top_p, rep_penalty, out);
+    return check_launch("sample");
+}

@@ -1,0 +1,82 @@
+"""A model built from a plan: the embedding, one arrangement object per layer (each
+holding its mixer, feed-forward and norms), the final norm and the head, plus the
+run order.  It knows nothing about any architecture: everything comes from the
+`ModelPlan` and the part registry."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import ops
+from . import parts as _parts  # noqa: F401  (registers the parts)
+from . import models as _models  # noqa: F401  (registers the architectures)
+from .cache import CacheManager
+from .config.base import ModelConfig, ModelPlan
+from .parts.base import Runtime, StepInfo, WeightSpec
+from .registry import part_impl, plan_for
+
+
+class Model:
+    def __init__(self, plan: ModelPlan, rt: Runtime):
+        plan.validate()
+        self.plan = plan
+        self.rt = rt
+        self.embedding = part_impl("embedding", plan.embedding.kind)(plan.embedding, rt)
+        self.layers = [part_impl("arrangement", ls.arrangement)(ls, rt) for ls in plan.layers]
+        self.final_norm = part_impl("norm", plan.final_norm.kind)(plan.final_norm, rt)
+        self.head = part_impl("head", plan.head.kind)(plan.head, rt)
+        self.schedule = list(plan.schedule)
+
+    def all_parts(self):
+        out = [self.embedding]
+        for layer in self.layers:
+            out.extend(layer.parts())
+        out.extend([self.final_norm, self.head])
+        return out
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs: List[WeightSpec] = []
+        seen = set()
+        for p in self.all_parts():
+            for s in p.weight_specs():
+                if s.name not in seen:
+                    seen.add(s.name)
+                    specs.append(s)
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.all_parts():
+            p.bind(tensors)
+
+    def new_cache(self, max_tokens: int, max_seq_len: Optional[int] = None,
+                  max_slots: Optional[int] = None) -> CacheManager:
+        kv_needs, cache_from, state_needs = [], [], []
+        for call in self.schedule:
+            mixer = self.layers[call.layer].mixer
+            kv_needs.append(mixer.kv_need())
+            cache_from.append(call.cache_from)
+            state_needs.append(mixer.state_needs())
+        return CacheManager(kv_needs, cache_from, state_needs, max_tokens,
+                            max_seq_len or self.plan.max_positions, self.rt.dtype, self.rt.device,
+                            max_slots)
+
+    def hidden(self, step: StepInfo, cache: CacheManager) -> torch.Tensor:
+        """The residual stream after the last entry of the run order, float32 [N, width]."""
+        x = self.embedding.forward(step.tokens, step)
+        for i, call in enumerate(self.schedule):
+            self.layers[call.layer].forward(x, step, cache.stores[i])
+        return x
+
+    def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """float32 [len(rows), vocab] for the given rows of the residual stream."""
+        if rows.shape[0] == 0:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=x.device)
+        picked = torch.empty((rows.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
+        ops.gather_rows(x, rows, picked)
+        return self.head.forward(self.final_norm.forward(picked))
+
+
+def weight_specs_for(config: ModelConfig) -> List[WeightSpec]:
+    """The tensors a model of this configuration wants (no GPU needed)."""
+    return Model(plan_for(config), Runtime(torch.device("cpu"), torch.bfloat16)).weight_specs()

@@ -1,0 +1,116 @@
+"""Softmax attention with grouped queries: q, k, v projections (one fused product),
+position encoding on q and k, keys and values kept in the paged cache, scores
+(q.k) * scale, optional soft-cap c*tanh(s/c), causal mask with an optional window
+of the last W keys, softmax, weighted values, output projection
+(src/forward.rs:300-363; head map h // (heads / kv_heads), :340).
+
+Every size and constant is a parameter: width, n_heads, n_kv_heads, head_dim,
+scale, softcap (0 = off), window (None = all keys), and the position encoding
+(a PartSpec of category "position").  The mixer asks the cache for keys and
+values of [n_kv_heads, head_dim] per position, all of them or a window.
+
+A prompt that starts at position 0 attends over its own freshly projected rows
+and only stores to the cache; every other step stores first and then attends
+over the cache.  An entry of the run order that reads another entry's cache
+projects q only and always attends over that cache.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from .. import ops
+from ..errors import KernelError, SpecError
+from ..registry import part_impl, register_part
+from . import linear
+from .base import CallStore, KVNeed, Mixer, StepInfo, WeightSpec
+
+
+class SoftmaxAttention(Mixer):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.width = int(p["width"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv_heads = int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.scale = float(p["scale"])
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.window: Optional[int] = p.get("window")
+        if self.n_heads % self.n_kv_heads != 0:
+            raise SpecError(f"arch spec error: {self.n_heads} heads are not a multiple of "
+                            f"{self.n_kv_heads} kv heads")
+        pos_spec = p.get("position")
+        self.position = part_impl("position", pos_spec.kind)(pos_spec, rt) if pos_spec else None
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv_heads * self.head_dim
+        self.w_qkv = self.w_q = self.w_o = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return [WeightSpec(w["q"], (self.q_dim, self.width), "matrix", 0.02),
+                WeightSpec(w["k"], (self.kv_dim, self.width), "matrix", 0.02),
+                WeightSpec(w["v"], (self.kv_dim, self.width), "matrix", 0.02),
+                WeightSpec(w["o"], (self.width, self.q_dim), "matrix", 0.02)]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        w = self.spec.weights
+        q, k, v = (self._matrix(tensors[w[r]]) for r in ("q", "k", "v"))
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = q.float(), k.float(), v.float()
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()    # one product for q, k and v
+        self.w_q = self.w_qkv[: self.q_dim]                      # a view: rows of q alone
+        self.w_o = self._matrix(tensors[w["o"]])
+
+    def kv_need(self) -> KVNeed:
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
+        n = h.shape[0]
+        cache = store.kv
+        if cache is None:
+            raise KernelError("attention needs a cache view")
+        inv_freq, rotary_dim, style = self.position.kernel_args() if self.position else (None, 0, 0)
+        if store.owns_kv:
+            qkv = linear.matmul(h, self.w_qkv)
+            ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
+                              step.seq_len_after, inv_freq, rotary_dim, style, cache,
+                              self.n_kv_heads, self.head_dim)
+        else:
+            qkv = linear.matmul(h, self.w_q)
+            ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
+                              step.seq_len_after, inv_freq, rotary_dim, style, None, 0, self.head_dim)
+        att = torch.empty((n, self.q_dim), dtype=h.dtype, device=h.device)
+        packed = step.from_zero and store.owns_kv
+        if not packed and cache.ring_pages > 0:
+            room = cache.ring_pages * ops.PAGE_TOKENS - int(self.window) + 1
+            if step.max_new > room:
+                raise KernelError(
+                    f"a step that continues sequences brings {step.max_new} tokens to a layer that "
+                    f"keeps a window of {self.window} keys in a ring of "
+                    f"{cache.ring_pages * ops.PAGE_TOKENS}: at most {room} fit without overwriting "
+                    f"keys that the step still reads")
+        self._attend(qkv, att, step, cache, packed)
+        return linear.matmul(att, self.w_o)
+
+    def _attend(self, qkv, att, step: StepInfo, cache, packed: bool) -> None:
+        stride = qkv.shape[1]
+        if self.rt.dtype == torch.bfloat16:
+            from . import attention_fast
+            if attention_fast.attend(self, qkv, att, step, cache, packed):
+                return
+        if packed:
+            k_rows = qkv[:, self.q_dim:]
+            v_rows = qkv[:, self.q_dim + self.kv_dim:]
+            ops.attn_plain(qkv, stride, att, step.token_pos, step.token_seq, step.n_tokens,
+                           self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.softcap,
+                           self.window, k_rows=k_rows, v_rows=v_rows, kv_stride=stride,
+                           cu_seqlens=step.cu_seqlens)
+        else:
+            ops.attn_plain(qkv, stride, att, step.token_pos, step.token_seq, step.n_tokens,
+                           self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.softcap,
+                           self.window, seq_slot=step.seq_slot, cache=cache)
+
+
+register_part("mixer", "softmax_attention", SoftmaxAttention)

@@ -1,0 +1,160 @@
+"""What a part is, and what it is handed when it runs.
+
+A model is put together from parts of seven categories (see `hos_b200.registry`):
+
+  embedding    tokens -> residual stream          forward(tokens, step) -> x  (float32 [N, width])
+  norm         rows -> normalised rows            forward(x, out)
+  position     encodes positions into q and k     (used by a mixer; see parts/rope.py)
+  mixer        mixes information between tokens   forward(h, step, store) -> y
+  feed_forward works on each token alone          forward(h, step) -> y
+  arrangement  wires norms, mixer, feed-forward and the residual stream of one layer
+               forward(x, step, store) -> None (x is updated in place)
+  head         rows -> logits                     forward(h) -> float32 [n, vocab]
+
+Every part is built from a `PartSpec` (its sizes and constants) and a `Runtime`
+(device, compute dtype), says which tensors it wants (`weight_specs`), and
+receives them once (`bind`).  No part knows which model it is in.
+
+Data types: the residual stream is float32; what a part hands to the next matrix
+product (`h`, `y`) has the runtime's compute dtype; logits are float32.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.base import PartSpec
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """A tensor a part wants from the checkpoint."""
+    name: str                        # checkpoint name
+    shape: Tuple[int, ...]
+    role: str                        # "matrix", "vector" or "table"
+    init_std: float                  # standard deviation of the random-weights mode
+    fallback: Optional[str] = None   # another tensor to use when this one is absent (tied head)
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A mixer's wish for keys and values per position.  Calls whose needs are equal
+    share one group of the cache (one page table, storage of their own)."""
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int]            # None: all keys; an int: the last `window` keys
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer's wish for per-sequence state of fixed size, zeroed when a sequence starts."""
+    name: str
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Runtime:
+    """Where and in what precision a model runs."""
+
+    def __init__(self, device: torch.device, dtype: torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, found {dtype}")
+        self.device = torch.device(device)
+        self.dtype = dtype
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+    def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+
+@dataclass
+class StepInfo:
+    """One step's batch as the kernels see it.  N tokens (rows) of B sequences, packed
+    sequence after sequence.  A row with token_seq < 0 is padding: it is computed on
+    but stores nothing and no other row reads it."""
+    n_tokens: int
+    n_seqs: int
+    tokens: torch.Tensor          # int32 [N], -1 for padding
+    token_pos: torch.Tensor       # int32 [N] position of each token in its sequence
+    token_seq: torch.Tensor       # int32 [N] row of the batch, -1 for padding
+    cu_seqlens: torch.Tensor      # int32 [B+1] first row of each sequence
+    seq_slot: torch.Tensor        # int32 [B] cache slot of each sequence
+    seq_len_after: torch.Tensor   # int32 [B] length of each sequence after this step
+    from_zero: bool               # every sequence starts at position 0 in this step
+    single_token: bool            # every sequence brings exactly one token
+    max_new: int                  # most tokens any sequence brings
+    max_len_after: int            # longest sequence after this step
+    slots_host: Sequence[int] = ()
+
+
+class CallStore:
+    """The storage of one entry of the run order: its view of the paged cache (or
+    of the cache of the entry it reads from) and its per-sequence state tensors."""
+
+    def __init__(self, kv=None, owns_kv: bool = True, state: Optional[Dict[str, torch.Tensor]] = None):
+        self.kv = kv                      # ops.PagedKVArgs or None
+        self.owns_kv = owns_kv            # False: another entry writes this cache
+        self.state = state or {}          # name -> tensor [n_slots, *shape]
+
+
+class Part:
+    """Base of every part."""
+
+    def __init__(self, spec: PartSpec, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receive the tensors named in weight_specs(), on the device, in their stored
+        dtype (bfloat16 kept, 32-bit kept).  Convert or fuse them here, once."""
+
+    # helpers -----------------------------------------------------------------------
+    def _matrix(self, t: torch.Tensor) -> torch.Tensor:
+        """A matrix as the products take it: float32 in the 32-bit path (an exact
+        widening of bfloat16), else as stored (bfloat16, or 32-bit if it was so)."""
+        if self.rt.is_fp32:
+            return t.to(torch.float32).contiguous()
+        if t.dtype == torch.float16:
+            return t.to(torch.bfloat16).contiguous()
+        return t.contiguous()
+
+    @staticmethod
+    def _vector32(t: torch.Tensor) -> torch.Tensor:
+        return t.to(torch.float32).contiguous()
+
+
+class Mixer(Part):
+    def kv_need(self) -> Optional[KVNeed]:
+        return None
+
+    def state_needs(self) -> List[StateNeed]:
+        return []
+
+    def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, step: StepInfo) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_to(self, y: torch.Tensor, x: torch.Tensor, then: Optional["Norm"] = None) -> Optional[torch.Tensor]:
+        """x += self(y).  If `then` is given, also return then(x).  The default does
+        it in separate kernels; a norm may fuse them."""
+        from .. import ops
+        n = self.forward(y)
+        ops.residual_add(n, x)
+        return then.forward(x) if then is not None else None

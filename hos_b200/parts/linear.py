@@ -1,0 +1,38 @@
+"""The matrix product that every part calls: y = x . W^T, W stored [out, in] as the
+checkpoint has it (src/model.rs:179-180).  Chooses the kernel: in bfloat16 the
+tcgen05/TMA kernel when the sizes meet its alignment rules, else (and always in
+the 32-bit path) the plain CUDA-core kernel.  Both accumulate in 32-bit."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+
+_force_plain = False
+
+
+def force_plain(on: bool) -> None:
+    """Tests use this to compare the tensor-core kernel's results with the plain kernel's."""
+    global _force_plain
+    _force_plain = on
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N or 2N, K]^T (2N rows with the gated epilogue)."""
+    m = x.shape[0]
+    n = w.shape[0] // 2 if epilogue == ops.EPI_GATED else w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
+    if m == 0:
+        return out
+    if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        from . import gemm_tc
+        if gemm_tc.can_take(x, w, out, epilogue):
+            gemm_tc.matmul(x, w, out, epilogue, cap, act)
+            return out
+    ops.gemm_plain(x, w, out, epilogue, cap, act)
+    return out
