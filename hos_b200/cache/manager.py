@@ -104,9 +104,14 @@ class CacheManager:
         if new_len > self.max_seq_len:
             raise CacheError(f"a sequence of {new_len} tokens is longer than the cache holds "
                              f"({self.max_seq_len})")
+        for g in self.groups:          # all or nothing: look before taking
+            more = g.pages_for(new_len) - len(g._slot_pages[slot])
+            if more > g.pages.n_free:
+                raise CacheError(f"the cache has no free page left for slot {slot} to reach "
+                                 f"{new_len} tokens ({more} wanted, {g.pages.n_free} free)")
         for g in self.groups:
             g.grow(slot, new_len)
-        self.lengths[slot] = new_len
+        self.lengths[slot] = max(self.lengths[slot], new_len)
 
     def release(self, slot: int) -> None:
         if slot not in self.lengths:

@@ -51,4 +51,4 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
         single_token=all(k == 1 for k in news),
         max_new=max(news) if news else 0,
         max_len_after=max(lens_after) if lens_after else 0,
-        slots_host=tuple(slots))
+        slots_host=tuple(slots), cu_host=tuple(cu), starts_host=tuple(starts))

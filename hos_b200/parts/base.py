@@ -89,7 +89,9 @@ class StepInfo:
     single_token: bool            # every sequence brings exactly one token
     max_new: int                  # most tokens any sequence brings
     max_len_after: int            # longest sequence after this step
-    slots_host: Sequence[int] = ()
+    slots_host: Sequence[int] = ()   # the same as seq_slot, on the host
+    cu_host: Sequence[int] = ()      # the same as cu_seqlens, on the host
+    starts_host: Sequence[int] = ()  # each sequence's length before the step
 
 
 class CallStore:

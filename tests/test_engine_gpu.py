@@ -1,0 +1,183 @@
+"""The step function and the Python entry point on the GPU against the plain implementation."""
+import random
+
+import pytest
+import torch
+
+from plain import gemma2_plain as P
+from helpers import TINY, TOL, assert_close, make_folder, plain_model, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def runner_for(folder, dtype, max_tokens=4096):
+    from hos_b200.engine import Runner
+    return Runner.from_folder(folder, dtype=dtype, max_tokens=max_tokens)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
+    """Positions 0, 1, 2: a one-token prompt beside a two-token prompt, then single tokens."""
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(3)
+    seqs = [random_tokens(rng, 4, vocab), random_tokens(rng, 5, vocab)]
+    r = runner_for(folder, dtype)
+    slots = r.admit(2)
+    got = [r.step(slots, [seqs[0][:1], seqs[1][:2]], [[0], [0, 1]])]
+    for t in range(3):
+        got.append(r.step(slots, [[seqs[0][1 + t]], [seqs[1][2 + t]]]))
+    want0, want1 = P.forward_logits(w, cfg, seqs[0]), P.forward_logits(w, cfg, seqs[1])
+    assert_close(got[0], torch.stack([want0[0], want1[0], want1[1]]), dtype, "prompt step")
+    for t in range(3):
+        assert_close(got[1 + t], torch.stack([want0[1 + t], want1[2 + t]]), dtype, f"decode step {t}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_wraps_the_window_ring(tmp_path, dtype):
+    """Config C keeps a window of 40 keys in a ring of 64 positions: decoding 300 tokens
+    one by one goes round it more than four times, beside a sequence that is much shorter."""
+    folder = make_folder(tmp_path, "C")
+    w, cfg = plain_model(folder)
+    rng = random.Random(4)
+    long_seq, short_seq = random_tokens(rng, 310, 331), random_tokens(rng, 40, 331)
+    r = runner_for(folder, dtype)
+    a, b = r.admit(2)
+    r.step([a, b], [long_seq[:7], short_seq[:3]])
+    want_long, want_short = P.forward_logits(w, cfg, long_seq), P.forward_logits(w, cfg, short_seq)
+    for t in range(7, 310):
+        k = t - 7 + 3
+        if k < 40:
+            got = r.step([a, b], [[long_seq[t]], [short_seq[k]]])
+            assert_close(got, torch.stack([want_long[t], want_short[k]]), dtype, f"position {t}/{k}")
+        else:
+            if k == 40:
+                r.release(b)
+            got = r.step([a], [[long_seq[t]]])
+            assert_close(got, want_long[t][None], dtype, f"position {t}")
+    r.release(a)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_rows_change_nothing(tmp_path, dtype):
+    """The same batch with padding rows appended gives the same logits, bit for bit."""
+    from hos_b200.engine.batch import build_step
+    folder = make_folder(tmp_path, "B")
+    rng = random.Random(5)
+    prompts = [random_tokens(rng, n, 512) for n in (3, 20, 9)]
+    outs = []
+    for pad in (0, 64):
+        r = runner_for(folder, dtype)
+        slots = r.admit(3)
+        for s, p in zip(slots, prompts):
+            r.cache.extend(s, len(p))
+        r.cache.flush()
+        n = sum(len(p) for p in prompts)
+        info = build_step(prompts, [0, 0, 0], slots, r.device, 512, pad_to=n + pad if pad else 0)
+        x = r.model.hidden(info, r.cache)
+        rows = torch.arange(n, dtype=torch.int32, device=r.device)
+        outs.append(r.model.logits(x, rows).cpu())
+        # and a decode step on top, padded the same way
+        info = build_step([[5], [6], [7]], [len(p) for p in prompts], slots, r.device, 512,
+                          pad_to=3 + pad if pad else 0)
+        for s, p in zip(slots, prompts):
+            r.cache.extend(s, len(p) + 1)
+        r.cache.flush()
+        x = r.model.hidden(info, r.cache)
+        outs.append(r.model.logits(x, torch.arange(3, dtype=torch.int32, device=r.device)).cpu())
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+
+
+def test_step_refuses_what_it_cannot_run(tmp_path):
+    from hos_b200.errors import CacheError, HosError
+    folder = make_folder(tmp_path, "A")
+    r = runner_for(folder, "float32", max_tokens=128)
+    a, b = r.admit(2)
+    r.step([a], [[1, 2, 3]])
+    with pytest.raises(HosError, match="either all start"):
+        r.step([a, b], [[4], [5, 6]])
+    with pytest.raises(HosError, match="outside the vocabulary"):
+        r.step([a], [[256]])
+    with pytest.raises(HosError, match="appears twice"):
+        r.step([a, a], [[1], [2]])
+    with pytest.raises(HosError, match="outside the 1 tokens"):
+        r.step([a], [[1]], [[1]])
+    with pytest.raises(CacheError):
+        r.step([b], [list(range(65))])          # config A's context holds 64 positions
+    assert r.length(a) == 3                      # refused steps left the cache as it was
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(6)
+    prompts = [random_tokens(rng, n, vocab) for n in (4, 1, 13, 7, 2)]
+    eng = Engine(folder, dtype=dtype, max_batch=3)             # five requests: two batches
+    outs = eng.generate_ids(prompts, 10, stop_ids=[])
+    assert [len(o) for o in outs] == [10] * 5
+    tol = TOL[dtype]
+    for p, o in zip(prompts, outs):
+        if dtype == "float32":
+            assert o == P.greedy_generate(w, cfg, p, 10)
+        else:
+            # bfloat16 may pick another token only where the plain logits nearly tie
+            seq = list(p)
+            for t in o:
+                l = P.forward_logits(w, cfg, seq)[-1]
+                assert float(l.max() - l[t]) <= 2 * (tol["atol"] + tol["rtol"] * float(l.abs().max()))
+                seq.append(t)
+    # one request alone gives what it gave in the batch
+    assert eng.generate_ids(prompts[2], 10, stop_ids=[]) == outs[2]
+    # a stop token ends the sequence and is not returned
+    stop = outs[0][4]
+    cut = outs[0].index(stop)
+    assert eng.generate_ids(prompts[0], 10, stop_ids=[stop]) == outs[0][:cut]
+    eng.runner.cache.check()
+    assert eng.runner.cache.slots.n_held == 0
+
+
+def test_sampling_through_the_entry_point_follows_the_reference_rule(tmp_path):
+    """temp, top-k, top-p and the repetition penalty together, in 32-bit, against the plain
+    sampler fed with the plain logits and the same xorshift stream."""
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, "A")
+    w, cfg = plain_model(folder)
+    eng = Engine(folder, dtype="float32")
+    prompts = [[5, 6, 7], [100, 3]]
+    kw = dict(temp=0.9, top_k=12, top_p=0.9, rep_penalty=1.3, repeat_last_n=4, seed=0x1234567890ABCDEF)
+    outs = eng.generate(prompts, 12, stop_ids=[], **kw)
+    from hos_b200.sampling import stream_seed
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        rng = stream_seed(kw["seed"], i)
+        seq, recent = list(p), []
+        for t in o:
+            l = P.forward_logits(w, cfg, seq)[-1]
+            want, rng = P.sample(l, kw["temp"], kw["top_k"], kw["top_p"], kw["rep_penalty"],
+                                 recent[-kw["repeat_last_n"]:], rng)
+            assert t == want
+            seq.append(t)
+            recent.append(t)
+    assert len({tuple(o) for o in outs}) == 2
+
+
+def test_perplexity_and_bench(tmp_path):
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, "B")
+    w, cfg = plain_model(folder)
+    eng = Engine(folder, dtype="float32")
+    ids = random_tokens(random.Random(7), 50, 512)
+    n, mean, ppl = eng.perplexity(ids)
+    logits = P.forward_logits(w, cfg, ids[:-1]).double()
+    want = float(-(torch.log_softmax(logits, -1).gather(1, torch.tensor(ids[1:])[:, None])).mean())
+    assert n == 49 and abs(mean - want) < 1e-5 and abs(ppl - torch.tensor(want).exp().item()) < 1e-2
+    b = eng.bench(ids[:20], 5)
+    assert b[0] == 20 and b[3] <= 5 and b[2] > 0 and (b[3] == 0 or b[5] > 0)

@@ -1,0 +1,158 @@
+"""The generation loop's decisions, driven with a fake step function (no GPU)."""
+import pytest
+
+from hos_b200.engine import generate as gen
+from hos_b200.errors import HosError
+from hos_b200.sampling import SamplingParams, next_rand, stream_seed
+
+
+class FakeBackend:
+    """`step` returns, per sequence, the list of tokens it has seen so far."""
+
+    def __init__(self, n_slots=8, max_seq_len=1000):
+        self.free = list(range(n_slots))
+        self.seen = {}
+        self.max_seq_len = max_seq_len
+        self.steps = []
+        self.taken_log = []
+
+    def admit(self, n):
+        assert n <= len(self.free)
+        out = [self.free.pop(0) for _ in range(n)]
+        for s in out:
+            self.seen[s] = []
+        self.taken_log.append(list(out))
+        return out
+
+    def step(self, slots, token_lists):
+        self.steps.append((list(slots), [list(t) for t in token_lists]))
+        if len(self.steps) > 1 and any(len(self.seen[s]) for s in slots):
+            assert all(len(t) == 1 for t in token_lists)          # decode steps bring one token
+        for s, t in zip(slots, token_lists):
+            self.seen[s].extend(t)
+        return [list(self.seen[s]) for s in slots]
+
+    def release(self, slot):
+        assert slot in self.seen, "released twice"
+        del self.seen[slot]
+        self.free.append(slot)
+        self.free.sort()
+
+
+class ScriptSampler:
+    """Next token = (sum of the sequence so far) % 50; deterministic, no GPU."""
+
+    def __init__(self):
+        self.open_keys = set()
+
+    def open(self, key, index):
+        self.open_keys.add(key)
+
+    def close(self, key):
+        self.open_keys.discard(key)
+
+    def sample(self, logits, keys):
+        assert len(logits) == len(keys)
+        return [sum(seq) % 50 for seq in logits]
+
+
+def reference(prompt, max_new, stop, max_len=1000):
+    seq, out = list(prompt), []
+    for _ in range(max_new):
+        t = sum(seq) % 50
+        if t in stop:
+            break
+        out.append(t)
+        if len(seq) >= max_len:
+            break
+        seq.append(t)
+    return out
+
+
+def test_plan_batches_respects_count_and_capacity():
+    assert gen.plan_batches([5, 5, 5, 5, 5], 10, 10_000, 2, 4096) == [[0, 1], [2, 3], [4]]
+    # each request needs round64(100 + 30) = 192 tokens; 400 hold two
+    assert gen.plan_batches([100, 100, 100], 30, 400, 8, 4096) == [[0, 1], [2]]
+    # the context caps what a request can ever hold
+    assert gen.plan_batches([60, 60], 1000, 128, 8, 64) == [[0, 1]]
+    with pytest.raises(HosError, match="empty prompt"):
+        gen.plan_batches([3, 0], 4, 1000, 8, 4096)
+    with pytest.raises(HosError, match="more than the context"):
+        gen.plan_batches([5000], 4, 100000, 8, 4096)
+    with pytest.raises(HosError, match="cache holds"):
+        gen.plan_batches([500], 4, 256, 8, 4096)
+
+
+def test_unequal_prompts_end_at_different_times_and_match_single_runs():
+    prompts = [[3, 4, 5], [1], [9, 9, 9, 9, 9, 9, 2], [11, 13]]
+    stop = set(range(0, 50, 4))
+    b = FakeBackend()
+    outs = gen.generate(b, ScriptSampler, prompts, 12, stop, 10_000, 8)
+    assert outs == [reference(p, 12, stop) for p in prompts]
+    assert len({len(o) for o in outs}) > 1                 # they did end at different times
+    assert b.seen == {} and b.free == list(range(8))       # every slot came back
+    first_slots, first_tokens = b.steps[0]
+    assert first_tokens == prompts                          # all prompts in ONE step
+    sizes = [len(s) for s, _ in b.steps]
+    assert sizes == sorted(sizes, reverse=True)             # the batch only shrinks
+
+
+def test_stop_token_is_not_returned_and_first_token_can_stop():
+    b = FakeBackend()
+    outs = gen.generate(b, ScriptSampler, [[7]], 5, {7}, 1000, 8)      # first sampled token is 7
+    assert outs == [[]] and len(b.steps) == 1 and b.seen == {}
+
+
+def test_max_new_bounds_the_output_and_no_step_follows_the_last_token():
+    b = FakeBackend()
+    outs = gen.generate(b, ScriptSampler, [[2, 3]], 4, set(), 1000, 8)
+    assert len(outs[0]) == 4
+    assert len(b.steps) == 4                 # prompt + 3 single tokens; the 4th token is not fed
+    assert gen.generate(FakeBackend(), ScriptSampler, [[2, 3]], 0, set(), 1000, 8) == [[]]
+
+
+def test_context_limit_ends_a_sequence():
+    b = FakeBackend(max_seq_len=6)
+    outs = gen.generate(b, ScriptSampler, [[1, 2, 3, 4]], 50, set(), 1000, 8)
+    assert outs == [reference([1, 2, 3, 4], 50, set(), max_len=6)]
+    assert len(outs[0]) == 3                 # positions 4 and 5 are fed, a third token is sampled
+    assert max(len(t) for _, toks in b.steps for t in toks) == 4
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    prompts = [[i + 1] * (i + 1) for i in range(7)]
+    b = FakeBackend(n_slots=3)
+    outs = gen.generate(b, ScriptSampler, prompts, 5, {0}, 10_000, 3)
+    assert outs == [reference(p, 5, {0}) for p in prompts]
+    assert b.taken_log == [[0, 1, 2], [0, 1, 2], [0]]
+    assert b.seen == {}
+
+
+def test_slots_come_back_when_a_step_fails():
+    class Boom(FakeBackend):
+        def step(self, slots, token_lists):
+            if len(self.steps) == 2:
+                raise RuntimeError("boom")
+            return super().step(slots, token_lists)
+    b = Boom()
+    with pytest.raises(RuntimeError):
+        gen.generate(b, ScriptSampler, [[1, 2], [3]], 9, set(), 1000, 8)
+    assert b.seen == {} and b.free == list(range(8))
+
+
+def test_host_random_stream_matches_the_reference_generator():
+    # xorshift64 (13, 7, 17), top 24 bits: src/lib.rs:78-85; first draws for seed 42
+    s, u1 = next_rand(42)
+    assert s == 45454805674 and u1 == (45454805674 >> 40) / (1 << 24)
+    s2, u2 = next_rand(s)
+    x = s
+    x ^= (x << 13) & ((1 << 64) - 1); x ^= x >> 7; x ^= (x << 17) & ((1 << 64) - 1)
+    assert s2 == x and 0.0 <= u2 < 1.0
+    assert stream_seed(42, 0) == 42 and stream_seed(42, 3) == 45 and stream_seed(0, 0) != 0
+
+
+def test_sampling_defaults_are_the_references():
+    p = SamplingParams()
+    assert (p.temp, p.top_k, p.top_p, p.rep_penalty, p.repeat_last_n, p.seed) == (0.0, 40, 0.95, 1.1, 64, 42)
+    q = SamplingParams.pure()
+    assert (q.top_k, q.top_p, q.rep_penalty) == (0, 1.0, 1.0)

@@ -1,0 +1,345 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch statement of the same operation,
+at sizes other than the engine's (widths and vocabularies that are no power of two, odd
+head counts, head sizes in steps of 16)."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def close(a, b, dtype, scale=1.0):
+    t = tol(dtype)
+    torch.testing.assert_close(a.float().cpu(), b.float().cpu(), atol=t["atol"] * scale, rtol=t["rtol"] * scale)
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from hos_b200.csrc import build
+    from hos_b200.errors import ExtensionMissingError
+    with pytest.raises(ExtensionMissingError):
+        build.load("no_such_library")
+
+
+@pytest.mark.parametrize("table_dtype", ["float32", "bfloat16"])
+def test_embed(table_dtype):
+    from hos_b200 import ops
+    V, D = 1003, 200
+    table = torch.randn(V, D, device=DEV).to(DT[table_dtype])
+    toks = torch.tensor([0, 1002, 7, -1, 500], dtype=torch.int32, device=DEV)
+    out = torch.full((5, D), 9.0, device=DEV)
+    ops.embed(toks, table, 14.142135, out)
+    want = table.float()[toks.clamp(min=0).long()] * torch.tensor(14.142135)
+    want[3] = 0
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D", [1, 80, 1000, 2304, 13000])
+def test_rmsnorm(D, out_dtype):
+    from hos_b200 import ops
+    x = torch.randn(7, D, device=DEV) * 3
+    w = torch.randn(D, device=DEV) * 0.1
+    out = torch.empty(7, D, device=DEV, dtype=DT[out_dtype])
+    ops.rmsnorm(x, w, 1e-6, True, out)
+    want = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6) * (1 + w)
+    close(out, want.to(DT[out_dtype]), DT[out_dtype])
+    ops.rmsnorm(x, w, 1e-3, False, out)
+    want = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-3) * w
+    close(out, want.to(DT[out_dtype]), DT[out_dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_add_norm(dtype):
+    from hos_b200 import ops
+    dt = DT[dtype]
+    N, D = 5, 328
+    y = (torch.randn(N, D, device=DEV) * 2).to(dt)
+    x0 = torch.randn(N, D, device=DEV)
+    w1, w2 = torch.randn(D, device=DEV) * 0.1, torch.randn(D, device=DEV) * 0.1
+
+    def norm(v, w, eps):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * (1 + w)
+    x = x0.clone()
+    h = torch.empty(N, D, device=DEV, dtype=dt)
+    ops.norm_add_norm(y, w1, 1e-6, True, x, w2, 1e-5, True, h)
+    want_x = x0 + norm(y.float(), w1, 1e-6)
+    close(x, want_x, torch.float32)                       # the residual sum is 32-bit in both paths
+    close(h, norm(want_x, w2, 1e-5).to(dt), dt)
+    x = x0.clone()
+    ops.norm_add_norm(y, w1, 1e-6, True, x)
+    close(x, want_x, torch.float32)
+    x = x0.clone()
+    ops.residual_add(y, x)
+    close(x, x0 + y.float(), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_gated_act(dtype, act):
+    from hos_b200 import ops
+    dt = DT[dtype]
+    gu = (torch.randn(6, 2 * 136, device=DEV) * 2).to(dt)
+    out = torch.empty(6, 136, device=DEV, dtype=dt)
+    ops.gated_act(gu, out, ops.ACTIVATIONS[act])
+    g, u = gu.float()[:, :136], gu.float()[:, 136:]
+    a = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
+    close(out, (a * u).to(dt), dt)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 70, 33), (65, 129, 200), (130, 64, 17), (8, 1003, 96)])
+def test_gemm_plain(shape, dtype):
+    from hos_b200 import ops
+    dt = DT[dtype]
+    M, N, K = shape
+    a = torch.randn(M, K, device=DEV).to(dt)
+    w = (torch.randn(2 * N, K, device=DEV) / math.sqrt(K)).to(dt)
+    out = torch.empty(M, N, device=DEV, dtype=dt)
+    ops.gemm_plain(a, w[:N].contiguous(), out)
+    ref = a.double() @ w[:N].double().T
+    close(out, ref.to(dt), dt)
+    out32 = torch.empty(M, N, device=DEV)
+    ops.gemm_plain(a, w[:N].contiguous(), out32, ops.EPI_SOFTCAP, cap=0.7)
+    close(out32, 0.7 * torch.tanh(ref / 0.7), torch.float32)
+    ops.gemm_plain(a, w, out, ops.EPI_GATED, act=ops.ACT_GELU_TANH)
+    g, u = a.double() @ w[:N].double().T, a.double() @ w[N:].double().T
+    close(out, (torch.nn.functional.gelu(g, approximate="tanh") * u).to(dt), dt)
+
+
+def _fill_cache(k_rows, v_rows, seq_lens, n_kv, hd, ring_pages, dtype, n_slots=4, scatter_seed=0):
+    """Put per-sequence keys/values [len, n_kv, hd] into a paged cache with scattered pages,
+    through the library's own write kernel (rope off)."""
+    from hos_b200 import ops
+    rng = random.Random(scatter_seed)
+    pages_per = [(min(l, ring_pages * 64) if ring_pages else l) for l in seq_lens]
+    pages_per = [(p + 63) // 64 for p in pages_per]
+    stride = max(pages_per)
+    n_pages = sum(pages_per) + 3
+    ids = list(range(n_pages))
+    rng.shuffle(ids)
+    table = torch.zeros(n_slots, stride, dtype=torch.int32)
+    slots = rng.sample(range(n_slots), len(seq_lens))
+    it = iter(ids)
+    for s, npg in zip(slots, pages_per):
+        for e in range(npg):
+            table[s, e] = next(it)
+    kp = torch.full((n_pages, n_kv, 64, hd), float("nan"), device=DEV).to(dtype)
+    vp = torch.full((n_pages, n_kv, 64, hd), float("nan"), device=DEV).to(dtype)
+    cache = ops.PagedKVArgs(kp, vp, table.to(DEV), ring_pages, n_kv, hd)
+    # rows: [q(0 heads) | k | v]
+    rows = torch.cat([torch.cat([k.reshape(len(k), -1), v.reshape(len(v), -1)], 1) for k, v in zip(k_rows, v_rows)])
+    pos = torch.cat([torch.arange(l) for l in seq_lens]).int().to(DEV)
+    seq = torch.cat([torch.full((l,), i) for i, l in enumerate(seq_lens)]).int().to(DEV)
+    ops.rope_kv_write(rows.to(dtype).contiguous(), 0, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV),
+                      torch.tensor(seq_lens, dtype=torch.int32, device=DEV), None, 0, 0, cache, n_kv, hd)
+    return cache, slots
+
+
+def _ref_attention(q, k, v, pos, scale, cap, window):
+    """q [nh, hd] at position pos; k, v [len, nkv, hd] -> [nh, hd] (float64)."""
+    nh, nkv = q.shape[0], k.shape[1]
+    lo = max(0, pos + 1 - window) if window else 0
+    out = torch.empty_like(q, dtype=torch.float64)
+    for h in range(nh):
+        kh, vh = k[lo:pos + 1, h // (nh // nkv)].double(), v[lo:pos + 1, h // (nh // nkv)].double()
+        s = (kh @ q[h].double()) * scale
+        if cap > 0:
+            s = cap * torch.tanh(s / cap)
+        out[h] = torch.softmax(s, 0) @ vh
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=None, cap=0.0),
+                                 dict(nh=6, nkv=1, hd=48, window=37, cap=20.0),
+                                 dict(nh=3, nkv=3, hd=64, window=64, cap=50.0),
+                                 dict(nh=8, nkv=4, hd=256, window=100, cap=30.0),
+                                 dict(nh=2, nkv=1, hd=128, window=None, cap=50.0)])
+def test_attention_plain_over_the_cache_and_over_packed_rows(cfg, dtype):
+    """One query per sequence at its last position over a scattered paged cache (with a
+    ring for windowed layers, wrapped), and whole prompts over their own packed rows."""
+    from hos_b200 import ops
+    dt = DT[dtype]
+    nh, nkv, hd, window, cap = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], cfg["cap"]
+    torch.manual_seed(1)
+    seq_lens = [1, 63, 64, 65, 300]
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(l, nh, hd).to(dt).float() for l in seq_lens]
+    # a far key that matters: in the longest sequence one early key is made to stand out
+    far = 300 - (window - 1 if window else 290)
+    ks[4][far] = qs[4][299, 0::max(1, nh // nkv)][: nkv] * 3.0
+    scale = 1.0 / math.sqrt(hd)
+    ring = (window + 63) // 64 if window else 0
+    # --- decode: one query per sequence over the cache ---
+    cache, slots = _fill_cache([k.to(DEV) for k in ks], [v.to(DEV) for v in vs], seq_lens, nkv, hd, ring, dt,
+                               n_slots=7)
+    q_last = torch.stack([q[-1] for q in qs]).reshape(len(seq_lens), nh * hd).to(DEV).to(dt).contiguous()
+    out = torch.empty_like(q_last)
+    pos = torch.tensor([l - 1 for l in seq_lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(len(seq_lens), dtype=torch.int32, device=DEV)
+    ops.attn_plain(q_last, nh * hd, out, pos, seq, len(seq_lens), nh, nkv, hd, scale, cap, window,
+                   seq_slot=torch.tensor(slots, dtype=torch.int32, device=DEV), cache=cache)
+    for i, l in enumerate(seq_lens):
+        want = _ref_attention(qs[i][-1], ks[i], vs[i], l - 1, scale, cap, window)
+        close(out[i].reshape(nh, hd), want.to(dt), dt)
+    # --- prompts: all positions over the step's own rows ---
+    rows = torch.cat([torch.cat([q.reshape(len(q), -1), k.reshape(len(k), -1), v.reshape(len(v), -1)], 1)
+                      for q, k, v in zip(qs, ks, vs)]).to(DEV).to(dt).contiguous()
+    N = rows.shape[0]
+    out = torch.empty(N, nh * hd, device=DEV, dtype=dt)
+    pos = torch.cat([torch.arange(l) for l in seq_lens]).int().to(DEV)
+    seq = torch.cat([torch.full((l,), i) for i, l in enumerate(seq_lens)]).int().to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(seq_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    stride = rows.shape[1]
+    ops.attn_plain(rows, stride, out, pos, seq, N, nh, nkv, hd, scale, cap, window,
+                   k_rows=rows[:, nh * hd:], v_rows=rows[:, (nh + nkv) * hd:], kv_stride=stride, cu_seqlens=cu)
+    base = 0
+    for i, l in enumerate(seq_lens):
+        for p in sorted({0, 1, l // 2, l - 1}):
+            want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
+            close(out[base + p].reshape(nh, hd), want.to(dt), dt)
+        base += l
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("style", ["rotate_half", "interleaved"])
+def test_rope_and_cache_write(dtype, style):
+    from hos_b200 import ops
+    dt = DT[dtype]
+    nh, nkv, hd, rot, theta = 3, 2, 32, 24, 5000.0          # partial rotation: 24 of 32 dimensions
+    N = 70
+    rows0 = torch.randn(N, (nh + 2 * nkv) * hd, device=DEV).to(dt)
+    rows = rows0.clone()
+    pos = torch.arange(N, dtype=torch.int32, device=DEV) + 1000
+    seq = torch.zeros(N, dtype=torch.int32, device=DEV)
+    seq[5] = -1                                              # a padding row: untouched, not stored
+    inv = (1.0 / torch.pow(torch.tensor(theta), 2.0 * torch.arange(rot // 2).float() / rot)).to(DEV)
+    table = torch.tensor([[9] + [0] * 16, list(range(16, 33))], dtype=torch.int32, device=DEV)
+    kp = torch.zeros(40, nkv, 64, hd, device=DEV, dtype=dt)
+    vp = torch.zeros_like(kp)
+    cache = ops.PagedKVArgs(kp, vp, table, 0, nkv, hd)
+    ops.rope_kv_write(rows, nh, pos, seq, torch.tensor([1], dtype=torch.int32, device=DEV),
+                      torch.tensor([1000 + N], dtype=torch.int32, device=DEV), inv, rot, ops.ROPE_STYLES[style],
+                      cache, nkv, hd)
+    x = rows0.float().view(N, nh + 2 * nkv, hd).clone()
+    ang = pos.float()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    want = x.clone()
+    if style == "rotate_half":
+        a, b = x[:, :nh + nkv, :rot // 2], x[:, :nh + nkv, rot // 2:rot]
+        want[:, :nh + nkv, :rot // 2], want[:, :nh + nkv, rot // 2:rot] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[:, :nh + nkv, 0:rot:2], x[:, :nh + nkv, 1:rot:2]
+        want[:, :nh + nkv, 0:rot:2], want[:, :nh + nkv, 1:rot:2] = a * c - b * s, a * s + b * c
+    want[5] = x[5]
+    close(rows.view(N, -1, hd), want.to(dt), dt)
+    # the cache holds the rotated keys and the values at (page of position, row of position)
+    for n in (0, 23, 24, 69):
+        p = 1000 + n
+        page = int(table[1, p // 64])
+        got_k = torch.stack([kp[page, :, p % 64, :]])[0]
+        assert torch.equal(got_k, rows.view(N, -1, hd)[n, nh:nh + nkv])
+        assert torch.equal(vp[page, :, p % 64, :], rows.view(N, -1, hd)[n, nh + nkv:])
+    assert float(kp[int(table[1, 1005 // 64]), :, 1005 % 64].abs().sum()) == 0      # the padding row stored nothing
+
+
+def test_cache_write_skips_ring_positions_that_the_same_step_overwrites():
+    from hos_b200 import ops
+    nkv, hd, N = 1, 16, 200                                   # ring of 2 pages = 128 positions
+    rows = torch.arange(N, device=DEV).float()[:, None].repeat(1, 2 * nkv * hd).contiguous()
+    kp = torch.full((4, nkv, 64, hd), -1.0, device=DEV)
+    vp = kp.clone()
+    table = torch.tensor([[2, 1]], dtype=torch.int32, device=DEV)
+    cache = ops.PagedKVArgs(kp, vp, table, 2, nkv, hd)
+    pos = torch.arange(N, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(rows, 0, pos, torch.zeros(N, dtype=torch.int32, device=DEV),
+                      torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([N], dtype=torch.int32, device=DEV),
+                      None, 0, 0, cache, nkv, hd)
+    for p in range(N - 128, N):                               # the last 128 positions are there
+        page = [2, 1][(p // 64) % 2]
+        assert float(kp[page, 0, p % 64, 0]) == p
+    assert float(kp[0].max()) == -1 and float(kp[3].max()) == -1
+
+
+def test_argmax_first_maximum_wins():
+    from hos_b200 import ops
+    V = 256000 + 37
+    logits = torch.randn(5, V, device=DEV)
+    logits[0, 77] = logits[0, 200000] = 9.0
+    logits[1, V - 1] = 9.0
+    logits[2, :] = 1.5                                        # all equal: token 0
+    logits[3, 0] = 9.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    assert out.tolist()[:4] == [77, V - 1, 0, 0]
+    assert out.tolist()[4] == int(logits[4].argmax())
+
+
+@pytest.mark.parametrize("params", [dict(temp=1.0, top_k=0, top_p=1.0, rep=1.0),
+                                    dict(temp=0.7, top_k=5, top_p=1.0, rep=1.0),
+                                    dict(temp=1.3, top_k=0, top_p=0.8, rep=1.0),
+                                    dict(temp=0.9, top_k=50, top_p=0.6, rep=1.4),
+                                    dict(temp=0.0, top_k=40, top_p=0.95, rep=1.5),
+                                    dict(temp=2.0, top_k=1, top_p=1.0, rep=1.0)])
+def test_sampling_kernel_follows_the_plain_sampler(params):
+    """Same logits, same uniform draw -> the same token as the plain restatement of the
+    reference's sampler, ties and repeated 'recent' tokens included."""
+    from plain import gemma2_plain as P
+    from hos_b200 import ops
+    V, B = 1003, 24
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(B, V, generator=g) * 2.0
+    logits[:, 100:110] = logits[:, 100:101]                  # ten exactly equal logits per row
+    logits[3, :] = 0.25                                       # a row where everything ties
+    logits[4, 500:520] = 6.0                                  # a tie at the top
+    recent = [[int(x) for x in torch.randint(0, V, (6,), generator=g)] + [int(logits[b].argmax())] * 2
+              for b in range(B)]
+    state = 0x9E3779B97F4A7C15
+    us = []
+    for b in range(B):
+        state, u = P.next_rand(state)
+        us.append(u)
+    us[5] = 0.0
+    want = []
+    for b in range(B):
+        class Fixed:                                          # make P.sample draw exactly us[b]
+            pass
+        tok, _ = _plain_sample_with_u(P, logits[b], params, recent[b], us[b])
+        want.append(tok)
+    dl = logits.to(DEV).contiguous()
+    keep = dl.clone()
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    ops.sample(dl, torch.tensor(us, device=DEV), out, params["temp"], params["top_k"], params["top_p"],
+               params["rep"], torch.tensor(recent, dtype=torch.int32, device=DEV),
+               torch.full((B,), 8, dtype=torch.int32, device=DEV))
+    assert out.tolist() == want
+    assert torch.equal(dl, keep)                              # the logits are handed back unchanged
+
+
+def _plain_sample_with_u(P, logits, params, recent, u):
+    """P.sample with its generator replaced by a fixed draw u."""
+    orig = P.next_rand
+    P.next_rand = lambda s: (s, u)
+    try:
+        return P.sample(logits, params["temp"], params["top_k"], params["top_p"], params["rep"], recent, 1)
+    finally:
+        P.next_rand = orig
+
+
+def test_gather_rows():
+    from hos_b200 import ops
+    x = torch.randn(50, 331, device=DEV)
+    idx = torch.tensor([49, 0, 7, 7], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, 331, device=DEV)
+    ops.gather_rows(x, idx, out)
+    assert torch.equal(out, x[idx.long()])

@@ -1,0 +1,48 @@
+"""Trace replay on the GPU, through bin/trace_run as a user runs it, compared with
+the plain implementation: each request alone and whole; with its last 32 tokens one
+by one; in batches of unequal lengths whose shorter requests end earlier, one batch
+after another so that slots and pages are used again.  In 32-bit and in bfloat16."""
+import random
+
+import pytest
+import torch
+
+from plain import gemma2_plain as P
+from helpers import TINY, Trace, check_trace, make_folder, plain_model, random_tokens, run_trace
+
+pytestmark = pytest.mark.gpu
+
+# lengths chosen around what is special: 1 token, the window's size and one more, a page (64)
+# and one more, and long enough that the window's ring of 64 positions wraps
+LENGTHS = {"A": [1, 5, 8, 9, 33, 64, 65, 97], "B": [1, 9, 16, 17, 23, 40, 80, 128],
+           "C": [2, 40, 41, 63, 129, 200, 333, 150]}
+
+
+def build(name):
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(100 + ord(name))
+    reqs = [random_tokens(rng, n, vocab) for n in LENGTHS[name]]
+    t = Trace()
+    for i, r in enumerate(reqs):
+        t.whole(f"w{i}", i, r)
+    for i, r in enumerate(reqs):
+        t.tail_one_by_one(f"t{i}", i, r)
+    # batches: prompts are a part of each request, the rest is decoded; unequal all the way
+    order = list(range(len(reqs)))
+    rng.shuffle(order)
+    for b, group in enumerate((order[:3], order[3:6], order[6:], order[1:5])):
+        members = [(f"b{b}_{i}", i, reqs[i]) for i in group]
+        plens = [max(1, len(reqs[i]) - rng.choice([0, 3, 32, 70])) for i in group]
+        t.batch(members, plens)
+    return reqs, t
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_matches_the_plain_implementation(tmp_path, name, dtype):
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    reqs, trace = build(name)
+    expected = {i: P.forward_logits(w, cfg, r) for i, r in enumerate(reqs)}
+    got = run_trace(folder, dtype, trace, str(tmp_path / "out"))
+    check_trace(trace, got, expected, dtype)
