@@ -36,7 +36,10 @@ def main(argv=None) -> int:
 
     print("[hos] loading the model (kernels are compiled at their first use)", file=sys.stderr, flush=True)
     from .runner import Runner
-    runner = Runner.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    # the cache alone bounds a request's length here: replay is not cut at the model's
+    # max_position_embeddings, which generation takes as its context limit
+    runner = Runner.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
+                                max_seq_len=args.max_tokens)
     slots: Dict[str, int] = {}
 
     for line in sys.stdin:

@@ -205,7 +205,7 @@ def test_attention_plain_over_the_cache_and_over_packed_rows(cfg, dtype):
                    k_rows=rows[:, nh * hd:], v_rows=rows[:, (nh + nkv) * hd:], kv_stride=stride, cu_seqlens=cu)
     base = 0
     for i, l in enumerate(seq_lens):
-        for p in sorted({0, 1, l // 2, l - 1}):
+        for p in sorted({0, min(1, l - 1), l // 2, l - 1}):
             want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
             close(out[base + p].reshape(nh, hd), want.to(dt), dt)
         base += l
