@@ -1,0 +1,297 @@
+#!/usr/bin/env python3
+"""Measurement: decode and prompt throughput of Gemma-2 2B sizes with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--ctx C] [--layers L]
+
+A "step" is one decode step of the whole batch.  The timed region is K decode steps that end
+at context length C (default 8192, the benchmark context of the 2B configuration), timed on
+the device with CUDA events; `value` is decoded tokens per second.  `e2e` is the same loop
+through the public entry point (`Engine.step` and the sampler), host token ids in and out
+every step.  `prefill` is one prompt of 2,048 tokens.  `roofline` relates the bytes a decode
+step must read (every weight once, and the cache of the live sequences) to its time.
+`points` holds decoding at batch 1 and 64.  One JSON line is printed.
+
+Random weights are made on the device; the cache of the decode measurements is filled with
+random keys and values instead of being computed by a prompt (a decode step reads the same
+bytes either way), and says so under config.cache_fill.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Gemma-2 2B layer sizes (BASELINE.json configs[2])
+GEMMA2_2B = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2", num_hidden_layers=26, hidden_size=2304,
+    num_attention_heads=8, num_key_value_heads=4, head_dim=256, intermediate_size=9216,
+    vocab_size=256000, rope_theta=10000.0, sliding_window=4096, max_position_embeddings=8192,
+    query_pre_attn_scalar=256, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
+    rms_norm_eps=1e-6, tie_word_embeddings=True)
+FULL_LAYERS = 26
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background while the timed region runs (reading only)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons)}
+
+
+def weight_bytes(cfg, n_layers) -> int:
+    """Bytes of every weight a decode step reads once (bfloat16): the layers' matrices and
+    norm vectors, the final norm, and the head (the tied embedding table, read whole by the
+    head; the embedding lookup reads one row per sequence, which is not counted)."""
+    d, qd = cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim
+    kvd, f = cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
+    per_layer = (qd + 2 * kvd) * d + d * qd + 2 * f * d + d * f
+    norms = 4 * d * 4                       # float32 vectors
+    return n_layers * (per_layer * 2 + norms) + d * 4 + cfg.vocab_size * d * 2
+
+
+def kv_bytes_at(cfg, n_layers, length) -> int:
+    """Cache bytes one sequence of `length` tokens makes a decode step read (bfloat16 keys
+    and values; even layers see the last sliding_window keys only)."""
+    per_tok = 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    sliding = sum(1 for l in range(n_layers) if cfg.layer_is_sliding(l))
+    return per_tok * (sliding * min(length, cfg.sliding_window) + (n_layers - sliding) * length)
+
+
+def prefill_flops(cfg, n_layers, t) -> float:
+    d, qd = cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim
+    kvd, f = cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
+    linear = 2.0 * t * ((qd + 2 * kvd) * d + d * qd + 3 * f * d)
+    flops = 0.0
+    for l in range(n_layers):
+        w = cfg.sliding_window if cfg.layer_is_sliding(l) else t
+        pairs = sum(min(p + 1, w) for p in range(t))
+        flops += linear + 4.0 * cfg.head_dim * cfg.num_attention_heads * pairs
+    return flops + 2.0 * d * cfg.vocab_size          # the head runs on the last row
+
+
+def fill_cache_random(runner):
+    import torch
+    for g in runner.cache.groups:
+        for t in g.k + g.v:
+            flat = t.view(-1)
+            for lo in range(0, flat.numel(), 1 << 28):
+                flat[lo:lo + (1 << 28)].normal_(0.0, 0.5)
+
+
+def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
+    """K timed decode steps that end at length ctx.  Returns (device ms per step, e2e ms per
+    step, kernel launches in the timed region, h2d bytes per step, d2h bytes per step, mean length)."""
+    import torch
+    from hos_b200 import ops
+    from hos_b200.sampling import Sampler, SamplingParams
+    r = eng.runner
+    vocab = r.vocab_size
+
+    def prepare():
+        slots = r.admit(batch)
+        start = ctx - (warmup + steps)
+        for s in slots:
+            r.cache.extend(s, start)
+        return slots, start
+
+    # ---- device-timed: steps issued back to back, tokens stay on the device ----
+    slots, start = prepare()
+    toks = [[rng.randrange(vocab)] for _ in range(batch)]
+    ms_dev, launches = r.decode_steps_timed(slots, toks, warmup, steps, clocks)
+    for s in slots:
+        r.release(s)
+
+    # ---- end to end: the public step and the sampler, host ids in and out every step ----
+    slots, start = prepare()
+    sampler = Sampler(SamplingParams.pure(), r.device)
+    for i, s in enumerate(slots):
+        sampler.open(s, i)
+    toks = [[rng.randrange(vocab)] for _ in range(batch)]
+    for _ in range(warmup):
+        toks = [[t] for t in sampler.sample(eng.step(slots, toks), slots)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        toks = [[t] for t in sampler.sample(eng.step(slots, toks), slots)]
+    torch.cuda.synchronize()
+    ms_e2e = (time.perf_counter() - t0) * 1e3 / steps
+    for s in slots:
+        sampler.close(s)
+        r.release(s)
+    h2d = (3 * batch + (batch + 1) + 2 * batch) * 4 + batch * 4     # step arrays + wanted rows
+    d2h = batch * 4
+    mean_len = ctx - steps / 2.0
+    return ms_dev, ms_e2e, launches, h2d, d2h, mean_len
+
+
+def measure_prefill(eng, tokens, rng, reps=3):
+    import torch
+    r = eng.runner
+    prompt = [rng.randrange(r.vocab_size) for _ in range(tokens)]
+    best = None
+    for i in range(reps + 1):
+        slot = r.admit(1)[0]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r.step([slot], [prompt])
+        e1.record()
+        torch.cuda.synchronize()
+        r.release(slot)
+        ms = e0.elapsed_time(e1)
+        if i > 0:                              # the first run warms up
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the configuration has, for a quick run")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--no-prefill", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate: no cargo/rustc in this image and no network "
+                          "to fetch its 38 crates; it also runs Gemma-2 on the CPU only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this library runs on a single GPU, --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import random
+    import torch
+    from hos_b200 import Engine, ops
+    from hos_b200 import models  # noqa: F401
+    from hos_b200.registry import config_from_dict
+
+    raw = dict(GEMMA2_2B, num_hidden_layers=args.layers)
+    cfg = config_from_dict(raw)
+    pk, pk_src = peaks()
+    rng = random.Random(0)
+    batches = [args.batch] + ([] if args.no_points else [1, 64])
+    cap_tokens = max(batches) * ((args.ctx + 63) // 64 * 64)
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_batch=max(batches), max_tokens=cap_tokens,
+                             max_seq_len=args.ctx)
+    fill_cache_random(eng.runner)
+    torch.cuda.synchronize()
+
+    clocks = ClockSampler(torch.cuda.current_device())
+    ms_dev, ms_e2e, launches, h2d, d2h, mean_len = measure_decode(
+        eng, args.batch, args.ctx, args.steps, args.warmup, rng, clocks)
+    clock_rec = clocks.result
+
+    wbytes = weight_bytes(cfg, args.layers)
+    step_bytes = wbytes + args.batch * kv_bytes_at(cfg, args.layers, int(mean_len))
+    achieved = step_bytes / (ms_dev * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Gemma-2 2B)",
+        "value": args.batch * 1e3 / ms_dev, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "gemma-2-2b sizes, random weights", "global_batch": args.batch, "seq_len": args.ctx,
+            "parallelism": "single_gpu", "layers": args.layers, "layers_full": FULL_LAYERS,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "sliding_window": cfg.sliding_window, "decode_ends_at": args.ctx,
+            "cache_fill": "random keys and values", "l2": "inputs larger than L2 (weights %.1f GB per step)" % (wbytes / 1e9),
+            "peaks": pk_src, "prefill_tokens": PREFILL_TOKENS},
+        "clocks": clock_rec,
+        "e2e": {"value": args.batch * 1e3 / ms_e2e, "unit": "tok/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes, "of": pk_src},
+    }
+    if not args.no_prefill:
+        ms = measure_prefill(eng, PREFILL_TOKENS, rng)
+        fl = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        line["prefill"] = {"value": PREFILL_TOKENS * 1e3 / ms, "tokens": PREFILL_TOKENS, "ms": ms,
+                           "frac": fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "tflop": fl / 1e12,
+                           "of": pk_src}
+    if not args.no_points:
+        pts = {}
+        for b in (1, 64):
+            m, _, _, _, _, _ = measure_decode(eng, b, args.ctx, max(8, args.steps // 2), args.warmup, rng)
+            pts[f"decode_b{b}"] = b * 1e3 / m
+        line["points"] = pts
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

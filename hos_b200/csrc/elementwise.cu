@@ -159,6 +159,18 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
     for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
 }
 
+// After a decode step whose tokens were chosen on the device: the chosen token becomes
+// the next step's input, positions and lengths move on by one (padding rows stay as they are).
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ token_pos,
+                                      int* __restrict__ seq_len_after, const int* __restrict__ token_seq,
+                                      const int* __restrict__ sampled, int B) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B || token_seq[i] < 0) return;
+    tokens[i] = sampled[i];
+    token_pos[i] += 1;
+    seq_len_after[i] += 1;
+}
+
 static int row_smem_ok(const void* kernel, int D) {
     size_t bytes = (size_t)D * sizeof(float);
     if (bytes > 200 * 1024) return -1;
@@ -276,4 +288,12 @@ extern "C" int hos_gather_rows(const float* x, const int* idx, float* out, int n
     if (n <= 0) return 0;
     gather_rows_kernel<<<n, 256, 0, stream>>>(x, idx, out, D);
     return check_launch("gather_rows");
+}
+
+extern "C" int hos_decode_advance(int* tokens, int* token_pos, int* seq_len_after, const int* token_seq,
+                                  const int* sampled, int B, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, token_pos, seq_len_after,
+                                                               token_seq, sampled, B);
+    return check_launch("decode_advance");
 }

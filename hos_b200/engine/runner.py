@@ -125,6 +125,31 @@ class Runner:
         info = build_step(token_lists, starts, slots, self.device, self.vocab_size)
         return self.model.hidden(info, self.cache)
 
+    def decode_steps_timed(self, slots, first_tokens, warmup: int, steps: int, clocks=None):
+        """`warmup` untimed and `steps` timed greedy decode steps, issued back to back with
+        the chosen tokens staying on the device; timed with CUDA events.  Returns
+        (milliseconds per step, kernel-launching calls in the timed region)."""
+        from .decode import DecodeSession
+        lengths = [self.cache.lengths[s] for s in slots]
+        for s, n in zip(slots, lengths):
+            self.cache.extend(s, n + warmup + steps)        # pages for every position written
+        sess = DecodeSession(self, slots)
+        sess.feed([t[0] for t in first_tokens], lengths)
+        for _ in range(warmup):
+            sess.run_greedy_on_device()
+        torch.cuda.synchronize()
+        if clocks is not None:
+            clocks.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sess.run_greedy_on_device()
+        e1.record()
+        torch.cuda.synchronize()
+        if clocks is not None:
+            clocks.result = clocks.stop()
+        return e0.elapsed_time(e1) / steps, sess.launches_per_step * steps
+
     @property
     def max_seq_len(self) -> int:
         return self.cache.max_seq_len

@@ -101,6 +101,8 @@ class Library:
         return f
 
     def call(self, name: str, *args, signature: Optional[str] = None) -> None:
+        global launch_count
+        launch_count += 1
         rc = self.fn(name, signature)(*args)
         if rc != 0:
             msg = self._last_error() if self._last_error else b""
@@ -108,6 +110,7 @@ class Library:
 
 
 _core: Optional[Library] = None
+launch_count = 0        # calls into the CUDA libraries so far (each launches one kernel or more)
 
 
 def core() -> Library:
@@ -299,3 +302,8 @@ def sample(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor, temp
     core().call("hos_sample", _ptr(logits), v, b, v, _ptr(uniforms), _ptr(recent),
                 recent.shape[1] if recent is not None else 0, _ptr(recent_len), float(temp),
                 int(top_k), float(top_p), float(rep_penalty), _ptr(out), _stream())
+
+
+def decode_advance(tokens, token_pos, seq_len_after, token_seq, sampled) -> None:
+    core().call("hos_decode_advance", _ptr(tokens), _ptr(token_pos), _ptr(seq_len_after), _ptr(token_seq),
+                _ptr(sampled), tokens.shape[0], _stream())
