@@ -1,10 +1,99 @@
 """Python face of the tensor-core attention kernels (csrc/attention_decode.cu,
-csrc/attention_prefill.cu), compiled per head size."""
+csrc/attention_prefill.cu).  They are compiled per head size (a multiple of 16, at most
+256) as library `attn_hd<N>`; other head sizes are left to the plain kernel."""
 from __future__ import annotations
 
-ENABLED = False     # switched on once the kernels are built and checked
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..errors import KernelError
+
+SM_COUNT = 148
+MAX_HEAD_DIM = 256
+
+_libs: Dict[int, ops.Library] = {}
+enabled = {"decode": True, "prefill": True}     # tests switch a kernel off to compare with the plain one
+
+
+def supports(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= MAX_HEAD_DIM
+
+
+def lib_for(head_dim: int) -> ops.Library:
+    lib = _libs.get(head_dim)
+    if lib is None:
+        lib = _libs[head_dim] = ops.Library(f"attn_hd{head_dim}")
+    return lib
+
+
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int]) -> int:
+    """How many shares the keys of one (token, kv head) are cut into: enough CTAs for two
+    waves over the SMs, but no share under two pages."""
+    chunks = (group + 15) // 16
+    span = min(max_len, window) if window else max_len
+    pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
+    ctas = max(1, n_tokens * n_kv_heads * chunks)
+    want = (2 * SM_COUNT + ctas - 1) // ctas
+    return max(1, min(want, (pages + 1) // 2))
+
+
+def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
+           cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
+           window: Optional[int], max_len: int, n_splits: Optional[int] = None) -> None:
+    """Attention of n_tokens single queries over the paged cache (each token at its own
+    position in its own sequence)."""
+    hd, nkv = cache.head_dim, cache.n_kv_heads
+    lib = lib_for(hd)
+    if n_splits is None:
+        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window)
+    ws = None
+    if n_splits > 1:
+        ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+    lib.call("hos_attn_decode", ops._ptr(q), q_stride, ops._ptr(out), out.shape[1], ops._ptr(ws),
+             ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(cache.k_pages),
+             ops._ptr(cache.v_pages), ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages,
+             n_tokens, n_heads, nkv, hd, float(scale), float(cap), int(window) if window else 0,
+             int(n_splits), ops._stream())
+
+
+def decode_gave_up(head_dim: int) -> bool:
+    """True if a launch since the last call left a bounded wait unfinished (synchronises)."""
+    lib = lib_for(head_dim)
+    f = lib.lib.hos_attn_decode_error
+    f.restype = ctypes.c_int
+    f.argtypes = []
+    return bool(f())
+
+
+def prefill(q, q_stride, k_rows, v_rows, kv_stride, out, cu_seqlens, cu_host, n_heads, n_kv_heads, head_dim,
+            scale, cap, window) -> None:
+    """Attention of whole prompts from position 0 over their own packed rows."""
+    lib = lib_for(head_dim)
+    n_seqs = len(cu_host) - 1
+    tiles = sum((cu_host[i + 1] - cu_host[i] + 63) // 64 for i in range(n_seqs))
+    lib.call("hos_attn_prefill", ops._ptr(q), q_stride, ops._ptr(k_rows), ops._ptr(v_rows), kv_stride,
+             ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens), n_seqs, tiles, n_heads, n_kv_heads, head_dim,
+             float(scale), float(cap), int(window) if window else 0, ops._stream())
 
 
 def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
     """Runs the tensor-core kernel if it takes the case; False hands it to the plain kernel."""
-    return False
+    if cache.k_pages.dtype != torch.bfloat16 or not supports(mixer.head_dim):
+        return False
+    if packed:
+        if not enabled["prefill"]:
+            return False
+        if step.n_tokens > step.cu_host[-1]:
+            att[step.cu_host[-1]:].zero_()       # padding rows: a defined output
+        prefill(qkv, qkv.shape[1], qkv[:, mixer.q_dim:], qkv[:, mixer.q_dim + mixer.kv_dim:], qkv.shape[1],
+                att, step.cu_seqlens, step.cu_host, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                mixer.scale, mixer.softcap, mixer.window)
+        return True
+    if not enabled["decode"]:
+        return False
+    decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
+           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after)
+    return True

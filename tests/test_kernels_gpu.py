@@ -115,7 +115,8 @@ def test_gemm_plain(shape, dtype):
     close(out, (torch.nn.functional.gelu(g, approximate="tanh") * u).to(dt), dt)
 
 
-def _fill_cache(k_rows, v_rows, seq_lens, n_kv, hd, ring_pages, dtype, n_slots=4, scatter_seed=0):
+def _fill_cache(k_rows, v_rows, seq_lens, n_kv, hd, ring_pages, dtype, n_slots=4, scatter_seed=0,
+                fill=float("nan")):
     """Put per-sequence keys/values [len, n_kv, hd] into a paged cache with scattered pages,
     through the library's own write kernel (rope off)."""
     from hos_b200 import ops
@@ -132,8 +133,8 @@ def _fill_cache(k_rows, v_rows, seq_lens, n_kv, hd, ring_pages, dtype, n_slots=4
     for s, npg in zip(slots, pages_per):
         for e in range(npg):
             table[s, e] = next(it)
-    kp = torch.full((n_pages, n_kv, 64, hd), float("nan"), device=DEV).to(dtype)
-    vp = torch.full((n_pages, n_kv, 64, hd), float("nan"), device=DEV).to(dtype)
+    kp = torch.full((n_pages, n_kv, 64, hd), fill, device=DEV).to(dtype)
+    vp = torch.full((n_pages, n_kv, 64, hd), fill, device=DEV).to(dtype)
     cache = ops.PagedKVArgs(kp, vp, table.to(DEV), ring_pages, n_kv, hd)
     # rows: [q(0 heads) | k | v]
     rows = torch.cat([torch.cat([k.reshape(len(k), -1), v.reshape(len(v), -1)], 1) for k, v in zip(k_rows, v_rows)])
@@ -343,3 +344,114 @@ def test_gather_rows():
     out = torch.empty(4, 331, device=DEV)
     ops.gather_rows(x, idx, out)
     assert torch.equal(out, x[idx.long()])
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=8, cap=50.0),
+                                 dict(nh=6, nkv=1, hd=32, window=16, cap=20.0),
+                                 dict(nh=5, nkv=5, hd=48, window=40, cap=30.0),
+                                 dict(nh=3, nkv=1, hd=64, window=None, cap=0.0),
+                                 dict(nh=40, nkv=2, hd=80, window=130, cap=9.0),
+                                 dict(nh=4, nkv=2, hd=128, window=None, cap=50.0),
+                                 dict(nh=8, nkv=4, hd=256, window=200, cap=50.0),
+                                 dict(nh=2, nkv=1, hd=256, window=None, cap=50.0)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attention_decode_kernel(cfg, n_splits):
+    """The tensor-core decode kernel over a scattered paged cache: rings that have wrapped,
+    a key at the window's edge that stands out, sequences of 1 token and of several pages,
+    more splits than pages, 20 heads on one kv head (two MMA tiles), a padding row, and
+    several tokens of one sequence in one launch."""
+    from hos_b200 import ops
+    from hos_b200.parts import attention_fast as af
+    dt = torch.bfloat16
+    nh, nkv, hd, window, cap = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], cfg["cap"]
+    torch.manual_seed(2)
+    seq_lens = [1, 64, 65, 130, 517]
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(l, nh, hd).to(dt).float() for l in seq_lens]
+    g = nh // nkv
+    lo = max(0, 517 - window) if window else 0
+    ks[4][lo] = qs[4][516, 0::g][:nkv] * 3.0           # the oldest visible key stands out
+    if lo > 0:
+        ks[4][lo - 1] = qs[4][516, 0::g][:nkv] * 6.0   # and the newest invisible one would even more
+    scale = 0.9 / math.sqrt(hd)
+    ring = (window + 63) // 64 if window else 0
+    cache, slots = _fill_cache([k.to(DEV) for k in ks], [v.to(DEV) for v in vs], seq_lens, nkv, hd, ring, dt,
+                               n_slots=9, scatter_seed=3, fill=0.0)
+    # queries: the last position of every sequence, a padding row, and three earlier positions
+    # of the longest sequence that are still answerable from what the cache holds
+    items = [(i, l - 1) for i, l in enumerate(seq_lens)] + [(-1, 0)]
+    keep_from = 517 - ring * 64 if ring else 0             # oldest position still stored
+    for p in (516 - 1, 516 - 7, 450):
+        if (max(0, p + 1 - window) if window else 0) >= keep_from:
+            items.append((4, p))
+    q = torch.stack([qs[i][p] if i >= 0 else torch.zeros(nh, hd) for i, p in items]).reshape(len(items), nh * hd)
+    q = q.to(DEV).to(dt).contiguous()
+    out = torch.full_like(q, 7.0)
+    pos = torch.tensor([p for _, p in items], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([i for i, _ in items], dtype=torch.int32, device=DEV)
+    af.decode(q, nh * hd, out, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), cache, len(items),
+              nh, scale, cap, window, 517, n_splits=n_splits)
+    assert not af.decode_gave_up(hd)
+    for j, (i, p) in enumerate(items):
+        if i < 0:
+            assert float(out[j].abs().sum()) == 0.0
+            continue
+        want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
+        close(out[j].reshape(nh, hd), want.to(dt), dt)
+    # the heuristic's own choice of splits gives the same
+    out2 = torch.empty_like(q)
+    af.decode(q, nh * hd, out2, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), cache, len(items),
+              nh, scale, cap, window, 517)
+    close(out2, out, dt)
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=8, cap=50.0),
+                                 dict(nh=6, nkv=1, hd=32, window=16, cap=20.0),
+                                 dict(nh=5, nkv=5, hd=48, window=40, cap=30.0),
+                                 dict(nh=3, nkv=1, hd=64, window=None, cap=0.0),
+                                 dict(nh=4, nkv=2, hd=128, window=100, cap=50.0),
+                                 dict(nh=8, nkv=4, hd=256, window=200, cap=50.0),
+                                 dict(nh=2, nkv=2, hd=256, window=None, cap=50.0)])
+def test_attention_prefill_kernel(cfg):
+    """The tensor-core prompt kernel over packed rows of unequal sequences (1, 63, 64, 65, 130
+    and 517 tokens): every position, causal and windowed, against float64."""
+    from hos_b200.parts import attention_fast as af
+    dt = torch.bfloat16
+    nh, nkv, hd, window, cap = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], cfg["cap"]
+    torch.manual_seed(3)
+    seq_lens = [1, 63, 64, 65, 130, 517]
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(l, nh, hd).to(dt).float() for l in seq_lens]
+    g = nh // nkv
+    if window:
+        ks[5][517 - window] = qs[5][516, 0::g][:nkv] * 3.0       # the window's oldest key stands out
+        ks[5][517 - window - 1] = qs[5][516, 0::g][:nkv] * 6.0   # just outside: must not be seen
+    scale = 0.9 / math.sqrt(hd)
+    rows = torch.cat([torch.cat([q.reshape(len(q), -1), k.reshape(len(k), -1), v.reshape(len(v), -1)], 1)
+                      for q, k, v in zip(qs, ks, vs)]).to(DEV).to(dt)
+    rows = torch.cat([rows, torch.full((5, rows.shape[1]), float("nan"), device=DEV, dtype=dt)]).contiguous()
+    N, stride = rows.shape
+    cu_host = [0]
+    for l in seq_lens:
+        cu_host.append(cu_host[-1] + l)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device=DEV)
+    out = torch.full((N, nh * hd), 7.0, device=DEV, dtype=dt)
+    af.prefill(rows, stride, rows[:, nh * hd:], rows[:, (nh + nkv) * hd:], stride, out, cu, cu_host, nh, nkv, hd,
+               scale, cap, window)
+    assert float((out[cu_host[-1]:] - 7.0).abs().sum()) == 0.0      # padding rows are not touched
+    base = 0
+    for i, l in enumerate(seq_lens):
+        q, k, v = qs[i].double(), ks[i].double(), vs[i].double()
+        pos = torch.arange(l)
+        vis = pos[None, :] <= pos[:, None]
+        if window:
+            vis &= pos[None, :] > pos[:, None] - window
+        for h in range(nh):
+            s = (q[:, h] @ k[:, h // g].T) * scale
+            if cap > 0:
+                s = cap * torch.tanh(s / cap)
+            want = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // g]
+            close(out[base:base + l, h * hd:(h + 1) * hd], want.to(dt), dt)
+        base += l
