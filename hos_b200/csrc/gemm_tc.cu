@@ -1,0 +1,552 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: out[M, N] = A[M, K] . W[N, K]^T.
+//
+// Both operands are K-major (rows of K contiguous elements), which is how activations and
+// checkpoint weights lie in memory.  TMA (cp.async.bulk.tensor, 128-byte swizzle) brings
+// [rows x 64] tiles of both into shared memory through a ring of stages; one thread issues
+// tcgen05.mma (M = 128, N = the other tile's rows, K = 16 per instruction) with the 32-bit
+// accumulator in tensor memory; four warps read the accumulator back (tcgen05.ld), apply the
+// epilogue and store.  The kernel is persistent: each CTA walks over output tiles, with two
+// accumulators in tensor memory so that the epilogue of one tile overlaps the products of
+// the next.  Warp roles: 0 TMA producer, 1 MMA issuer (and tensor-memory allocation), 2-5
+// epilogue.
+//
+// Two orientations share the code.  "Normal": the 128-row MMA operand is a tile of A
+// (tokens), the N operand 256 rows of W; thread t of the epilogue holds one token's row of
+// the output tile.  "Swapped" (few tokens, e.g. decoding): the 128-row operand is a tile of W
+// and the N operand is all of A's rows (16, 32 or 64); the accumulator holds the output
+// transposed and the epilogue writes it back in place, coalesced over output features.  In
+// the swapped orientation K may be split over several CTAs, each writing 32-bit partial sums
+// that a small kernel adds in a fixed order.
+//
+// Epilogues: none; soft-cap c*tanh(x/c) with 32-bit output (logits); gated act(gate)*up,
+// where W holds the gate rows followed by the up rows and a tile loads matching rows of both.
+//
+// Every wait on an mbarrier is bounded in time: a wait that runs out sets an error flag,
+// the roles leave their loops, tensor memory is freed and the kernel returns.
+#include <cuda.h>
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace hos {
+
+constexpr int GM = 128;            // rows of the M operand per tile (UMMA M)
+constexpr int GK = 64;             // K elements per stage: 128 bytes, one swizzle atom
+constexpr int kGemmThreads = 192;
+constexpr long long kWaitCycles = 1ll << 31;     // about a second
+
+enum { kGEpiNone = 0, kGEpiSoftcap = 1, kGEpiGated = 2 };
+
+__device__ int g_gemm_error = 0;
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > kWaitCycles) return false;
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i)'s columns.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (the tile base is 1024-byte aligned).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                               // layout: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct GemmParams {
+    void* out;            // [M, N] row-major (bf16 or f32); with K splits: f32 partials [splits][M][N]
+    int M, N, K;          // the product's logical sizes: rows of A, rows of W (per half if gated), K
+    int ldo;
+    int k_splits;
+    int gate_rows;        // gated: row of W where the up rows begin
+    float cap;
+    int act;
+};
+
+template <int BN, bool SWAP>
+struct GemmCfg {
+    static constexpr int kABytes = GM * GK * 2;
+    static constexpr int kBBytes = BN * GK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static constexpr int kExchangeBytes = SWAP ? 64 * BN * 4 : 0;          // gated + swapped: up rows cross warps
+    static constexpr int kSmem = kStages * kStageBytes + kExchangeBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;            // two accumulators; a power of two >= 32
+};
+
+template <int BN, int EPI, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row operand: A (normal) or W (swapped)
+               const __grid_constant__ CUtensorMap map_n,     // the BN-row operand: W (normal) or A (swapped)
+               GemmParams p) {
+    using Cfg = GemmCfg<BN, SWAP>;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = smem;
+    float* exchange = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kExchangeBytes);
+    uint64_t* full = bars;                          // [kStages] TMA -> MMA
+    uint64_t* empty = bars + Cfg::kStages;          // [kStages] MMA -> TMA
+    uint64_t* acc_full = empty + Cfg::kStages;      // [2] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;             // [2] epilogue -> MMA
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // rows of the two MMA operands in the product's terms
+    const int rows_m = SWAP ? p.N : p.M;            // what the 128-row operand spans
+    const int rows_n = SWAP ? p.M : p.N;
+    const int m_tiles = (rows_m + (EPI == kGEpiGated && SWAP ? 64 : GM) - 1) / (EPI == kGEpiGated && SWAP ? 64 : GM);
+    const int n_span = (EPI == kGEpiGated && !SWAP) ? BN / 2 : BN;        // output columns (normal) per tile
+    const int n_tiles = (rows_n + n_span - 1) / n_span;
+    const int k_blocks = (p.K + GK - 1) / GK;
+    const int kb_per_split = (k_blocks + p.k_splits - 1) / p.k_splits;
+    const int total_tiles = m_tiles * n_tiles * p.k_splits;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&map_m);
+        prefetch_tmap(&map_n);
+        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    auto tile_coords = [&](int tile, int& mt, int& nt, int& ks) {
+        ks = tile % p.k_splits;
+        const int t = tile / p.k_splits;
+        mt = t % m_tiles;
+        nt = t / m_tiles;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int mt, nt, ks;
+                tile_coords(tile, mt, nt, ks);
+                const int kb0 = ks * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    if (it >= Cfg::kStages && !mbar_wait_timed(&empty[s], ((it / Cfg::kStages) - 1) & 1)) { ok = false; break; }
+                    unsigned char* a_dst = stages + (size_t)s * Cfg::kStageBytes;
+                    unsigned char* b_dst = a_dst + Cfg::kABytes;
+                    mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                    if (EPI == kGEpiGated && SWAP) {        // 64 gate rows, then the 64 matching up rows
+                        tma_load_2d(a_dst, &map_m, kb * GK, mt * 64, &full[s]);
+                        tma_load_2d(a_dst + Cfg::kABytes / 2, &map_m, kb * GK, p.gate_rows + mt * 64, &full[s]);
+                    } else {
+                        tma_load_2d(a_dst, &map_m, kb * GK, mt * GM, &full[s]);
+                    }
+                    if (EPI == kGEpiGated && !SWAP) {       // BN/2 gate rows, then the matching up rows
+                        tma_load_2d(b_dst, &map_n, kb * GK, nt * (BN / 2), &full[s]);
+                        tma_load_2d(b_dst + Cfg::kBBytes / 2, &map_n, kb * GK, p.gate_rows + nt * (BN / 2), &full[s]);
+                    } else {
+                        tma_load_2d(b_dst, &map_n, kb * GK, nt * BN, &full[s]);
+                    }
+                }
+            }
+            if (!ok) atomicExch(&g_gemm_error, 1);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(GM, BN);
+            int it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+                int mt, nt, ks;
+                tile_coords(tile, mt, nt, ks);
+                const int kb0 = ks * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
+                const int acc = local_tile & 1;
+                if (local_tile >= 2 && !mbar_wait_timed(&acc_empty[acc], ((local_tile >> 1) - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    if (!mbar_wait_timed(&full[s], (it / Cfg::kStages) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stages + (size_t)s * Cfg::kStageBytes);
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(a_addr + Cfg::kABytes);
+#pragma unroll
+                    for (int k = 0; k < GK / 16; ++k)     // 32 bytes further along K: +2 in 16-byte units
+                        umma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);               // the stage is free once these products have read it
+                }
+                if (ok) umma_commit(&acc_full[acc]);      // the accumulator is complete
+            }
+            if (!ok) atomicExch(&g_gemm_error, 1);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: warps 2..5, each owns the TMEM lanes 32*(warp%4).. ----------------
+        const int quarter = warp & 3;
+        int local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+            int mt, nt, ks;
+            tile_coords(tile, mt, nt, ks);
+            const int acc = local_tile & 1;
+            if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            const int r = quarter * 32 + lane;            // this thread's row of the accumulator
+            if (!SWAP) {
+                // row r = token mt*128 + r; columns = output features
+                const int m = mt * GM + r;
+                OutT* orow = reinterpret_cast<OutT*>(p.out) + (size_t)m * p.ldo;
+                constexpr int COLS = (EPI == kGEpiGated) ? BN / 2 : BN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < COLS; c0 += 32) {
+                    uint32_t v[32], u[32];
+                    tmem_ld_32x32(t_lane + c0, v);
+                    if (EPI == kGEpiGated) tmem_ld_32x32(t_lane + BN / 2 + c0, u);
+                    tmem_ld_wait();
+                    const int n0 = nt * COLS + c0;
+                    if (m < p.M) {
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float x = __uint_as_float(v[j]);
+                            if (EPI == kGEpiSoftcap) x = softcap_precise(x, p.cap);
+                            if (EPI == kGEpiGated) {
+                                const float a = p.act == 0 ? gelu_tanh(x) : x / (1.f + __expf(-x));
+                                x = a * __uint_as_float(u[j]);
+                            }
+                            f[j] = x;
+                        }
+                        if (n0 + 32 <= p.N && (p.ldo % 8) == 0) {
+                            if (sizeof(OutT) == 2) {
+                                uint4* dst = reinterpret_cast<uint4*>(orow + n0);
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    dst[q] = make_uint4(pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
+                                                        pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+                            } else {
+                                float4* dst = reinterpret_cast<float4*>(orow + n0);
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) dst[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n0 + j < p.N) orow[n0 + j] = from_float<OutT>(f[j]);
+                        }
+                    }
+                }
+            } else {
+                // row r = output feature; columns = tokens.  out[token][feature]: a warp's 32
+                // lanes write 32 consecutive features of one token.
+                const bool gated = EPI == kGEpiGated;
+                const int feat = gated ? mt * 64 + (r & 63) : mt * GM + r;
+                const int feat_count = p.N;
+                OutT* obase = reinterpret_cast<OutT*>(p.out) + (p.k_splits > 1 ? (size_t)ks * p.M * p.ldo : 0);
+                constexpr int CH = BN < 32 ? BN : 32;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += CH) {
+                    float f[CH];
+                    if (CH == 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(t_lane + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                    } else {
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_lane + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) f[j] = __uint_as_float(v[j]);
+                    }
+                    if (gated) {
+                        // lanes 64..127 hold the up rows of the features whose gate rows lanes 0..63 hold
+                        if (r >= 64) {
+#pragma unroll
+                            for (int j = 0; j < CH; ++j) exchange[(r - 64) * BN + c0 + j] = f[j];
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (r < 64) {
+#pragma unroll
+                            for (int j = 0; j < CH; ++j) {
+                                const float a = p.act == 0 ? gelu_tanh(f[j]) : f[j] / (1.f + __expf(-f[j]));
+                                f[j] = a * exchange[r * BN + c0 + j];
+                            }
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (r >= 64) continue;
+                    }
+                    if (feat < feat_count) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int tok = nt * BN + c0 + j;
+                            if (tok < p.M) {
+                                float x = f[j];
+                                if (EPI == kGEpiSoftcap) x = softcap_precise(x, p.cap);
+                                obase[(size_t)tok * p.ldo + feat] = from_float<OutT>(x);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(&g_gemm_error, 1);
+    }
+    // ---- teardown: everyone is done with tensor memory ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+// Sum K-split partials [splits][M][N] (f32) in a fixed order into out[M][N].
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int M, int N, int ldo,
+                                     int splits) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * N) return;
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += part[(size_t)k * M * N + i];
+    out[(i / N) * ldo + (i % N)] = from_float<OutT>(s);
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// A [rows, K] bf16 matrix with `ld` elements between rows, cut into boxes of [box_rows x 64].
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) HOS_REFUSE("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)GK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) HOS_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d box %d)", (int)r, rows, K, ld, box_rows);
+    return 0;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int EPI, bool SWAP, typename OutT>
+static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams& p, int total_tiles, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN, SWAP>;
+    auto kernel = gemm_tc_kernel<BN, EPI, SWAP, OutT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) != cudaSuccess)
+            HOS_REFUSE("gemm_tc: cannot get %d bytes of shared memory", Cfg::kSmem);
+        attr_set = true;
+    }
+    const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
+    kernel<<<grid, kGemmThreads, Cfg::kSmem, stream>>>(mm, mn, p);
+    return check_launch("gemm_tc");
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
+// 1 if an earlier launch gave up a bounded wait (and clears the flag).  Synchronises.
+extern "C" int hos_gemm_tc_error() {
+    int v = 0, zero = 0;
+    cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return v;
+}
+
+// Floats of workspace for the K-split partial sums of a swapped product (0: no split).
+extern "C" long long hos_gemm_tc_workspace(int M, int N, int k_splits) {
+    return k_splits > 1 ? (long long)k_splits * M * N : 0;
+}
+
+// out[M, N] = A[M, K] . W[N, K]^T, bf16 operands.  out_dtype: 1 bf16, 0 f32.  epilogue: 0 none,
+// 1 soft-cap (f32 output), 2 gated (W has 2N rows: gate rows, then up rows at row N).
+// M <= 64 runs swapped; k_splits > 1 is allowed only then and only without an epilogue, and
+// needs `workspace` (see hos_gemm_tc_workspace).  lda, ldw, ldo in elements.
+extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K, int lda,
+                           int ldw, int ldo, int epilogue, float cap, int act, int k_splits, float* workspace,
+                           cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) HOS_REFUSE("gemm_tc: K must be positive");
+    if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
+        HOS_REFUSE("gemm_tc: K and the leading dimensions must be multiples of 8 elements and the operands "
+                   "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
+    if (epilogue == kGEpiSoftcap && out_dtype != kF32) HOS_REFUSE("gemm_tc: the soft-cap epilogue writes 32-bit");
+    if (epilogue == kGEpiGated && out_dtype != kBF16) HOS_REFUSE("gemm_tc: the gated epilogue writes bfloat16");
+    if (k_splits < 1) k_splits = 1;
+    const bool swap = M <= 64;
+    if (k_splits > 1 && (!swap || epilogue != kGEpiNone || workspace == nullptr))
+        HOS_REFUSE("gemm_tc: K splits need the swapped orientation, no epilogue and a workspace");
+    const int w_rows = epilogue == kGEpiGated ? 2 * N : N;
+    GemmParams p;
+    p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.k_splits = k_splits; p.gate_rows = N; p.cap = cap; p.act = act;
+    CUtensorMap mm, mn;
+    const int k_blocks = (K + GK - 1) / GK;
+    if (k_splits > k_blocks) k_splits = p.k_splits = k_blocks;
+    // no split may be empty: shrink the count until ceil-division leaves none
+    while (k_splits > 1 && (k_splits - 1) * ((k_blocks + k_splits - 1) / k_splits) >= k_blocks) k_splits = --p.k_splits;
+    int rc;
+#define HOS_GO(BN, EPI, SWAP, T, TILES) return launch<BN, EPI, SWAP, T>(mm, mn, p, (TILES), stream)
+    if (!swap) {
+        const int m_tiles = (M + GM - 1) / GM;
+        constexpr int BN = 256;
+        if ((rc = make_map(&mm, A, M, K, lda, GM))) return rc;
+        if (epilogue == kGEpiGated) {
+            if ((rc = make_map(&mn, W, w_rows, K, ldw, BN / 2))) return rc;
+            HOS_GO(256, kGEpiGated, false, bf16, m_tiles * ((N + BN / 2 - 1) / (BN / 2)));
+        }
+        if ((rc = make_map(&mn, W, w_rows, K, ldw, BN))) return rc;
+        const int tiles = m_tiles * ((N + BN - 1) / BN);
+        if (epilogue == kGEpiSoftcap) HOS_GO(256, kGEpiSoftcap, false, float, tiles);
+        if (out_dtype == kBF16) HOS_GO(256, kGEpiNone, false, bf16, tiles);
+        HOS_GO(256, kGEpiNone, false, float, tiles);
+    }
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if ((rc = make_map(&mn, A, M, K, lda, bn))) return rc;
+    if (epilogue == kGEpiGated) {
+        if ((rc = make_map(&mm, W, w_rows, K, ldw, 64))) return rc;
+        const int tiles = (N + 63) / 64;
+        if (bn == 16) HOS_GO(16, kGEpiGated, true, bf16, tiles);
+        if (bn == 32) HOS_GO(32, kGEpiGated, true, bf16, tiles);
+        HOS_GO(64, kGEpiGated, true, bf16, tiles);
+    }
+    if ((rc = make_map(&mm, W, w_rows, K, ldw, GM))) return rc;
+    const int tiles = ((N + GM - 1) / GM) * k_splits;
+    if (k_splits > 1) {
+        p.out = workspace;
+        p.ldo = N;
+        if (bn == 16) rc = launch<16, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
+        else if (bn == 32) rc = launch<32, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
+        else rc = launch<64, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
+        if (rc) return rc;
+        const size_t n = (size_t)M * N;
+        if (out_dtype == kBF16)
+            splitk_reduce_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(workspace, (bf16*)out, M, N, ldo, k_splits);
+        else
+            splitk_reduce_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(workspace, (float*)out, M, N, ldo, k_splits);
+        return check_launch("gemm_tc split-K reduce");
+    }
+    if (epilogue == kGEpiSoftcap) {
+        if (bn == 16) HOS_GO(16, kGEpiSoftcap, true, float, tiles);
+        if (bn == 32) HOS_GO(32, kGEpiSoftcap, true, float, tiles);
+        HOS_GO(64, kGEpiSoftcap, true, float, tiles);
+    }
+    if (out_dtype == kBF16) {
+        if (bn == 16) HOS_GO(16, kGEpiNone, true, bf16, tiles);
+        if (bn == 32) HOS_GO(32, kGEpiNone, true, bf16, tiles);
+        HOS_GO(64, kGEpiNone, true, bf16, tiles);
+    }
+    if (bn == 16) HOS_GO(16, kGEpiNone, true, float, tiles);
+    if (bn == 32) HOS_GO(32, kGEpiNone, true, float, tiles);
+    HOS_GO(64, kGEpiNone, true, float, tiles);
+#undef HOS_GO
+}

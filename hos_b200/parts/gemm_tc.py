@@ -1,16 +1,73 @@
-"""Python face of the tcgen05/TMA matrix product (csrc/gemm_tc.cu)."""
+"""Python face of the tcgen05/TMA matrix product (csrc/gemm_tc.cu): bfloat16 operands, both
+K-major, 32-bit accumulation in tensor memory.  Up to 64 rows of activations run in the
+swapped orientation (the weight tile is the 128-row operand), where K may be split over
+CTAs when the output alone gives too few tiles to fill the GPU."""
 from __future__ import annotations
+
+import ctypes
+from typing import Optional
 
 import torch
 
 from .. import ops
 
-ENABLED = False     # switched on once the kernel is built and checked
+SM_COUNT = 148
+_lib: Optional[ops.Library] = None
+enabled = True          # tests switch it off to compare with the plain kernel
+
+
+def lib() -> ops.Library:
+    global _lib
+    if _lib is None:
+        _lib = ops.Library("gemm_tc")
+    return _lib
 
 
 def can_take(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    return False
+    """bfloat16 operands, K a multiple of 8, rows 16-byte aligned; else the plain kernel runs."""
+    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    k = x.shape[1]
+    if k % 8 != 0 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    if x.data_ptr() % 16 or w.data_ptr() % 16 or out.data_ptr() % 16 or not out.is_contiguous():
+        return False
+    if epilogue == ops.EPI_GATED and out.dtype != torch.bfloat16:
+        return False
+    if epilogue == ops.EPI_SOFTCAP and out.dtype != torch.float32:
+        return False
+    return out.dtype in (torch.bfloat16, torch.float32)
 
 
-def matmul(x, w, out, epilogue, cap, act) -> None:
-    raise NotImplementedError
+def k_splits_for(m: int, n: int, k: int, epilogue: int) -> int:
+    """Swapped products whose output gives few tiles split K so that about every SM has work,
+    keeping at least four 64-wide K blocks per share."""
+    if m > 64 or epilogue != ops.EPI_NONE:
+        return 1
+    tiles = (n + 127) // 128
+    if tiles >= SM_COUNT // 2:
+        return 1
+    k_blocks = (k + 63) // 64
+    return max(1, min((SM_COUNT + tiles - 1) // tiles, k_blocks // 4))
+
+
+def matmul(x, w, out, epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,
+           k_splits: Optional[int] = None) -> None:
+    m, k = x.shape
+    n = out.shape[1]
+    if k_splits is None:
+        k_splits = k_splits_for(m, n, k, epilogue)
+    ws = None
+    if k_splits > 1:
+        ws = torch.empty(k_splits * m * n, dtype=torch.float32, device=x.device)
+    lib().call("hos_gemm_tc", ops._ptr(x), ops._ptr(w), ops._ptr(out), ops.dtype_code(out.dtype), m, n, k,
+               x.stride(0), w.stride(0), out.stride(0), epilogue, float(cap), act, k_splits, ops._ptr(ws),
+               ops._stream())
+
+
+def gave_up() -> bool:
+    """True if a launch since the last call left a bounded wait unfinished (synchronises)."""
+    f = lib().lib.hos_gemm_tc_error
+    f.restype = ctypes.c_int
+    f.argtypes = []
+    return bool(f())

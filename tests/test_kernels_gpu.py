@@ -455,3 +455,64 @@ def test_attention_prefill_kernel(cfg):
             want = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // g]
             close(out[base:base + l, h * hd:(h + 1) * hd], want.to(dt), dt)
         base += l
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (200, 300, 136), (257, 520, 2304), (1, 128, 64), (8, 1000, 200),
+                                   (16, 512, 72), (17, 264, 640), (33, 2304, 96), (64, 384, 192), (65, 136, 80)])
+@pytest.mark.parametrize("variant", ["plain_out", "f32_out", "softcap", "gated_gelu", "gated_silu", "split_k"])
+def test_gemm_tensor_core(shape, variant):
+    """The tcgen05/TMA product against float64, in both orientations (more than 64 rows: the
+    activation tile is the 128-row operand; up to 64: the weight tile is), with row and column
+    counts and a K that fill no tile, and every epilogue; and against the plain kernel."""
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc
+    M, N, K = shape
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gated = variant.startswith("gated")
+    w = (torch.randn(2 * N if gated else N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double() @ w[:N].double().T
+    if variant == "plain_out":
+        out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+        gemm_tc.matmul(a, w, out)
+        close(out, ref.to(torch.bfloat16), torch.bfloat16)
+        plain = torch.empty_like(out)
+        ops.gemm_plain(a, w, plain)
+        close(out, plain, torch.bfloat16)
+    elif variant == "f32_out":
+        out = torch.empty((M, N), device=DEV)
+        gemm_tc.matmul(a, w, out)
+        close(out, ref, torch.float32, scale=3)
+    elif variant == "softcap":
+        out = torch.empty((M, N), device=DEV)
+        gemm_tc.matmul(a, w, out, ops.EPI_SOFTCAP, cap=0.6)
+        close(out, 0.6 * torch.tanh(ref / 0.6), torch.float32, scale=3)
+    elif gated:
+        act = "gelu_tanh" if variant == "gated_gelu" else "silu"
+        out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+        gemm_tc.matmul(a, w, out, ops.EPI_GATED, act=ops.ACTIVATIONS[act])
+        g, u = ref, a.double() @ w[N:].double().T
+        af = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
+        close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
+    else:
+        if M > 64:
+            pytest.skip("K is split in the swapped orientation only")
+        for ks in (2, 3, 100):
+            out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+            gemm_tc.matmul(a, w, out, k_splits=ks)
+            close(out, ref.to(torch.bfloat16), torch.bfloat16)
+    assert not gemm_tc.gave_up()
+
+
+def test_gemm_tensor_core_refuses_what_it_cannot_take():
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc, linear
+    a = torch.randn(4, 100, device=DEV).to(torch.bfloat16)          # K = 100 is no multiple of 8
+    w = torch.randn(24, 100, device=DEV).to(torch.bfloat16)
+    out = torch.empty(4, 24, device=DEV, dtype=torch.bfloat16)
+    assert not gemm_tc.can_take(a, w, out, ops.EPI_NONE)
+    from hos_b200.errors import KernelError
+    with pytest.raises(KernelError, match="multiples of 8"):
+        gemm_tc.matmul(a, w, out)
+    got = linear.matmul(a, w)                                        # the dispatcher falls back to the plain kernel
+    close(got, (a.double() @ w.double().T).to(torch.bfloat16), torch.bfloat16)
