@@ -78,6 +78,119 @@ __global__ void norm_add_norm_kernel(const TY* __restrict__ y, const float* __re
         h[base + d] = from_float<TH>(row[d] * r2 * (w_next[d] + add_one_next));
 }
 
+// ---- the same two norms with the row in registers ---------------------------------------
+// For widths that are a multiple of 4 and fit CH chunks of 4 per thread: every load is issued
+// before the first reduction, nothing goes through shared memory but the two block sums.
+// `y` may be given as n_parts partial sums of 32-bit floats, [n_parts][rows][D] (what a
+// matrix product that split K leaves): they are added here, in a fixed order.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TIn, typename TOut, int CH>
+__global__ void rmsnorm_vec_kernel(const TIn* __restrict__ x, const float* __restrict__ w, float eps,
+                                   float add_one, TOut* __restrict__ out, int D) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * D;
+    float4 xv[CH], wv[CH];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < D) {
+            xv[c] = load4(x + base + i);
+            wv[c] = load4(w + i);
+            ss += xv[c].x * xv[c].x + xv[c].y * xv[c].y + xv[c].z * xv[c].z + xv[c].w * xv[c].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < D)
+            store4(out + base + i, make_float4(xv[c].x * r * (wv[c].x + add_one), xv[c].y * r * (wv[c].y + add_one),
+                                               xv[c].z * r * (wv[c].z + add_one), xv[c].w * r * (wv[c].w + add_one)));
+    }
+}
+
+template <typename TY, typename TH, int CH>
+__global__ void norm_add_norm_vec_kernel(const TY* __restrict__ y, int n_parts, size_t part_stride,
+                                         const float* __restrict__ w_post, float eps_post, float add_one_post,
+                                         float* __restrict__ x, const float* __restrict__ w_next, float eps_next,
+                                         float add_one_next, TH* __restrict__ h, int D) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * D;
+    float4 yv[CH], xv[CH], wp[CH], wn[CH];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < D) {
+            yv[c] = load4(y + base + i);
+            for (int p = 1; p < n_parts; ++p) {
+                const float4 t = load4(y + p * part_stride + base + i);
+                yv[c].x += t.x; yv[c].y += t.y; yv[c].z += t.z; yv[c].w += t.w;
+            }
+            xv[c] = load4(x + base + i);
+            wp[c] = load4(w_post + i);
+            if (h != nullptr) wn[c] = load4(w_next + i);
+            ss += yv[c].x * yv[c].x + yv[c].y * yv[c].y + yv[c].z * yv[c].z + yv[c].w * yv[c].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps_post);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < D) {
+            xv[c].x += yv[c].x * r * (wp[c].x + add_one_post);
+            xv[c].y += yv[c].y * r * (wp[c].y + add_one_post);
+            xv[c].z += yv[c].z * r * (wp[c].z + add_one_post);
+            xv[c].w += yv[c].w * r * (wp[c].w + add_one_post);
+            store4(x + base + i, xv[c]);
+            ss2 += xv[c].x * xv[c].x + xv[c].y * xv[c].y + xv[c].z * xv[c].z + xv[c].w * xv[c].w;
+        }
+    }
+    if (h == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float r2 = 1.0f / sqrtf(ss2 / (float)D + eps_next);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < D)
+            store4(h + base + i, make_float4(xv[c].x * r2 * (wn[c].x + add_one_next), xv[c].y * r2 * (wn[c].y + add_one_next),
+                                             xv[c].z * r2 * (wn[c].z + add_one_next), xv[c].w * r2 * (wn[c].w + add_one_next)));
+    }
+}
+
+// Threads per row and chunks per thread for the register-resident kernels; chunks 0: use the others.
+static void vec_shape(int D, int* threads, int* chunks) {
+    *chunks = 0;
+    if (D % 4 != 0) return;
+    const int quads = D / 4;
+    for (int ch = 1; ch <= 4; ch *= 2) {
+        if (quads <= 1024 * ch) {
+            *chunks = ch;
+            *threads = (((quads + ch - 1) / ch) + 31) / 32 * 32;
+            return;
+        }
+    }
+}
+
 // x += y (plain residual sum in 32-bit, for arrangements without a post norm).
 template <typename TY>
 __global__ void residual_add_kernel(const TY* __restrict__ y, float* __restrict__ x, size_t n) {
@@ -86,38 +199,65 @@ __global__ void residual_add_kernel(const TY* __restrict__ y, float* __restrict_
 }
 
 // ---- rotary encoding + cache write --------------------------------------------------
-// One block per token.  q and k rows of the fused projection output are rotated in
-// place (angle = position * inv_freq[i], sincosf in 32-bit); the rotated key and the
-// value go to the token's place in the paged cache.  A token whose place in a ring
-// is overwritten by a later token of the same step is not stored.
+// One block per token.  The q and k heads of the fused projection row are rotated
+// (angle = position * inv_freq[i], sincosf in 32-bit, once per pair and token), the row is
+// left in `qkv` as the activation type, and the rotated key and the value go to the token's
+// place in the paged cache.  The source is `qkv` itself (rotation in place) or n_parts
+// partial sums of 32-bit floats [n_parts][rows][row_stride] from a matrix product that split
+// K, added here in a fixed order.  A token whose place in a ring is overwritten by a later
+// token of the same step is not stored.
 // style 0: pairs (i, i + rot/2) ("rotate half"); style 1: pairs (2i, 2i+1).
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int n_heads,
+template <typename TSrc, typename T>
+__global__ void rope_kv_write_kernel(const TSrc* __restrict__ src, int n_parts, size_t part_stride,
+                                     T* __restrict__ qkv, int row_stride, int n_heads,
                                      const int* __restrict__ token_pos,
                                      const int* __restrict__ token_seq,
                                      const int* __restrict__ seq_slot,
                                      const int* __restrict__ seq_len_after,
                                      const float* __restrict__ inv_freq, int rotary_dim, int style,
                                      PagedKV cache, int write_cache) {
+    extern __shared__ float2 sincos_tab[];          // [rotary_dim / 2]
     const int n = blockIdx.x;
     const int seq = token_seq[n];
     if (seq < 0) return;
     const int pos = token_pos[n];
     const int hd = cache.head_dim, nkv = cache.n_kv_heads;
     const int half = rotary_dim >> 1;
+    const bool in_place = (const void*)src == (const void*)qkv;
+    const TSrc* srow = src + (size_t)n * row_stride;
     T* row = qkv + (size_t)n * row_stride;
-    // rotate q heads and k heads: heads [0, n_heads) are q, [n_heads, n_heads+nkv) are k
+    auto value = [&](int e) {
+        float v = to_float(srow[e]);
+        for (int p = 1; p < n_parts; ++p) v += to_float(srow[p * part_stride + e]);
+        return v;
+    };
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sincos_tab[i] = make_float2(s, c);
+    }
+    __syncthreads();
+    // heads [0, n_heads) are q, [n_heads, n_heads + nkv) are k, then nkv heads of v
     const int n_rot_heads = n_heads + nkv;
     for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
         const int head = idx / half, i = idx - head * half;
         const int a = style == 0 ? i : 2 * i;
         const int b = style == 0 ? i + half : 2 * i + 1;
-        T* hp = row + (size_t)head * hd;
-        float s, c;
-        sincosf((float)pos * inv_freq[i], &s, &c);
-        const float x0 = to_float(hp[a]), x1 = to_float(hp[b]);
-        hp[a] = from_float<T>(x0 * c - x1 * s);
-        hp[b] = from_float<T>(x0 * s + x1 * c);
+        const float2 sc = sincos_tab[i];
+        const float x0 = value(head * hd + a), x1 = value(head * hd + b);
+        row[head * hd + a] = from_float<T>(x0 * sc.y - x1 * sc.x);
+        row[head * hd + b] = from_float<T>(x0 * sc.x + x1 * sc.y);
+    }
+    if (!in_place) {      // what is not rotated still has to reach the activation row
+        const int pass = hd - rotary_dim;
+        for (int idx = threadIdx.x; idx < n_rot_heads * pass; idx += blockDim.x) {
+            const int head = idx / pass, d = rotary_dim + idx % pass;
+            row[head * hd + d] = from_float<T>(value(head * hd + d));
+        }
+        for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+            const int e = (n_heads + nkv) * hd + idx;
+            row[e] = from_float<T>(value(e));
+        }
     }
     if (!write_cache) return;
     __syncthreads();
@@ -202,11 +342,20 @@ extern "C" int hos_rmsnorm(const void* x, int x_dtype, const float* w, float eps
     if (N <= 0) return 0;
     const size_t smem = (size_t)D * sizeof(float);
     const float a1 = add_one ? 1.f : 0.f;
+    int threads = 0, chunks = 0;
+    vec_shape(D, &threads, &chunks);
+    if (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) % 16) chunks = 0;
+#define HOS_VEC(TI, TO, CH) rmsnorm_vec_kernel<TI, TO, CH><<<N, threads, 0, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D)
 #define HOS_LAUNCH_NORM(TI, TO)                                                              \
     do {                                                                                     \
-        if (row_smem_ok((const void*)rmsnorm_kernel<TI, TO>, D))                             \
-            HOS_REFUSE("rmsnorm: width %d does not fit a block's shared memory", D);         \
-        rmsnorm_kernel<TI, TO><<<N, 256, smem, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D); \
+        if (chunks == 1) HOS_VEC(TI, TO, 1);                                                 \
+        else if (chunks == 2) HOS_VEC(TI, TO, 2);                                            \
+        else if (chunks == 4) HOS_VEC(TI, TO, 4);                                            \
+        else {                                                                               \
+            if (row_smem_ok((const void*)rmsnorm_kernel<TI, TO>, D))                         \
+                HOS_REFUSE("rmsnorm: width %d does not fit a block's shared memory", D);     \
+            rmsnorm_kernel<TI, TO><<<N, 256, smem, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D); \
+        }                                                                                    \
     } while (0)
     if (x_dtype == kF32 && out_dtype == kF32) HOS_LAUNCH_NORM(float, float);
     else if (x_dtype == kF32 && out_dtype == kBF16) HOS_LAUNCH_NORM(float, bf16);
@@ -214,29 +363,46 @@ extern "C" int hos_rmsnorm(const void* x, int x_dtype, const float* w, float eps
     else if (x_dtype == kBF16 && out_dtype == kF32) HOS_LAUNCH_NORM(bf16, float);
     else HOS_REFUSE("rmsnorm: unknown dtypes %d -> %d", x_dtype, out_dtype);
 #undef HOS_LAUNCH_NORM
+#undef HOS_VEC
     return check_launch("rmsnorm");
 }
 
-// x += RMSNorm(y; w_post); if h != NULL also h = RMSNorm(x; w_next).  y and h share a dtype.
-extern "C" int hos_norm_add_norm(const void* y, int y_dtype, const float* w_post, float eps_post,
+// x += RMSNorm(y; w_post); if h != NULL also h = RMSNorm(x; w_next), written as h_dtype.
+// n_parts > 1: y is n_parts partial sums of 32-bit floats, [n_parts][N][D], added here.
+extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const float* w_post, float eps_post,
                                  int add_one_post, float* x, const float* w_next, float eps_next,
-                                 int add_one_next, void* h, int N, int D, cudaStream_t stream) {
+                                 int add_one_next, void* h, int h_dtype, int N, int D, cudaStream_t stream) {
     if (N <= 0) return 0;
+    if (n_parts < 1 || (n_parts > 1 && y_dtype != kF32))
+        HOS_REFUSE("norm_add_norm: partial sums are 32-bit floats (n_parts %d, dtype %d)", n_parts, y_dtype);
     const size_t smem = (size_t)D * sizeof(float);
     const float a1 = add_one_post ? 1.f : 0.f, a2 = add_one_next ? 1.f : 0.f;
-    if (y_dtype == kF32) {
-        if (row_smem_ok((const void*)norm_add_norm_kernel<float, float>, D))
-            HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);
-        norm_add_norm_kernel<float, float><<<N, 256, smem, stream>>>(
-            (const float*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (float*)h, D);
-    } else if (y_dtype == kBF16) {
-        if (row_smem_ok((const void*)norm_add_norm_kernel<bf16, bf16>, D))
-            HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);
-        norm_add_norm_kernel<bf16, bf16><<<N, 256, smem, stream>>>(
-            (const bf16*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (bf16*)h, D);
-    } else {
-        HOS_REFUSE("norm_add_norm: unknown dtype %d", y_dtype);
-    }
+    const size_t ps = (size_t)N * D;
+    int threads = 0, chunks = 0;
+    vec_shape(D, &threads, &chunks);
+    if (((uintptr_t)y | (uintptr_t)x | (uintptr_t)h | (uintptr_t)w_post | (uintptr_t)w_next) % 16) chunks = 0;
+    if (chunks == 0 && n_parts > 1) HOS_REFUSE("norm_add_norm: partial sums need a width that is a multiple of 4 (%d)", D);
+#define HOS_VEC(TY, TH, CH) norm_add_norm_vec_kernel<TY, TH, CH><<<N, threads, 0, stream>>>(                 \
+        (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D)
+#define HOS_LAUNCH(TY, TH)                                                                                  \
+    do {                                                                                                    \
+        if (chunks == 1) HOS_VEC(TY, TH, 1);                                                                \
+        else if (chunks == 2) HOS_VEC(TY, TH, 2);                                                           \
+        else if (chunks == 4) HOS_VEC(TY, TH, 4);                                                           \
+        else {                                                                                              \
+            if (row_smem_ok((const void*)norm_add_norm_kernel<TY, TH>, D))                                  \
+                HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);              \
+            norm_add_norm_kernel<TY, TH><<<N, 256, smem, stream>>>(                                         \
+                (const TY*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D);                    \
+        }                                                                                                   \
+    } while (0)
+    if (h == nullptr) h_dtype = y_dtype == kF32 ? kF32 : kBF16;
+    if (y_dtype == kF32 && h_dtype == kF32) HOS_LAUNCH(float, float);
+    else if (y_dtype == kF32 && h_dtype == kBF16) HOS_LAUNCH(float, bf16);
+    else if (y_dtype == kBF16 && h_dtype == kBF16) HOS_LAUNCH(bf16, bf16);
+    else HOS_REFUSE("norm_add_norm: no kernel for dtypes %d -> %d", y_dtype, h_dtype);
+#undef HOS_LAUNCH
+#undef HOS_VEC
     return check_launch("norm_add_norm");
 }
 
@@ -250,7 +416,10 @@ extern "C" int hos_residual_add(const void* y, int y_dtype, float* x, long long 
     return check_launch("residual_add");
 }
 
-extern "C" int hos_rope_kv_write(void* qkv, int dtype, int row_stride, int n_heads,
+// src_dtype/n_parts: the source of the rows; src == qkv (same dtype, n_parts 1) rotates in place,
+// a 32-bit source with n_parts >= 1 is summed over its parts and written to qkv.
+extern "C" int hos_rope_kv_write(const void* src, int src_dtype, int n_parts, void* qkv, int dtype,
+                                 int row_stride, int n_heads,
                                  const int* token_pos, const int* token_seq, const int* seq_slot,
                                  const int* seq_len_after, const float* inv_freq, int rotary_dim,
                                  int style, void* k_pages, void* v_pages, const int* page_table,
@@ -260,15 +429,19 @@ extern "C" int hos_rope_kv_write(void* qkv, int dtype, int row_stride, int n_hea
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
         HOS_REFUSE("rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
     if (style != 0 && style != 1) HOS_REFUSE("rope: unknown pairing style %d", style);
+    if (n_parts < 1 || (src != qkv && src_dtype != kF32) || (src == qkv && (n_parts != 1 || src_dtype != dtype)))
+        HOS_REFUSE("rope: the source is the rows themselves or 32-bit partial sums");
     PagedKV c{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
-    if (dtype == kF32)
-        rope_kv_write_kernel<float><<<N, 256, 0, stream>>>((float*)qkv, row_stride, n_heads, token_pos,
-            token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
-    else if (dtype == kBF16)
-        rope_kv_write_kernel<bf16><<<N, 256, 0, stream>>>((bf16*)qkv, row_stride, n_heads, token_pos,
-            token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
-    else
-        HOS_REFUSE("rope: unknown dtype %d", dtype);
+    const size_t smem = (size_t)(rotary_dim / 2) * sizeof(float2);
+    const size_t ps = (size_t)N * row_stride;
+#define HOS_ROPE(TS, T)                                                                              \
+    rope_kv_write_kernel<TS, T><<<N, 256, smem, stream>>>((const TS*)src, n_parts, ps, (T*)qkv, row_stride, \
+        n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache)
+    if (dtype == kF32) HOS_ROPE(float, float);
+    else if (dtype == kBF16 && src_dtype == kBF16) HOS_ROPE(bf16, bf16);
+    else if (dtype == kBF16 && src_dtype == kF32) HOS_ROPE(float, bf16);
+    else HOS_REFUSE("rope: unknown dtype %d", dtype);
+#undef HOS_ROPE
     return check_launch("rope_kv_write");
 }
 

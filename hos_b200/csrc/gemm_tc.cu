@@ -471,10 +471,13 @@ extern "C" long long hos_gemm_tc_workspace(int M, int N, int k_splits) {
 // out[M, N] = A[M, K] . W[N, K]^T, bf16 operands.  out_dtype: 1 bf16, 0 f32.  epilogue: 0 none,
 // 1 soft-cap (f32 output), 2 gated (W has 2N rows: gate rows, then up rows at row N).
 // M <= 64 runs swapped; k_splits > 1 is allowed only then and only without an epilogue, and
-// needs `workspace` (see hos_gemm_tc_workspace).  lda, ldw, ldo in elements.
+// needs `workspace` (see hos_gemm_tc_workspace).  With reduce_now == 0 the partial sums are left
+// in the workspace as [k_splits_used][M][N] floats for the consumer to add, `out` is not written,
+// and the number of parts is returned through *parts_used.  lda, ldw, ldo in elements.
 extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K, int lda,
                            int ldw, int ldo, int epilogue, float cap, int act, int k_splits, float* workspace,
-                           cudaStream_t stream) {
+                           int reduce_now, int* parts_used, cudaStream_t stream) {
+    if (parts_used) *parts_used = 1;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) HOS_REFUSE("gemm_tc: K must be positive");
     if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
@@ -528,6 +531,8 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
         else if (bn == 32) rc = launch<32, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
         else rc = launch<64, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
         if (rc) return rc;
+        if (parts_used) *parts_used = k_splits;
+        if (!reduce_now) return 0;
         const size_t n = (size_t)M * N;
         if (out_dtype == kBF16)
             splitk_reduce_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(workspace, (bf16*)out, M, N, ldo, k_splits);

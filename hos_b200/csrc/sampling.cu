@@ -256,36 +256,63 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
 }
 
 // Arg max alone (first maximum wins), for the greedy loop: reads, never writes, the logits.
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* l = logits + (size_t)blockIdx.x * ld;
+// A row is cut into chunks, one block each; a block leaves its (maximum, id) in `partial`
+// and takes a ticket; the block that takes a row's last ticket reduces the row's partials
+// and puts the counter back to zero for the next launch.
+constexpr int kArgmaxThreads = 256;
+
+__device__ __forceinline__ void argmax_merge(float& best, int& best_i, float ov, int oi) {
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+}
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int chunk, float* __restrict__ partial_val,
+              int* __restrict__ partial_idx, int* __restrict__ tickets, int* __restrict__ out) {
+    __shared__ float sv[kArgmaxThreads / 32];
+    __shared__ int si[kArgmaxThreads / 32];
+    __shared__ int is_last;
+    const int row = blockIdx.y, nchunks = gridDim.x;
+    const float* l = logits + (size_t)row * ld;
+    const int lo = blockIdx.x * chunk, hi = min(V, lo + chunk);
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += kArgmaxThreads) {
         const float v = l[i];
         if (v > best) { best = v; best_i = i; }     // ids rise within a thread: first maximum kept
     }
+    auto block_reduce = [&]() {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        const int nw = (blockDim.x + 31) >> 5;
-        best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
-        best_i = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1)
+            argmax_merge(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
+        if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            best = threadIdx.x < kArgmaxThreads / 32 ? sv[threadIdx.x] : -INFINITY;
+            best_i = threadIdx.x < kArgmaxThreads / 32 ? si[threadIdx.x] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+            for (int o = 16; o > 0; o >>= 1)
+                argmax_merge(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    };
+    block_reduce();
+    if (threadIdx.x == 0) {
+        partial_val[(size_t)row * nchunks + blockIdx.x] = best;
+        partial_idx[(size_t)row * nchunks + blockIdx.x] = best_i;
+        __threadfence();
+        is_last = atomicAdd(&tickets[row], 1) == nchunks - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    best = -INFINITY;
+    best_i = 0x7fffffff;
+    for (int c = threadIdx.x; c < nchunks; c += kArgmaxThreads)
+        argmax_merge(best, best_i, __ldcg(&partial_val[(size_t)row * nchunks + c]), __ldcg(&partial_idx[(size_t)row * nchunks + c]));
+    __syncthreads();
+    block_reduce();
+    if (threadIdx.x == 0) {
+        out[row] = best_i == 0x7fffffff ? 0 : best_i;
+        tickets[row] = 0;
     }
 }
 
@@ -293,10 +320,22 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
 
 using namespace hos;
 
-extern "C" int hos_argmax(const float* logits, int ld, int B, int V, int* out, cudaStream_t stream) {
+// Chunks a row is cut into, and the floats of workspace the arg max needs: partial maxima
+// and ids, [B][chunks] each.  `tickets` is B ints that are zero before the first launch.
+extern "C" int hos_argmax_chunks(int V) {
+    int c = (V + 4095) / 4096;
+    return c < 1 ? 1 : (c > 256 ? 256 : c);
+}
+extern "C" int hos_argmax(const float* logits, int ld, int B, int V, int* out, float* workspace, int* tickets,
+                          cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) HOS_REFUSE("argmax: empty vocabulary");
-    argmax_kernel<<<B, 1024, 0, stream>>>(logits, ld, V, out);
+    if (B > 65535) HOS_REFUSE("argmax: %d rows are more than one launch takes", B);
+    const int chunks = hos_argmax_chunks(V);
+    const int chunk = (V + chunks - 1) / chunks;
+    dim3 grid(chunks, B);
+    argmax_kernel<<<grid, kArgmaxThreads, 0, stream>>>(logits, ld, V, chunk, workspace,
+                                                      reinterpret_cast<int*>(workspace + (size_t)B * chunks), tickets, out);
     return check_launch("argmax");
 }
 

@@ -22,6 +22,22 @@ from .runner import Runner
 Prompt = Union[Sequence[int], Sequence[Sequence[int]]]
 
 
+class _LoopBackend:
+    """What the generation loop drives: the runner, with logits handed over without a copy
+    (the loop samples from them before the next step overwrites them)."""
+
+    def __init__(self, runner: Runner):
+        self.runner = runner
+        self.admit, self.release = runner.admit, runner.release
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.runner.max_seq_len
+
+    def step(self, slots, token_lists):
+        return self.runner.step(slots, token_lists, copy=False)
+
+
 def _is_batch(prompt) -> bool:
     return len(prompt) > 0 and not isinstance(prompt[0], int)
 
@@ -92,14 +108,14 @@ class Engine:
         batch = _is_batch(prompt)
         prompts = [list(p) for p in prompt] if batch else [list(prompt)]
         stops = self.stop_ids if stop_ids is None else tuple(stop_ids)
-        outs = gen.generate(self.runner, lambda: Sampler(params, self.runner.device), prompts,
+        outs = gen.generate(_LoopBackend(self.runner), lambda: Sampler(params, self.runner.device), prompts,
                             max_tokens, stops, self.runner.cache.tokens_capacity(), self.max_batch,
                             on_token)
         return outs if batch else outs[0]
 
     # ---- the step function, for callers that drive it themselves ------------------------
-    def step(self, slots, token_lists, want=None) -> torch.Tensor:
-        return self.runner.step(slots, token_lists, want)
+    def step(self, slots, token_lists, want=None, copy: bool = True) -> torch.Tensor:
+        return self.runner.step(slots, token_lists, want, copy)
 
     # ---- measurements -------------------------------------------------------------------
     def perplexity(self, ids: Sequence[int]) -> Tuple[int, float, float]:

@@ -47,6 +47,8 @@ class Runner:
         del tensors
         self.cache: CacheManager = self.model.new_cache(max_tokens, max_seq_len, max_slots)
         self.vocab_size = self.plan.vocab_size
+        self._sessions = {}
+        self.use_sessions = True        # single-token steps run through DecodeSession
 
     @classmethod
     def from_folder(cls, model_dir: str, **kw) -> "Runner":
@@ -79,11 +81,13 @@ class Runner:
 
     # ---- the step -------------------------------------------------------------------
     def step(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+             want: Optional[Sequence[Sequence[int]]] = None, copy: bool = True) -> torch.Tensor:
         """Run `token_lists[i]` as the next tokens of the sequence in `slots[i]`.
         `want[i]` lists the places among sequence i's new tokens whose logits are
         returned (default: the last one); the result is float32
-        [sum of len(want[i]), vocab], in the order of the sequences and of `want`."""
+        [sum of len(want[i]), vocab], in the order of the sequences and of `want`.
+        With copy=False the result of a single-token step is a view of a buffer that the
+        next step overwrites (the generation loop reads it at once)."""
         if len(slots) != len(token_lists):
             raise HosError("step: one token list per slot is needed")
         if len(set(slots)) != len(slots):
@@ -114,6 +118,18 @@ class Runner:
                     raise HosError(f"step: wanted place {j} is outside the {len(toks)} tokens brought")
                 rows.append(base + j)
             base += len(toks)
+        if single and not from_zero and len(rows) == len(slots) and self.use_sessions:
+            # decoding: static buffers and a captured graph, one per batch-size bucket
+            from .decode import DecodeSession, bucket_for
+            for s, st in zip(slots, starts):
+                self.cache.extend(s, st + 1)
+            bucket = bucket_for(len(slots))
+            sess = self._sessions.get(bucket)
+            if sess is None:
+                sess = self._sessions[bucket] = DecodeSession(self, bucket)
+            sess.feed(slots, [t[0] for t in token_lists], starts)
+            out = sess.run()
+            return out.clone() if copy else out
         x = self._hidden(slots, starts, token_lists)
         rows_t = torch.tensor(rows, dtype=torch.int32).to(self.device)
         return self.model.logits(x, rows_t)
@@ -133,8 +149,9 @@ class Runner:
         lengths = [self.cache.lengths[s] for s in slots]
         for s, n in zip(slots, lengths):
             self.cache.extend(s, n + warmup + steps)        # pages for every position written
-        sess = DecodeSession(self, slots)
-        sess.feed([t[0] for t in first_tokens], lengths)
+        from .decode import bucket_for
+        sess = DecodeSession(self, bucket_for(len(slots)))
+        sess.feed(slots, [t[0] for t in first_tokens], lengths)
         for _ in range(warmup):
             sess.run_greedy_on_device()
         torch.cuda.synchronize()

@@ -64,8 +64,16 @@ class Model:
     def hidden(self, step: StepInfo, cache: CacheManager) -> torch.Tensor:
         """The residual stream after the last entry of the run order, float32 [N, width]."""
         x = self.embedding.forward(step.tokens, step)
+        h = None
         for i, call in enumerate(self.schedule):
-            self.layers[call.layer].forward(x, step, cache.stores[i])
+            layer = self.layers[call.layer]
+            if not layer.chains:
+                layer.forward(x, step, cache.stores[i])
+                h = None
+                continue
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            next_norm = nxt.entry_norm() if nxt is not None and nxt.chains else None
+            h = layer.forward(x, step, cache.stores[i], h_in=h, next_norm=next_norm)
         return x
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

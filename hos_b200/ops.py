@@ -173,21 +173,23 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, add_one: bool, out: to
 def norm_add_norm(y: torch.Tensor, w_post: torch.Tensor, eps_post: float, add_one_post: bool,
                   x: torch.Tensor, w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0,
                   add_one_next: bool = False, h: Optional[torch.Tensor] = None) -> None:
-    """x += RMSNorm(y; w_post); if h is given, h = RMSNorm(x; w_next)."""
-    _check(y, "norm input", None, 2)
+    """x += RMSNorm(y; w_post); if h is given, h = RMSNorm(x; w_next).  y is [N, D], or
+    [parts, N, D] float32 partial sums (of a matrix product that split K), added here."""
+    _check(y, "norm input")
     _check(x, "residual stream", torch.float32, 2)
     _check(w_post, "norm weight", torch.float32, 1)
-    n, d = y.shape
-    if x.shape != y.shape or w_post.shape[0] != d:
+    n_parts = y.shape[0] if y.dim() == 3 else 1
+    n, d = x.shape
+    if tuple(y.shape[-2:]) != (n, d) or w_post.shape[0] != d or y.dim() not in (2, 3):
         raise KernelError("norm_add_norm: sizes disagree")
     if h is not None:
-        _check(h, "next norm output", y.dtype, 2)
+        _check(h, "next norm output", None, 2)
         _check(w_next, "next norm weight", torch.float32, 1)
-        if h.shape != y.shape or w_next.shape[0] != d:
+        if h.shape != x.shape or w_next.shape[0] != d:
             raise KernelError("norm_add_norm: sizes of the next norm disagree")
-    core().call("hos_norm_add_norm", _ptr(y), dtype_code(y.dtype), _ptr(w_post), float(eps_post),
+    core().call("hos_norm_add_norm", _ptr(y), dtype_code(y.dtype), n_parts, _ptr(w_post), float(eps_post),
                 int(add_one_post), _ptr(x), _ptr(w_next), float(eps_next), int(add_one_next),
-                _ptr(h), n, d, _stream())
+                _ptr(h), dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
 
 
 def residual_add(y: torch.Tensor, x: torch.Tensor) -> None:
@@ -200,9 +202,12 @@ def residual_add(y: torch.Tensor, x: torch.Tensor) -> None:
 
 def rope_kv_write(qkv: torch.Tensor, n_heads: int, token_pos, token_seq, seq_slot, seq_len_after,
                   inv_freq: Optional[torch.Tensor], rotary_dim: int, style: int,
-                  cache: Optional[PagedKVArgs], n_kv_heads: int, head_dim: int) -> None:
-    """Rotate the q and k heads of the fused projection rows in place; if `cache` is
-    given, store the rotated keys and the values at the tokens' places."""
+                  cache: Optional[PagedKVArgs], n_kv_heads: int, head_dim: int,
+                  partials: Optional[torch.Tensor] = None) -> None:
+    """Rotate the q and k heads of the fused projection rows `qkv` in place; if `cache` is
+    given, store the rotated keys and the values at the tokens' places.  With `partials`
+    ([parts, N, width] float32 partial sums of the projection) the rows are first formed from
+    them and written to `qkv`."""
     _check(qkv, "qkv rows", None, 2)
     n, stride = qkv.shape
     if stride != (n_heads + 2 * n_kv_heads) * head_dim:
@@ -215,7 +220,14 @@ def rope_kv_write(qkv: torch.Tensor, n_heads: int, token_pos, token_seq, seq_slo
             raise KernelError("rope: one inverse frequency per rotated pair is needed")
     if cache is not None and cache.k_pages.dtype != qkv.dtype:
         raise KernelError("rope: cache and activations differ in dtype")
-    core().call("hos_rope_kv_write", _ptr(qkv), dtype_code(qkv.dtype), stride, n_heads,
+    src, n_parts = qkv, 1
+    if partials is not None:
+        _check(partials, "partial sums", torch.float32, 3)
+        if tuple(partials.shape[1:]) != (n, stride):
+            raise KernelError("rope: partial sums and rows differ in size")
+        src, n_parts = partials, partials.shape[0]
+    core().call("hos_rope_kv_write", _ptr(src), dtype_code(src.dtype), n_parts, _ptr(qkv), dtype_code(qkv.dtype),
+                stride, n_heads,
                 _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(seq_len_after),
                 _ptr(inv_freq), rotary_dim, style,
                 _ptr(cache.k_pages) if cache else None, _ptr(cache.v_pages) if cache else None,
@@ -282,11 +294,23 @@ def attn_plain(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, tok
 
 # ---- sampling ----------------------------------------------------------------------------
 
+_argmax_state = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _check(logits, "logits", torch.float32, 2)
     _check(out, "tokens", torch.int32, 1)
     b, v = logits.shape
-    core().call("hos_argmax", _ptr(logits), v, b, v, _ptr(out), _stream())
+    lib = core()
+    f = lib.lib.hos_argmax_chunks
+    f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int]
+    chunks = f(v)
+    key = (logits.device, b, chunks)
+    st = _argmax_state.get(key)
+    if st is None:       # partial maxima and ids, and the tickets (zero between launches)
+        st = _argmax_state[key] = (torch.empty(2 * b * chunks, dtype=torch.float32, device=logits.device),
+                                   torch.zeros(b, dtype=torch.int32, device=logits.device))
+    lib.call("hos_argmax", _ptr(logits), v, b, v, _ptr(out), _ptr(st[0]), _ptr(st[1]), _stream())
 
 
 def sample(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor, temp: float, top_k: int,

@@ -67,16 +67,27 @@ class SoftmaxAttention(Mixer):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
+        return self._run(h, step, store, False)
+
+    def forward_partial(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
+        """As forward, but the output projection may come back as float32 partial sums
+        [parts, N, width] for a consumer that adds them (see linear.matmul_or_partials)."""
+        return self._run(h, step, store, True)
+
+    def _run(self, h: torch.Tensor, step: StepInfo, store: CallStore, partial_ok: bool) -> torch.Tensor:
         n = h.shape[0]
         cache = store.kv
         if cache is None:
             raise KernelError("attention needs a cache view")
         inv_freq, rotary_dim, style = self.position.kernel_args() if self.position else (None, 0, 0)
         if store.owns_kv:
-            qkv = linear.matmul(h, self.w_qkv)
+            qkv = linear.matmul_or_partials(h, self.w_qkv)
+            parts = None
+            if qkv.dim() == 3:       # partial sums: the rotate-and-store kernel adds them
+                parts, qkv = qkv, torch.empty(qkv.shape[1:], dtype=h.dtype, device=h.device)
             ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
                               step.seq_len_after, inv_freq, rotary_dim, style, cache,
-                              self.n_kv_heads, self.head_dim)
+                              self.n_kv_heads, self.head_dim, partials=parts)
         else:
             qkv = linear.matmul(h, self.w_q)
             ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
@@ -92,7 +103,7 @@ class SoftmaxAttention(Mixer):
                     f"{cache.ring_pages * ops.PAGE_TOKENS}: at most {room} fit without overwriting "
                     f"keys that the step still reads")
         self._attend(qkv, att, step, cache, packed)
-        return linear.matmul(att, self.w_o)
+        return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
 
     def _attend(self, qkv, att, step: StepInfo, cache, packed: bool) -> None:
         stride = qkv.shape[1]

@@ -36,7 +36,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
     ctas = max(1, n_tokens * n_kv_heads * chunks)
-    want = (2 * SM_COUNT + ctas - 1) // ctas
+    want = (2 * SM_COUNT) // ctas        # never a few CTAs over a whole number of waves
     return max(1, min(want, (pages + 1) // 2))
 
 

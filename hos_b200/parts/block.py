@@ -38,26 +38,47 @@ class Layer:
     def parts(self):
         return [self.mixer, self.feed_forward] + list(self.norms.values())
 
-    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore) -> None:
+    # An arrangement whose first act is a norm of x may say so (`entry_norm`) and set
+    # `chains = True`: the model then hands it `h_in`, that norm's output already computed by
+    # the layer before, and `next_norm`, the entry norm of the layer after, whose output it
+    # returns (computed in the kernel that makes its last residual sum).
+    chains = False
+
+    def entry_norm(self):
+        return None
+
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
         raise NotImplementedError
+
+    @staticmethod
+    def _branch(part, takes_partials: bool, *args):
+        """Run a mixer or feed-forward; let it hand back partial sums if it can and its consumer adds them."""
+        if takes_partials and hasattr(part, "forward_partial"):
+            return part.forward_partial(*args)
+        return part.forward(*args)
 
 
 class SandwichLayer(Layer):
     norm_roles = ("pre_mixer", "post_mixer", "pre_ffn", "post_ffn")
 
-    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore) -> None:
+    chains = True
+
+    def entry_norm(self):
+        return self.norms["pre_mixer"]
+
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
         n = self.norms
-        h = n["pre_mixer"].forward(x)
-        a = self.mixer.forward(h, step, store)
+        h = h_in if h_in is not None else n["pre_mixer"].forward(x)
+        a = self._branch(self.mixer, getattr(n["post_mixer"], "accepts_partials", False), h, step, store)
         h = n["post_mixer"].add_to(a, x, then=n["pre_ffn"])     # x += post(a); h = pre_ffn(x)
-        f = self.feed_forward.forward(h, step)
-        n["post_ffn"].add_to(f, x)
+        f = self._branch(self.feed_forward, getattr(n["post_ffn"], "accepts_partials", False), h, step)
+        return n["post_ffn"].add_to(f, x, then=next_norm)       # x += post(f); next layer's entry norm
 
 
 class PreNormLayer(Layer):
     norm_roles = ("pre_mixer", "pre_ffn")
 
-    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore) -> None:
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
         n = self.norms
         a = self.mixer.forward(n["pre_mixer"].forward(x), step, store)
         ops.residual_add(a, x)

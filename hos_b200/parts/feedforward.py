@@ -45,5 +45,11 @@ class GatedMLP(FeedForward):
         z = linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
         return linear.matmul(z, self.w_down)
 
+    def forward_partial(self, h: torch.Tensor, step: StepInfo = None) -> torch.Tensor:
+        """As forward, but the down projection may come back as float32 partial sums
+        [parts, N, width] for a consumer that adds them."""
+        z = linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
+        return linear.matmul_or_partials(z, self.w_down)
+
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

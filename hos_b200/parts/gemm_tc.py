@@ -62,7 +62,23 @@ def matmul(x, w, out, epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int =
         ws = torch.empty(k_splits * m * n, dtype=torch.float32, device=x.device)
     lib().call("hos_gemm_tc", ops._ptr(x), ops._ptr(w), ops._ptr(out), ops.dtype_code(out.dtype), m, n, k,
                x.stride(0), w.stride(0), out.stride(0), epilogue, float(cap), act, k_splits, ops._ptr(ws),
-               ops._stream())
+               1, None, ops._stream())
+
+
+def matmul_partials(x, w, k_splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """x . w^T as partial sums [parts, M, N] (float32) for a consumer that adds them, if K is
+    worth splitting for these sizes; None if it is not (call `matmul` then)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if k_splits is None:
+        k_splits = k_splits_for(m, n, k, ops.EPI_NONE)
+    if k_splits <= 1:
+        return None
+    ws = torch.empty((k_splits, m, n), dtype=torch.float32, device=x.device)
+    used = ctypes.c_int(0)
+    lib().call("hos_gemm_tc", ops._ptr(x), ops._ptr(w), None, ops.F32, m, n, k, x.stride(0), w.stride(0), n,
+               ops.EPI_NONE, 0.0, 0, k_splits, ops._ptr(ws), 0, ctypes.byref(used), ops._stream())
+    return ws[: used.value]
 
 
 def gave_up() -> bool:

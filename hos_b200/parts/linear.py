@@ -36,3 +36,17 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             return out
     ops.gemm_plain(x, w, out, epilogue, cap, act)
     return out
+
+
+def matmul_or_partials(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x . w^T for a consumer that can add partial sums: either the product [M, N] in the
+    activation type, or float32 partial sums [parts, M, N] when the tensor-core kernel splits K
+    (few rows, few output tiles: decoding).  No epilogue."""
+    if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0):
+        from . import gemm_tc
+        if gemm_tc.enabled and x.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 \
+                and x.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            parts = gemm_tc.matmul_partials(x, w)
+            if parts is not None:
+                return parts
+    return matmul(x, w)

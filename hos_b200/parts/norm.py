@@ -31,13 +31,15 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, self.eps, self.add_one, out)
         return out
 
+    accepts_partials = True      # y may be [parts, N, width] float32 partial sums
+
     def add_to(self, y: torch.Tensor, x: torch.Tensor, then: Optional[Norm] = None):
         """x += self(y); with another RMSNorm as `then`, its output comes from the same kernel."""
         if then is None:
             ops.norm_add_norm(y, self.weight, self.eps, self.add_one, x)
             return None
         if isinstance(then, RMSNorm):
-            h = torch.empty(y.shape, dtype=y.dtype, device=y.device)
+            h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
             ops.norm_add_norm(y, self.weight, self.eps, self.add_one, x,
                               then.weight, then.eps, then.add_one, h)
             return h

@@ -516,3 +516,44 @@ def test_gemm_tensor_core_refuses_what_it_cannot_take():
         gemm_tc.matmul(a, w, out)
     got = linear.matmul(a, w)                                        # the dispatcher falls back to the plain kernel
     close(got, (a.double() @ w.double().T).to(torch.bfloat16), torch.bfloat16)
+
+
+def test_consumers_add_partial_sums():
+    """What a K-split product leaves ([parts, rows, width] float32) is added by its consumers:
+    the norm-and-residual kernel and the rotate-and-store kernel give what they give on the sum."""
+    from hos_b200 import ops
+    torch.manual_seed(9)
+    N, D = 5, 328
+    parts = torch.randn(3, N, D, device=DEV)
+    total = parts.sum(0)
+    x0 = torch.randn(N, D, device=DEV)
+    w1, w2 = torch.randn(D, device=DEV) * 0.1, torch.randn(D, device=DEV) * 0.1
+    xa, xb = x0.clone(), x0.clone()
+    ha = torch.empty(N, D, device=DEV, dtype=torch.bfloat16)
+    hb = torch.empty_like(ha)
+    ops.norm_add_norm(parts, w1, 1e-6, True, xa, w2, 1e-6, True, ha)
+    ops.norm_add_norm(total, w1, 1e-6, True, xb, w2, 1e-6, True, hb)
+    close(xa, xb, torch.float32)
+    close(ha, hb, torch.bfloat16)
+    # rope: rows formed from partial sums, rotated, stored
+    nh, nkv, hd = 3, 1, 32
+    width = (nh + 2 * nkv) * hd
+    parts = torch.randn(4, N, width, device=DEV)
+    rows_ref = parts.sum(0).to(torch.bfloat16)
+    rows_out = torch.full((N, width), 7.0, device=DEV, dtype=torch.bfloat16)
+    pos = torch.arange(N, dtype=torch.int32, device=DEV) + 3
+    seq = torch.zeros(N, dtype=torch.int32, device=DEV)
+    inv = (1.0 / torch.pow(torch.tensor(100.0), 2.0 * torch.arange(8).float() / 16)).to(DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    after = torch.tensor([3 + N], dtype=torch.int32, device=DEV)
+    def cache():
+        return ops.PagedKVArgs(torch.zeros(2, nkv, 64, hd, device=DEV, dtype=torch.bfloat16),
+                               torch.zeros(2, nkv, 64, hd, device=DEV, dtype=torch.bfloat16),
+                               torch.tensor([[1]], dtype=torch.int32, device=DEV), 0, nkv, hd)
+    ca, cb = cache(), cache()
+    ops.rope_kv_write(rows_out, nh, pos, seq, slot, after, inv, 16, 0, ca, nkv, hd, partials=parts)
+    ops.rope_kv_write(rows_ref, nh, pos, seq, slot, after, inv, 16, 0, cb, nkv, hd)
+    close(rows_out, rows_ref, torch.bfloat16)
+    close(ca.k_pages, cb.k_pages, torch.bfloat16)
+    close(ca.v_pages, cb.v_pages, torch.bfloat16)
+    assert float(cb.k_pages[1, 0, 3:3 + N].abs().sum()) > 0
