@@ -38,19 +38,21 @@ class DecodeSession:
         if use_graph is None:
             use_graph = os.environ.get("HOS_NO_GRAPH", "") == ""
         self.use_graph = use_graph
-        # one int32 buffer, one pinned host mirror, one copy per step
-        self._host = torch.zeros(6 * b + 1, dtype=torch.int32).pin_memory()
+        # one int32 device buffer; two pinned host mirrors used in turn, each guarded by an event,
+        # so that the host may run a step ahead of the device without overwriting a copy's source
+        self._hosts = [torch.zeros(6 * b + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._copied = [None, None]
+        self._turn = 0
         self._dev = torch.zeros(6 * b + 1, dtype=torch.int32, device=dev)
         o = 0
 
         def take(n):
             nonlocal o
-            v = (self._host[o:o + n], self._dev[o:o + n])
+            v = self._dev[o:o + n]
             o += n
             return v
-        (self.h_tokens, self.tokens), (self.h_pos, self.pos) = take(b), take(b)
-        (self.h_seq, self.seq), (self.h_cu, self.cu) = take(b), take(b + 1)
-        (self.h_slot, self.slot), (self.h_after, self.after) = take(b), take(b)
+        self.tokens, self.pos, self.seq, self.cu = take(b), take(b), take(b), take(b + 1)
+        self.slot, self.after = take(b), take(b)
         self.rows = torch.arange(b, dtype=torch.int32, device=dev)
         self.sampled = torch.zeros(b, dtype=torch.int32, device=dev)
         self.logits: Optional[torch.Tensor] = None
@@ -75,7 +77,11 @@ class DecodeSession:
         n = len(slots)
         self.n_live = n
         pad = self.b - n
-        h = self._host
+        turn = self._turn
+        self._turn ^= 1
+        if self._copied[turn] is not None:
+            self._copied[turn].synchronize()       # the copy that last read this mirror is done
+        h = self._hosts[turn]
         b = self.b
         h[0:b] = torch.tensor(list(tokens) + [-1] * pad, dtype=torch.int32)
         lb = torch.tensor(list(lengths_before) + [0] * pad, dtype=torch.int32)
@@ -84,7 +90,10 @@ class DecodeSession:
         h[3 * b:4 * b + 1] = torch.arange(b + 1, dtype=torch.int32).clamp(max=n)
         h[4 * b + 1:5 * b + 1] = torch.tensor(list(slots) + [0] * pad, dtype=torch.int32)
         h[5 * b + 1:6 * b + 1] = lb + 1
-        self._dev.copy_(self._host, non_blocking=True)
+        self._dev.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._copied[turn] = ev
 
     def _forward(self) -> torch.Tensor:
         r = self.runner

@@ -48,7 +48,7 @@ class Runner:
         self.cache: CacheManager = self.model.new_cache(max_tokens, max_seq_len, max_slots)
         self.vocab_size = self.plan.vocab_size
         self._sessions = {}
-        self.use_sessions = True        # single-token steps run through DecodeSession
+        self.use_sessions = self.model.graph_safe     # single-token steps run through DecodeSession
 
     @classmethod
     def from_folder(cls, model_dir: str, **kw) -> "Runner":

@@ -27,6 +27,7 @@ class Model:
         self.final_norm = part_impl("norm", plan.final_norm.kind)(plan.final_norm, rt)
         self.head = part_impl("head", plan.head.kind)(plan.head, rt)
         self.schedule = list(plan.schedule)
+        self.graph_safe = all(p.graph_safe for p in self.all_parts())
 
     def all_parts(self):
         out = [self.embedding]

@@ -28,6 +28,8 @@ from .base import CallStore, KVNeed, Mixer, StepInfo, WeightSpec
 
 
 class SoftmaxAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         p = spec.params

@@ -107,6 +107,12 @@ class CallStore:
 class Part:
     """Base of every part."""
 
+    # True if forward() only launches kernels on device data (no host reads of the step's
+    # lists, no host-device synchronisation): single-token steps of a model whose parts all
+    # say so are captured in a CUDA graph and replayed.  A part that loops over
+    # `step.slots_host` or the like leaves it False and is run step by step.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, rt: Runtime):
         self.spec = spec
         self.rt = rt

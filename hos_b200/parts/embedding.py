@@ -16,6 +16,8 @@ from .base import Part, StepInfo, WeightSpec
 
 
 class ScaledEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.vocab = int(spec.params["vocab"])
@@ -36,6 +38,8 @@ class ScaledEmbedding(Part):
 
 
 class LinearHead(Part):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.vocab = int(spec.params["vocab"])

@@ -17,6 +17,8 @@ from .base import FeedForward, StepInfo, WeightSpec
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.width = int(spec.params["width"])

@@ -48,7 +48,7 @@ def k_splits_for(m: int, n: int, k: int, epilogue: int) -> int:
     if tiles >= SM_COUNT // 2:
         return 1
     k_blocks = (k + 63) // 64
-    return max(1, min((SM_COUNT + tiles - 1) // tiles, k_blocks // 4))
+    return max(1, min(SM_COUNT // tiles, k_blocks // 4))      # tiles x splits stays within one wave
 
 
 def matmul(x, w, out, epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,

@@ -12,6 +12,8 @@ from .base import Norm, WeightSpec
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.width = int(spec.params["width"])

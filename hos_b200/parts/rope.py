@@ -18,6 +18,8 @@ from .base import Part
 
 
 class Rotary(Part):
+    graph_safe = True
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.theta = float(spec.params["theta"])
@@ -41,6 +43,8 @@ class Rotary(Part):
 
 class NoPosition(Part):
     """No position encoding: q and k are used as projected."""
+    graph_safe = True
+
 
     def kernel_args(self):
         return None, 0, 0
