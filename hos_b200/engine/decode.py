@@ -12,7 +12,9 @@ the sequences first.
 """
 from __future__ import annotations
 
+import gc
 import os
+import weakref
 from typing import Optional, Sequence
 
 import torch
@@ -32,7 +34,7 @@ def bucket_for(n: int) -> int:
 
 class DecodeSession:
     def __init__(self, runner, bucket: int, use_graph: Optional[bool] = None):
-        self.runner = runner
+        self._runner = weakref.ref(runner)      # the runner owns its sessions: no reference cycle
         b = self.b = bucket
         dev = runner.device
         if use_graph is None:
@@ -63,6 +65,10 @@ class DecodeSession:
         self.launches_per_step = 0
         self._max_len = runner.cache.max_seq_len
         self.n_live = 0
+
+    @property
+    def runner(self):
+        return self._runner()
 
     def _info(self) -> StepInfo:
         return StepInfo(n_tokens=self.b, n_seqs=self.b, tokens=self.tokens, token_pos=self.pos,
@@ -115,8 +121,16 @@ class DecodeSession:
             return None, out
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            out = fn()
+        # nothing but this thread's own launches may touch the capture: no collection of old
+        # graphs or tensors (whose release frees device memory) while it is under way
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                out = fn()
+        finally:
+            if gc_was_on:
+                gc.enable()
         return g, out
 
     def run(self) -> torch.Tensor:

@@ -13,6 +13,7 @@ from ..errors import KernelError
 
 SM_COUNT = 148
 MAX_HEAD_DIM = 256
+MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
 enabled = {"decode": True, "prefill": True}     # tests switch a kernel off to compare with the plain one
@@ -30,14 +31,26 @@ def lib_for(head_dim: int) -> ops.Library:
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int]) -> int:
-    """How many shares the keys of one (token, kv head) are cut into: enough CTAs for two
-    waves over the SMs, but no share under two pages."""
+    """How many shares the keys of one (token, kv head) are cut into: as many as give every SM
+    one work item (measured: more items per CTA cost more than they balance), but no share
+    under two pages."""
     chunks = (group + 15) // 16
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
-    ctas = max(1, n_tokens * n_kv_heads * chunks)
-    want = (2 * SM_COUNT) // ctas        # never a few CTAs over a whole number of waves
-    return max(1, min(want, (pages + 1) // 2))
+    pairs = max(1, n_tokens * n_kv_heads * chunks)
+    want = SM_COUNT // pairs        # one item per CTA while that fills the GPU: an item's fixed cost is high
+    return max(1, min(want, (pages + 1) // 2, MAX_SPLITS))
+
+
+_ticket_store: Dict[object, torch.Tensor] = {}
+
+
+def _tickets(device, n: int) -> torch.Tensor:
+    """Zeroed counters that the kernel leaves zeroed: one allocation per device, grown on demand."""
+    t = _ticket_store.get(device)
+    if t is None or t.numel() < n:
+        t = _ticket_store[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return t
 
 
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
@@ -49,11 +62,12 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
     lib = lib_for(hd)
     if n_splits is None:
         n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window)
-    ws = None
+    ws = tickets = None
     if n_splits > 1:
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+        tickets = _tickets(q.device, n_tokens * nkv * ((n_heads // nkv + 15) // 16))
     lib.call("hos_attn_decode", ops._ptr(q), q_stride, ops._ptr(out), out.shape[1], ops._ptr(ws),
-             ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(cache.k_pages),
+             ops._ptr(tickets), ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(cache.k_pages),
              ops._ptr(cache.v_pages), ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages,
              n_tokens, n_heads, nkv, hd, float(scale), float(cap), int(window) if window else 0,
              int(n_splits), ops._stream())
