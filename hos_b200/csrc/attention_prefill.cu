@@ -2,7 +2,8 @@
 //
 // Queries, keys and values are the rows of this step's own fused projection output, packed
 // sequence after sequence (nothing is read from the cache).  One CTA (4 warps) takes 64
-// consecutive queries of one sequence and one query head; key/value tiles of 64 rows stream
+// consecutive queries of one sequence and one query head; key/value tiles of 64 rows (32 for
+// head sizes above 128, where two CTAs then share an SM) stream
 // through a two-stage cp.async pipeline into XOR-permuted shared memory.  Per tile each warp
 // computes S = Q K^T for its 16 queries (m16n8k16 bf16, 32-bit accumulators), scales,
 // soft-caps, masks (causal, and the window's lower edge), keeps a running max and sum in
@@ -20,7 +21,10 @@ namespace hos {
 
 constexpr int PHD = HOS_HEAD_DIM;
 static_assert(PHD % 16 == 0 && PHD >= 16 && PHD <= 256, "head_dim must be a multiple of 16, at most 256");
-constexpr int BQ = 64, BKV = 64;
+constexpr int BQ = 64;
+// keys per tile: 32 for the largest heads, so that two CTAs fit an SM's shared memory and registers
+constexpr int BKV = PHD > 128 ? 32 : 64;
+constexpr int KB = BKV / 16;                                  // blocks of 16 keys per tile
 constexpr int kPrefillSmem = (BQ + 4 * BKV) * PHD * 2;        // Q + 2 stages x (K, V)
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
@@ -44,7 +48,7 @@ __device__ __forceinline__ void load_tile(bf16* tile, const bf16* src, int strid
     }
 }
 
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, PHD > 128 ? 2 : 1)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k,
                     const bf16* __restrict__ v, int kv_stride, bf16* __restrict__ out, int out_stride,
                     const int* __restrict__ cu_seqlens, int n_seqs, int n_heads, int n_kv_heads,
@@ -102,9 +106,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         const uint32_t v_base = smem_u32(kv_s + (size_t)(2 * stage + 1) * BKV * PHD);
         const int key0 = (kt_lo + it) * BKV;
 
-        float sc[8][4];
+        float sc[2 * KB][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+        for (int i = 0; i < 2 * KB; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < PHD / 16; ++kk) {
             uint32_t qa[4];
@@ -113,7 +117,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                 ldmatrix_x4(qa, q_base + 2 * tile_chunk_offset<PHD>(row, kk * 2 + (lane >> 4)));
             }
 #pragma unroll
-            for (int kb = 0; kb < 4; ++kb) {
+            for (int kb = 0; kb < KB; ++kb) {
                 uint32_t b[4];
                 const int row = kb * 16 + (lane & 7) + (lane >> 4) * 8;
                 ldmatrix_x4(b, k_base + 2 * tile_chunk_offset<PHD>(row, kk * 2 + ((lane >> 3) & 1)));
@@ -123,7 +127,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         }
         float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < 2 * KB; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
@@ -149,7 +153,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
             o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
+        for (int kb = 0; kb < KB; ++kb) {
             uint32_t pa[4];
             {
                 float p[2][4];

@@ -125,6 +125,12 @@ def _compile(name: str, path: str, verbose_ptxas: bool = False) -> None:
                             f"link {name}")
         os.replace(tmp_so, path)     # atomic: a concurrent builder sees all or nothing
         _say(f"built {os.path.basename(path)}")
+        for old in os.listdir(os.path.dirname(path)):     # builds of earlier sources of this library
+            if old.startswith(f"hos_{name}-") and old.endswith(".so") and old != os.path.basename(path):
+                try:
+                    os.remove(os.path.join(os.path.dirname(path), old))
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(workdir, ignore_errors=True)
 
