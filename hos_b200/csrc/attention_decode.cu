@@ -456,3 +456,54 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     attn_decode_kernel<<<grid, kDecodeThreads, smem, stream>>>(a);
     return check_launch("attn_decode");
 }
+
+// ---- the entry point that allocates nothing (see attn_decode_noalloc.h) -----------------------
+#include "attn_decode_noalloc.h"
+
+namespace hos {
+// Partial results of the shares, then the counters.  In host code this name is only a handle
+// for cudaGetSymbolAddress: the device address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[HOS_NOALLOC_SCRATCH_BYTES + HOS_NOALLOC_TICKETS * sizeof(int)];
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace hos
+
+extern "C" int hos_attn_decode_noalloc(const void* q, int q_stride, void* out, int out_stride,
+                                       const int* token_pos, const int* token_seq, const int* seq_slot,
+                                       void* k_pages, void* v_pages, const int* page_table, int table_stride,
+                                       int ring_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                       float scale, float cap, int window, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        HOS_REFUSE("attn_decode_noalloc: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    if (n_splits < 1) HOS_REFUSE("attn_decode_noalloc: %d splits", n_splits);
+    const long long floats = hos_attn_decode_workspace(n_tokens, n_heads, n_splits);
+    const long long pairs = hos_attn_decode_tickets(n_tokens, n_heads, n_kv_heads);
+    if (floats * (long long)sizeof(float) > (long long)HOS_NOALLOC_SCRATCH_BYTES)
+        HOS_REFUSE("attn_decode_noalloc: the partial results of %d tokens x %d heads x %d splits need %lld bytes, "
+                   "the built-in scratch holds %u: use fewer splits or tokens, or hos_attn_decode with a workspace",
+                   n_tokens, n_heads, n_splits, floats * (long long)sizeof(float), HOS_NOALLOC_SCRATCH_BYTES);
+    if (pairs > HOS_NOALLOC_TICKETS)
+        HOS_REFUSE("attn_decode_noalloc: %lld (token, kv head) pairs, the built-in counters hold %d", pairs,
+                   HOS_NOALLOC_TICKETS);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        HOS_REFUSE("attn_decode_noalloc: cannot tell the current device");
+    if (g_noalloc_ptr[dev] == nullptr) {       // once per device, with that device current
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            HOS_REFUSE("attn_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = p;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+    float* workspace = reinterpret_cast<float*>(base);
+    int* tickets = reinterpret_cast<int*>(base + HOS_NOALLOC_SCRATCH_BYTES);
+    if (n_splits > 1) {                        // the counters must start at zero whatever the last call left
+        cudaError_t e = cudaMemsetAsync(tickets, 0, (size_t)pairs * sizeof(int), stream);
+        if (e != cudaSuccess) HOS_REFUSE("attn_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    }
+    return hos_attn_decode(q, q_stride, out, out_stride, workspace, tickets, token_pos, token_seq, seq_slot, k_pages,
+                           v_pages, page_table, table_stride, ring_pages, n_tokens, n_heads, n_kv_heads, head_dim,
+                           scale, cap, window, n_splits, stream);
+}

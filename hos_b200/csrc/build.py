@@ -70,7 +70,7 @@ def _flags(extra: Sequence[str]) -> List[str]:
 def _digest(sources: Sequence[str], extra: Sequence[str]) -> str:
     h = hashlib.sha1()
     for f in sorted(os.listdir(HERE)):
-        if f.endswith(".cuh") or f in sources:
+        if f.endswith(".cuh") or f.endswith(".h") or f in sources:
             h.update(f.encode())
             with open(os.path.join(HERE, f), "rb") as fh:
                 h.update(fh.read())
