@@ -15,6 +15,7 @@ Libraries and what needs them:
   attn_hdN    bfloat16 models with head_dim N: tensor-core attention for prompts
               and for decoding over the paged cache
   gemm_tc     bfloat16 models: the tcgen05/TMA matrix product
+  gemm_skinny bfloat16 models: the matrix product for up to 16 rows (decoding)
 """
 from __future__ import annotations
 
@@ -40,6 +41,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
+    "gemm_skinny": (["gemm_skinny.cu"], []),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,153 @@
+// Matrix product for a handful of rows (decoding): out[M, N] = A[M, K] . W[N, K]^T with M <= 16,
+// bfloat16 operands, 32-bit accumulation.  The work is reading W once; everything is arranged so
+// that nothing stands between the launch and the first bytes of W:
+//
+//  * no shared-memory staging, no descriptors, no tensor-memory allocation: every thread loads
+//    16 bytes of a row of W straight into registers, several loads in flight per thread;
+//  * the registers are fed to mma.sync m16n8k16 as they are.  A 16-byte load gives a thread 8
+//    consecutive k of one row, while the MMA wants (2t, 2t+1) and (2t+8, 2t+9): since a dot
+//    product does not care in which order k is visited, the same permutation of k is applied
+//    to both operands (the thread's 16 bytes of an activation row are split the same way), and
+//    no shuffle is needed;
+//  * a CTA owns 16 output features (rows of W) and its 8 warps split K; their partial tiles
+//    are added through shared memory in a fixed order, so no partial sums go through global
+//    memory and the result does not depend on timing.
+//
+// Epilogues: none (bf16 or f32 output); gated, where the CTA owns 16 gate rows and the 16
+// matching up rows (4 warps each) and writes act(gate) * up.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace hos {
+
+constexpr int kSkinnyWarps = 8;
+constexpr int kSkinnyThreads = kSkinnyWarps * 32;
+constexpr int kUnroll = 8;          // k-blocks of 32 whose loads are issued before any is used
+
+__device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// streaming load for the weights: read once, do not keep in L1
+__device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// MT: token tiles of 8 (1: M <= 8, 2: M <= 16).  GATED: rows come in gate/up pairs.
+template <int MT, bool GATED, typename OutT>
+__global__ void __launch_bounds__(kSkinnyThreads, 2)
+gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
+                   int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
+    __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    // which rows of W this warp reads, and which share of K
+    const int k_ways = GATED ? kSkinnyWarps / 2 : kSkinnyWarps;
+    const int k_way = GATED ? (warp & 3) : warp;
+    const int row_base = (GATED && warp >= 4) ? gate_rows + n0 : n0;
+    const int row_limit = (GATED && warp >= 4) ? gate_rows + N : N;
+    const int k_blocks = (K + 31) / 32;
+    const int per_way = (k_blocks + k_ways - 1) / k_ways;
+    const int kb_begin = k_way * per_way, kb_end = min(k_blocks, kb_begin + per_way);
+
+    const int r0 = row_base + g, r1 = row_base + g + 8;
+    const bool ok0 = r0 < row_limit, ok1 = r1 < row_limit;
+    const bf16* w0 = W + (size_t)(ok0 ? r0 : row_base) * ldw + 8 * t4;
+    const bf16* w1 = W + (size_t)(ok1 ? r1 : row_base) * ldw + 8 * t4;
+    const bf16* a0 = A + (size_t)min(g, M - 1) * lda + 8 * t4;
+    const bf16* a1 = A + (size_t)min(g + 8, M - 1) * lda + 8 * t4;
+    const bool tok0 = g < M, tok1 = MT == 2 && g + 8 < M;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+        uint4 wa[kUnroll], wb[kUnroll], xa[kUnroll], xb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int k = (kb + u) * 32 + 8 * t4;
+            const bool in = (kb + u) < kb_end && k < K;          // K is a multiple of 8: a 16-byte load is whole
+            wa[u] = (in && ok0) ? ldg16_stream(w0 + (size_t)(kb + u) * 32) : zero;
+            wb[u] = (in && ok1) ? ldg16_stream(w1 + (size_t)(kb + u) * 32) : zero;
+            xa[u] = (in && tok0) ? ldg16(a0 + (size_t)(kb + u) * 32) : zero;
+            if (MT == 2) xb[u] = (in && tok1) ? ldg16(a1 + (size_t)(kb + u) * 32) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            // the thread's 8 consecutive k as two MMAs: k slots (2t,2t+1,2t+8,2t+9) <- elements (0,1,2,3) then (4,5,6,7)
+            const uint32_t fa[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+            const uint32_t fb[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+            mma_bf16(acc[0], fa, xa[u].x, xa[u].y);
+            mma_bf16(acc[0], fb, xa[u].z, xa[u].w);
+            if (MT == 2) {
+                mma_bf16(acc[1], fa, xb[u].x, xb[u].y);
+                mma_bf16(acc[1], fb, xb[u].z, xb[u].w);
+            }
+        }
+    }
+    // C fragment: c0 (row g, token 2t), c1 (row g, token 2t+1), c2 (row g+8, token 2t), c3 (row g+8, token 2t+1)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        part[warp][m][g][2 * t4] = acc[m][0];
+        part[warp][m][g][2 * t4 + 1] = acc[m][1];
+        part[warp][m][g + 8][2 * t4] = acc[m][2];
+        part[warp][m][g + 8][2 * t4 + 1] = acc[m][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += kSkinnyThreads) {
+        const int tok = idx / 16, r = idx % 16;            // consecutive threads: consecutive features of one token
+        const int m = tok >> 3, t = tok & 7;
+        const int n = n0 + r;
+        if (tok >= M || n >= N) continue;
+        float v;
+        if (GATED) {
+            float gsum = 0.f, usum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { gsum += part[w][m][r][t]; usum += part[4 + w][m][r][t]; }
+            const float a = act == 0 ? gelu_tanh(gsum) : gsum / (1.f + __expf(-gsum));
+            v = a * usum;
+        } else {
+            v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSkinnyWarps; ++w) v += part[w][m][r][t];
+        }
+        out[(size_t)tok * ldo + n] = from_float<OutT>(v);
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
+// out[M, N] = A[M, K] . W[N, K]^T for M <= 16.  epilogue 0: none (out bf16 or f32); 2: gated (W has
+// 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
+// multiples of 8 elements, A and W 16-byte aligned.
+extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
+                               int lda, int ldw, int ldo, int epilogue, int act, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16) HOS_REFUSE("gemm_skinny: %d rows are more than 16", M);
+    if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
+        HOS_REFUSE("gemm_skinny: K and the leading dimensions must be multiples of 8 elements and the operands "
+                   "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
+    if (epilogue != 0 && epilogue != 2) HOS_REFUSE("gemm_skinny: epilogue %d is not offered", epilogue);
+    if (epilogue == 2 && out_dtype != kBF16) HOS_REFUSE("gemm_skinny: the gated epilogue writes bfloat16");
+    const unsigned grid = (unsigned)((N + 15) / 16);
+#define HOS_SK(MT, G, T)                                                                                     \
+    gemm_skinny_kernel<MT, G, T><<<grid, kSkinnyThreads, 0, stream>>>((const bf16*)A, (const bf16*)W, (T*)out, \
+                                                                       M, N, K, lda, ldw, ldo, N, act)
+    if (epilogue == 2) {
+        if (M <= 8) HOS_SK(1, true, bf16); else HOS_SK(2, true, bf16);
+    } else if (out_dtype == kBF16) {
+        if (M <= 8) HOS_SK(1, false, bf16); else HOS_SK(2, false, bf16);
+    } else if (out_dtype == kF32) {
+        if (M <= 8) HOS_SK(1, false, float); else HOS_SK(2, false, float);
+    } else {
+        HOS_REFUSE("gemm_skinny: unknown output dtype %d", out_dtype);
+    }
+#undef HOS_SK
+    return check_launch("gemm_skinny");
+}

@@ -1,7 +1,8 @@
 """The matrix product that every part calls: y = x . W^T, W stored [out, in] as the
-checkpoint has it (src/model.rs:179-180).  Chooses the kernel: in bfloat16 the
-tcgen05/TMA kernel when the sizes meet its alignment rules, else (and always in
-the 32-bit path) the plain CUDA-core kernel.  Both accumulate in 32-bit."""
+checkpoint has it (src/model.rs:179-180).  Chooses the kernel: in bfloat16, for up to 16
+rows the register-streaming kernel, else the tcgen05/TMA kernel, when the sizes meet their
+alignment rules; otherwise (and always in the 32-bit path) the plain CUDA-core kernel.  All
+accumulate in 32-bit."""
 from __future__ import annotations
 
 from typing import Optional
@@ -30,7 +31,10 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if m == 0:
         return out
     if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
-        from . import gemm_tc
+        from . import gemm_skinny, gemm_tc
+        if gemm_skinny.can_take(x, w, out, epilogue):
+            gemm_skinny.matmul(x, w, out, epilogue, act)
+            return out
         if gemm_tc.can_take(x, w, out, epilogue):
             gemm_tc.matmul(x, w, out, epilogue, cap, act)
             return out
@@ -43,7 +47,9 @@ def matmul_or_partials(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     activation type, or float32 partial sums [parts, M, N] when the tensor-core kernel splits K
     (few rows, few output tiles: decoding).  No epilogue."""
     if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0):
-        from . import gemm_tc
+        from . import gemm_skinny, gemm_tc
+        if gemm_skinny.enabled and x.shape[0] <= gemm_skinny.MAX_ROWS:
+            return matmul(x, w)          # a handful of rows: the skinny kernel adds its K shares itself
         if gemm_tc.enabled and x.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 \
                 and x.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
             parts = gemm_tc.matmul_partials(x, w)

@@ -557,3 +557,37 @@ def test_consumers_add_partial_sums():
     close(ca.k_pages, cb.k_pages, torch.bfloat16)
     close(ca.v_pages, cb.v_pages, torch.bfloat16)
     assert float(cb.k_pages[1, 0, 3:3 + N].abs().sum()) > 0
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 32), (3, 40, 72), (8, 2304, 2048), (8, 1000, 200), (9, 136, 264),
+                                   (16, 520, 2304), (5, 2304, 9216)])
+@pytest.mark.parametrize("variant", ["bf16_out", "f32_out", "gated_gelu", "gated_silu"])
+def test_gemm_skinny(shape, variant):
+    """The product for up to 16 rows against float64: row counts on both sides of a token tile,
+    feature counts and K that fill no tile, both epilogues."""
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_skinny
+    M, N, K = shape
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gated = variant.startswith("gated")
+    w = (torch.randn(2 * N if gated else N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double() @ w[:N].double().T
+    if variant == "bf16_out":
+        out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+        assert gemm_skinny.can_take(a, w, out, ops.EPI_NONE)
+        gemm_skinny.matmul(a, w, out)
+        close(out, ref.to(torch.bfloat16), torch.bfloat16)
+    elif variant == "f32_out":
+        out = torch.empty((M, N), device=DEV)
+        gemm_skinny.matmul(a, w, out)
+        close(out, ref, torch.float32, scale=3)
+    else:
+        act = "gelu_tanh" if variant == "gated_gelu" else "silu"
+        out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+        gemm_skinny.matmul(a, w, out, ops.EPI_GATED, act=ops.ACTIVATIONS[act])
+        g, u = ref, a.double() @ w[N:].double().T
+        af = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
+        close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
+    big = torch.empty((17, N), device=DEV, dtype=torch.bfloat16)
+    assert not gemm_skinny.can_take(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w, big, ops.EPI_NONE)
