@@ -1,0 +1,450 @@
+// Attention of whole prompts from position 0 on the 5th-generation tensor cores (head sizes
+// 64, 128 and 256), bfloat16.
+//
+// One CTA takes 128 consecutive queries of one sequence and one query head and walks over
+// key tiles of 64.  Queries, keys and values are rows of the step's fused projection output;
+// TMA brings [rows x 64] column blocks of them into shared memory with the 128-byte swizzle.
+// Per key tile:  S = Q K^T  (tcgen05.mma, M=128, N=64, K=head_dim; accumulator in tensor
+// memory, two buffers so that the next tile's product runs under this tile's softmax);
+// the four softmax warps read S back, one query row per thread (no shuffles: a row's maximum
+// and sum live in one thread), scale, soft-cap, mask, exponentiate and write P as bfloat16
+// into shared memory in the K-major swizzled layout;  O += P V  (tcgen05.mma, M=128,
+// N=head_dim, K=64, V used as it lies in memory: an MN-major operand), O staying in tensor
+// memory for the whole walk.  The running maximum is only raised when a tile's maximum
+// exceeds it by more than 8 (probabilities up to e^8 are harmless in 32-bit sums and
+// bfloat16 P), so O is rescaled rarely; when it is, the thread reads its O row from tensor
+// memory, scales it and writes it back.  At the end each thread divides its row by its sum
+// and stores it.  Warp roles: 0 TMA, 1 MMA issue and tensor-memory allocation, 2-5 softmax,
+// correction and epilogue.  Every mbarrier wait is bounded in time.
+//
+// Compiled per head size: -DHOS_HEAD_DIM=N; the kernel exists for N in {64, 128, 256}.
+#include <cuda.h>
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+#ifndef HOS_HEAD_DIM
+#define HOS_HEAD_DIM 64
+#endif
+
+namespace hos {
+
+constexpr int THD = HOS_HEAD_DIM;
+constexpr bool kHasTcPrefill = (THD == 64 || THD == 128 || THD == 256);
+
+#if (HOS_HEAD_DIM == 64) || (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+
+constexpr int TQ = 128, TK = 64;
+constexpr int CBLK = THD / 64;                         // 64-element (128-byte) column blocks of a head
+constexpr int kQBlockBytes = TQ * 128;                 // one column block of the Q tile
+constexpr int kKVBlockBytes = TK * 128;                // one column block of a K or V tile
+constexpr int kQBytesTc = CBLK * kQBlockBytes;
+constexpr int kKVTileBytes = CBLK * kKVBlockBytes;
+constexpr int kPBytes = TQ * 128;                      // 128 rows x 64 keys bf16
+constexpr int kKVStages = 2;
+constexpr int kTcSmem = kQBytesTc + kKVStages * 2 * kKVTileBytes + kPBytes + 1024 + 256;
+constexpr int kTmemColsTc = (128 + THD) <= 256 ? 256 : 512;
+constexpr int kColS = 0, kColO = 128;
+constexpr long long kTcWaitCycles = 1ll << 31;
+constexpr float kRescaleSlack = 8.0f;
+
+__device__ int g_prefill_tc_error = 0;
+
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > kTcWaitCycles) return false;
+    return true;
+}
+__device__ __forceinline__ void tc_tma_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major tile (the N dimension contiguous), 128-byte swizzle: a [K rows][64 N elements] block has rows
+// of 128 bytes; 8-row K groups are 1024 bytes apart (stride offset), 64-element N blocks `block_bytes`
+// apart (leading offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_bytes) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(block_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// bf16 x bf16 -> f32; b_mn: B operand is MN-major.
+__host__ __device__ constexpr uint32_t tc_idesc(int m, int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+struct PrefillTcArgs {
+    bf16* out;
+    int out_stride;
+    const int* cu_seqlens;
+    int n_seqs, n_heads, n_kv_heads;
+    int q_col0, k_col0, v_col0;     // first column of the q, k and v heads in a projection row
+    float scale, cap;
+    int window;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
+                       const __grid_constant__ CUtensorMap map_kv,     // boxes of [64 rows x 64 columns]
+                       PrefillTcArgs a) {
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* kv_s = q_s + kQBytesTc;                       // stage s: K tile then V tile
+    unsigned char* p_s = kv_s + kKVStages * 2 * kKVTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kPBytes);
+    uint64_t* q_full = bars;                 // 1
+    uint64_t* kv_full = bars + 1;            // [2]
+    uint64_t* kv_empty = bars + 3;           // [2]
+    uint64_t* s_full = bars + 5;             // [2]
+    uint64_t* s_empty = bars + 7;            // [2]
+    uint64_t* p_full = bars + 9;             // 1
+    uint64_t* pv_done = bars + 10;           // 1
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 11);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which sequence and which block of 128 queries (long blocks first: late queries have most keys)
+    int seq = 0, tile = blockIdx.x, row0 = 0, len = 0, nt = 0;
+    for (; seq < a.n_seqs; ++seq) {
+        row0 = a.cu_seqlens[seq];
+        len = a.cu_seqlens[seq + 1] - row0;
+        nt = (len + TQ - 1) / TQ;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (seq >= a.n_seqs) return;
+    const int q0 = (nt - 1 - tile) * TQ;
+    const int head = blockIdx.y, kvh = head / (a.n_heads / a.n_kv_heads);
+    const int last_q = min(len - 1, q0 + TQ - 1);
+    const int first_key = a.window > 0 ? max(0, q0 + 1 - a.window) : 0;
+    const int kt_lo = first_key / TK, kt_hi = last_q / TK;
+    const int n_tiles = kt_hi - kt_lo + 1;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_smem)),
+                     "r"(kTmemColsTc) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(q_full, kQBytesTc);
+            for (int c = 0; c < CBLK; ++c)
+                tc_tma_2d(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % kKVStages;
+                if (j >= kKVStages && !tc_wait(&kv_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
+                unsigned char* kd = kv_s + (size_t)s * 2 * kKVTileBytes;
+                unsigned char* vd = kd + kKVTileBytes;
+                const int krow = row0 + (kt_lo + j) * TK;
+                mbar_expect_tx(&kv_full[s], 2 * kKVTileBytes);
+                for (int c = 0; c < CBLK; ++c) {
+                    tc_tma_2d(kd + c * kKVBlockBytes, &map_kv, a.k_col0 + kvh * THD + 64 * c, krow, &kv_full[s]);
+                    tc_tma_2d(vd + c * kKVBlockBytes, &map_kv, a.v_col0 + kvh * THD + 64 * c, krow, &kv_full[s]);
+                }
+            }
+            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = tc_idesc(TQ, TK, 0);        // S = Q K^T: both K-major
+            constexpr uint32_t idesc_o = tc_idesc(TQ, THD, 1);       // O = P V: V is MN-major
+            bool ok = tc_wait(q_full, 0);
+            tc_fence_after_sync();
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % kKVStages, sb = j & 1;
+                if (!tc_wait(&kv_full[s], (j / kKVStages) & 1)) return false;
+                if (j >= 2 && !tc_wait(&s_empty[sb], ((j >> 1) - 1) & 1)) return false;
+                tc_fence_after_sync();
+                const uint32_t k_addr = smem_u32(kv_s + (size_t)s * 2 * kKVTileBytes);
+#pragma unroll
+                for (int kk = 0; kk < THD / 16; ++kk) {
+                    const uint64_t ad = desc_kmajor(smem_u32(q_s) + (kk / 4) * kQBlockBytes) + 2 * (kk % 4);
+                    const uint64_t bd = desc_kmajor(k_addr + (kk / 4) * kKVBlockBytes) + 2 * (kk % 4);
+                    tc_mma(tmem_base + kColS + sb * TK, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(&s_full[sb]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }      // the next S runs under this tile's softmax
+                if (!tc_wait(p_full, j & 1)) { ok = false; break; }
+                tc_fence_after_sync();
+                const int s = j % kKVStages;
+                const uint32_t v_addr = smem_u32(kv_s + (size_t)s * 2 * kKVTileBytes + kKVTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < TK / 16; ++ks) {
+                    const uint64_t ad = desc_kmajor(smem_u32(p_s)) + 2 * ks;
+                    const uint64_t bd = desc_mnmajor(v_addr + ks * 16 * 128, kKVBlockBytes);
+                    tc_mma(tmem_base + kColO, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(&kv_empty[s]);      // K and V of this stage have been read
+                tc_commit(pv_done);           // P has been read, O holds tile j
+            }
+            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax, correction, epilogue: one query row per thread ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int qpos = q0 + r;
+        const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int sb = j & 1;
+            if (!tc_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+            tc_fence_after_sync();
+            float sc[TK];
+            {
+                uint32_t v0[32], v1[32];
+                tc_ld32(t_lane + kColS + sb * TK, v0);
+                tc_ld32(t_lane + kColS + sb * TK + 32, v1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(v0[i]); sc[32 + i] = __uint_as_float(v1[i]); }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[sb]);            // this S buffer may be overwritten
+            const int k0 = (kt_lo + j) * TK;
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < TK; ++i) {
+                const int key = k0 + i;
+                float s = softcap_fast(sc[i] * a.scale, a.cap, inv_cap);
+                const bool vis = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+                s = vis ? s : -INFINITY;
+                sc[i] = s;
+                m_tile = fmaxf(m_tile, s);
+            }
+            // raise the reference maximum only when it is exceeded by a margin
+            float factor = 1.f;
+            if (m_tile > m_ref + kRescaleSlack || (m_ref == -INFINITY && m_tile > -INFINITY)) {
+                factor = m_ref == -INFINITY ? 0.f : __expf(m_ref - m_tile);
+                m_ref = m_tile;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            float psum = 0.f;
+            uint32_t packed[TK / 2];
+#pragma unroll
+            for (int i = 0; i < TK; i += 2) {
+                const float p0 = __expf(sc[i] - m_use), p1 = __expf(sc[i + 1] - m_use);
+                psum += p0 + p1;
+                packed[i / 2] = pack_bf16(p0, p1);
+            }
+            l_run = l_run * factor + psum;
+            // P and O may be touched once the products of the tile before have finished
+            if (j > 0 && !tc_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+#pragma unroll 1
+                for (int c = 0; c < THD; c += 32) {
+                    uint32_t o[32];
+                    tc_ld32(t_lane + kColO + c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tc_st32(t_lane + kColO + c, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            // P row r: 8 chunks of 16 bytes, chunk c at position c ^ (r & 7)
+            {
+                unsigned char* prow = p_s + (size_t)r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the tensor core
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        // ---- epilogue: O / l -> bfloat16 -> global ----
+        if (ok && !tc_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* orow = a.out + (size_t)(row0 + qpos) * a.out_stride + (size_t)head * THD;
+#pragma unroll 1
+            for (int c = 0; c < THD; c += 32) {
+                uint32_t o[32];
+                tc_ld32(t_lane + kColO + c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (qpos < len) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        dst[q4] = make_uint4(
+                            pack_bf16(__uint_as_float(o[8 * q4]) * inv, __uint_as_float(o[8 * q4 + 1]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 2]) * inv, __uint_as_float(o[8 * q4 + 3]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 4]) * inv, __uint_as_float(o[8 * q4 + 5]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 6]) * inv, __uint_as_float(o[8 * q4 + 7]) * inv));
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(&g_prefill_tc_error, 1);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsTc) : "memory");
+}
+
+typedef CUresult (*TcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TcEncodeFn tc_encode_fn() {
+    static TcEncodeFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TcEncodeFn>(sym);
+    }
+    return fn;
+}
+static int tc_make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int ld, int box_rows) {
+    TcEncodeFn fn = tc_encode_fn();
+    if (!fn) HOS_REFUSE("attn_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) HOS_REFUSE("attn_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+#endif   // head sizes with the kernel
+
+}  // namespace hos
+
+using namespace hos;
+
+// 1 if this library has the tensor-core prompt kernel (head sizes 64, 128, 256).
+extern "C" int hos_attn_prefill_tc_available() { return kHasTcPrefill ? 1 : 0; }
+
+// 1 if an earlier launch gave up a bounded wait (and clears the flag).  Synchronises.
+extern "C" int hos_attn_prefill_tc_error() {
+#if (HOS_HEAD_DIM == 64) || (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+    int v = 0, zero = 0;
+    cudaMemcpyFromSymbol(&v, g_prefill_tc_error, sizeof(int));
+    if (v) cudaMemcpyToSymbol(g_prefill_tc_error, &zero, sizeof(int));
+    return v;
+#else
+    return 0;
+#endif
+}
+
+// rows: the fused projection output [n_rows, row_stride] (q heads, then k heads, then v heads);
+// sequences occupy rows cu_seqlens[s] .. cu_seqlens[s+1]-1, each from position 0; n_q_tiles is the
+// sum over sequences of ceil(len / 128).
+extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_stride, void* out, int out_stride,
+                                   const int* cu_seqlens, int n_seqs, int n_q_tiles, int n_heads, int n_kv_heads,
+                                   int head_dim, float scale, float cap, int window, cudaStream_t stream) {
+#if (HOS_HEAD_DIM == 64) || (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+    if (n_q_tiles <= 0 || n_seqs <= 0) return 0;
+    if (head_dim != THD) HOS_REFUSE("attn_prefill_tc: built for head_dim %d, asked for %d", THD, head_dim);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        HOS_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    if (n_heads > 65535) HOS_REFUSE("attn_prefill_tc: %d heads are more than one launch takes", n_heads);
+    if (row_stride != (n_heads + 2 * n_kv_heads) * THD)
+        HOS_REFUSE("attn_prefill_tc: a row of %d elements is not q, k and v heads of %d", row_stride, THD);
+    if ((row_stride % 8) || ((uintptr_t)rows % 16) || (out_stride % 8) || ((uintptr_t)out % 16))
+        HOS_REFUSE("attn_prefill_tc: rows must be 16-byte aligned");
+    CUtensorMap mq, mkv;
+    int rc;
+    if ((rc = tc_make_map(&mq, rows, n_rows, row_stride, row_stride, TQ))) return rc;
+    if ((rc = tc_make_map(&mkv, rows, n_rows, row_stride, row_stride, TK))) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+            HOS_REFUSE("attn_prefill_tc: cannot get %d bytes of shared memory", kTcSmem);
+        attr_set = true;
+    }
+    PrefillTcArgs a;
+    a.out = (bf16*)out; a.out_stride = out_stride; a.cu_seqlens = cu_seqlens; a.n_seqs = n_seqs;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
+    a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
+    a.scale = scale; a.cap = cap; a.window = window;
+    dim3 grid(n_q_tiles, n_heads);
+    attn_prefill_tc_kernel<<<grid, 192, kTcSmem, stream>>>(mq, mkv, a);
+    return check_launch("attn_prefill_tc");
+#else
+    HOS_REFUSE("attn_prefill_tc: no tensor-core prompt kernel for head_dim %d (64, 128 and 256 have one)", HOS_HEAD_DIM);
+#endif
+}

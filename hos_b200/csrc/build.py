@@ -53,7 +53,7 @@ def library_spec(name: str) -> Tuple[List[str], List[str]]:
         return _STATIC_LIBS[name]
     if name.startswith("attn_hd"):
         hd = int(name[len("attn_hd"):])
-        return ["attention_decode.cu", "attention_prefill.cu"], [f"-DHOS_HEAD_DIM={hd}"]
+        return ["attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu"], [f"-DHOS_HEAD_DIM={hd}"]
     raise ExtensionMissingError(f"no CUDA library named {name!r}")
 
 

@@ -223,6 +223,10 @@ __global__ void rope_kv_write_kernel(const TSrc* __restrict__ src, int n_parts, 
     const int pos = token_pos[n];
     const int hd = cache.head_dim, nkv = cache.n_kv_heads;
     const int half = rotary_dim >> 1;
+    // where the token's key and value go: looked up now, so that these dependent loads overlap the rotation
+    int page = -1;
+    if (write_cache && !(cache.ring_pages > 0 && pos + cache.ring_pages * kPageTokens < seq_len_after[seq]))
+        page = cache.page_table[(size_t)seq_slot[seq] * cache.table_stride + kv_table_entry(cache, pos / kPageTokens)];
     const bool in_place = (const void*)src == (const void*)qkv;
     const TSrc* srow = src + (size_t)n * row_stride;
     T* row = qkv + (size_t)n * row_stride;
@@ -259,12 +263,9 @@ __global__ void rope_kv_write_kernel(const TSrc* __restrict__ src, int n_parts, 
             row[e] = from_float<T>(value(e));
         }
     }
-    if (!write_cache) return;
+    if (page < 0) return;          // nothing to store (no cache, or a ring position that this step overwrites)
     __syncthreads();
-    if (cache.ring_pages > 0 && pos + cache.ring_pages * kPageTokens < seq_len_after[seq]) return;
-    const int slot = seq_slot[seq];
-    const int lp = pos / kPageTokens, r = pos % kPageTokens;
-    const int page = cache.page_table[(size_t)slot * cache.table_stride + kv_table_entry(cache, lp)];
+    const int r = pos % kPageTokens;
     const T* ksrc = row + (size_t)n_heads * hd;
     const T* vsrc = ksrc + (size_t)nkv * hd;
     T* kp = (T*)cache.k_pages;

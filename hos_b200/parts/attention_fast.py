@@ -16,7 +16,7 @@ MAX_HEAD_DIM = 256
 MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
-enabled = {"decode": True, "prefill": True}     # tests switch a kernel off to compare with the plain one
+enabled = {"decode": True, "prefill": True, "prefill_tc": True}     # tests switch a kernel off to compare with the plain one
 
 
 def supports(head_dim: int) -> bool:
@@ -82,9 +82,32 @@ def decode_gave_up(head_dim: int) -> bool:
     return bool(f())
 
 
+def has_tc_prefill(head_dim: int) -> bool:
+    f = lib_for(head_dim).lib.hos_attn_prefill_tc_available
+    f.restype, f.argtypes = ctypes.c_int, []
+    return bool(f())
+
+
+def prefill_tc(rows: torch.Tensor, out, cu_seqlens, cu_host, n_heads, n_kv_heads, head_dim, scale, cap, window) -> None:
+    """Attention of whole prompts from position 0 on the tcgen05 tensor cores; `rows` is the
+    fused projection output [N, (n_heads + 2 n_kv_heads) * head_dim] (head sizes 64, 128, 256)."""
+    lib = lib_for(head_dim)
+    n_seqs = len(cu_host) - 1
+    tiles = sum((cu_host[i + 1] - cu_host[i] + 127) // 128 for i in range(n_seqs))
+    lib.call("hos_attn_prefill_tc", ops._ptr(rows), rows.shape[0], rows.shape[1], ops._ptr(out), out.shape[1],
+             ops._ptr(cu_seqlens), n_seqs, tiles, n_heads, n_kv_heads, head_dim, float(scale), float(cap),
+             int(window) if window else 0, ops._stream())
+
+
+def prefill_tc_gave_up(head_dim: int) -> bool:
+    f = lib_for(head_dim).lib.hos_attn_prefill_tc_error
+    f.restype, f.argtypes = ctypes.c_int, []
+    return bool(f())
+
+
 def prefill(q, q_stride, k_rows, v_rows, kv_stride, out, cu_seqlens, cu_host, n_heads, n_kv_heads, head_dim,
             scale, cap, window) -> None:
-    """Attention of whole prompts from position 0 over their own packed rows."""
+    """Attention of whole prompts from position 0 over their own packed rows (mma.sync kernel)."""
     lib = lib_for(head_dim)
     n_seqs = len(cu_host) - 1
     tiles = sum((cu_host[i + 1] - cu_host[i] + 63) // 64 for i in range(n_seqs))
@@ -102,6 +125,10 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
             return False
         if step.n_tokens > step.cu_host[-1]:
             att[step.cu_host[-1]:].zero_()       # padding rows: a defined output
+        if enabled["prefill_tc"] and qkv.is_contiguous() and has_tc_prefill(mixer.head_dim):
+            prefill_tc(qkv, att, step.cu_seqlens, step.cu_host, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                       mixer.scale, mixer.softcap, mixer.window)
+            return True
         prefill(qkv, qkv.shape[1], qkv[:, mixer.q_dim:], qkv[:, mixer.q_dim + mixer.kv_dim:], qkv.shape[1],
                 att, step.cu_seqlens, step.cu_host, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                 mixer.scale, mixer.softcap, mixer.window)

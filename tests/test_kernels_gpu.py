@@ -591,3 +591,56 @@ def test_gemm_skinny(shape, variant):
         close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
     big = torch.empty((17, N), device=DEV, dtype=torch.bfloat16)
     assert not gemm_skinny.can_take(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w, big, ops.EPI_NONE)
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=3, nkv=1, hd=64, window=None, cap=0.0),
+                                 dict(nh=2, nkv=2, hd=64, window=70, cap=30.0),
+                                 dict(nh=4, nkv=2, hd=128, window=100, cap=50.0),
+                                 dict(nh=8, nkv=4, hd=256, window=200, cap=50.0),
+                                 dict(nh=2, nkv=1, hd=256, window=None, cap=50.0)])
+def test_attention_prefill_tensor_core_kernel(cfg):
+    """The tcgen05 prompt kernel over packed rows of unequal sequences (1 to 517 tokens; blocks
+    of 128 queries that are full, partial, and cut by the window), every position against
+    float64.  One logit is made large early in a sequence so that the running maximum has to
+    be raised, and O rescaled, in the middle of a walk."""
+    from hos_b200.parts import attention_fast as af
+    dt = torch.bfloat16
+    nh, nkv, hd, window, cap = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], cfg["cap"]
+    assert af.has_tc_prefill(hd)
+    torch.manual_seed(4)
+    seq_lens = [1, 127, 128, 129, 300, 517]
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(l, nh, hd).to(dt).float() * 0.5 for l in seq_lens]
+    g = nh // nkv
+    ks[5][400] = qs[5][516, 0::g][:nkv] * 4.0          # a late key that dwarfs the earlier maxima
+    if window:
+        ks[5][517 - window] = qs[5][516, 0::g][:nkv] * 3.0
+        ks[5][517 - window - 1] = qs[5][516, 0::g][:nkv] * 8.0       # just outside the window: must not be seen
+    scale = 0.9 / math.sqrt(hd)
+    rows = torch.cat([torch.cat([q.reshape(len(q), -1), k.reshape(len(k), -1), v.reshape(len(v), -1)], 1)
+                      for q, k, v in zip(qs, ks, vs)]).to(DEV).to(dt)
+    rows = torch.cat([rows, torch.full((5, rows.shape[1]), 1e4, device=DEV, dtype=dt)]).contiguous()   # padding rows
+    N = rows.shape[0]
+    cu_host = [0]
+    for l in seq_lens:
+        cu_host.append(cu_host[-1] + l)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device=DEV)
+    out = torch.full((N, nh * hd), 7.0, device=DEV, dtype=dt)
+    af.prefill_tc(rows, out, cu, cu_host, nh, nkv, hd, scale, cap, window)
+    assert not af.prefill_tc_gave_up(hd)
+    assert float((out[cu_host[-1]:] - 7.0).abs().sum()) == 0.0      # padding rows are not touched
+    base = 0
+    for i, l in enumerate(seq_lens):
+        q, k, v = qs[i].double(), ks[i].double(), vs[i].double()
+        pos = torch.arange(l)
+        vis = pos[None, :] <= pos[:, None]
+        if window:
+            vis &= pos[None, :] > pos[:, None] - window
+        for h in range(nh):
+            s = (q[:, h] @ k[:, h // g].T) * scale
+            if cap > 0:
+                s = cap * torch.tanh(s / cap)
+            want = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // g]
+            close(out[base:base + l, h * hd:(h + 1) * hd], want.to(dt), dt)
+        base += l
