@@ -6,16 +6,21 @@
 // TMA brings [rows x 64] column blocks of them into shared memory with the 128-byte swizzle.
 // Per key tile:  S = Q K^T  (tcgen05.mma, M=128, N=64, K=head_dim; accumulator in tensor
 // memory, two buffers so that the next tile's product runs under this tile's softmax);
-// the four softmax warps read S back, one query row per thread (no shuffles: a row's maximum
-// and sum live in one thread), scale, soft-cap, mask, exponentiate and write P as bfloat16
-// into shared memory in the K-major swizzled layout;  O += P V  (tcgen05.mma, M=128,
+// the softmax warps read S back (a thread's registers hold a run of one query row: no
+// shuffles), scale, soft-cap, mask, exponentiate and write P as bfloat16 into shared memory in
+// the K-major swizzled layout;  O += P V  (tcgen05.mma, M=128,
 // N=head_dim, K=64, V used as it lies in memory: an MN-major operand), O staying in tensor
 // memory for the whole walk.  The running maximum is only raised when a tile's maximum
 // exceeds it by more than 8 (probabilities up to e^8 are harmless in 32-bit sums and
 // bfloat16 P), so O is rescaled rarely; when it is, the thread reads its O row from tensor
 // memory, scales it and writes it back.  At the end each thread divides its row by its sum
-// and stores it.  Warp roles: 0 TMA, 1 MMA issue and tensor-memory allocation, 2-5 softmax,
-// correction and epilogue.  Every mbarrier wait is bounded in time.
+// and stores it.  Warp roles: 0 TMA, 1 MMA issue and tensor-memory allocation, 2-9 softmax,
+// correction and epilogue: two threads per query row, each with 32 of a tile's 64 keys (warps w
+// and w+4 share a quarter of the tensor-memory lanes), exchanging the row's maximum through
+// shared memory.  P has two buffers, so the softmax of a tile does not wait for the P.V product
+// of the tile before.  The soft-cap uses tanh.approx (relative error 2^-11 of the tanh value:
+// a few 1e-3 in a logit of ordinary size, 0.024 at the cap of 50), the 32-bit path and the
+// decode kernel use the exact form.  Every mbarrier wait is bounded in time.
 //
 // Compiled per head size: -DHOS_HEAD_DIM=N; the kernel exists for N in {64, 128, 256}.
 #include <cuda.h>
@@ -41,7 +46,9 @@ constexpr int kQBytesTc = CBLK * kQBlockBytes;
 constexpr int kKVTileBytes = CBLK * kKVBlockBytes;
 constexpr int kPBytes = TQ * 128;                      // 128 rows x 64 keys bf16
 constexpr int kKVStages = 2;
-constexpr int kTcSmem = kQBytesTc + kKVStages * 2 * kKVTileBytes + kPBytes + 1024 + 256;
+constexpr int kXchgBytes = 2 * TQ * 4;                 // one float per (half, row)
+constexpr int kTcSmem = kQBytesTc + kKVStages * 2 * kKVTileBytes + 2 * kPBytes + kXchgBytes + 128 + 1008;
+constexpr int kTcThreads = 320;                        // TMA warp, MMA warp, 8 softmax warps
 constexpr int kTmemColsTc = (128 + THD) <= 256 ? 256 : 512;
 constexpr int kColS = 0, kColO = 128;
 constexpr long long kTcWaitCycles = 1ll << 31;
@@ -128,7 +135,7 @@ struct PrefillTcArgs {
     int window;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
                        const __grid_constant__ CUtensorMap map_kv,     // boxes of [64 rows x 64 columns]
                        PrefillTcArgs a) {
@@ -137,15 +144,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
     unsigned char* q_s = smem;
     unsigned char* kv_s = q_s + kQBytesTc;                       // stage s: K tile then V tile
     unsigned char* p_s = kv_s + kKVStages * 2 * kKVTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kPBytes);
+    float* xchg = reinterpret_cast<float*>(p_s + 2 * kPBytes);                 // [2 halves][128 rows]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * kPBytes + kXchgBytes);
     uint64_t* q_full = bars;                 // 1
     uint64_t* kv_full = bars + 1;            // [2]
     uint64_t* kv_empty = bars + 3;           // [2]
     uint64_t* s_full = bars + 5;             // [2]
     uint64_t* s_empty = bars + 7;            // [2]
-    uint64_t* p_full = bars + 9;             // 1
-    uint64_t* pv_done = bars + 10;           // 1
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* p_full = bars + 9;             // [2] one per P buffer
+    uint64_t* pv_done = bars + 11;           // [2] one per P buffer
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 13);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -172,10 +180,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8);
+            mbar_init(&p_full[s], 8); mbar_init(&pv_done[s], 1);
         }
-        mbar_init(p_full, 4);
-        mbar_init(pv_done, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -235,80 +242,94 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             if (ok) ok = issue_s(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }      // the next S runs under this tile's softmax
-                if (!tc_wait(p_full, j & 1)) { ok = false; break; }
+                const int pb = j & 1;
+                if (!tc_wait(&p_full[pb], (j >> 1) & 1)) { ok = false; break; }
                 tc_fence_after_sync();
                 const int s = j % kKVStages;
                 const uint32_t v_addr = smem_u32(kv_s + (size_t)s * 2 * kKVTileBytes + kKVTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < TK / 16; ++ks) {
-                    const uint64_t ad = desc_kmajor(smem_u32(p_s)) + 2 * ks;
+                    const uint64_t ad = desc_kmajor(smem_u32(p_s) + pb * kPBytes) + 2 * ks;
                     const uint64_t bd = desc_mnmajor(v_addr + ks * 16 * 128, kKVBlockBytes);
                     tc_mma(tmem_base + kColO, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(&kv_empty[s]);      // K and V of this stage have been read
-                tc_commit(pv_done);           // P has been read, O holds tile j
+                tc_commit(&pv_done[pb]);      // this P buffer has been read, O holds tile j
             }
             if (!ok) atomicExch(&g_prefill_tc_error, 1);
         }
         __syncwarp();
     } else {
-        // ---------------- softmax, correction, epilogue: one query row per thread ----------------
+        // ---------------- softmax, correction, epilogue: two threads per query row ----------------
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                        // which 32 of the tile's 64 keys
         const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = q0 + r;
         const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
-        float m_ref = -INFINITY, l_run = 0.f;
+        const float kLog2e = 1.4426950408889634f;
+        float m_ref = -INFINITY, l_run = 0.f;                    // l_run: this thread's keys only
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int sb = j & 1;
+            const int sb = j & 1, pb = j & 1;
             if (!tc_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
             tc_fence_after_sync();
-            float sc[TK];
+            float sc[32];
             {
-                uint32_t v0[32], v1[32];
-                tc_ld32(t_lane + kColS + sb * TK, v0);
-                tc_ld32(t_lane + kColS + sb * TK + 32, v1);
+                uint32_t v0[32];
+                tc_ld32(t_lane + kColS + sb * TK + 32 * half, v0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(v0[i]); sc[32 + i] = __uint_as_float(v1[i]); }
+                for (int i = 0; i < 32; ++i) sc[i] = __uint_as_float(v0[i]);
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[sb]);            // this S buffer may be overwritten
-            const int k0 = (kt_lo + j) * TK;
-            float m_tile = -INFINITY;
+            if (lane == 0) mbar_arrive(&s_empty[sb]);            // this warp has its part of the S buffer
+            const int k0 = (kt_lo + j) * TK + 32 * half;
+            float m_half = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < TK; ++i) {
+            for (int i = 0; i < 32; ++i) {
                 const int key = k0 + i;
-                float s = softcap_fast(sc[i] * a.scale, a.cap, inv_cap);
+                float s = sc[i] * a.scale;
+                if (a.cap > 0.f) {
+                    float th;
+                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(s * inv_cap));
+                    s = a.cap * th;
+                }
                 const bool vis = key <= qpos && (a.window <= 0 || key > qpos - a.window);
                 s = vis ? s : -INFINITY;
                 sc[i] = s;
-                m_tile = fmaxf(m_tile, s);
+                m_half = fmaxf(m_half, s);
             }
-            // raise the reference maximum only when it is exceeded by a margin
+            // the row's maximum over both halves
+            xchg[half * TQ + r] = m_half;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float m_tile = fmaxf(m_half, xchg[(half ^ 1) * TQ + r]);
+            asm volatile("bar.sync 1, 256;" ::: "memory");       // both have read before the next tile writes
+            // raise the reference maximum only when it is exceeded by a margin (both threads of a row decide alike)
             float factor = 1.f;
             if (m_tile > m_ref + kRescaleSlack || (m_ref == -INFINITY && m_tile > -INFINITY)) {
                 factor = m_ref == -INFINITY ? 0.f : __expf(m_ref - m_tile);
                 m_ref = m_tile;
             }
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            const float m_use2 = (m_ref == -INFINITY ? 0.f : m_ref) * kLog2e;
             float psum = 0.f;
-            uint32_t packed[TK / 2];
+            uint32_t packed[16];
 #pragma unroll
-            for (int i = 0; i < TK; i += 2) {
-                const float p0 = __expf(sc[i] - m_use), p1 = __expf(sc[i + 1] - m_use);
+            for (int i = 0; i < 32; i += 2) {
+                const float p0 = exp2f(fmaf(sc[i], kLog2e, -m_use2)), p1 = exp2f(fmaf(sc[i + 1], kLog2e, -m_use2));
                 psum += p0 + p1;
                 packed[i / 2] = pack_bf16(p0, p1);
             }
             l_run = l_run * factor + psum;
-            // P and O may be touched once the products of the tile before have finished
-            if (j > 0 && !tc_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
-            tc_fence_after_sync();
+            // this P buffer is free once the product of two tiles ago has read it
+            if (j >= 2 && !tc_wait(&pv_done[pb], ((j >> 1) - 1) & 1)) { ok = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O is touched only between products: wait for the one of the tile before
+                if (!tc_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+                tc_fence_after_sync();
 #pragma unroll 1
-                for (int c = 0; c < THD; c += 32) {
+                for (int c = half * (THD / 2); c < (half + 1) * (THD / 2); c += 32) {
                     uint32_t o[32];
                     tc_ld32(t_lane + kColO + c, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -318,27 +339,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // P row r: 8 chunks of 16 bytes, chunk c at position c ^ (r & 7)
+            // P row r, this thread's 32 keys: chunks 4*half .. 4*half+3 of 16 bytes, chunk c at position c ^ (r & 7)
             {
-                unsigned char* prow = p_s + (size_t)r * 128;
+                unsigned char* prow = p_s + (size_t)pb * kPBytes + (size_t)r * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(prow + (((4 * half + c) ^ (r & 7)) << 4)) =
                         make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> visible to the tensor core
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(&p_full[pb]);
         }
-        // ---- epilogue: O / l -> bfloat16 -> global ----
-        if (ok && !tc_wait(pv_done, (n_tiles - 1) & 1)) ok = false;
+        // ---- epilogue: O / l -> bfloat16 -> global; each thread half of its row ----
+        if (ok && !tc_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) ok = false;
         if (ok) {
             tc_fence_after_sync();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");      // every reader of xchg's maxima is done
+            xchg[half * TQ + r] = l_run;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float l_row = l_run + xchg[(half ^ 1) * TQ + r];
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
             bf16* orow = a.out + (size_t)(row0 + qpos) * a.out_stride + (size_t)head * THD;
 #pragma unroll 1
-            for (int c = 0; c < THD; c += 32) {
+            for (int c = half * (THD / 2); c < (half + 1) * (THD / 2); c += 32) {
                 uint32_t o[32];
                 tc_ld32(t_lane + kColO + c, o);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -442,7 +467,7 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
     a.scale = scale; a.cap = cap; a.window = window;
     dim3 grid(n_q_tiles, n_heads);
-    attn_prefill_tc_kernel<<<grid, 192, kTcSmem, stream>>>(mq, mkv, a);
+    attn_prefill_tc_kernel<<<grid, kTcThreads, kTcSmem, stream>>>(mq, mkv, a);
     return check_launch("attn_prefill_tc");
 #else
     HOS_REFUSE("attn_prefill_tc: no tensor-core prompt kernel for head_dim %d (64, 128 and 256 have one)", HOS_HEAD_DIM);
