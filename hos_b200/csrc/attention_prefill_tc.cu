@@ -47,7 +47,7 @@ constexpr int kKVTileBytes = CBLK * kKVBlockBytes;
 constexpr int kPBytes = TQ * 128;                      // 128 rows x 64 keys bf16
 constexpr int kKVStages = 2;
 constexpr int kXchgBytes = 2 * TQ * 4;                 // one float per (half, row)
-constexpr int kTcSmem = kQBytesTc + kKVStages * 2 * kKVTileBytes + 2 * kPBytes + kXchgBytes + 128 + 1008;
+constexpr int kTcSmem = kQBytesTc + kKVStages * 2 * kKVTileBytes + 2 * kPBytes + kXchgBytes + 160 + 976;
 constexpr int kTcThreads = 320;                        // TMA warp, MMA warp, 8 softmax warps
 constexpr int kTmemColsTc = (128 + THD) <= 256 ? 256 : 512;
 constexpr int kColS = 0, kColO = 128;
@@ -147,13 +147,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
     float* xchg = reinterpret_cast<float*>(p_s + 2 * kPBytes);                 // [2 halves][128 rows]
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * kPBytes + kXchgBytes);
     uint64_t* q_full = bars;                 // 1
-    uint64_t* kv_full = bars + 1;            // [2]
-    uint64_t* kv_empty = bars + 3;           // [2]
+    uint64_t* k_full = bars + 1;             // [2] keys of a stage have landed
+    uint64_t* k_empty = bars + 3;            // [2] S of that stage has been computed: its keys may be replaced
     uint64_t* s_full = bars + 5;             // [2]
     uint64_t* s_empty = bars + 7;            // [2]
     uint64_t* p_full = bars + 9;             // [2] one per P buffer
     uint64_t* pv_done = bars + 11;           // [2] one per P buffer
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* v_full = bars + 13;            // [2] values of a stage have landed
+    uint64_t* v_empty = bars + 15;           // [2] P.V of that stage is done: its values may be replaced
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 17);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -179,7 +181,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8);
             mbar_init(&p_full[s], 8); mbar_init(&pv_done[s], 1);
         }
@@ -202,17 +205,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             mbar_expect_tx(q_full, kQBytesTc);
             for (int c = 0; c < CBLK; ++c)
                 tc_tma_2d(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
+            // keys and values travel separately: a stage's keys are free again as soon as its S is
+            // computed, long before its values are, so the next keys are fetched that much earlier
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % kKVStages;
-                if (j >= kKVStages && !tc_wait(&kv_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
                 unsigned char* kd = kv_s + (size_t)s * 2 * kKVTileBytes;
                 unsigned char* vd = kd + kKVTileBytes;
                 const int krow = row0 + (kt_lo + j) * TK;
-                mbar_expect_tx(&kv_full[s], 2 * kKVTileBytes);
-                for (int c = 0; c < CBLK; ++c) {
-                    tc_tma_2d(kd + c * kKVBlockBytes, &map_kv, a.k_col0 + kvh * THD + 64 * c, krow, &kv_full[s]);
-                    tc_tma_2d(vd + c * kKVBlockBytes, &map_kv, a.v_col0 + kvh * THD + 64 * c, krow, &kv_full[s]);
-                }
+                if (j >= kKVStages && !tc_wait(&k_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], kKVTileBytes);
+                for (int c = 0; c < CBLK; ++c)
+                    tc_tma_2d(kd + c * kKVBlockBytes, &map_kv, a.k_col0 + kvh * THD + 64 * c, krow, &k_full[s]);
+                if (j >= kKVStages && !tc_wait(&v_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
+                mbar_expect_tx(&v_full[s], kKVTileBytes);
+                for (int c = 0; c < CBLK; ++c)
+                    tc_tma_2d(vd + c * kKVBlockBytes, &map_kv, a.v_col0 + kvh * THD + 64 * c, krow, &v_full[s]);
             }
             if (!ok) atomicExch(&g_prefill_tc_error, 1);
         }
@@ -226,7 +233,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             tc_fence_after_sync();
             auto issue_s = [&](int j) -> bool {
                 const int s = j % kKVStages, sb = j & 1;
-                if (!tc_wait(&kv_full[s], (j / kKVStages) & 1)) return false;
+                if (!tc_wait(&k_full[s], (j / kKVStages) & 1)) return false;
                 if (j >= 2 && !tc_wait(&s_empty[sb], ((j >> 1) - 1) & 1)) return false;
                 tc_fence_after_sync();
                 const uint32_t k_addr = smem_u32(kv_s + (size_t)s * 2 * kKVTileBytes);
@@ -237,6 +244,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                     tc_mma(tmem_base + kColS + sb * TK, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(&s_full[sb]);
+                tc_commit(&k_empty[s]);       // the keys of this stage have been read
                 return true;
             };
             if (ok) ok = issue_s(0);
@@ -244,8 +252,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }      // the next S runs under this tile's softmax
                 const int pb = j & 1;
                 if (!tc_wait(&p_full[pb], (j >> 1) & 1)) { ok = false; break; }
-                tc_fence_after_sync();
                 const int s = j % kKVStages;
+                if (!tc_wait(&v_full[s], (j / kKVStages) & 1)) { ok = false; break; }
+                tc_fence_after_sync();
                 const uint32_t v_addr = smem_u32(kv_s + (size_t)s * 2 * kKVTileBytes + kKVTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < TK / 16; ++ks) {
@@ -253,7 +262,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                     const uint64_t bd = desc_mnmajor(v_addr + ks * 16 * 128, kKVBlockBytes);
                     tc_mma(tmem_base + kColO, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(&kv_empty[s]);      // K and V of this stage have been read
+                tc_commit(&v_empty[s]);       // the values of this stage have been read
                 tc_commit(&pv_done[pb]);      // this P buffer has been read, O holds tile j
             }
             if (!ok) atomicExch(&g_prefill_tc_error, 1);
