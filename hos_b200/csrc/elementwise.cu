@@ -278,6 +278,115 @@ __global__ void rope_kv_write_kernel(const TSrc* __restrict__ src, int n_parts, 
     }
 }
 
+// The same for bfloat16 rows rotated in place, 16 bytes at a time: a thread takes a chunk of 8
+// elements of a head (and, for the rotate-half pairing, its partner chunk half a rotation
+// away), rotates it, writes it back and, if it belongs to a key, also to the cache; value
+// chunks and unrotated key chunks are copied to the cache.  One pass, one barrier (for the
+// table of sines and cosines); the look-ups that lead to the token's page run beside it.
+// Needs head_dim % 8 == 0 and rotary_dim % 16 == 0 (rotate-half) or % 8 == 0 (interleaved).
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(p[i]); f[2 * i + 1] = __high2float(p[i]); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+}
+
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
+                         const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                         const int* __restrict__ seq_slot, const int* __restrict__ seq_len_after,
+                         const float* __restrict__ inv_freq, int rotary_dim, int style,
+                         PagedKV cache, int write_cache) {
+    extern __shared__ float2 sincos_tab[];          // [rotary_dim / 2]
+    const int n = blockIdx.x;
+    const int seq = token_seq[n];
+    if (seq < 0) return;
+    const int pos = token_pos[n];
+    const int hd = cache.head_dim, nkv = cache.n_kv_heads;
+    const int half = rotary_dim >> 1;
+    int page = -1;
+    if (write_cache && !(cache.ring_pages > 0 && pos + cache.ring_pages * kPageTokens < seq_len_after[seq]))
+        page = cache.page_table[(size_t)seq_slot[seq] * cache.table_stride + kv_table_entry(cache, pos / kPageTokens)];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sincos_tab[i] = make_float2(s, c);
+    }
+    __syncthreads();
+    bf16* row = qkv + (size_t)n * row_stride;
+    bf16* kp = (bf16*)cache.k_pages;
+    bf16* vp = (bf16*)cache.v_pages;
+    const int r = pos % kPageTokens;
+    const int chunks = hd / 8;                                  // 16-byte chunks per head
+    const int rot_chunks = rotary_dim / 8;
+    const int rot_items = style == 0 ? rot_chunks / 2 : rot_chunks;   // rotate-half: a chunk and its partner
+    const int tail_chunks = chunks - rot_chunks;
+    const int per_qk_head = rot_items + tail_chunks;
+    const int n_qk = n_heads + nkv;
+    const int total = n_qk * per_qk_head + nkv * chunks;
+    for (int item = threadIdx.x; item < total; item += blockDim.x) {
+        if (item < n_qk * per_qk_head) {
+            const int head = item / per_qk_head, j = item % per_qk_head;
+            bf16* hp = row + (size_t)head * hd;
+            const bool is_k = head >= n_heads;
+            const size_t tile = is_k && page >= 0 ? kv_tile_offset(cache, page, head - n_heads) : 0;
+            if (j >= rot_items) {                                // beyond the rotated dimensions: keys go to the cache as they are
+                if (is_k && page >= 0) {
+                    const int d0 = rotary_dim + (j - rot_items) * 8;
+                    *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, d0, hd)) = *reinterpret_cast<const uint4*>(hp + d0);
+                }
+                continue;
+            }
+            float fa[8], fb[8];
+            if (style == 0) {
+                const int da = j * 8, db = half + j * 8;
+                const uint4 ua = *reinterpret_cast<const uint4*>(hp + da), ub = *reinterpret_cast<const uint4*>(hp + db);
+                unpack8(ua, fa); unpack8(ub, fb);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float2 sc = sincos_tab[j * 8 + e];
+                    const float x0 = fa[e], x1 = fb[e];
+                    fa[e] = x0 * sc.y - x1 * sc.x;
+                    fb[e] = x0 * sc.x + x1 * sc.y;
+                }
+                const uint4 oa = pack8(fa), ob = pack8(fb);
+                *reinterpret_cast<uint4*>(hp + da) = oa;
+                *reinterpret_cast<uint4*>(hp + db) = ob;
+                if (is_k && page >= 0) {
+                    *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, da, hd)) = oa;
+                    *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, db, hd)) = ob;
+                }
+            } else {
+                const int d0 = j * 8;
+                const uint4 ua = *reinterpret_cast<const uint4*>(hp + d0);
+                unpack8(ua, fa);
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const float2 sc = sincos_tab[(d0 + e) >> 1];
+                    const float x0 = fa[e], x1 = fa[e + 1];
+                    fa[e] = x0 * sc.y - x1 * sc.x;
+                    fa[e + 1] = x0 * sc.x + x1 * sc.y;
+                }
+                const uint4 oa = pack8(fa);
+                *reinterpret_cast<uint4*>(hp + d0) = oa;
+                if (is_k && page >= 0) *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, d0, hd)) = oa;
+            }
+        } else if (page >= 0) {
+            const int v = item - n_qk * per_qk_head;
+            const int kvh = v / chunks, d0 = (v % chunks) * 8;
+            const bf16* src = row + (size_t)(n_heads + nkv + kvh) * hd + d0;
+            *reinterpret_cast<uint4*>(vp + kv_tile_offset(cache, page, kvh) + kv_elem_offset(r, d0, hd)) =
+                *reinterpret_cast<const uint4*>(src);
+        }
+    }
+}
+
 // ---- gated activation ---------------------------------------------------------------
 // out[n, f] = act(gu[n, f]) * gu[n, F + f]; act 0 = tanh-form GELU, 1 = SiLU.
 template <typename T>
@@ -438,6 +547,14 @@ extern "C" int hos_rope_kv_write(const void* src, int src_dtype, int n_parts, vo
 #define HOS_ROPE(TS, T)                                                                              \
     rope_kv_write_kernel<TS, T><<<N, 256, smem, stream>>>((const TS*)src, n_parts, ps, (T*)qkv, row_stride, \
         n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache)
+    const bool vec_ok = dtype == kBF16 && src == qkv && (head_dim % 8) == 0 && (row_stride % 8) == 0 &&
+                        ((uintptr_t)qkv % 16) == 0 && (rotary_dim % (style == 0 ? 16 : 8)) == 0 &&
+                        (!write_cache || (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0);
+    if (vec_ok) {
+        rope_kv_write_vec_kernel<<<N, 256, smem, stream>>>((bf16*)qkv, row_stride, n_heads, token_pos, token_seq,
+            seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
+        return check_launch("rope_kv_write");
+    }
     if (dtype == kF32) HOS_ROPE(float, float);
     else if (dtype == kBF16 && src_dtype == kBF16) HOS_ROPE(bf16, bf16);
     else if (dtype == kBF16 && src_dtype == kF32) HOS_ROPE(float, bf16);

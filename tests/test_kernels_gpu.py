@@ -214,10 +214,14 @@ def test_attention_plain_over_the_cache_and_over_packed_rows(cfg, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("style", ["rotate_half", "interleaved"])
-def test_rope_and_cache_write(dtype, style):
+@pytest.mark.parametrize("rot", [24, 16, 32])
+def test_rope_and_cache_write(dtype, style, rot):
+    """Rotation in place and the store into the paged cache, for both pairings, with all and
+    with a part of the head rotated (24 of 32 is no multiple of 16: the one-element-at-a-time
+    kernel; 16 and 32: the 16-bytes-at-a-time kernel in bfloat16)."""
     from hos_b200 import ops
     dt = DT[dtype]
-    nh, nkv, hd, rot, theta = 3, 2, 32, 24, 5000.0          # partial rotation: 24 of 32 dimensions
+    nh, nkv, hd, theta = 3, 2, 32, 5000.0
     N = 70
     rows0 = torch.randn(N, (nh + 2 * nkv) * hd, device=DEV).to(dt)
     rows = rows0.clone()
