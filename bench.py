@@ -35,6 +35,12 @@ GEMMA2_2B = dict(
     vocab_size=256000, rope_theta=10000.0, sliding_window=4096, max_position_embeddings=8192,
     query_pre_attn_scalar=256, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
     rms_norm_eps=1e-6, tie_word_embeddings=True)
+# Gemma-2 9B and 27B layer sizes (BASELINE.json configs[3] and [4]); not part of the default line
+GEMMA2_9B = dict(GEMMA2_2B, num_hidden_layers=42, hidden_size=3584, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=256, intermediate_size=14336, query_pre_attn_scalar=256)
+GEMMA2_27B = dict(GEMMA2_2B, num_hidden_layers=46, hidden_size=4608, num_attention_heads=32,
+                  num_key_value_heads=16, head_dim=128, intermediate_size=36864, query_pre_attn_scalar=144)
+MODELS = {"2b": GEMMA2_2B, "9b": GEMMA2_9B, "27b": GEMMA2_27B}
 FULL_LAYERS = 26
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -214,8 +220,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=8192)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has, for a quick run")
+    ap.add_argument("--model", default="2b", choices=sorted(MODELS), help="layer sizes (default: Gemma-2 2B)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-prefill", action="store_true")
@@ -238,7 +245,10 @@ def main() -> int:
     from hos_b200 import models  # noqa: F401
     from hos_b200.registry import config_from_dict
 
-    raw = dict(GEMMA2_2B, num_hidden_layers=args.layers)
+    full_layers = MODELS[args.model]["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    raw = dict(MODELS[args.model], num_hidden_layers=args.layers)
     cfg = config_from_dict(raw)
     pk, pk_src = peaks()
     rng = random.Random(0)
@@ -263,8 +273,8 @@ def main() -> int:
         "warmup": args.warmup, "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "gemma-2-2b sizes, random weights", "global_batch": args.batch, "seq_len": args.ctx,
-            "parallelism": "single_gpu", "layers": args.layers, "layers_full": FULL_LAYERS,
+            "model": f"gemma-2-{args.model} sizes, random weights", "global_batch": args.batch, "seq_len": args.ctx,
+            "parallelism": "single_gpu", "layers": args.layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "sliding_window": cfg.sliding_window, "decode_ends_at": args.ctx,

@@ -120,6 +120,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_enter();      // the kernels before this one (which wrote q and the newest keys) are complete from here on
 
     if (warp == 4) {
         // ---------------- producer: one thread feeds the ring, item after item ----------------
@@ -453,7 +454,7 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_splits = n_splits;
     a.scale = scale; a.cap = cap; a.window = window;
     const int grid = items < sm_count() ? (int)items : sm_count();
-    attn_decode_kernel<<<grid, kDecodeThreads, smem, stream>>>(a);
+    launch_pdl(attn_decode_kernel, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
     return check_launch("attn_decode");
 }
 

@@ -53,6 +53,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                     const bf16* __restrict__ v, int kv_stride, bf16* __restrict__ out, int out_stride,
                     const int* __restrict__ cu_seqlens, int n_seqs, int n_heads, int n_kv_heads,
                     float scale, float cap, int window) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv_s = q_s + BQ * PHD;                               // stage s: K at 2s, V at 2s+1 (tiles of BKV*PHD)
@@ -223,7 +224,7 @@ extern "C" int hos_attn_prefill(const void* q, int q_stride, const void* k, cons
         attr_set = true;
     }
     dim3 grid(n_q_tiles, n_heads);
-    attn_prefill_kernel<<<grid, 128, kPrefillSmem, stream>>>(
+    launch_pdl(attn_prefill_kernel, dim3(grid), dim3(128), kPrefillSmem, stream, 
         (const bf16*)q, q_stride, (const bf16*)k, (const bf16*)v, kv_stride, (bf16*)out, out_stride, cu_seqlens,
         n_seqs, n_heads, n_kv_heads, scale, cap, window);
     return check_launch("attn_prefill");

@@ -139,6 +139,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
                        const __grid_constant__ CUtensorMap map_kv,     // boxes of [64 rows x 64 columns]
                        PrefillTcArgs a) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
@@ -476,7 +477,7 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
     a.scale = scale; a.cap = cap; a.window = window;
     dim3 grid(n_q_tiles, n_heads);
-    attn_prefill_tc_kernel<<<grid, kTcThreads, kTcSmem, stream>>>(mq, mkv, a);
+    launch_pdl(attn_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, stream, mq, mkv, a);
     return check_launch("attn_prefill_tc");
 #else
     HOS_REFUSE("attn_prefill_tc: no tensor-core prompt kernel for head_dim %d (64, 128 and 256 have one)", HOS_HEAD_DIM);

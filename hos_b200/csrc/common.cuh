@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace hos {
 
@@ -35,6 +36,43 @@ inline int check_launch(const char* what) {
         return -2;
     }
     return 0;
+}
+
+// ---- programmatic dependent launch -----------------------------------------------------
+// Kernels that follow one another on a stream are launched so that the next one may be set
+// up (its CTAs placed, its prologue run) while the one before is still finishing.  Every such
+// kernel calls pdl_wait() before it reads or writes anything in global memory: that returns
+// once the kernels before it are complete and their writes visible.  pdl_launch_dependents()
+// lets the kernel after it be set up in turn.  Both are no-ops for a kernel launched the
+// ordinary way, which is the default: measured on Gemma-2 2B sizes the attribute gains 3% on a
+// 2,048-token prompt and loses 5% on a decode step at batch 8 (the step's kernels are short and
+// the graph replays them back to back anyway).  HOS_PDL=1 in the environment switches it on.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("HOS_PDL");
+        on = (e && e[0] && e[0] != '0') ? 1 : 0;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);      // the caller reads the error with check_launch()
 }
 
 // ---- conversions -------------------------------------------------------------------

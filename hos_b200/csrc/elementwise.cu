@@ -13,6 +13,7 @@ namespace hos {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float scale, float* __restrict__ out, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     const int n = blockIdx.x;
     const int tok = tokens[n];
     float* o = out + (size_t)n * D;
@@ -30,6 +31,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 template <typename TIn, typename TOut>
 __global__ void rmsnorm_kernel(const TIn* __restrict__ x, const float* __restrict__ w, float eps,
                                float add_one, TOut* __restrict__ out, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * D;
@@ -53,6 +55,7 @@ __global__ void norm_add_norm_kernel(const TY* __restrict__ y, const float* __re
                                      float eps_post, float add_one_post, float* __restrict__ x,
                                      const float* __restrict__ w_next, float eps_next,
                                      float add_one_next, TH* __restrict__ h, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * D;
@@ -102,6 +105,7 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename TIn, typename TOut, int CH>
 __global__ void rmsnorm_vec_kernel(const TIn* __restrict__ x, const float* __restrict__ w, float eps,
                                    float add_one, TOut* __restrict__ out, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * D;
     float4 xv[CH], wv[CH];
@@ -131,6 +135,7 @@ __global__ void norm_add_norm_vec_kernel(const TY* __restrict__ y, int n_parts, 
                                          const float* __restrict__ w_post, float eps_post, float add_one_post,
                                          float* __restrict__ x, const float* __restrict__ w_next, float eps_next,
                                          float add_one_next, TH* __restrict__ h, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * D;
     float4 yv[CH], xv[CH], wp[CH], wn[CH];
@@ -194,6 +199,7 @@ static void vec_shape(int D, int* threads, int* chunks) {
 // x += y (plain residual sum in 32-bit, for arrangements without a post norm).
 template <typename TY>
 __global__ void residual_add_kernel(const TY* __restrict__ y, float* __restrict__ x, size_t n) {
+    pdl_enter();      // the kernels before this one are complete from here on
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_float(y[i]);
 }
@@ -216,6 +222,7 @@ __global__ void rope_kv_write_kernel(const TSrc* __restrict__ src, int n_parts, 
                                      const int* __restrict__ seq_len_after,
                                      const float* __restrict__ inv_freq, int rotary_dim, int style,
                                      PagedKV cache, int write_cache) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ float2 sincos_tab[];          // [rotary_dim / 2]
     const int n = blockIdx.x;
     const int seq = token_seq[n];
@@ -303,6 +310,7 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_len_after,
                          const float* __restrict__ inv_freq, int rotary_dim, int style,
                          PagedKV cache, int write_cache) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ float2 sincos_tab[];          // [rotary_dim / 2]
     const int n = blockIdx.x;
     const int seq = token_seq[n];
@@ -391,6 +399,7 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
 // out[n, f] = act(gu[n, f]) * gu[n, F + f]; act 0 = tanh-form GELU, 1 = SiLU.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, int act) {
+    pdl_enter();      // the kernels before this one are complete from here on
     const size_t n = blockIdx.x;
     const int f = blockIdx.y * blockDim.x + threadIdx.x;
     if (f >= F) return;
@@ -403,6 +412,7 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 // ---- row gather ----------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
                                    float* __restrict__ out, int D) {
+    pdl_enter();      // the kernels before this one are complete from here on
     const int i = blockIdx.x;
     const float* src = x + (size_t)idx[i] * D;
     float* dst = out + (size_t)i * D;
@@ -414,6 +424,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ token_pos,
                                       int* __restrict__ seq_len_after, const int* __restrict__ token_seq,
                                       const int* __restrict__ sampled, int B) {
+    pdl_enter();      // the kernels before this one are complete from here on
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= B || token_seq[i] < 0) return;
     tokens[i] = sampled[i];
@@ -439,9 +450,9 @@ extern "C" int hos_embed(const int* tokens, const void* table, int table_dtype, 
                          float* out, int N, int D, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (table_dtype == kBF16)
-        embed_kernel<bf16><<<N, 256, 0, stream>>>(tokens, (const bf16*)table, scale, out, D);
+        launch_pdl(embed_kernel<bf16>, dim3(N), dim3(256), 0, stream, tokens, (const bf16*)table, scale, out, D);
     else if (table_dtype == kF32)
-        embed_kernel<float><<<N, 256, 0, stream>>>(tokens, (const float*)table, scale, out, D);
+        launch_pdl(embed_kernel<float>, dim3(N), dim3(256), 0, stream, tokens, (const float*)table, scale, out, D);
     else
         HOS_REFUSE("embed: unknown table dtype %d", table_dtype);
     return check_launch("embed");
@@ -455,7 +466,7 @@ extern "C" int hos_rmsnorm(const void* x, int x_dtype, const float* w, float eps
     int threads = 0, chunks = 0;
     vec_shape(D, &threads, &chunks);
     if (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) % 16) chunks = 0;
-#define HOS_VEC(TI, TO, CH) rmsnorm_vec_kernel<TI, TO, CH><<<N, threads, 0, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D)
+#define HOS_VEC(TI, TO, CH) launch_pdl(rmsnorm_vec_kernel<TI, TO, CH>, dim3(N), dim3(threads), 0, stream, (const TI*)x, w, eps, a1, (TO*)out, D)
 #define HOS_LAUNCH_NORM(TI, TO)                                                              \
     do {                                                                                     \
         if (chunks == 1) HOS_VEC(TI, TO, 1);                                                 \
@@ -464,7 +475,7 @@ extern "C" int hos_rmsnorm(const void* x, int x_dtype, const float* w, float eps
         else {                                                                               \
             if (row_smem_ok((const void*)rmsnorm_kernel<TI, TO>, D))                         \
                 HOS_REFUSE("rmsnorm: width %d does not fit a block's shared memory", D);     \
-            rmsnorm_kernel<TI, TO><<<N, 256, smem, stream>>>((const TI*)x, w, eps, a1, (TO*)out, D); \
+            launch_pdl(rmsnorm_kernel<TI, TO>, dim3(N), dim3(256), smem, stream, (const TI*)x, w, eps, a1, (TO*)out, D); \
         }                                                                                    \
     } while (0)
     if (x_dtype == kF32 && out_dtype == kF32) HOS_LAUNCH_NORM(float, float);
@@ -492,7 +503,7 @@ extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const 
     vec_shape(D, &threads, &chunks);
     if (((uintptr_t)y | (uintptr_t)x | (uintptr_t)h | (uintptr_t)w_post | (uintptr_t)w_next) % 16) chunks = 0;
     if (chunks == 0 && n_parts > 1) HOS_REFUSE("norm_add_norm: partial sums need a width that is a multiple of 4 (%d)", D);
-#define HOS_VEC(TY, TH, CH) norm_add_norm_vec_kernel<TY, TH, CH><<<N, threads, 0, stream>>>(                 \
+#define HOS_VEC(TY, TH, CH) launch_pdl(norm_add_norm_vec_kernel<TY, TH, CH>, dim3(N), dim3(threads), 0, stream,                  \
         (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D)
 #define HOS_LAUNCH(TY, TH)                                                                                  \
     do {                                                                                                    \
@@ -502,7 +513,7 @@ extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const 
         else {                                                                                              \
             if (row_smem_ok((const void*)norm_add_norm_kernel<TY, TH>, D))                                  \
                 HOS_REFUSE("norm_add_norm: width %d does not fit a block's shared memory", D);              \
-            norm_add_norm_kernel<TY, TH><<<N, 256, smem, stream>>>(                                         \
+            launch_pdl(norm_add_norm_kernel<TY, TH>, dim3(N), dim3(256), smem, stream,                                          \
                 (const TY*)y, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D);                    \
         }                                                                                                   \
     } while (0)
@@ -520,8 +531,8 @@ extern "C" int hos_residual_add(const void* y, int y_dtype, float* x, long long 
                                 cudaStream_t stream) {
     if (n <= 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (y_dtype == kF32) residual_add_kernel<float><<<blocks, 256, 0, stream>>>((const float*)y, x, (size_t)n);
-    else if (y_dtype == kBF16) residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)y, x, (size_t)n);
+    if (y_dtype == kF32) launch_pdl(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)y, x, (size_t)n);
+    else if (y_dtype == kBF16) launch_pdl(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)y, x, (size_t)n);
     else HOS_REFUSE("residual_add: unknown dtype %d", y_dtype);
     return check_launch("residual_add");
 }
@@ -545,13 +556,13 @@ extern "C" int hos_rope_kv_write(const void* src, int src_dtype, int n_parts, vo
     const size_t smem = (size_t)(rotary_dim / 2) * sizeof(float2);
     const size_t ps = (size_t)N * row_stride;
 #define HOS_ROPE(TS, T)                                                                              \
-    rope_kv_write_kernel<TS, T><<<N, 256, smem, stream>>>((const TS*)src, n_parts, ps, (T*)qkv, row_stride, \
+    launch_pdl(rope_kv_write_kernel<TS, T>, dim3(N), dim3(256), smem, stream, (const TS*)src, n_parts, ps, (T*)qkv, row_stride, \
         n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache)
     const bool vec_ok = dtype == kBF16 && src == qkv && (head_dim % 8) == 0 && (row_stride % 8) == 0 &&
                         ((uintptr_t)qkv % 16) == 0 && (rotary_dim % (style == 0 ? 16 : 8)) == 0 &&
                         (!write_cache || (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0);
     if (vec_ok) {
-        rope_kv_write_vec_kernel<<<N, 256, smem, stream>>>((bf16*)qkv, row_stride, n_heads, token_pos, token_seq,
+        launch_pdl(rope_kv_write_vec_kernel, dim3(N), dim3(256), smem, stream, (bf16*)qkv, row_stride, n_heads, token_pos, token_seq,
             seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
         return check_launch("rope_kv_write");
     }
@@ -568,8 +579,8 @@ extern "C" int hos_gated_act(const void* gu, void* out, int dtype, int N, int F,
     if (N <= 0) return 0;
     if (act != 0 && act != 1) HOS_REFUSE("gated_act: unknown activation %d", act);
     dim3 grid(N, (F + 255) / 256);
-    if (dtype == kF32) gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, F, act);
-    else if (dtype == kBF16) gated_act_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, act);
+    if (dtype == kF32) launch_pdl(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gu, (float*)out, F, act);
+    else if (dtype == kBF16) launch_pdl(gated_act_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, F, act);
     else HOS_REFUSE("gated_act: unknown dtype %d", dtype);
     return check_launch("gated_act");
 }
@@ -577,14 +588,14 @@ extern "C" int hos_gated_act(const void* gu, void* out, int dtype, int N, int F,
 extern "C" int hos_gather_rows(const float* x, const int* idx, float* out, int n, int D,
                                cudaStream_t stream) {
     if (n <= 0) return 0;
-    gather_rows_kernel<<<n, 256, 0, stream>>>(x, idx, out, D);
+    launch_pdl(gather_rows_kernel, dim3(n), dim3(256), 0, stream, x, idx, out, D);
     return check_launch("gather_rows");
 }
 
 extern "C" int hos_decode_advance(int* tokens, int* token_pos, int* seq_len_after, const int* token_seq,
                                   const int* sampled, int B, cudaStream_t stream) {
     if (B <= 0) return 0;
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, token_pos, seq_len_after,
+    launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, token_pos, seq_len_after,
                                                                token_seq, sampled, B);
     return check_launch("decode_advance");
 }

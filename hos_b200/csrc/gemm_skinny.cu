@@ -38,6 +38,7 @@ template <int MT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
+    pdl_enter();      // the kernels before this one are complete from here on
     __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -137,7 +138,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     if (epilogue == 2 && out_dtype != kBF16) HOS_REFUSE("gemm_skinny: the gated epilogue writes bfloat16");
     const unsigned grid = (unsigned)((N + 15) / 16);
 #define HOS_SK(MT, G, T)                                                                                     \
-    gemm_skinny_kernel<MT, G, T><<<grid, kSkinnyThreads, 0, stream>>>((const bf16*)A, (const bf16*)W, (T*)out, \
+    launch_pdl(gemm_skinny_kernel<MT, G, T>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
     if (epilogue == 2) {
         if (M <= 8) HOS_SK(1, true, bf16); else HOS_SK(2, true, bf16);

@@ -187,6 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_smem;
+    pdl_enter();      // barriers and tensor memory were set up beside the tail of the kernel before; its results are read from here on
 
     auto tile_coords = [&](int tile, int& mt, int& nt, int& ks) {
         ks = tile % p.k_splits;
@@ -384,6 +385,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int M, int N, int ldo,
                                      int splits) {
+    pdl_enter();      // the kernels before this one are complete from here on
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)M * N) return;
     float s = 0.f;
@@ -445,7 +447,7 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
         attr_set = true;
     }
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
-    kernel<<<grid, kGemmThreads, Cfg::kSmem, stream>>>(mm, mn, p);
+    launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), Cfg::kSmem, stream, mm, mn, p);
     return check_launch("gemm_tc");
 }
 
@@ -535,9 +537,9 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
         if (!reduce_now) return 0;
         const size_t n = (size_t)M * N;
         if (out_dtype == kBF16)
-            splitk_reduce_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(workspace, (bf16*)out, M, N, ldo, k_splits);
+            launch_pdl(splitk_reduce_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, workspace, (bf16*)out, M, N, ldo, k_splits);
         else
-            splitk_reduce_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(workspace, (float*)out, M, N, ldo, k_splits);
+            launch_pdl(splitk_reduce_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, workspace, (float*)out, M, N, ldo, k_splits);
         return check_launch("gemm_tc split-K reduce");
     }
     if (epilogue == kGEpiSoftcap) {

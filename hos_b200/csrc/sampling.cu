@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(kThreads)
 sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict__ uniforms,
               const int* __restrict__ recent, int recent_stride, const int* __restrict__ recent_len,
               float temp, int top_k, float top_p, float rep_penalty, int* __restrict__ out) {
+    pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ float smem[];
     float* hist = smem;                       // kBins * kThreads
     float* red = hist + kBins * kThreads;     // kBins
@@ -268,6 +269,7 @@ __device__ __forceinline__ void argmax_merge(float& best, int& best_i, float ov,
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int chunk, float* __restrict__ partial_val,
               int* __restrict__ partial_idx, int* __restrict__ tickets, int* __restrict__ out) {
+    pdl_enter();      // the kernels before this one are complete from here on
     __shared__ float sv[kArgmaxThreads / 32];
     __shared__ int si[kArgmaxThreads / 32];
     __shared__ int is_last;
@@ -334,7 +336,7 @@ extern "C" int hos_argmax(const float* logits, int ld, int B, int V, int* out, f
     const int chunks = hos_argmax_chunks(V);
     const int chunk = (V + chunks - 1) / chunks;
     dim3 grid(chunks, B);
-    argmax_kernel<<<grid, kArgmaxThreads, 0, stream>>>(logits, ld, V, chunk, workspace,
+    launch_pdl(argmax_kernel, dim3(grid), dim3(kArgmaxThreads), 0, stream, logits, ld, V, chunk, workspace,
                                                       reinterpret_cast<int*>(workspace + (size_t)B * chunks), tickets, out);
     return check_launch("argmax");
 }
@@ -354,7 +356,7 @@ extern "C" int hos_sample(float* logits, int ld, int B, int V, const float* unif
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    sample_kernel<<<B, kThreads, smem, stream>>>(logits, ld, V, uniforms, recent, recent_stride,
+    launch_pdl(sample_kernel, dim3(B), dim3(kThreads), smem, stream, logits, ld, V, uniforms, recent, recent_stride,
                                                  recent_len, temp, top_k, top_p, rep_penalty, out);
     return check_launch("sample");
 }
