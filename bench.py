@@ -28,14 +28,14 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Gemma-2 2B layer sizes (BASELINE.json configs[2])
+# Gemma-2 2B layer sizes
 GEMMA2_2B = dict(
     architectures=["Gemma2ForCausalLM"], model_type="gemma2", num_hidden_layers=26, hidden_size=2304,
     num_attention_heads=8, num_key_value_heads=4, head_dim=256, intermediate_size=9216,
     vocab_size=256000, rope_theta=10000.0, sliding_window=4096, max_position_embeddings=8192,
     query_pre_attn_scalar=256, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
     rms_norm_eps=1e-6, tie_word_embeddings=True)
-# Gemma-2 9B and 27B layer sizes (BASELINE.json configs[3] and [4]); not part of the default line
+# Gemma-2 9B and 27B layer sizes; not part of the default line
 GEMMA2_9B = dict(GEMMA2_2B, num_hidden_layers=42, hidden_size=3584, num_attention_heads=16,
                  num_key_value_heads=8, head_dim=256, intermediate_size=14336, query_pre_attn_scalar=256)
 GEMMA2_27B = dict(GEMMA2_2B, num_hidden_layers=46, hidden_size=4608, num_attention_heads=32,

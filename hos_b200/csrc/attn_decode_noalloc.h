@@ -7,7 +7,7 @@
 // Some callers cannot do that: a serving loop that has handed all device memory to its own
 // pool (an allocation may then fail, and cudaMalloc / cudaFree synchronise the whole device,
 // which such a loop cannot afford in the middle of a step), or a plugin that runs inside
-// another framework's memory budget and was given input and output buffers and nothing else.
+// another framework's memory allowance and was given input and output buffers and nothing else.
 // For them the workspace lives inside the library: a file-scope `static __device__` array of
 // HOS_NOALLOC_SCRATCH_BYTES (8 MiB) plus 16 KiB of counters, which every GPU that loads the
 // library holds until the process ends.

@@ -1,7 +1,7 @@
 """The entry point that allocates nothing, `hos_attn_decode_noalloc` (csrc/attn_decode_noalloc.h).
 
 It is for embedders that may not allocate device memory while a step runs: a serving loop
-whose memory all belongs to its own pool, or a plugin inside another framework's budget.
+whose memory all belongs to its own pool, or a plugin inside another framework's memory allowance.
 The test calls it through its exported C symbol, as such a caller would, with buffers the
 caller owns, twice in a row (the second call finds the first call's partial results in the
 library's built-in scratch), and checks each result against the ordinary entry point, which
