@@ -38,7 +38,7 @@ class CacheManager:
         self.device = torch.device(device)
         self.n_pages = (max_tokens + PAGE - 1) // PAGE
         self.max_seq_len = min(max_seq_len, self.n_pages * PAGE)
-        self.n_slots = max(1, min(self.n_pages, max_slots or 1024))
+        self.n_slots = max(1, min(self.n_pages, max_slots or 4096))
         self.slots = IdPool(self.n_slots, "slot")
         self.lengths: Dict[int, int] = {}
         # group entries by need

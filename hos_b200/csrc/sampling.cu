@@ -21,6 +21,8 @@ namespace hos {
 constexpr int kThreads = 512;
 constexpr int kDigitBits = 5;
 constexpr int kBins = 1 << kDigitBits;
+constexpr int kScanUnroll = 8;
+constexpr int kSmallSet = 1024;       // kept sets up to this size are sorted in shared memory, as the reference sorts
 
 __device__ __forceinline__ uint32_t order_key(float v) {
     uint32_t u = __float_as_uint(v);
@@ -59,11 +61,19 @@ __device__ SelectResult radix_select(int V, int nbits, float target, bool strict
         const int width = min(kDigitBits, nbits - pass * kDigitBits);
         const uint32_t dmask = (1u << width) - 1u;
         for (int b = 0; b < kBins; ++b) hist[b * kThreads + tid] = 0.f;
-        for (int i = tid; i < V; i += kThreads) {
-            if (!filter(i)) continue;
-            const uint32_t key = keyfn(i);
-            if ((key & prefix_mask) != prefix) continue;
-            hist[((key >> shift) & dmask) * kThreads + tid] += wfn(i);
+        for (int i0 = tid; i0 < V; i0 += kThreads * kScanUnroll) {        // several loads in flight per thread
+            uint32_t key[kScanUnroll];
+            bool take[kScanUnroll];
+#pragma unroll
+            for (int u = 0; u < kScanUnroll; ++u) {
+                const int i = i0 + u * kThreads;
+                take[u] = i < V && filter(i);
+                key[u] = take[u] ? keyfn(i) : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < kScanUnroll; ++u)
+                if (take[u] && (key[u] & prefix_mask) == prefix)       // the weight only of what is still in the running
+                    hist[((key[u] >> shift) & dmask) * kThreads + tid] += wfn(i0 + u * kThreads);
         }
         __syncthreads();
         // reduce each bin over the threads: 16 threads per bin, 32 columns each
@@ -117,6 +127,42 @@ __device__ int nth_equal_id(int V, uint32_t x, const Kept& kept, int j, int id_b
     return (int)((~r.x) & idmask);
 }
 
+// One scan: how many kept elements have key x, and the lowest and highest id among them.  With
+// these the j-th of them is known at once when it is the first or the last (the common cases: a
+// key that occurs once, or all of the equals wanted); only otherwise is a selection on the id run.
+struct EqualInfo { int n, min_id, max_id; };
+template <typename KeyFn>
+__device__ EqualInfo equal_scan(int V, uint32_t x, const Kept& kept, KeyFn keyfn, int* sh3) {
+    int n = 0, lo = 0x7fffffff, hi = -1;
+    for (int i0 = threadIdx.x; i0 < V; i0 += kThreads * kScanUnroll) {
+        uint32_t key[kScanUnroll];
+#pragma unroll
+        for (int u = 0; u < kScanUnroll; ++u) key[u] = (i0 + u * kThreads) < V ? keyfn(i0 + u * kThreads) : 0u;
+#pragma unroll
+        for (int u = 0; u < kScanUnroll; ++u) {
+            const int i = i0 + u * kThreads;
+            if (i < V && key[u] == x && in_kept(kept, x, i)) { ++n; lo = min(lo, i); hi = max(hi, i); }
+        }
+    }
+    if (threadIdx.x == 0) { sh3[0] = 0; sh3[1] = 0x7fffffff; sh3[2] = -1; }
+    __syncthreads();
+    if (n) { atomicAdd(&sh3[0], n); atomicMin(&sh3[1], lo); atomicMax(&sh3[2], hi); }     // integers: order does not matter
+    __syncthreads();
+    EqualInfo e{sh3[0], sh3[1], sh3[2]};
+    __syncthreads();
+    return e;
+}
+template <typename KeyFn>
+__device__ int jth_equal(int V, uint32_t x, const Kept& kept, int j, const EqualInfo& e, int id_bits, KeyFn keyfn,
+                         float* hist, float* red) {
+    if (j <= 1) return e.min_id;
+    if (j >= e.n) return e.max_id;
+    return nth_equal_id(V, x, kept, j, id_bits, keyfn, hist, red);
+}
+__device__ __forceinline__ float value_of_key(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
 // One block per row.  logits rows are modified in place for the penalty and restored.
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict__ uniforms,
@@ -131,6 +177,7 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
     __shared__ int saved_id[256];
     __shared__ int n_saved;
     __shared__ int best_id_sh;
+    __shared__ int eq_sh[3];
     const int row = blockIdx.x, tid = threadIdx.x;
     float* l = logits + (size_t)row * ld;
 
@@ -184,11 +231,18 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
         int id_bits = 1;
         while ((1 << id_bits) < V) ++id_bits;
         float z = 0.f;
-        for (int i = tid; i < V; i += kThreads) z += prob(i);
+        for (int i0 = tid; i0 < V; i0 += kThreads * kScanUnroll) {
+            float v[kScanUnroll];
+#pragma unroll
+            for (int u = 0; u < kScanUnroll; ++u) v[u] = (i0 + u * kThreads) < V ? l[i0 + u * kThreads] : -INFINITY;
+#pragma unroll
+            for (int u = 0; u < kScanUnroll; ++u) z += expf((v[u] - maxv) / temp);      // exp(-inf) = 0 beyond the end
+        }
         z = block_sum(z, scratch);
 
         Kept kept{0u, V};      // everything
         float kept_mass = z;
+        bool small_done = false;
         auto all = [&](int) { return true; };
         auto kept_filter = [&](int i) { return in_kept(kept, keyfn(i), i); };
         // ---- top-k ----
@@ -198,28 +252,96 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
             // r.found always holds here: top_k < V elements exist
             const int need = top_k - (int)r.above;          // how many of the equals stay
             Kept whole{r.x, V};
-            const int last = nth_equal_id(V, r.x, whole, need, id_bits, keyfn, hist, red);
+            const EqualInfo eq = equal_scan(V, r.x, whole, keyfn, eq_sh);
+            const int last = jth_equal(V, r.x, whole, need, eq, id_bits, keyfn, hist, red);
             kept = Kept{r.x, last};
-            float m = 0.f;
-            for (int i = tid; i < V; i += kThreads)
-                if (kept_filter(i)) m += prob(i);
-            kept_mass = block_sum(m, scratch);
+            if (top_k <= kSmallSet) {
+                // The kept tokens fit shared memory: gather them, sort them (probability falling, id
+                // rising among equals) and let one thread do what the reference does on its sorted list.
+                __shared__ unsigned long long cand[kSmallSet];
+                __shared__ int n_cand;
+                if (tid == 0) n_cand = 0;
+                __syncthreads();
+                for (int i0 = tid; i0 < V; i0 += kThreads * kScanUnroll) {
+                    float v[kScanUnroll];
+#pragma unroll
+                    for (int u = 0; u < kScanUnroll; ++u) v[u] = (i0 + u * kThreads) < V ? l[i0 + u * kThreads] : 0.f;
+#pragma unroll
+                    for (int u = 0; u < kScanUnroll; ++u) {
+                        const int i = i0 + u * kThreads;
+                        if (i < V && in_kept(kept, order_key(v[u]), i)) {
+                            const int at = atomicAdd(&n_cand, 1);
+                            if (at < kSmallSet)
+                                cand[at] = ((unsigned long long)order_key(v[u]) << 32) | (uint32_t)(~(uint32_t)i);
+                        }
+                    }
+                }
+                __syncthreads();
+                const int n = min(n_cand, kSmallSet);
+                int n2 = 1;
+                while (n2 < n) n2 <<= 1;
+                for (int i = n + tid; i < n2; i += kThreads) cand[i] = 0ull;        // padding sorts last
+                __syncthreads();
+                for (int k = 2; k <= n2; k <<= 1)                                   // bitonic sort, descending
+                    for (int j = k >> 1; j > 0; j >>= 1) {
+                        for (int i = tid; i < n2; i += kThreads) {
+                            const int ixj = i ^ j;
+                            if (ixj > i) {
+                                const unsigned long long a = cand[i], b = cand[ixj];
+                                const bool desc = (i & k) == 0;
+                                if (desc ? (a < b) : (a > b)) { cand[i] = b; cand[ixj] = a; }
+                            }
+                        }
+                        __syncthreads();
+                    }
+                if (tid == 0) {
+                    auto value_of = [](unsigned long long c) {
+                        const uint32_t key = (uint32_t)(c >> 32);
+                        return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+                    };
+                    auto prob_of = [&](unsigned long long c) { return expf((value_of(c) - maxv) / temp) / z; };
+                    int cut = n;
+                    if (top_p < 1.0f) {
+                        float cum = 0.f;
+                        for (int i = 0; i < n; ++i) {
+                            cum += prob_of(cand[i]);
+                            if (cum >= top_p) { cut = i + 1; break; }
+                        }
+                    }
+                    float total = 0.f;
+                    for (int i = 0; i < cut; ++i) total += prob_of(cand[i]);
+                    const float rr = uniforms[row] * total;
+                    float cdf = 0.f;
+                    int pick = cut - 1;
+                    for (int i = 0; i < cut; ++i) {
+                        cdf += prob_of(cand[i]);
+                        if (rr < cdf) { pick = i; break; }
+                    }
+                    best_id_sh = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
+                }
+                __syncthreads();
+                result = best_id_sh;
+                small_done = true;
+            } else {
+                float m = 0.f;
+                for (int i = tid; i < V; i += kThreads)
+                    if (kept_filter(i)) m += prob(i);
+                kept_mass = block_sum(m, scratch);
+            }
         }
+        if (!small_done) {
         // ---- top-p: shortest prefix whose mass reaches top_p of the WHOLE distribution ----
         if (top_p < 1.0f) {
             const float target = top_p * z;
             SelectResult r = radix_select(V, 32, target, false, keyfn, prob, kept_filter, hist, red);
             if (r.found) {
                 // equals share one probability; the prefix needs j of them
-                int n_eq = 0;
-                float p_eq = 0.f;
-                for (int i = tid; i < V; i += kThreads)
-                    if (keyfn(i) == r.x && kept_filter(i)) { ++n_eq; p_eq = prob(i); }
-                n_eq = (int)(block_sum((float)n_eq, scratch) + 0.5f);
-                p_eq = block_max(p_eq, scratch);
+                const EqualInfo eq = equal_scan(V, r.x, kept, keyfn, eq_sh);
+                const int n_eq = eq.n;
+                const float p_eq = expf((value_of_key(r.x) - maxv) / temp);
                 int j = (int)ceilf((target - r.above) / p_eq);
                 j = max(1, min(j, n_eq));
-                const int last = nth_equal_id(V, r.x, kept, j, id_bits, keyfn, hist, red);
+                const int last = jth_equal(V, r.x, kept, j, eq, id_bits, keyfn, hist, red);
                 kept = Kept{r.x, last};
                 kept_mass = r.above + (float)j * p_eq;
             }
@@ -238,16 +360,14 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
                 result = nth_equal_id(V, lo.x, whole, n_eq, id_bits, keyfn, hist, red);
             }
         } else {
-            int n_eq = 0;
-            float p_eq = 0.f;
-            for (int i = tid; i < V; i += kThreads)
-                if (keyfn(i) == r.x && kept_filter(i)) { ++n_eq; p_eq = prob(i); }
-            n_eq = (int)(block_sum((float)n_eq, scratch) + 0.5f);
-            p_eq = block_max(p_eq, scratch);
+            const EqualInfo eq = equal_scan(V, r.x, kept, keyfn, eq_sh);
+            const int n_eq = eq.n;
+            const float p_eq = expf((value_of_key(r.x) - maxv) / temp);
             int j = (int)floorf((rr - r.above) / p_eq) + 1;
             j = max(1, min(j, n_eq));
-            result = nth_equal_id(V, r.x, kept, j, id_bits, keyfn, hist, red);
+            result = jth_equal(V, r.x, kept, j, eq, id_bits, keyfn, hist, red);
         }
+        }   // !small_done
     }
     __syncthreads();
     if (tid == 0) {
