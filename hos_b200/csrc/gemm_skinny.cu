@@ -16,6 +16,7 @@
 // Epilogues: none (bf16 or f32 output); gated, where the CTA owns 16 gate rows and the 16
 // matching up rows (4 warps each) and writes act(gate) * up.
 #include "common.cuh"
+#include "kv_layout.cuh"
 #include "mma_utils.cuh"
 
 namespace hos {
@@ -118,6 +119,142 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
     }
 }
 
+
+// ---- the q/k/v projection of a decode step with the rotary encoding and the cache write in its
+// epilogue ------------------------------------------------------------------------------------
+// Same streaming product, but a CTA's 16 rows of W are chosen so that the two rows a rotation pairs
+// are rows g and g+8 of the MMA tile: after the K shares are added, one thread holds both values
+// of a pair for a token, rotates them (angle = position * inv_freq[i], sincosf in 32-bit), writes
+// them to the activation row and, for a key, to the token's place in the paged cache.  Values and
+// unrotated dimensions pass straight through.  This saves the separate rotate-and-store launch
+// and one round trip of the projection output through memory.
+//
+// Tiles, in order: for every q head and k head, rot/16 rotation tiles (rotate-half: dims i0..i0+7
+// with their partners i0+rot/2..; interleaved: dims 16b..16b+15 as (even, odd)), then (hd-rot)/16
+// plain tiles; then hd/16 plain tiles per v head.  Needs head_dim % 16 == 0 and rotary_dim % 16 == 0.
+struct QkvRopeArgs {
+    const int* token_pos;
+    const int* token_seq;
+    const int* seq_slot;
+    const int* seq_len_after;
+    const float* inv_freq;
+    PagedKV cache;
+    int n_heads, rotary_dim, style, write_cache;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(kSkinnyThreads, 2)
+qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* __restrict__ out,
+                       int M, int K, int lda, int ldw, int ldo, QkvRopeArgs q) {
+    pdl_enter();
+    __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
+    __shared__ int tok_page[MT * 8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int hd = q.cache.head_dim, nkv = q.cache.n_kv_heads, nh = q.n_heads;
+    const int rot = q.rotary_dim, half = rot >> 1;
+    const int tiles_per_head = hd / 16, rot_tiles = rot / 16;
+    // which tile: head (q heads, then k heads, then v heads) and tile within the head
+    const int head = blockIdx.x / tiles_per_head, t = blockIdx.x % tiles_per_head;
+    const bool is_v = head >= nh + nkv;
+    const bool rotated = !is_v && t < rot_tiles;
+    // feature (row of W = column of the output) of MMA rows r (0..7) and r+8
+    int f_lo, f_hi, step;          // row r -> f_lo + step*r, row r+8 -> f_hi + step*r
+    if (rotated && q.style == 0) { f_lo = head * hd + 8 * t; f_hi = f_lo + half; step = 1; }
+    else if (rotated) { f_lo = head * hd + 16 * t; f_hi = f_lo + 1; step = 2; }
+    else { f_lo = head * hd + 16 * t; f_hi = f_lo + 8; step = 1; }
+
+    // where each token's key/value goes (looked up while the product runs)
+    if (threadIdx.x < MT * 8) {
+        int page = -1;
+        const int tok = threadIdx.x;
+        if (tok < M && q.write_cache) {
+            const int seq = q.token_seq[tok];
+            if (seq >= 0) {
+                const int pos = q.token_pos[tok];
+                if (!(q.cache.ring_pages > 0 && pos + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq]))
+                    page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
+                                              kv_table_entry(q.cache, pos / kPageTokens)];
+            }
+        }
+        tok_page[tok] = page;
+    }
+
+    const int k_blocks = (K + 31) / 32;
+    const int per_way = (k_blocks + kSkinnyWarps - 1) / kSkinnyWarps;
+    const int kb_begin = warp * per_way, kb_end = min(k_blocks, kb_begin + per_way);
+    const bf16* w0 = W + (size_t)(f_lo + step * g) * ldw + 8 * t4;
+    const bf16* w1 = W + (size_t)(f_hi + step * g) * ldw + 8 * t4;
+    const bf16* a0 = A + (size_t)min(g, M - 1) * lda + 8 * t4;
+    const bf16* a1 = A + (size_t)min(g + 8, M - 1) * lda + 8 * t4;
+    const bool tok0 = g < M, tok1 = MT == 2 && g + 8 < M;
+    float acc[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+        uint4 wa[kUnroll], wb[kUnroll], xa[kUnroll], xb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int k = (kb + u) * 32 + 8 * t4;
+            const bool in = (kb + u) < kb_end && k < K;
+            wa[u] = in ? ldg16_stream(w0 + (size_t)(kb + u) * 32) : zero;
+            wb[u] = in ? ldg16_stream(w1 + (size_t)(kb + u) * 32) : zero;
+            xa[u] = (in && tok0) ? ldg16(a0 + (size_t)(kb + u) * 32) : zero;
+            if (MT == 2) xb[u] = (in && tok1) ? ldg16(a1 + (size_t)(kb + u) * 32) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t fa[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+            const uint32_t fb[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+            mma_bf16(acc[0], fa, xa[u].x, xa[u].y);
+            mma_bf16(acc[0], fb, xa[u].z, xa[u].w);
+            if (MT == 2) {
+                mma_bf16(acc[1], fa, xb[u].x, xb[u].y);
+                mma_bf16(acc[1], fb, xb[u].z, xb[u].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        part[warp][m][g][2 * t4] = acc[m][0];
+        part[warp][m][g][2 * t4 + 1] = acc[m][1];
+        part[warp][m][g + 8][2 * t4] = acc[m][2];
+        part[warp][m][g + 8][2 * t4 + 1] = acc[m][3];
+    }
+    __syncthreads();
+    // one thread per (token, pair): rows r and r+8 of the tile
+    for (int idx = threadIdx.x; idx < MT * 8 * 8; idx += kSkinnyThreads) {
+        const int tok = idx / 8, r = idx % 8;
+        if (tok >= M) continue;
+        const int m = tok >> 3, tt = tok & 7;
+        float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSkinnyWarps; ++w) { v0 += part[w][m][r][tt]; v1 += part[w][m][r + 8][tt]; }
+        const int seq = q.token_seq[tok];
+        if (seq < 0) continue;                                   // padding: nothing is stored
+        const int fa_ = f_lo + step * r, fb_ = f_hi + step * r;
+        if (rotated) {
+            const int i = 8 * t + r;                             // index of the pair within the head
+            float sn, cs;
+            sincosf((float)q.token_pos[tok] * q.inv_freq[i], &sn, &cs);
+            const float x0 = v0, x1 = v1;
+            v0 = x0 * cs - x1 * sn;
+            v1 = x0 * sn + x1 * cs;
+        }
+        const bf16 b0 = __float2bfloat16_rn(v0), b1 = __float2bfloat16_rn(v1);
+        out[(size_t)tok * ldo + fa_] = b0;
+        out[(size_t)tok * ldo + fb_] = b1;
+        const int page = tok_page[tok];
+        if (head >= nh && page >= 0) {                          // a key or a value: into the cache
+            const int kvh = is_v ? head - nh - nkv : head - nh;
+            bf16* base = (bf16*)(is_v ? q.cache.v_pages : q.cache.k_pages) + kv_tile_offset(q.cache, page, kvh);
+            const int rr = q.token_pos[tok] % kPageTokens;
+            base[kv_elem_offset(rr, fa_ - head * hd, hd)] = b0;
+            base[kv_elem_offset(rr, fb_ - head * hd, hd)] = b1;
+        }
+    }
+}
+
 }  // namespace hos
 
 using namespace hos;
@@ -151,4 +288,35 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     }
 #undef HOS_SK
     return check_launch("gemm_skinny");
+}
+
+// The q/k/v projection of up to 16 tokens with rotary encoding and cache write fused in:
+// out[M, (n_heads + 2 n_kv_heads) * head_dim] = A[M, K] . W^T, q and k heads rotated, keys and values
+// stored at the tokens' places.  Needs head_dim % 16 == 0 and rotary_dim % 16 == 0 (0: no rotation).
+extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int M, int K, int lda, int ldw, int ldo,
+                                   int n_heads, int n_kv_heads, int head_dim, const int* token_pos,
+                                   const int* token_seq, const int* seq_slot, const int* seq_len_after,
+                                   const float* inv_freq, int rotary_dim, int style, void* k_pages, void* v_pages,
+                                   const int* page_table, int table_stride, int ring_pages, int write_cache,
+                                   cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) HOS_REFUSE("qkv_rope_skinny: %d rows are more than 16", M);
+    if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
+        HOS_REFUSE("qkv_rope_skinny: K and the leading dimensions must be multiples of 8 elements and the operands "
+                   "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
+    if ((head_dim % 16) || (rotary_dim % 16) || rotary_dim < 0 || rotary_dim > head_dim || (style != 0 && style != 1))
+        HOS_REFUSE("qkv_rope_skinny: head_dim %d and rotary_dim %d must be multiples of 16", head_dim, rotary_dim);
+    QkvRopeArgs q;
+    q.token_pos = token_pos; q.token_seq = token_seq; q.seq_slot = seq_slot; q.seq_len_after = seq_len_after;
+    q.inv_freq = inv_freq;
+    q.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
+    q.n_heads = n_heads; q.rotary_dim = rotary_dim; q.style = style; q.write_cache = write_cache;
+    const unsigned grid = (unsigned)((n_heads + 2 * n_kv_heads) * (head_dim / 16));
+    if (M <= 8)
+        launch_pdl(qkv_rope_skinny_kernel<1>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W,
+                   (bf16*)out, M, K, lda, ldw, ldo, q);
+    else
+        launch_pdl(qkv_rope_skinny_kernel<2>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W,
+                   (bf16*)out, M, K, lda, ldw, ldo, q);
+    return check_launch("qkv_rope_skinny");
 }

@@ -82,8 +82,16 @@ class SoftmaxAttention(Mixer):
         if cache is None:
             raise KernelError("attention needs a cache view")
         inv_freq, rotary_dim, style = self.position.kernel_args() if self.position else (None, 0, 0)
-        if store.owns_kv:
-            qkv = linear.matmul_or_partials(h, self.w_qkv)
+        w = self.w_qkv if store.owns_kv else self.w_q
+        n_kv = self.n_kv_heads if store.owns_kv else 0
+        from . import gemm_skinny
+        if not linear.plain_forced() and gemm_skinny.can_fuse_qkv_rope(h, w, self.head_dim, rotary_dim):
+            # a handful of rows: projection, rotation and cache write in one kernel
+            qkv = torch.empty((n, w.shape[0]), dtype=h.dtype, device=h.device)
+            gemm_skinny.qkv_rope(h, w, qkv, self.n_heads, n_kv, self.head_dim, step, inv_freq, rotary_dim, style,
+                                 cache if store.owns_kv else None)
+        elif store.owns_kv:
+            qkv = linear.matmul_or_partials(h, w)
             parts = None
             if qkv.dim() == 3:       # partial sums: the rotate-and-store kernel adds them
                 parts, qkv = qkv, torch.empty(qkv.shape[1:], dtype=h.dtype, device=h.device)
@@ -91,7 +99,7 @@ class SoftmaxAttention(Mixer):
                               step.seq_len_after, inv_freq, rotary_dim, style, cache,
                               self.n_kv_heads, self.head_dim, partials=parts)
         else:
-            qkv = linear.matmul(h, self.w_q)
+            qkv = linear.matmul(h, w)
             ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
                               step.seq_len_after, inv_freq, rotary_dim, style, None, 0, self.head_dim)
         att = torch.empty((n, self.q_dim), dtype=h.dtype, device=h.device)

@@ -40,3 +40,29 @@ def matmul(x, w, out, epilogue: int = ops.EPI_NONE, act: int = 0) -> None:
     n = out.shape[1]
     lib().call("hos_gemm_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(out), ops.dtype_code(out.dtype), m, n, k,
                x.stride(0), w.stride(0), out.stride(0), epilogue, act, ops._stream())
+
+
+def can_fuse_qkv_rope(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
+    """Whether the projection of q, k, v with the rotary encoding and the cache write in its
+    epilogue can run: the product's own rules, and head and rotary sizes in steps of 16."""
+    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not 0 < x.shape[0] <= MAX_ROWS:
+        return False
+    if x.shape[1] % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    if x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    return head_dim % 16 == 0 and rotary_dim % 16 == 0
+
+
+def qkv_rope(x, w, out, n_heads: int, n_kv_heads: int, head_dim: int, step, inv_freq, rotary_dim: int, style: int,
+             cache) -> None:
+    """out[M, (n_heads + 2 n_kv_heads) * head_dim] = x . w^T with q and k heads rotated and, if `cache` is
+    given, keys and values stored at the tokens' places.  n_kv_heads = 0: q heads only."""
+    m, k = x.shape
+    lib().call("hos_qkv_rope_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(out), m, k, x.stride(0), w.stride(0),
+               out.stride(0), n_heads, n_kv_heads, head_dim, ops._ptr(step.token_pos), ops._ptr(step.token_seq),
+               ops._ptr(step.seq_slot), ops._ptr(step.seq_len_after), ops._ptr(inv_freq) if inv_freq is not None else None,
+               rotary_dim if inv_freq is not None else 0, style,
+               ops._ptr(cache.k_pages) if cache else None, ops._ptr(cache.v_pages) if cache else None,
+               ops._ptr(cache.page_table) if cache else None, cache.table_stride if cache else 0,
+               cache.ring_pages if cache else 0, 1 if cache else 0, ops._stream())

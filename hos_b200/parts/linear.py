@@ -20,6 +20,10 @@ def force_plain(on: bool) -> None:
     _force_plain = on
 
 
+def plain_forced() -> bool:
+    return _force_plain
+
+
 def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:

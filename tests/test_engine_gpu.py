@@ -65,13 +65,15 @@ def test_long_decoding_wraps_the_window_ring(tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_padding_rows_change_nothing(tmp_path, dtype):
-    """The same batch with padding rows appended gives the same logits, bit for bit."""
+    """The same batch with padding rows appended gives the same logits: bit for bit while the
+    padded batch runs the same kernels (5 rows more), and within the engine's tolerance when
+    padding takes a decode step from the few-rows kernels to the many-rows ones (64 more)."""
     from hos_b200.engine.batch import build_step
     folder = make_folder(tmp_path, "B")
     rng = random.Random(5)
     prompts = [random_tokens(rng, n, 512) for n in (3, 20, 9)]
     outs = []
-    for pad in (0, 64):
+    for pad in (0, 5, 64):
         r = runner_for(folder, dtype)
         slots = r.admit(3)
         for s, p in zip(slots, prompts):
@@ -91,6 +93,11 @@ def test_padding_rows_change_nothing(tmp_path, dtype):
         x = r.model.hidden(info, r.cache)
         outs.append(r.model.logits(x, torch.arange(3, dtype=torch.int32, device=r.device)).cpu())
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+    assert torch.equal(outs[0], outs[4])
+    if dtype == "float32":
+        assert torch.equal(outs[1], outs[5])
+    else:
+        assert_close(outs[5], outs[1], dtype, "decode step padded past the few-rows kernels")
 
 
 def test_step_refuses_what_it_cannot_run(tmp_path):

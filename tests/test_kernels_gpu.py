@@ -597,6 +597,70 @@ def test_gemm_skinny(shape, variant):
     assert not gemm_skinny.can_take(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w, big, ops.EPI_NONE)
 
 
+@pytest.mark.parametrize("cfg", [dict(M=1, nh=3, nkv=1, hd=48, rot=48, style="rotate_half", K=72, ring=0),
+                                 dict(M=7, nh=2, nkv=2, hd=64, rot=32, style="rotate_half", K=200, ring=2),
+                                 dict(M=9, nh=4, nkv=2, hd=64, rot=64, style="interleaved", K=136, ring=0),
+                                 dict(M=16, nh=8, nkv=4, hd=256, rot=256, style="rotate_half", K=2304, ring=0),
+                                 dict(M=5, nh=2, nkv=1, hd=32, rot=0, style="rotate_half", K=64, ring=0),
+                                 dict(M=4, nh=3, nkv=0, hd=32, rot=16, style="interleaved", K=96, ring=0)])
+def test_qkv_projection_with_rotation_and_cache_write_fused(cfg):
+    """The one-kernel q/k/v projection of a handful of tokens against a float64 product and
+    rotation, and its cache against the separate rotate-and-store kernel given the same rows:
+    head sizes that are and are not permuted in the cache, a part of the head rotated, both
+    pairings, a ring, padding rows, q heads alone."""
+    from types import SimpleNamespace
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_skinny
+    M, nh, nkv, hd, rot, style, K, ring = (cfg[k] for k in ("M", "nh", "nkv", "hd", "rot", "style", "K", "ring"))
+    torch.manual_seed(11)
+    width = (nh + 2 * nkv) * hd
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(width, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    # tokens of two sequences at far positions; one padding row if there is room
+    pos = torch.tensor([700 + 3 * i for i in range(M)], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([i % 2 for i in range(M)], dtype=torch.int32, device=DEV)
+    if M > 2:
+        seq[2] = -1
+    slot = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
+    # in a ring, sequence 0's tokens are overwritten later in the same step and must not be stored
+    len_after = torch.tensor([850 if ring else 760, 760], dtype=torch.int32, device=DEV)
+    inv = (1.0 / torch.pow(torch.tensor(5000.0), 2.0 * torch.arange(rot // 2).float() / max(rot, 1))).to(DEV) if rot else None
+    n_entries = ring if ring else 16
+    table = (torch.randperm(3 * n_entries, device=DEV)[: 3 * n_entries].view(3, n_entries)).to(torch.int32)
+    step = SimpleNamespace(token_pos=pos, token_seq=seq, seq_slot=slot, seq_len_after=len_after)
+
+    def caches():
+        kp = torch.zeros(3 * n_entries, max(nkv, 1), 64, hd, device=DEV, dtype=torch.bfloat16)
+        return ops.PagedKVArgs(kp, torch.zeros_like(kp), table, ring, max(nkv, 1), hd)
+
+    assert gemm_skinny.can_fuse_qkv_rope(x, w, hd, rot)
+    out = torch.full((M, width), 7.0, device=DEV, dtype=torch.bfloat16)
+    ca = caches()
+    gemm_skinny.qkv_rope(x, w, out, nh, nkv, hd, step, inv, rot, ops.ROPE_STYLES[style], ca if nkv else None)
+    # float64 product, rotation in float64
+    y = (x.double() @ w.double().T).view(M, nh + 2 * nkv, hd)
+    want = y.clone()
+    if rot:
+        ang = pos.double()[:, None] * inv.double()[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        if style == "rotate_half":
+            a, b = y[:, :nh + nkv, :rot // 2], y[:, :nh + nkv, rot // 2:rot]
+            want[:, :nh + nkv, :rot // 2], want[:, :nh + nkv, rot // 2:rot] = a * c - b * s, a * s + b * c
+        else:
+            a, b = y[:, :nh + nkv, 0:rot:2], y[:, :nh + nkv, 1:rot:2]
+            want[:, :nh + nkv, 0:rot:2], want[:, :nh + nkv, 1:rot:2] = a * c - b * s, a * s + b * c
+    live = seq >= 0
+    close(out.view(M, -1, hd)[live], want.to(torch.bfloat16)[live], torch.bfloat16)
+    if nkv:
+        # the separate kernel stores the fused kernel's own rows: the caches must be equal bit for bit
+        cb = caches()
+        rows = out.clone()
+        rows[~live] = 0
+        ops.rope_kv_write(rows, nh, pos, seq, slot, len_after, None, 0, 0, cb, nkv, hd)   # no rotation: store only
+        assert torch.equal(ca.k_pages, cb.k_pages) and torch.equal(ca.v_pages, cb.v_pages)
+        assert float(ca.k_pages.abs().sum()) > 0
+
+
 @pytest.mark.parametrize("cfg", [dict(nh=3, nkv=1, hd=64, window=None, cap=0.0),
                                  dict(nh=2, nkv=2, hd=64, window=70, cap=30.0),
                                  dict(nh=4, nkv=2, hd=128, window=100, cap=50.0),
