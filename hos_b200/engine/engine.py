@@ -129,7 +129,7 @@ class Engine:
         slot = r.admit(1)[0]
         try:
             feed = ids[:-1]
-            x = r._hidden([slot], [0], [feed])
+            x, _ = r._hidden([slot], [0], [feed])
             nll = 0.0
             for lo in range(0, len(feed), 256):
                 hi = min(lo + 256, len(feed))

@@ -104,10 +104,6 @@ class Runner:
         if not (from_zero or single):
             raise HosError("step: the sequences of a step either all start at their first token or "
                            "all go on by one token")
-        for toks in token_lists:
-            for t in toks:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise HosError(f"token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
         if want is None:
             want = [[len(t) - 1] for t in token_lists]
         rows: List[int] = []
@@ -121,6 +117,9 @@ class Runner:
         if single and not from_zero and len(rows) == len(slots) and self.use_sessions:
             # decoding: static buffers and a captured graph, one per batch-size bucket
             from .decode import DecodeSession, bucket_for
+            for toks in token_lists:
+                if not (0 <= int(toks[0]) < self.vocab_size):
+                    raise HosError(f"token id {toks[0]} is outside the vocabulary (0..{self.vocab_size - 1})")
             for s, st in zip(slots, starts):
                 self.cache.extend(s, st + 1)
             bucket = bucket_for(len(slots))
@@ -130,16 +129,16 @@ class Runner:
             sess.feed(slots, [t[0] for t in token_lists], starts)
             out = sess.run()
             return out.clone() if copy else out
-        x = self._hidden(slots, starts, token_lists)
-        rows_t = torch.tensor(rows, dtype=torch.int32).to(self.device)
+        x, rows_t = self._hidden(slots, starts, token_lists, rows)
         return self.model.logits(x, rows_t)
 
-    def _hidden(self, slots, starts, token_lists) -> torch.Tensor:
+    def _hidden(self, slots, starts, token_lists, rows=()):
+        """The hidden rows of a step, and `rows` (indices into them) as a device tensor."""
+        info, rows_t = build_step(token_lists, starts, slots, self.device, self.vocab_size, extra=rows)
         for s, st, toks in zip(slots, starts, token_lists):
             self.cache.extend(s, st + len(toks))
         self.cache.flush()
-        info = build_step(token_lists, starts, slots, self.device, self.vocab_size)
-        return self.model.hidden(info, self.cache)
+        return self.model.hidden(info, self.cache), rows_t
 
     def decode_steps_timed(self, slots, first_tokens, warmup: int, steps: int, clocks=None):
         """`warmup` untimed and `steps` timed greedy decode steps, issued back to back with

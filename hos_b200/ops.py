@@ -69,8 +69,19 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index: Optional[int] = None
+
+
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream as a raw handle.  Asked for at every launch, so it goes the
+    short way: one call into torch's C layer instead of building a Stream object."""
+    global _device_index
+    if _raw_stream is None:
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return ctypes.c_void_p(_raw_stream(_device_index))
 
 
 class Library:
