@@ -56,6 +56,7 @@ struct DecodeArgs {
     int stages, merge_rows;
     float scale, cap;
     int window;
+    int max_new;          // most new tokens any sequence brings in this step: what lies below them is old
 };
 
 __device__ __forceinline__ bool wait_timed(uint64_t* bar, uint32_t parity) {
@@ -120,7 +121,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
         mbar_fence_init();
     }
     __syncthreads();
-    pdl_enter();      // the kernels before this one (which wrote q and the newest keys) are complete from here on
+    pdl_launch_dependents();
+    // This kernel is launched so that it may start while the projection before it still runs.  That
+    // kernel writes q and the step's new keys and values, nothing else that is read here: the
+    // producer may look up pages and fetch tiles that lie wholly below the step's new positions
+    // before pdl_wait(); everything else comes after it.  (The slot and page tables were written
+    // at least two kernels earlier.  In a ring the oldest tile of the window can share its page
+    // with the newest positions: the rows that are being written are masked in that tile.)
 
     if (warp == 4) {
         // ---------------- producer: one thread feeds the ring, item after item ----------------
@@ -128,13 +135,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             const bf16* k_pages = reinterpret_cast<const bf16*>(a.cache.k_pages);
             const bf16* v_pages = reinterpret_cast<const bf16*>(a.cache.v_pages);
             int t = 0;            // tiles issued so far by this CTA
-            bool ok = true;
+            bool ok = true, waited = false;
             for (int index = blockIdx.x; index < total_items && ok; index += gridDim.x) {
                 const Item it = make_item(a, index, group, chunks);
                 if (it.n_tiles == 0) continue;
                 const int* table = a.cache.page_table + (size_t)a.seq_slot[it.seq] * a.cache.table_stride;
                 for (int tile = 0; tile < it.n_tiles; ++tile, ++t) {
                     const int s = t % stages;
+                    if (!waited && (t >= stages || (it.lp_begin + tile + 1) * kPageTokens > it.pos + 1 - a.max_new)) {
+                        pdl_wait();
+                        waited = true;
+                    }
                     if (t >= stages && !wait_timed(&empty[s], ((t / stages) - 1) & 1)) { ok = false; break; }
                     const int page = table[kv_table_entry(a.cache, it.lp_begin + tile)];
                     const size_t off = kv_tile_offset(a.cache, page, it.kvh);
@@ -150,6 +161,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
     }
 
     // ---------------- consumers: warps 0..3 ----------------
+    pdl_wait();                   // q and the newest keys are complete from here on
     const int g = lane >> 2, t4 = lane & 3;
     const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
     const uint32_t q_base = smem_u32(q_s);
@@ -416,8 +428,9 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
                                int* tickets, const int* token_pos, const int* token_seq, const int* seq_slot,
                                void* k_pages, void* v_pages, const int* page_table, int table_stride,
                                int ring_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                               float scale, float cap, int window, int n_splits, cudaStream_t stream) {
+                               float scale, float cap, int window, int n_splits, int max_new, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (max_new < 1) HOS_REFUSE("attn_decode: max_new %d (the most new tokens of a sequence in this step) must be at least 1", max_new);
     if (head_dim != HD) HOS_REFUSE("attn_decode: built for head_dim %d, asked for %d", HD, head_dim);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         HOS_REFUSE("attn_decode: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -452,9 +465,9 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     a.token_pos = token_pos; a.token_seq = token_seq; a.seq_slot = seq_slot;
     a.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
     a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_splits = n_splits;
-    a.scale = scale; a.cap = cap; a.window = window;
+    a.scale = scale; a.cap = cap; a.window = window; a.max_new = max_new;
     const int grid = items < sm_count() ? (int)items : sm_count();
-    launch_pdl(attn_decode_kernel, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
+    launch_ahead(true, attn_decode_kernel, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
     return check_launch("attn_decode");
 }
 
@@ -506,5 +519,5 @@ extern "C" int hos_attn_decode_noalloc(const void* q, int q_stride, void* out, i
     }
     return hos_attn_decode(q, q_stride, out, out_stride, workspace, tickets, token_pos, token_seq, seq_slot, k_pages,
                            v_pages, page_table, table_stride, ring_pages, n_tokens, n_heads, n_kv_heads, head_dim,
-                           scale, cap, window, n_splits, stream);
+                           scale, cap, window, n_splits, /*max_new: nothing is fetched ahead*/ 1 << 30, stream);
 }

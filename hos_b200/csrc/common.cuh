@@ -46,7 +46,10 @@ inline int check_launch(const char* what) {
 // lets the kernel after it be set up in turn.  Both are no-ops for a kernel launched the
 // ordinary way, which is the default: measured on Gemma-2 2B sizes the attribute gains 3% on a
 // 2,048-token prompt and loses 5% on a decode step at batch 8 (the step's kernels are short and
-// the graph replays them back to back anyway).  HOS_PDL=1 in the environment switches it on.
+// the graph replays them back to back anyway); issuing the first weight loads of the few-rows
+// products before the wait changed nothing at batch 8 and gained 3% at batch 1.  HOS_PDL=1 in the
+// environment switches it on for every kernel.  One pair uses it always: the decode attention
+// kernel fetches old keys while the q/k/v projection before it still runs (launch_ahead).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
@@ -60,8 +63,11 @@ inline bool pdl_enabled() {
     return on == 1;
 }
 
+// `ahead`: the kernel may be set up while the one before it on the stream is still running (if that
+// one lets it: pdl_launch_dependents()), and must call pdl_wait() before it touches what that one wrote.
 template <typename... KArgs, typename... Args>
-inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+inline void launch_ahead(bool ahead, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                         Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -71,8 +77,14 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = ahead ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);      // the caller reads the error with check_launch()
+}
+
+// The ordinary launch of every kernel here: ahead of its turn only if HOS_PDL asks for it.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    launch_ahead(pdl_enabled(), kernel, grid, block, smem, stream, args...);
 }
 
 // ---- conversions -------------------------------------------------------------------

@@ -146,7 +146,10 @@ template <int MT>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* __restrict__ out,
                        int M, int K, int lda, int ldw, int ldo, QkvRopeArgs q) {
-    pdl_enter();
+    // The attention kernel after this one may start now: it fetches old keys and values, which this
+    // kernel does not touch, and waits for this kernel's end before it reads q or the newest page.
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
     __shared__ int tok_page[MT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;

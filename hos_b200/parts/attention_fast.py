@@ -55,9 +55,12 @@ def _tickets(device, n: int) -> torch.Tensor:
 
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
-           window: Optional[int], max_len: int, n_splits: Optional[int] = None) -> None:
+           window: Optional[int], max_len: int, n_splits: Optional[int] = None,
+           max_new: Optional[int] = None) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
-    position in its own sequence)."""
+    position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
+    the kernel may fetch keys that lie below them while the kernel before it (which writes the
+    step's new keys) still runs.  None: it fetches nothing ahead."""
     hd, nkv = cache.head_dim, cache.n_kv_heads
     lib = lib_for(hd)
     if n_splits is None:
@@ -70,7 +73,7 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
              ops._ptr(tickets), ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(cache.k_pages),
              ops._ptr(cache.v_pages), ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages,
              n_tokens, n_heads, nkv, hd, float(scale), float(cap), int(window) if window else 0,
-             int(n_splits), ops._stream())
+             int(n_splits), int(max_new) if max_new else 1 << 30, ops._stream())
 
 
 def decode_gave_up(head_dim: int) -> bool:
@@ -136,5 +139,5 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
     if not enabled["decode"]:
         return False
     decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
-           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after)
+           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new)
     return True

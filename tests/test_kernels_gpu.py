@@ -403,10 +403,11 @@ def test_attention_decode_kernel(cfg, n_splits):
             continue
         want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
         close(out[j].reshape(nh, hd), want.to(dt), dt)
-    # the heuristic's own choice of splits gives the same
+    # the heuristic's own choice of splits gives the same, and so does fetching ahead of the kernel before
+    # (here nothing is being written, so every page may be fetched ahead)
     out2 = torch.empty_like(q)
     af.decode(q, nh * hd, out2, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), cache, len(items),
-              nh, scale, cap, window, 517)
+              nh, scale, cap, window, 517, max_new=1)
     close(out2, out, dt)
 
 
