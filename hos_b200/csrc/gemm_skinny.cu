@@ -48,9 +48,13 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
     const int k_way = GATED ? (warp & 3) : warp;
     const int row_base = (GATED && warp >= 4) ? gate_rows + n0 : n0;
     const int row_limit = (GATED && warp >= 4) ? gate_rows + N : N;
+    // gridDim.y > 1: K is split over CTAs too; CTA (x, y) writes its 32-bit partial sums to out + y * M * ldo
     const int k_blocks = (K + 31) / 32;
-    const int per_way = (k_blocks + k_ways - 1) / k_ways;
-    const int kb_begin = k_way * per_way, kb_end = min(k_blocks, kb_begin + per_way);
+    const int per_cta = (k_blocks + gridDim.y - 1) / gridDim.y;
+    const int cta_begin = blockIdx.y * per_cta, cta_end = min(k_blocks, cta_begin + per_cta);
+    const int per_way = (max(0, cta_end - cta_begin) + k_ways - 1) / k_ways;
+    const int kb_begin = cta_begin + k_way * per_way, kb_end = min(cta_end, kb_begin + per_way);
+    out += (size_t)blockIdx.y * M * ldo;
 
     const int r0 = row_base + g, r1 = row_base + g + 8;
     const bool ok0 = r0 < row_limit, ok1 = r1 < row_limit;
@@ -267,8 +271,9 @@ extern "C" const char* hos_last_error() { return error_buffer(); }
 // out[M, N] = A[M, K] . W[N, K]^T for M <= 16.  epilogue 0: none (out bf16 or f32); 2: gated (W has
 // 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
 // multiples of 8 elements, A and W 16-byte aligned.
+// k_splits > 1: `out` is [k_splits][M][ldo] 32-bit partial sums for a consumer that adds them (no epilogue).
 extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                               int lda, int ldw, int ldo, int epilogue, int act, cudaStream_t stream) {
+                               int lda, int ldw, int ldo, int epilogue, int act, int k_splits, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16) HOS_REFUSE("gemm_skinny: %d rows are more than 16", M);
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
@@ -276,9 +281,12 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
                    "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
     if (epilogue != 0 && epilogue != 2) HOS_REFUSE("gemm_skinny: epilogue %d is not offered", epilogue);
     if (epilogue == 2 && out_dtype != kBF16) HOS_REFUSE("gemm_skinny: the gated epilogue writes bfloat16");
+    if (k_splits < 1 || k_splits > 64) HOS_REFUSE("gemm_skinny: %d splits of K (1..64)", k_splits);
+    if (k_splits > 1 && (epilogue != 0 || out_dtype != kF32))
+        HOS_REFUSE("gemm_skinny: partial sums over a split K are 32-bit and take no epilogue");
     const unsigned grid = (unsigned)((N + 15) / 16);
 #define HOS_SK(MT, G, T)                                                                                     \
-    launch_pdl(gemm_skinny_kernel<MT, G, T>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+    launch_pdl(gemm_skinny_kernel<MT, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
     if (epilogue == 2) {
         if (M <= 8) HOS_SK(1, true, bf16); else HOS_SK(2, true, bf16);

@@ -20,15 +20,16 @@ def lib() -> ops.Library:
     return _lib
 
 
+def operands_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not 0 < x.shape[0] <= MAX_ROWS:
+        return False
+    if x.shape[1] % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    return x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
 def can_take(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] > MAX_ROWS:
-        return False
-    if epilogue not in (ops.EPI_NONE, ops.EPI_GATED):
-        return False
-    k = x.shape[1]
-    if k % 8 != 0 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
-        return False
-    if x.data_ptr() % 16 or w.data_ptr() % 16 or not out.is_contiguous():
+    if not operands_ok(x, w) or epilogue not in (ops.EPI_NONE, ops.EPI_GATED) or not out.is_contiguous():
         return False
     if epilogue == ops.EPI_GATED:
         return out.dtype == torch.bfloat16
@@ -39,19 +40,39 @@ def matmul(x, w, out, epilogue: int = ops.EPI_NONE, act: int = 0) -> None:
     m, k = x.shape
     n = out.shape[1]
     lib().call("hos_gemm_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(out), ops.dtype_code(out.dtype), m, n, k,
-               x.stride(0), w.stride(0), out.stride(0), epilogue, act, ops._stream())
+               x.stride(0), w.stride(0), out.stride(0), epilogue, act, 1, ops._stream())
+
+
+SM_COUNT = 148
+_MIN_K_PER_CTA = 4096      # below this a CTA's 8 warps have too few loads each to be worth another CTA
+
+
+def k_splits_for(n: int, k: int) -> int:
+    """CTAs own 16 output features each; with fewer of them than two per SM, K is split over
+    more CTAs while each keeps enough of K to fill its loads."""
+    ctas = (n + 15) // 16
+    return max(1, min(2 * SM_COUNT // ctas, k // _MIN_K_PER_CTA, 8))
+
+
+def matmul_partials(x, w, k_splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """x . w^T as float32 partial sums [parts, M, N] for a consumer that adds them, if K is worth
+    splitting for these sizes; None if it is not (call `matmul` then)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if k_splits is None:
+        k_splits = k_splits_for(n, k)
+    if k_splits <= 1:
+        return None
+    parts = torch.empty((k_splits, m, n), dtype=torch.float32, device=x.device)
+    lib().call("hos_gemm_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(parts), ops.F32, m, n, k,
+               x.stride(0), w.stride(0), n, ops.EPI_NONE, 0, k_splits, ops._stream())
+    return parts
 
 
 def can_fuse_qkv_rope(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
     """Whether the projection of q, k, v with the rotary encoding and the cache write in its
     epilogue can run: the product's own rules, and head and rotary sizes in steps of 16."""
-    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not 0 < x.shape[0] <= MAX_ROWS:
-        return False
-    if x.shape[1] % 8 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
-        return False
-    if x.data_ptr() % 16 or w.data_ptr() % 16:
-        return False
-    return head_dim % 16 == 0 and rotary_dim % 16 == 0
+    return operands_ok(x, w) and head_dim % 16 == 0 and rotary_dim % 16 == 0
 
 
 def qkv_rope(x, w, out, n_heads: int, n_kv_heads: int, head_dim: int, step, inv_freq, rotary_dim: int, style: int,

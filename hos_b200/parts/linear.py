@@ -53,7 +53,12 @@ def matmul_or_partials(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] > 0):
         from . import gemm_skinny, gemm_tc
         if gemm_skinny.enabled and x.shape[0] <= gemm_skinny.MAX_ROWS:
-            return matmul(x, w)          # a handful of rows: the skinny kernel adds its K shares itself
+            # a handful of rows: K is split over CTAs only when there are few output features
+            if gemm_skinny.operands_ok(x, w):
+                parts = gemm_skinny.matmul_partials(x, w)
+                if parts is not None:
+                    return parts
+            return matmul(x, w)
         if gemm_tc.enabled and x.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 \
                 and x.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
             parts = gemm_tc.matmul_partials(x, w)

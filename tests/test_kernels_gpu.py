@@ -566,7 +566,7 @@ def test_consumers_add_partial_sums():
 
 @pytest.mark.parametrize("shape", [(1, 16, 32), (3, 40, 72), (8, 2304, 2048), (8, 1000, 200), (9, 136, 264),
                                    (16, 520, 2304), (5, 2304, 9216)])
-@pytest.mark.parametrize("variant", ["bf16_out", "f32_out", "gated_gelu", "gated_silu"])
+@pytest.mark.parametrize("variant", ["bf16_out", "f32_out", "gated_gelu", "gated_silu", "k_split"])
 def test_gemm_skinny(shape, variant):
     """The product for up to 16 rows against float64: row counts on both sides of a token tile,
     feature counts and K that fill no tile, both epilogues."""
@@ -587,6 +587,14 @@ def test_gemm_skinny(shape, variant):
         out = torch.empty((M, N), device=DEV)
         gemm_skinny.matmul(a, w, out)
         close(out, ref, torch.float32, scale=3)
+    elif variant == "k_split":
+        # partial sums over shares of K that do not divide it, more shares than k-blocks included
+        for splits in (2, 3, 7):
+            parts = gemm_skinny.matmul_partials(a, w, k_splits=splits)
+            assert parts.shape == (splits, M, N) and parts.dtype == torch.float32
+            close(parts.sum(0), ref, torch.float32, scale=3)
+        assert gemm_skinny.k_splits_for(2304, 9216) == 2 and gemm_skinny.k_splits_for(2304, 2048) == 1
+        assert gemm_skinny.k_splits_for(18432, 2304) == 1
     else:
         act = "gelu_tanh" if variant == "gated_gelu" else "silu"
         out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
