@@ -182,6 +182,95 @@ __global__ void norm_add_norm_vec_kernel(const TY* __restrict__ y, int n_parts, 
     }
 }
 
+// ---- the same for many rows (a prompt) -----------------------------------------------------
+// A CTA of D/8 threads walks over rows (row = blockIdx.x, += gridDim.x); a thread owns 8 columns,
+// keeps the two norms' weights for them in registers for all its rows, and issues the loads of its
+// next row before it reduces the current one, so that the two block sums of a row do not leave
+// the memory pipe empty.  bfloat16 branch output and next-norm output, 32-bit residual stream.
+constexpr int kRowsKernelMinRows = 256;
+struct Row8 { float v[8]; };
+__device__ __forceinline__ Row8 load8(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    return Row8{{a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}};
+}
+__device__ __forceinline__ Row8 load8(const bf16* p) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    Row8 r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { r.v[2 * i] = __low2float(h2[i]); r.v[2 * i + 1] = __high2float(h2[i]); }
+    return r;
+}
+__device__ __forceinline__ void store8(float* p, const Row8& r) {
+    *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(r.v[4], r.v[5], r.v[6], r.v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const Row8& r) {
+    uint4 u;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(r.v[2 * i], r.v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+template <typename TY, typename TH>
+__global__ void norm_add_norm_rows_kernel(const TY* __restrict__ y, int n_parts, size_t part_stride,
+                                          const float* __restrict__ w_post, float eps_post, float add_one_post,
+                                          float* __restrict__ x, const float* __restrict__ w_next, float eps_next,
+                                          float add_one_next, TH* __restrict__ h, int D, int N) {
+    pdl_enter();      // the kernels before this one are complete from here on
+    __shared__ float scratch[32];
+    const int c0 = threadIdx.x * 8;
+    const bool live = c0 < D;                       // the block is rounded up to whole warps
+    Row8 wp, wn;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wp.v[i] = wn.v[i] = 0.f;
+    if (live) {
+        wp = load8(w_post + c0);
+        if (h != nullptr) wn = load8(w_next + c0);
+    }
+    auto fetch_y = [&](int row) {
+        Row8 r = load8(y + (size_t)row * D + c0);
+        for (int p = 1; p < n_parts; ++p) {
+            const Row8 t = load8(y + p * part_stride + (size_t)row * D + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r.v[i] += t.v[i];
+        }
+        return r;
+    };
+    int row = blockIdx.x;
+    Row8 yv, xv;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) yv.v[i] = xv.v[i] = 0.f;
+    if (row < N && live) { yv = fetch_y(row); xv = load8(x + (size_t)row * D + c0); }
+    while (row < N) {
+        const int next = row + gridDim.x;
+        Row8 yn = yv, xn = xv;
+        if (next < N && live) { yn = fetch_y(next); xn = load8(x + (size_t)next * D + c0); }   // in flight during the sums
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += yv.v[i] * yv.v[i];
+        ss = block_sum(ss, scratch);
+        const float r = 1.0f / sqrtf(ss / (float)D + eps_post);
+        float ss2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            xv.v[i] += yv.v[i] * r * (wp.v[i] + add_one_post);
+            ss2 += xv.v[i] * xv.v[i];
+        }
+        if (live) store8(x + (size_t)row * D + c0, xv);
+        if (h != nullptr) {
+            ss2 = block_sum(ss2, scratch);
+            const float r2 = 1.0f / sqrtf(ss2 / (float)D + eps_next);
+            Row8 o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o.v[i] = xv.v[i] * r2 * (wn.v[i] + add_one_next);
+            if (live) store8(h + (size_t)row * D + c0, o);
+        }
+        yv = yn; xv = xn; row = next;
+    }
+}
+
 // Threads per row and chunks per thread for the register-resident kernels; chunks 0: use the others.
 static void vec_shape(int D, int* threads, int* chunks) {
     *chunks = 0;
@@ -518,6 +607,22 @@ extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const 
         }                                                                                                   \
     } while (0)
     if (h == nullptr) h_dtype = y_dtype == kF32 ? kF32 : kBF16;
+    // many rows of a width in steps of 8: CTAs that walk over rows with the next row's loads in flight
+    if (N >= kRowsKernelMinRows && chunks != 0 && D % 8 == 0 && D / 8 <= 1024) {
+        const int threads_r = (D / 8 + 31) / 32 * 32;
+        // about 1024 threads per SM: measured best (3 CTAs of 288 threads at width 2304; more CTAs with fewer rows each
+        // lose what the loads in flight across the sums gain)
+        const int per_sm = 1024 / threads_r < 1 ? 1 : 1024 / threads_r;
+        const int grid_r = N < sm_count_cached() * per_sm ? N : sm_count_cached() * per_sm;
+#define HOS_ROWS(TY, TH) launch_pdl(norm_add_norm_rows_kernel<TY, TH>, dim3(grid_r), dim3(threads_r), 0, stream,            \
+        (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D, N)
+        if (y_dtype == kF32 && h_dtype == kF32) HOS_ROWS(float, float);
+        else if (y_dtype == kF32 && h_dtype == kBF16) HOS_ROWS(float, bf16);
+        else if (y_dtype == kBF16 && h_dtype == kBF16) HOS_ROWS(bf16, bf16);
+        else HOS_REFUSE("norm_add_norm: no kernel for dtypes %d -> %d", y_dtype, h_dtype);
+#undef HOS_ROWS
+        return check_launch("norm_add_norm");
+    }
     if (y_dtype == kF32 && h_dtype == kF32) HOS_LAUNCH(float, float);
     else if (y_dtype == kF32 && h_dtype == kBF16) HOS_LAUNCH(float, bf16);
     else if (y_dtype == kBF16 && h_dtype == kBF16) HOS_LAUNCH(bf16, bf16);

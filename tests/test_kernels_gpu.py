@@ -58,10 +58,13 @@ def test_rmsnorm(D, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_norm_add_norm(dtype):
+@pytest.mark.parametrize("shape", [(5, 328), (3, 30), (700, 328), (300, 2304), (257, 72)])
+def test_norm_add_norm(dtype, shape):
+    """Few rows (a block per row; width 30 is no multiple of 4: the shared-memory kernel) and many
+    rows (blocks that walk over rows, 8 columns per thread; 328/8 = 41 threads fill no warp)."""
     from hos_b200 import ops
     dt = DT[dtype]
-    N, D = 5, 328
+    N, D = shape
     y = (torch.randn(N, D, device=DEV) * 2).to(dt)
     x0 = torch.randn(N, D, device=DEV)
     w1, w2 = torch.randn(D, device=DEV) * 0.1, torch.randn(D, device=DEV) * 0.1
@@ -80,6 +83,13 @@ def test_norm_add_norm(dtype):
     x = x0.clone()
     ops.residual_add(y, x)
     close(x, x0 + y.float(), torch.float32)
+    if D % 4 == 0:                                        # 32-bit partial sums of the branch output
+        parts = torch.randn(3, N, D, device=DEV)
+        x = x0.clone()
+        ops.norm_add_norm(parts, w1, 1e-6, True, x, w2, 1e-5, True, h)
+        want_x = x0 + norm(parts.sum(0), w1, 1e-6)
+        close(x, want_x, torch.float32, scale=2)
+        close(h, norm(want_x, w2, 1e-5).to(dt), dt)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
