@@ -44,24 +44,34 @@ inline int check_launch(const char* what) {
 // kernel calls pdl_wait() before it reads or writes anything in global memory: that returns
 // once the kernels before it are complete and their writes visible.  pdl_launch_dependents()
 // lets the kernel after it be set up in turn.  Both are no-ops for a kernel launched the
-// ordinary way, which is the default: measured on Gemma-2 2B sizes the attribute gains 3% on a
+// ordinary way.  Measured on Gemma-2 2B sizes the attribute gains 3% on a
 // 2,048-token prompt and loses 5% on a decode step at batch 8 (the step's kernels are short and
 // the graph replays them back to back anyway); issuing the first weight loads of the few-rows
-// products before the wait changed nothing at batch 8 and gained 3% at batch 1.  HOS_PDL=1 in the
-// environment switches it on for every kernel.  One pair uses it always: the decode attention
-// kernel fetches old keys while the q/k/v projection before it still runs (launch_ahead).
+// products before the wait changed nothing at batch 8 and gained 3% at batch 1.  So the engine
+// switches it on for prompt steps and off for single-token steps (hos_set_pdl); HOS_PDL=0 or 1 in
+// the environment fixes it for all.  One pair uses it always: the decode attention kernel fetches
+// old keys while the q/k/v projection before it still runs (launch_ahead).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
 
-inline bool pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char* e = getenv("HOS_PDL");
-        on = (e && e[0] && e[0] != '0') ? 1 : 0;
-    }
-    return on == 1;
+// Whether launch_pdl() launches ahead: the caller of the library says so per step (hos_set_pdl:
+// prompts gain from it, single-token steps do not); HOS_PDL=1 or 0 in the environment overrides it.
+inline int& pdl_state() {
+    static int on = 0;
+    return on;
 }
+inline int pdl_env() {
+    static int env = -2;                   // -1: not set
+    if (env == -2) {
+        const char* e = getenv("HOS_PDL");
+        env = (e && e[0]) ? (e[0] != '0' ? 1 : 0) : -1;
+    }
+    return env;
+}
+inline bool pdl_enabled() { return pdl_env() >= 0 ? pdl_env() == 1 : pdl_state() == 1; }
+// One definition per library however many of its files include this header.
+extern "C" __attribute__((weak)) void hos_set_pdl(int on) { hos::pdl_state() = on ? 1 : 0; }
 
 // `ahead`: the kernel may be set up while the one before it on the stream is still running (if that
 // one lets it: pdl_launch_dependents()), and must call pdl_wait() before it touches what that one wrote.

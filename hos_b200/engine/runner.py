@@ -14,6 +14,7 @@ import torch
 
 from ..cache import CacheManager
 from ..config.base import ModelConfig, read_config_json
+from .. import ops
 from ..errors import ExtensionMissingError, HosError
 from ..model import Model
 from ..parts.base import Runtime
@@ -21,6 +22,7 @@ from ..registry import config_from_dict, plan_for
 from ..weights import RandomSource, SafetensorsFolder, load_tensors
 from .batch import build_step
 
+LAUNCH_AHEAD_MIN_TOKENS = 256       # steps of at least this many tokens launch their kernels ahead
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
           "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
 
@@ -138,7 +140,12 @@ class Runner:
         for s, st, toks in zip(slots, starts, token_lists):
             self.cache.extend(s, st + len(toks))
         self.cache.flush()
-        return self.model.hidden(info, self.cache), rows_t
+        # a step of many tokens: its kernels are long enough for the next one's set-up to hide under them
+        ops.set_launch_ahead(info.n_tokens >= LAUNCH_AHEAD_MIN_TOKENS)
+        try:
+            return self.model.hidden(info, self.cache), rows_t
+        finally:
+            ops.set_launch_ahead(False)
 
     def decode_steps_timed(self, slots, first_tokens, warmup: int, steps: int, clocks=None):
         """`warmup` untimed and `steps` timed greedy decode steps, issued back to back with

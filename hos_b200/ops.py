@@ -12,7 +12,7 @@ import ctypes
 import os
 import re
 from dataclasses import dataclass
-from typing import Optional
+from typing import List, Optional
 
 import torch
 
@@ -97,6 +97,11 @@ class Library:
             self._last_error = self.lib.hos_last_error
             self._last_error.restype = ctypes.c_char_p
             self._last_error.argtypes = []
+        self._set_pdl = getattr(self.lib, "hos_set_pdl", None)
+        if self._set_pdl is not None:
+            self._set_pdl.restype, self._set_pdl.argtypes = None, [ctypes.c_int]
+            self._set_pdl(1 if _launch_ahead else 0)
+        _libraries.append(self)
 
     def fn(self, name: str, signature: Optional[str] = None):
         f = self._fns.get(name)
@@ -118,6 +123,23 @@ class Library:
         if rc != 0:
             msg = self._last_error() if self._last_error else b""
             raise KernelError((msg or b"").decode(errors="replace") or f"{name} failed with code {rc}")
+
+
+_libraries: List["Library"] = []
+_launch_ahead = False
+
+
+def set_launch_ahead(on: bool) -> None:
+    """Whether kernels are launched so that they may be set up while the kernel before them still
+    runs (programmatic dependent launch).  It pays for steps of many tokens, whose kernels are
+    launched one by one, and costs for single-token steps; the runner switches it per step."""
+    global _launch_ahead
+    if on == _launch_ahead:
+        return
+    _launch_ahead = on
+    for lib in _libraries:
+        if lib._set_pdl is not None:
+            lib._set_pdl(1 if on else 0)
 
 
 _core: Optional[Library] = None
