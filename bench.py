@@ -52,11 +52,21 @@ def peaks():
         try:
             with open(path) as f:
                 raw = json.load(f)
-            out = dict(FALLBACK_PEAKS)
-            for k in out:
-                if isinstance(raw.get(k), (int, float)):
-                    out[k] = float(raw[k])
-            return out, "measured"
+            out, found = dict(FALLBACK_PEAKS), 0
+
+            def look(node):            # the keys may sit at the top or one level down
+                nonlocal found
+                if not isinstance(node, dict):
+                    return
+                for k, v in node.items():
+                    if k in out and isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+                        out[k] = float(v)
+                        found += 1
+                    elif isinstance(v, dict):
+                        look(v)
+            look(raw)
+            if found:
+                return out, "measured"
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
@@ -292,7 +302,7 @@ def main() -> int:
         fl = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
         line["prefill"] = {"value": PREFILL_TOKENS * 1e3 / ms, "tokens": PREFILL_TOKENS, "ms": ms,
                            "frac": fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "tflop": fl / 1e12,
-                           "of": pk_src}
+                           "peak_tflops": pk["bf16_tflops"], "of": pk_src}
     if not args.no_points:
         pts = {}
         for b in (1, 64):
