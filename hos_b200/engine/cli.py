@@ -3,7 +3,7 @@
 
     hos -m <dir> -p <ids> [-n 64] [--temp 0.0] [--top-k 40] [--top-p 0.95]
         [--repeat-penalty 1.1] [--repeat-last-n 64] [--seed 42] [--no-echo]
-    hos -m <dir> --bench [-n 64] [-p <ids>]        # prompt and decode throughput
+    hos -m <dir> --bench [-n 64] [-p <ids>] [--batch B] [--prompt-len T] [--ctx C]   # prompt and decode throughput
     hos -m <dir> --perplexity <ids>                # score a token sequence
 
 Prompts are token ids separated by commas (tokenizers are not part of this library); -p may
@@ -25,7 +25,9 @@ USAGE = """usage: hos -m model_dir -p "id,id,..." [-n 64] [--temp 0.0] [--seed 4
        hos -m model_dir --bench                  # prefill/decode throughput
        hos -m model_dir --perplexity "id,id,..." # score a token sequence
 options: --top-k 40 --top-p 0.95 --repeat-penalty 1.1 --repeat-last-n 64 --no-echo --fp32
-         --random config.json (random weights from --seed instead of -m)"""
+         --random config.json (random weights from --seed instead of -m)
+         --ctx C (longest sequence the cache is sized for)
+         --bench: --batch B sequences of --prompt-len T fixed ids each (default: one prompt of 16)"""
 
 
 def parse_ids(text: str) -> List[int]:
@@ -45,6 +47,7 @@ class Args:
         self.gpu, self.no_echo, self.bench, self.fp32 = True, False, False, False
         self.perplexity: Optional[List[int]] = None
         self.random: Optional[str] = None
+        self.batch, self.prompt_len, self.ctx = 1, 16, None
 
 
 def parse_args(argv: List[str]) -> Args:
@@ -88,6 +91,12 @@ def parse_args(argv: List[str]) -> Args:
             a.random = value(arg)
         elif arg == "--perplexity":
             a.perplexity = parse_ids(value(arg))
+        elif arg == "--batch":
+            a.batch = max(1, int(value(arg)))
+        elif arg == "--prompt-len":
+            a.prompt_len = max(1, int(value(arg)))
+        elif arg == "--ctx":
+            a.ctx = max(1, int(value(arg)))
         elif arg in ("-h", "--help"):
             print(USAGE, file=sys.stderr)
             sys.exit(0)
@@ -99,10 +108,10 @@ def parse_args(argv: List[str]) -> Args:
     return a
 
 
-def bench_prompt(vocab: int) -> List[int]:
+def bench_prompt(vocab: int, length: int = 16, which: int = 0) -> List[int]:
     """A fixed prompt, so that numbers compare from run to run (the reference's is a fixed
-    sentence, src/main.rs:44; here 16 fixed ids)."""
-    return [(i * 7919 + 13) % vocab for i in range(1, 17)]
+    sentence, src/main.rs:44; here fixed ids, another run of them for each sequence of a batch)."""
+    return [((i + 1000003 * which) * 7919 + 13) % vocab for i in range(1, length + 1)]
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -115,24 +124,32 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .. import HosError
     from .engine import Engine
     dtype = "float32" if args.fp32 else "bfloat16"
+    n_seqs = max(1, len(args.prompts), args.batch if args.bench else 1)
+    size = {}
+    if args.ctx is not None:
+        size = dict(max_seq_len=args.ctx, max_tokens=n_seqs * ((args.ctx + 63) // 64 * 64))
     try:
         if args.random:
             from .. import models  # noqa: F401
             from ..registry import config_from_dict
             with open(args.random) as f:
                 cfg = config_from_dict(json.load(f))
-            eng = Engine.from_config(cfg, seed=args.seed, dtype=dtype, max_batch=max(1, len(args.prompts)))
+            eng = Engine.from_config(cfg, seed=args.seed, dtype=dtype, max_batch=n_seqs, **size)
         else:
             model = args.model or os.environ.get("HOS_MODEL")
-            eng = Engine(model, gpu=args.gpu, dtype=dtype, max_batch=max(1, len(args.prompts)))
+            eng = Engine(model, gpu=args.gpu, dtype=dtype, max_batch=n_seqs, **size)
     except (HosError, OSError) as e:
         print(f"[hos] error: {e}", file=sys.stderr)
         return 1
     print(f"[hos] load took {time.perf_counter() - t0:.2f}s", file=sys.stderr)
 
     if args.bench:
-        prompt = args.prompts[0] if args.prompts else bench_prompt(eng.vocab_size())
-        b = eng.bench(prompt, args.n_predict if args.n_predict > 0 else 64)
+        prompts = args.prompts or [bench_prompt(eng.vocab_size(), args.prompt_len, i) for i in range(args.batch)]
+        try:
+            b = eng.bench(prompts if len(prompts) > 1 else prompts[0], args.n_predict if args.n_predict > 0 else 64)
+        except HosError as e:
+            print(f"[hos] error: {e}", file=sys.stderr)
+            return 1
         print("=== HOS benchmark ===")
         print(f"backend    : B200 GPU ({dtype})")
         print(f"prefill    : {b[0]} tok in {b[1]:.3f}s  ({b[2]:.1f} tok/s)")

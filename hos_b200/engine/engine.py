@@ -143,38 +143,48 @@ class Engine:
         mean = nll / len(feed)
         return len(feed), mean, math.exp(mean)
 
-    def bench(self, prompt: Sequence[int], decode_tokens: int = 64):
+    def bench(self, prompt: Prompt, decode_tokens: int = 64):
         """Time the prompt step and greedy decoding separately, after one warm-up prompt
-        step (src/lib.rs:683-727).  Returns (prefill_tokens, prefill_secs, prefill_tps,
-        decode_tokens, decode_secs, decode_tps)."""
+        step (src/lib.rs:683-727).  `prompt` is one prompt or a batch of them (decoded
+        together; a sequence that meets a stop token or the context's end leaves the batch).
+        Returns (prefill_tokens, prefill_secs, prefill_tps, decode_tokens, decode_secs,
+        decode_tps), tokens counted over the batch."""
         r = self.runner
-        prompt = list(prompt)
+        prompts = [list(p) for p in prompt] if _is_batch(prompt) else [list(prompt)]
+        n_prompt = sum(len(p) for p in prompts)
         sampler = Sampler(SamplingParams.pure(), r.device)
-        slot = r.admit(1)[0]
-        r.step([slot], [prompt])
-        r.release(slot)
-        slot = r.admit(1)[0]
-        sampler.open(slot, 0)
+        slots = r.admit(len(prompts))
+        r.step(slots, prompts)
+        for s in slots:
+            r.release(s)
+        slots = r.admit(len(prompts))
+        for i, s in enumerate(slots):
+            sampler.open(s, i)
+        live = list(slots)
         try:
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            logits = r.step([slot], [prompt])
+            logits = r.step(live, prompts)
             torch.cuda.synchronize()
             prefill_secs = time.perf_counter() - t0
             produced = 0
             t1 = time.perf_counter()
             for _ in range(decode_tokens):
-                tok = sampler.sample(logits, [slot])[0]
-                if tok in self.stop_ids or r.length(slot) >= r.max_seq_len:
+                toks = sampler.sample(logits, live)
+                keep = [i for i, (s, t) in enumerate(zip(live, toks))
+                        if t not in self.stop_ids and r.length(s) < r.max_seq_len]
+                if not keep:
                     break
-                logits = r.step([slot], [[tok]])
-                produced += 1
+                live, toks = [live[i] for i in keep], [toks[i] for i in keep]
+                logits = r.step(live, [[t] for t in toks])
+                produced += len(live)
             torch.cuda.synchronize()
             decode_secs = time.perf_counter() - t1
         finally:
-            sampler.close(slot)
-            r.release(slot)
-        return (len(prompt), prefill_secs, len(prompt) / max(prefill_secs, 1e-9),
+            for s in slots:
+                sampler.close(s)
+                r.release(s)
+        return (n_prompt, prefill_secs, n_prompt / max(prefill_secs, 1e-9),
                 produced, decode_secs, produced / max(decode_secs, 1e-9))
 
     def vocab_size(self) -> int:

@@ -22,8 +22,10 @@ def test_defaults_are_the_references():
 def test_options_parse():
     a = cli.parse_args(["-m", "dir", "-p", "1,2, 3", "--prompt", "7", "-n", "5", "--temp", "0.7", "--top-k", "3",
                         "--top-p", "0.5", "--repeat-penalty", "1.3", "--repeat-last-n", "9", "--seed", "11",
-                        "--no-echo", "--bench", "--fp32", "--gpu"])
+                        "--no-echo", "--bench", "--fp32", "--gpu", "--batch", "4", "--prompt-len", "100", "--ctx", "512"])
     assert a.model == "dir" and a.prompts == [[1, 2, 3], [7]]
+    assert (a.batch, a.prompt_len, a.ctx) == (4, 100, 512)
+    assert cli.bench_prompt(50, 7, 0) != cli.bench_prompt(50, 7, 1) and len(cli.bench_prompt(50, 7, 1)) == 7
     assert (a.n_predict, a.temp, a.top_k, a.top_p, a.rep_penalty, a.repeat_last_n, a.seed) == (5, 0.7, 3, 0.5, 1.3, 9, 11)
     assert a.no_echo and a.bench and a.fp32
 
@@ -64,3 +66,8 @@ def test_generation_and_bench_through_the_command_line(tmp_path):
                        env=dict(os.environ, HOS_MODEL=folder))
     out = p.stdout.decode()
     assert p.returncode == 0 and "=== HOS benchmark ===" in out and "prefill    : 16 tok" in out and "decode     : " in out
+    p = subprocess.run([HOS, "--bench", "-n", "4", "--batch", "3", "--prompt-len", "10", "--ctx", "64"],
+                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, env=dict(os.environ, HOS_MODEL=folder))
+    out = p.stdout.decode()
+    assert p.returncode == 0, p.stderr.decode()
+    assert "prefill    : 30 tok" in out and "decode     : " in out

@@ -188,3 +188,7 @@ def test_perplexity_and_bench(tmp_path):
     assert n == 49 and abs(mean - want) < 1e-5 and abs(ppl - torch.tensor(want).exp().item()) < 1e-2
     b = eng.bench(ids[:20], 5)
     assert b[0] == 20 and b[3] <= 5 and b[2] > 0 and (b[3] == 0 or b[5] > 0)
+    b = eng.bench([ids[:20], ids[5:12], ids[30:31]], 4)           # a batch: tokens counted over it
+    assert b[0] == 28 and b[3] <= 12 and b[2] > 0
+    eng.runner.cache.check()
+    assert not eng.runner.cache.lengths                            # every slot was given back
