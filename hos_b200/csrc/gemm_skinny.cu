@@ -1,4 +1,4 @@
-// Matrix product for a handful of rows (decoding): out[M, N] = A[M, K] . W[N, K]^T with M <= 16,
+// Matrix product for a handful of rows (decoding): out[M, N] = A[M, K] . W[N, K]^T with M <= 32,
 // bfloat16 operands, 32-bit accumulation.  The work is reading W once; everything is arranged so
 // that nothing stands between the launch and the first bytes of W:
 //
@@ -23,7 +23,9 @@ namespace hos {
 
 constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
-constexpr int kUnroll = 8;          // k-blocks of 32 whose loads are issued before any is used
+constexpr int kUnroll = 8;          // k-blocks of 32 whose loads are issued before any is used: fewer with more token tiles (registers)
+template <int MT> struct Unroll { static constexpr int value = MT == 1 ? 8 : (MT == 2 ? 4 : 2); };
+constexpr int kMaxTokenTiles = 4;       // token tiles of 8: up to 32 rows
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 // streaming load for the weights: read once, do not keep in L1
@@ -34,7 +36,7 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
     return v;
 }
 
-// MT: token tiles of 8 (1: M <= 8, 2: M <= 16).  GATED: rows come in gate/up pairs.
+// MT: token tiles of 8 (M <= 8 MT).  GATED: rows come in gate/up pairs.
 template <int MT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
@@ -60,9 +62,13 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
     const bool ok0 = r0 < row_limit, ok1 = r1 < row_limit;
     const bf16* w0 = W + (size_t)(ok0 ? r0 : row_base) * ldw + 8 * t4;
     const bf16* w1 = W + (size_t)(ok1 ? r1 : row_base) * ldw + 8 * t4;
-    const bf16* a0 = A + (size_t)min(g, M - 1) * lda + 8 * t4;
-    const bf16* a1 = A + (size_t)min(g + 8, M - 1) * lda + 8 * t4;
-    const bool tok0 = g < M, tok1 = MT == 2 && g + 8 < M;
+    const bf16* a[MT];
+    bool tok[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        a[m] = A + (size_t)min(8 * m + g, M - 1) * lda + 8 * t4;
+        tok[m] = 8 * m + g < M;
+    }
 
     float acc[MT][4];
 #pragma unroll
@@ -70,26 +76,25 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
     for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
-        uint4 wa[kUnroll], wb[kUnroll], xa[kUnroll], xb[kUnroll];
+        uint4 wa[kUnroll], wb[kUnroll], x[MT][kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (kb + u) * 32 + 8 * t4;
             const bool in = (kb + u) < kb_end && k < K;          // K is a multiple of 8: a 16-byte load is whole
             wa[u] = (in && ok0) ? ldg16_stream(w0 + (size_t)(kb + u) * 32) : zero;
             wb[u] = (in && ok1) ? ldg16_stream(w1 + (size_t)(kb + u) * 32) : zero;
-            xa[u] = (in && tok0) ? ldg16(a0 + (size_t)(kb + u) * 32) : zero;
-            if (MT == 2) xb[u] = (in && tok1) ? ldg16(a1 + (size_t)(kb + u) * 32) : zero;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) x[m][u] = (in && tok[m]) ? ldg16(a[m] + (size_t)(kb + u) * 32) : zero;
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             // the thread's 8 consecutive k as two MMAs: k slots (2t,2t+1,2t+8,2t+9) <- elements (0,1,2,3) then (4,5,6,7)
             const uint32_t fa[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
             const uint32_t fb[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
-            mma_bf16(acc[0], fa, xa[u].x, xa[u].y);
-            mma_bf16(acc[0], fb, xa[u].z, xa[u].w);
-            if (MT == 2) {
-                mma_bf16(acc[1], fa, xb[u].x, xb[u].y);
-                mma_bf16(acc[1], fb, xb[u].z, xb[u].w);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                mma_bf16(acc[m], fa, x[m][u].x, x[m][u].y);
+                mma_bf16(acc[m], fb, x[m][u].z, x[m][u].w);
             }
         }
     }
@@ -191,33 +196,36 @@ qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, b
     const int kb_begin = warp * per_way, kb_end = min(k_blocks, kb_begin + per_way);
     const bf16* w0 = W + (size_t)(f_lo + step * g) * ldw + 8 * t4;
     const bf16* w1 = W + (size_t)(f_hi + step * g) * ldw + 8 * t4;
-    const bf16* a0 = A + (size_t)min(g, M - 1) * lda + 8 * t4;
-    const bf16* a1 = A + (size_t)min(g + 8, M - 1) * lda + 8 * t4;
-    const bool tok0 = g < M, tok1 = MT == 2 && g + 8 < M;
+    const bf16* a[MT];
+    bool tok[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        a[m] = A + (size_t)min(8 * m + g, M - 1) * lda + 8 * t4;
+        tok[m] = 8 * m + g < M;
+    }
     float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
-        uint4 wa[kUnroll], wb[kUnroll], xa[kUnroll], xb[kUnroll];
+        uint4 wa[kUnroll], wb[kUnroll], x[MT][kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int k = (kb + u) * 32 + 8 * t4;
             const bool in = (kb + u) < kb_end && k < K;
             wa[u] = in ? ldg16_stream(w0 + (size_t)(kb + u) * 32) : zero;
             wb[u] = in ? ldg16_stream(w1 + (size_t)(kb + u) * 32) : zero;
-            xa[u] = (in && tok0) ? ldg16(a0 + (size_t)(kb + u) * 32) : zero;
-            if (MT == 2) xb[u] = (in && tok1) ? ldg16(a1 + (size_t)(kb + u) * 32) : zero;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) x[m][u] = (in && tok[m]) ? ldg16(a[m] + (size_t)(kb + u) * 32) : zero;
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const uint32_t fa[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
             const uint32_t fb[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
-            mma_bf16(acc[0], fa, xa[u].x, xa[u].y);
-            mma_bf16(acc[0], fb, xa[u].z, xa[u].w);
-            if (MT == 2) {
-                mma_bf16(acc[1], fa, xb[u].x, xb[u].y);
-                mma_bf16(acc[1], fb, xb[u].z, xb[u].w);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                mma_bf16(acc[m], fa, x[m][u].x, x[m][u].y);
+                mma_bf16(acc[m], fb, x[m][u].z, x[m][u].w);
             }
         }
     }
@@ -268,14 +276,14 @@ using namespace hos;
 
 extern "C" const char* hos_last_error() { return error_buffer(); }
 
-// out[M, N] = A[M, K] . W[N, K]^T for M <= 16.  epilogue 0: none (out bf16 or f32); 2: gated (W has
+// out[M, N] = A[M, K] . W[N, K]^T for M <= 32.  epilogue 0: none (out bf16 or f32); 2: gated (W has
 // 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
 // multiples of 8 elements, A and W 16-byte aligned.
 // k_splits > 1: `out` is [k_splits][M][ldo] 32-bit partial sums for a consumer that adds them (no epilogue).
 extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
                                int lda, int ldw, int ldo, int epilogue, int act, int k_splits, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16) HOS_REFUSE("gemm_skinny: %d rows are more than 16", M);
+    if (M > 8 * kMaxTokenTiles) HOS_REFUSE("gemm_skinny: %d rows are more than %d", M, 8 * kMaxTokenTiles);
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
         HOS_REFUSE("gemm_skinny: K and the leading dimensions must be multiples of 8 elements and the operands "
                    "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
@@ -288,20 +296,28 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
 #define HOS_SK(MT, G, T)                                                                                     \
     launch_pdl(gemm_skinny_kernel<MT, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
+#define HOS_SK_M(G, T)                                  \
+    do {                                                \
+        if (M <= 8) HOS_SK(1, G, T);                    \
+        else if (M <= 16) HOS_SK(2, G, T);              \
+        else if (M <= 24) HOS_SK(3, G, T);              \
+        else HOS_SK(4, G, T);                           \
+    } while (0)
     if (epilogue == 2) {
-        if (M <= 8) HOS_SK(1, true, bf16); else HOS_SK(2, true, bf16);
+        HOS_SK_M(true, bf16);
     } else if (out_dtype == kBF16) {
-        if (M <= 8) HOS_SK(1, false, bf16); else HOS_SK(2, false, bf16);
+        HOS_SK_M(false, bf16);
     } else if (out_dtype == kF32) {
-        if (M <= 8) HOS_SK(1, false, float); else HOS_SK(2, false, float);
+        HOS_SK_M(false, float);
     } else {
         HOS_REFUSE("gemm_skinny: unknown output dtype %d", out_dtype);
     }
+#undef HOS_SK_M
 #undef HOS_SK
     return check_launch("gemm_skinny");
 }
 
-// The q/k/v projection of up to 16 tokens with rotary encoding and cache write fused in:
+// The q/k/v projection of up to 32 tokens with rotary encoding and cache write fused in:
 // out[M, (n_heads + 2 n_kv_heads) * head_dim] = A[M, K] . W^T, q and k heads rotated, keys and values
 // stored at the tokens' places.  Needs head_dim % 16 == 0 and rotary_dim % 16 == 0 (0: no rotation).
 extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int M, int K, int lda, int ldw, int ldo,
@@ -311,7 +327,7 @@ extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int 
                                    const int* page_table, int table_stride, int ring_pages, int write_cache,
                                    cudaStream_t stream) {
     if (M <= 0) return 0;
-    if (M > 16) HOS_REFUSE("qkv_rope_skinny: %d rows are more than 16", M);
+    if (M > 8 * kMaxTokenTiles) HOS_REFUSE("qkv_rope_skinny: %d rows are more than %d", M, 8 * kMaxTokenTiles);
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
         HOS_REFUSE("qkv_rope_skinny: K and the leading dimensions must be multiples of 8 elements and the operands "
                    "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
@@ -323,11 +339,13 @@ extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int 
     q.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
     q.n_heads = n_heads; q.rotary_dim = rotary_dim; q.style = style; q.write_cache = write_cache;
     const unsigned grid = (unsigned)((n_heads + 2 * n_kv_heads) * (head_dim / 16));
-    if (M <= 8)
-        launch_pdl(qkv_rope_skinny_kernel<1>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W,
-                   (bf16*)out, M, K, lda, ldw, ldo, q);
-    else
-        launch_pdl(qkv_rope_skinny_kernel<2>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W,
-                   (bf16*)out, M, K, lda, ldw, ldo, q);
+#define HOS_QR(MT)                                                                                                      \
+    launch_pdl(qkv_rope_skinny_kernel<MT>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, \
+               (bf16*)out, M, K, lda, ldw, ldo, q)
+    if (M <= 8) HOS_QR(1);
+    else if (M <= 16) HOS_QR(2);
+    else if (M <= 24) HOS_QR(3);
+    else HOS_QR(4);
+#undef HOS_QR
     return check_launch("qkv_rope_skinny");
 }

@@ -22,7 +22,7 @@ import torch
 from .. import ops
 from ..parts.base import StepInfo
 
-BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+BUCKETS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
 def bucket_for(n: int) -> int:
@@ -30,6 +30,12 @@ def bucket_for(n: int) -> int:
         if n <= b:
             return b
     return (n + 63) // 64 * 64
+
+
+def smaller_bucket(b: int) -> int:
+    """The largest bucket below b (0 if there is none): a session of b rows holds more live rows than that."""
+    below = [x for x in BUCKETS if x < b]
+    return below[-1] if below else max(0, b - 64)
 
 
 class DecodeSession:
@@ -75,7 +81,7 @@ class DecodeSession:
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot,
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
                         max_len_after=self._max_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
-                        starts_host=())
+                        starts_host=(), min_live=smaller_bucket(self.b) + 1)
 
     def feed(self, slots: Sequence[int], tokens: Sequence[int], lengths_before: Sequence[int]) -> None:
         """Host token ids, slots and each sequence's length before the step -> the static

@@ -30,16 +30,32 @@ def lib_for(head_dim: int) -> ops.Library:
     return lib
 
 
-def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int]) -> int:
-    """How many shares the keys of one (token, kv head) are cut into: as many as give every SM
-    one work item (measured: more items per CTA cost more than they balance), but no share
-    under two pages."""
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int],
+                  min_live: int = 0) -> int:
+    """How many shares the keys of one (token, kv head) are cut into.  The kernel's CTAs (one per
+    SM) take items one after another; an item costs a fixed part (look-ups, first loads, the merge)
+    and a part per page.  The number of shares is the one that makes the step shortest by that
+    model (constants measured at head size 256), for all `n_tokens` rows live and, if the step is
+    a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well."""
     chunks = (group + 15) // 16
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
-    pairs = max(1, n_tokens * n_kv_heads * chunks)
-    want = SM_COUNT // pairs        # one item per CTA while that fills the GPU: an item's fixed cost is high
-    return max(1, min(want, (pages + 1) // 2, MAX_SPLITS))
+    per_token = max(1, n_kv_heads * chunks)
+    hi = max(1, n_tokens)
+    lo = min(max(1, min_live), hi) if min_live else hi
+    lives = (lo, (lo + hi) // 2, hi) if lo < hi else (hi,)          # fewest, middle and most live rows
+    best, best_cost = 1, None
+    for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
+        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + (_MERGE_US if s > 1 else 0.0)
+        cost = sum(-(-live * per_token * s // SM_COUNT) * per_item for live in lives)
+        if best_cost is None or cost < 0.97 * best_cost:          # more shares only for a clear gain
+            best, best_cost = s, cost
+    return best
+
+
+# measured: 8 sequences of 8192 keys take 130 / 76 / 65.5 / 72.6 us with 1 / 2 / 4 / 9 shares; at 64 sequences two
+# shares instead of one cost 27 us more per layer
+_ITEM_US, _PAGE_US, _MERGE_US = 7.0, 1.1, 4.0
 
 
 _ticket_store: Dict[object, torch.Tensor] = {}
@@ -56,7 +72,7 @@ def _tickets(device, n: int) -> torch.Tensor:
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
            window: Optional[int], max_len: int, n_splits: Optional[int] = None,
-           max_new: Optional[int] = None) -> None:
+           max_new: Optional[int] = None, min_live: int = 0) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
     position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
     the kernel may fetch keys that lie below them while the kernel before it (which writes the
@@ -64,7 +80,7 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
     hd, nkv = cache.head_dim, cache.n_kv_heads
     lib = lib_for(hd)
     if n_splits is None:
-        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window)
+        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live)
     ws = tickets = None
     if n_splits > 1:
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
@@ -139,5 +155,6 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
     if not enabled["decode"]:
         return False
     decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
-           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new)
+           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new,
+           min_live=getattr(step, "min_live", 0))
     return True

@@ -92,6 +92,7 @@ class StepInfo:
     slots_host: Sequence[int] = ()   # the same as seq_slot, on the host
     cu_host: Sequence[int] = ()      # the same as cu_seqlens, on the host
     starts_host: Sequence[int] = ()  # each sequence's length before the step
+    min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
 
 
 class CallStore:

@@ -1,4 +1,4 @@
-"""Python face of the matrix product for up to 16 rows (csrc/gemm_skinny.cu): what decoding at
+"""Python face of the matrix product for up to 32 rows (csrc/gemm_skinny.cu): what decoding at
 small batch runs.  bfloat16 operands, K a multiple of 8; epilogues none and gated."""
 from __future__ import annotations
 
@@ -8,7 +8,7 @@ import torch
 
 from .. import ops
 
-MAX_ROWS = 16
+MAX_ROWS = 32
 _lib: Optional[ops.Library] = None
 enabled = True          # tests switch it off to compare with the other kernels
 

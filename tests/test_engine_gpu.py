@@ -71,7 +71,7 @@ def test_padding_rows_change_nothing(tmp_path, dtype):
     from hos_b200.engine.batch import build_step
     folder = make_folder(tmp_path, "B")
     rng = random.Random(5)
-    prompts = [random_tokens(rng, n, 512) for n in (3, 20, 9)]
+    prompts = [random_tokens(rng, n, 512) for n in (3, 20, 19)]       # 42 rows: past the few-rows kernels
     outs = []
     for pad in (0, 5, 64):
         r = runner_for(folder, dtype)

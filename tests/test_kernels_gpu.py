@@ -575,11 +575,12 @@ def test_consumers_add_partial_sums():
 
 
 @pytest.mark.parametrize("shape", [(1, 16, 32), (3, 40, 72), (8, 2304, 2048), (8, 1000, 200), (9, 136, 264),
-                                   (16, 520, 2304), (5, 2304, 9216)])
+                                   (16, 520, 2304), (5, 2304, 9216), (17, 136, 520), (24, 2304, 2048),
+                                   (25, 40, 72), (32, 520, 2304)])
 @pytest.mark.parametrize("variant", ["bf16_out", "f32_out", "gated_gelu", "gated_silu", "k_split"])
 def test_gemm_skinny(shape, variant):
-    """The product for up to 16 rows against float64: row counts on both sides of a token tile,
-    feature counts and K that fill no tile, both epilogues."""
+    """The product for up to 32 rows against float64: row counts on both sides of every token
+    tile of 8, feature counts and K that fill no tile, both epilogues."""
     from hos_b200 import ops
     from hos_b200.parts import gemm_skinny
     M, N, K = shape
@@ -612,14 +613,16 @@ def test_gemm_skinny(shape, variant):
         g, u = ref, a.double() @ w[N:].double().T
         af = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
         close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
-    big = torch.empty((17, N), device=DEV, dtype=torch.bfloat16)
-    assert not gemm_skinny.can_take(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w, big, ops.EPI_NONE)
+    big = torch.empty((33, N), device=DEV, dtype=torch.bfloat16)
+    assert not gemm_skinny.can_take(torch.zeros(33, K, device=DEV, dtype=torch.bfloat16), w, big, ops.EPI_NONE)
 
 
 @pytest.mark.parametrize("cfg", [dict(M=1, nh=3, nkv=1, hd=48, rot=48, style="rotate_half", K=72, ring=0),
                                  dict(M=7, nh=2, nkv=2, hd=64, rot=32, style="rotate_half", K=200, ring=2),
                                  dict(M=9, nh=4, nkv=2, hd=64, rot=64, style="interleaved", K=136, ring=0),
                                  dict(M=16, nh=8, nkv=4, hd=256, rot=256, style="rotate_half", K=2304, ring=0),
+                                 dict(M=23, nh=2, nkv=1, hd=64, rot=64, style="interleaved", K=72, ring=0),
+                                 dict(M=32, nh=4, nkv=2, hd=128, rot=128, style="rotate_half", K=520, ring=2),
                                  dict(M=5, nh=2, nkv=1, hd=32, rot=0, style="rotate_half", K=64, ring=0),
                                  dict(M=4, nh=3, nkv=0, hd=32, rot=16, style="interleaved", K=96, ring=0)])
 def test_qkv_projection_with_rotation_and_cache_write_fused(cfg):
