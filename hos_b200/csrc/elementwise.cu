@@ -393,8 +393,13 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return u;
 }
 
+// PARTS: the rows come as n_parts partial sums of 32-bit floats (what a matrix product that split K
+// leaves) and are formed here; everything, rotated or not, is then written to the bfloat16 row.
+// Otherwise the bfloat16 rows are rotated in place.  gridDim.y CTAs share a token's chunks.
+template <bool PARTS>
 __global__ void __launch_bounds__(256)
-rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
+rope_kv_write_vec_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride,
+                         bf16* __restrict__ qkv, int row_stride, int n_heads,
                          const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_len_after,
                          const float* __restrict__ inv_freq, int rotary_dim, int style,
@@ -417,6 +422,21 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
     }
     __syncthreads();
     bf16* row = qkv + (size_t)n * row_stride;
+    const float* prow = PARTS ? parts + (size_t)n * row_stride : nullptr;
+    // 8 elements of the row from element e on, as floats
+    auto fetch = [&](int e, float (&f)[8]) {
+        if (PARTS) {
+            const float4 a = *reinterpret_cast<const float4*>(prow + e), b2 = *reinterpret_cast<const float4*>(prow + e + 4);
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b2.x; f[5] = b2.y; f[6] = b2.z; f[7] = b2.w;
+            for (int p = 1; p < n_parts; ++p) {
+                const float4 c = *reinterpret_cast<const float4*>(prow + p * part_stride + e);
+                const float4 d = *reinterpret_cast<const float4*>(prow + p * part_stride + e + 4);
+                f[0] += c.x; f[1] += c.y; f[2] += c.z; f[3] += c.w; f[4] += d.x; f[5] += d.y; f[6] += d.z; f[7] += d.w;
+            }
+        } else {
+            unpack8(*reinterpret_cast<const uint4*>(row + e), f);
+        }
+    };
     bf16* kp = (bf16*)cache.k_pages;
     bf16* vp = (bf16*)cache.v_pages;
     const int r = pos % kPageTokens;
@@ -427,24 +447,25 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
     const int per_qk_head = rot_items + tail_chunks;
     const int n_qk = n_heads + nkv;
     const int total = n_qk * per_qk_head + nkv * chunks;
-    for (int item = threadIdx.x; item < total; item += blockDim.x) {
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < total; item += gridDim.y * blockDim.x) {
         if (item < n_qk * per_qk_head) {
             const int head = item / per_qk_head, j = item % per_qk_head;
-            bf16* hp = row + (size_t)head * hd;
+            const int h0 = head * hd;
             const bool is_k = head >= n_heads;
             const size_t tile = is_k && page >= 0 ? kv_tile_offset(cache, page, head - n_heads) : 0;
-            if (j >= rot_items) {                                // beyond the rotated dimensions: keys go to the cache as they are
-                if (is_k && page >= 0) {
-                    const int d0 = rotary_dim + (j - rot_items) * 8;
-                    *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, d0, hd)) = *reinterpret_cast<const uint4*>(hp + d0);
-                }
+            float fa[8], fb[8];
+            if (j >= rot_items) {                                // beyond the rotated dimensions: as they are
+                const int d0 = rotary_dim + (j - rot_items) * 8;
+                if (!PARTS && !(is_k && page >= 0)) continue;
+                fetch(h0 + d0, fa);
+                const uint4 oa = pack8(fa);
+                if (PARTS) *reinterpret_cast<uint4*>(row + h0 + d0) = oa;
+                if (is_k && page >= 0) *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, d0, hd)) = oa;
                 continue;
             }
-            float fa[8], fb[8];
             if (style == 0) {
                 const int da = j * 8, db = half + j * 8;
-                const uint4 ua = *reinterpret_cast<const uint4*>(hp + da), ub = *reinterpret_cast<const uint4*>(hp + db);
-                unpack8(ua, fa); unpack8(ub, fb);
+                fetch(h0 + da, fa); fetch(h0 + db, fb);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float2 sc = sincos_tab[j * 8 + e];
@@ -453,16 +474,15 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
                     fb[e] = x0 * sc.x + x1 * sc.y;
                 }
                 const uint4 oa = pack8(fa), ob = pack8(fb);
-                *reinterpret_cast<uint4*>(hp + da) = oa;
-                *reinterpret_cast<uint4*>(hp + db) = ob;
+                *reinterpret_cast<uint4*>(row + h0 + da) = oa;
+                *reinterpret_cast<uint4*>(row + h0 + db) = ob;
                 if (is_k && page >= 0) {
                     *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, da, hd)) = oa;
                     *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, db, hd)) = ob;
                 }
             } else {
                 const int d0 = j * 8;
-                const uint4 ua = *reinterpret_cast<const uint4*>(hp + d0);
-                unpack8(ua, fa);
+                fetch(h0 + d0, fa);
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
                     const float2 sc = sincos_tab[(d0 + e) >> 1];
@@ -471,15 +491,18 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int row_stride, int n_heads,
                     fa[e + 1] = x0 * sc.x + x1 * sc.y;
                 }
                 const uint4 oa = pack8(fa);
-                *reinterpret_cast<uint4*>(hp + d0) = oa;
+                *reinterpret_cast<uint4*>(row + h0 + d0) = oa;
                 if (is_k && page >= 0) *reinterpret_cast<uint4*>(kp + tile + kv_elem_offset(r, d0, hd)) = oa;
             }
-        } else if (page >= 0) {
+        } else if (PARTS || page >= 0) {
             const int v = item - n_qk * per_qk_head;
             const int kvh = v / chunks, d0 = (v % chunks) * 8;
-            const bf16* src = row + (size_t)(n_heads + nkv + kvh) * hd + d0;
-            *reinterpret_cast<uint4*>(vp + kv_tile_offset(cache, page, kvh) + kv_elem_offset(r, d0, hd)) =
-                *reinterpret_cast<const uint4*>(src);
+            const int e0 = (n_heads + nkv + kvh) * hd + d0;
+            float fv[8];
+            fetch(e0, fv);
+            const uint4 ov = pack8(fv);
+            if (PARTS) *reinterpret_cast<uint4*>(row + e0) = ov;
+            if (page >= 0) *reinterpret_cast<uint4*>(vp + kv_tile_offset(cache, page, kvh) + kv_elem_offset(r, d0, hd)) = ov;
         }
     }
 }
@@ -663,12 +686,24 @@ extern "C" int hos_rope_kv_write(const void* src, int src_dtype, int n_parts, vo
 #define HOS_ROPE(TS, T)                                                                              \
     launch_pdl(rope_kv_write_kernel<TS, T>, dim3(N), dim3(256), smem, stream, (const TS*)src, n_parts, ps, (T*)qkv, row_stride, \
         n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache)
-    const bool vec_ok = dtype == kBF16 && src == qkv && (head_dim % 8) == 0 && (row_stride % 8) == 0 &&
+    const bool from_parts = src != qkv;             // then src_dtype is kF32 (checked above)
+    const bool vec_ok = dtype == kBF16 && (head_dim % 8) == 0 && (row_stride % 8) == 0 &&
                         ((uintptr_t)qkv % 16) == 0 && (rotary_dim % (style == 0 ? 16 : 8)) == 0 &&
+                        (!from_parts || (((uintptr_t)src % 16) == 0 && (ps % 4) == 0)) &&
                         (!write_cache || (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0);
     if (vec_ok) {
-        launch_pdl(rope_kv_write_vec_kernel, dim3(N), dim3(256), smem, stream, (bf16*)qkv, row_stride, n_heads, token_pos, token_seq,
-            seq_slot, seq_len_after, inv_freq, rotary_dim, style, c, write_cache);
+        // few tokens: several CTAs share a token's chunks, so that the launch fills more of the GPU
+        const int chunks_per_token = (n_heads + 2 * n_kv_heads) * (head_dim / 8);
+        int share = 1;
+        while (share < 8 && N * share < 2 * sm_count_cached() && chunks_per_token / (share * 2) >= 128) share *= 2;
+        if (from_parts)
+            launch_pdl(rope_kv_write_vec_kernel<true>, dim3(N, share), dim3(256), smem, stream, (const float*)src, n_parts, ps,
+                (bf16*)qkv, row_stride, n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c,
+                write_cache);
+        else
+            launch_pdl(rope_kv_write_vec_kernel<false>, dim3(N, share), dim3(256), smem, stream, (const float*)nullptr, 1, ps,
+                (bf16*)qkv, row_stride, n_heads, token_pos, token_seq, seq_slot, seq_len_after, inv_freq, rotary_dim, style, c,
+                write_cache);
         return check_launch("rope_kv_write");
     }
     if (dtype == kF32) HOS_ROPE(float, float);
