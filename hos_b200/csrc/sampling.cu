@@ -376,6 +376,253 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const float* __restrict
     }
 }
 
+// ---- the same choice by a cluster of 8 CTAs per row, for temp > 0 and 1 <= top_k <= 1024 ----------
+// A CTA keeps an eighth of the row in its shared memory (read from global memory once, the
+// repetition penalty applied to the copy), so every later pass runs on shared memory; what the
+// CTAs have to agree on (maximum, normaliser, the histograms of the radix selection of the
+// top_k-th key, how many of its equals each holds) goes through distributed shared memory and a
+// cluster barrier.  The kept tokens are gathered into the first CTA, which sorts them
+// (probability falling, id rising among equals) and walks them as the reference walks its list.
+// Every CTA takes the same branches, so every cluster barrier is reached by all eight.
+constexpr int kClusterCtas = 8;
+constexpr int kClThreads = 1024;
+constexpr int kClBins = 256;
+constexpr int kSubHists = 8;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of one of this CTA's shared variables in the CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t remote_addr(const void* p, uint32_t rank) {
+    uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p)), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void remote_store(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void remote_store64(uint32_t addr, unsigned long long v) {
+    asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t remote_add(uint32_t addr, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
+}
+
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClThreads, 1)
+sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ uniforms,
+                      const int* __restrict__ recent, int recent_stride, const int* __restrict__ recent_len,
+                      float temp, int top_k, float top_p, float rep_penalty, int* __restrict__ out, int per) {
+    pdl_enter();      // the kernels before this one are complete from here on
+    extern __shared__ float sl[];                              // this CTA's part of the row: `per` floats
+    __shared__ float scratch[32];
+    __shared__ float xf[2][kClusterCtas];                      // one float per CTA, two rounds in flight
+    __shared__ uint32_t xhist[2][kClusterCtas][kClBins];       // every CTA's histogram, two passes in flight
+    __shared__ uint32_t hist[kClBins];
+    __shared__ uint32_t subhist[kSubHists][kClBins];
+    __shared__ uint32_t xeq[kClusterCtas];
+    __shared__ uint32_t sel[2];                                // chosen bin, what is still wanted
+    __shared__ unsigned long long cand[kSmallSet];             // gathered in the first CTA
+    __shared__ uint32_t n_cand;
+    __shared__ uint32_t eq_here;
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x / kClusterCtas;
+    const uint32_t rank = cluster_rank();
+    const int lo = (int)rank * per;
+    const int n = max(0, min(per, V - lo));
+    const float* l = logits + (size_t)row * ld + lo;
+
+    if (tid == 0) { n_cand = 0; eq_here = 0; }
+    if ((((size_t)row * ld + lo) & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int n4 = n >> 2;
+        for (int i = tid; i < n4; i += kClThreads)
+            reinterpret_cast<float4*>(sl)[i] = __ldg(reinterpret_cast<const float4*>(l) + i);
+        for (int i = 4 * n4 + tid; i < n; i += kClThreads) sl[i] = l[i];
+    } else {
+        for (int i = tid; i < n; i += kClThreads) sl[i] = l[i];
+    }
+    __syncthreads();
+    // repetition penalty, once per occurrence, on the copy
+    if (tid == 0 && recent != nullptr && rep_penalty != 1.0f) {
+        const int nrec = min(recent_len[row], 256);
+        for (int j = 0; j < nrec; ++j) {
+            const int t = recent[(size_t)row * recent_stride + j] - lo;
+            if (t < 0 || t >= n) continue;
+            const float v = sl[t];
+            sl[t] = v > 0.f ? v / rep_penalty : v * rep_penalty;
+        }
+    }
+    __syncthreads();
+
+    int round = 0;
+    // all CTAs' values of one float, in rank order, to every CTA
+    auto share = [&](float mine, float (&all)[kClusterCtas]) {
+        const int buf = round & 1;
+        ++round;
+        if (tid < kClusterCtas) remote_store(remote_addr(&xf[buf][rank], (uint32_t)tid), __float_as_uint(mine));
+        cluster_sync_all();
+#pragma unroll
+        for (int r = 0; r < kClusterCtas; ++r) all[r] = xf[buf][r];
+    };
+
+    // ---- maximum and normaliser ----
+    float m = -INFINITY;
+    for (int i = tid; i < n; i += kClThreads) m = fmaxf(m, sl[i]);
+    m = block_max(m, scratch);
+    float all[kClusterCtas];
+    share(m, all);
+    float maxv = all[0];
+#pragma unroll
+    for (int r = 1; r < kClusterCtas; ++r) maxv = fmaxf(maxv, all[r]);
+    float z = 0.f;
+    for (int i = tid; i < n; i += kClThreads) z += expf((sl[i] - maxv) / temp);
+    z = block_sum(z, scratch);
+    share(z, all);
+    z = 0.f;
+#pragma unroll
+    for (int r = 0; r < kClusterCtas; ++r) z += all[r];        // the same order in every CTA
+
+    // ---- the top_k-th key by radix selection over all parts, 8 bits a pass ----
+    uint32_t prefix = 0, mask = 0, want = (uint32_t)top_k;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass, buf = pass & 1;
+        for (int i = tid; i < kSubHists * kClBins; i += kClThreads) (&subhist[0][0])[i] = 0;
+        __syncthreads();
+        // the leading bits of logits crowd into a few bins: several copies of the histogram, chosen
+        // by the thread, keep the atomics from queueing up on one address
+        uint32_t* mine = subhist[tid % kSubHists];
+        for (int i = tid; i < n; i += kClThreads) {
+            const uint32_t key = order_key(sl[i]);
+            if ((key & mask) == prefix) atomicAdd(&mine[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < kClBins) {
+            uint32_t h = 0;
+#pragma unroll
+            for (int c = 0; c < kSubHists; ++c) h += subhist[c][tid];
+#pragma unroll
+            for (uint32_t r = 0; r < kClusterCtas; ++r) remote_store(remote_addr(&xhist[buf][rank][tid], r), h);
+        }
+        cluster_sync_all();
+        if (tid < kClBins) {
+            uint32_t t = 0;
+#pragma unroll
+            for (int r = 0; r < kClusterCtas; ++r) t += xhist[buf][r][tid];
+            hist[tid] = t;
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // one warp finds the bin, from the top: lane L holds bins 255-8L .. 248-8L
+            uint32_t c[8], mine_sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { c[j] = hist[255 - 8 * tid - j]; mine_sum += c[j]; }
+            uint32_t incl = mine_sum;                       // counts of this lane's bins and of all higher bins
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (tid >= o) incl += v;
+            }
+            uint32_t above = incl - mine_sum;
+            const bool here = above < want && incl >= want;
+            const bool last_resort = tid == 31 && incl < want;       // cannot happen while top_k <= the number of elements
+            if (here || last_resort) {
+                int j = 0;
+                for (; j < 7; ++j) {
+                    if (above + c[j] >= want) break;
+                    above += c[j];
+                }
+                sel[0] = (uint32_t)(255 - 8 * tid - j);
+                sel[1] = want - above;
+            }
+        }
+        __syncthreads();
+        prefix |= sel[0] << shift;
+        mask |= 255u << shift;
+        want = sel[1];
+    }
+    const uint32_t x = prefix;            // the top_k-th key; `want` of the tokens that have it are kept, lowest ids first
+
+    // ---- how many of the equals each CTA holds ----
+    {
+        uint32_t c = 0;
+        for (int i = tid; i < n; i += kClThreads) c += (order_key(sl[i]) == x);
+        if (c) atomicAdd(&eq_here, c);
+        __syncthreads();
+        if (tid < kClusterCtas) remote_store(remote_addr(&xeq[rank], (uint32_t)tid), eq_here);
+        cluster_sync_all();
+    }
+    uint32_t eq_before = 0;
+    for (uint32_t r = 0; r < rank; ++r) eq_before += xeq[r];
+    const uint32_t quota = eq_before >= want ? 0u : min(want - eq_before, xeq[rank]);   // equals this CTA contributes
+    const bool all_equals = quota == xeq[rank];
+
+    // ---- gather the kept tokens into the first CTA ----
+    const uint32_t cand0 = remote_addr(&cand[0], 0), ncand0 = remote_addr(&n_cand, 0);
+    auto push = [&](uint32_t key, int i) {
+        const uint32_t at = remote_add(ncand0, 1u);
+        if (at < (uint32_t)kSmallSet)
+            remote_store64(cand0 + at * 8u, ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)(lo + i)));
+    };
+    for (int i = tid; i < n; i += kClThreads) {
+        const uint32_t key = order_key(sl[i]);
+        if (key > x || (key == x && all_equals)) push(key, i);
+    }
+    if (!all_equals && quota > 0 && tid == 0) {          // a tie across the cut inside this part: the lowest ids, in order
+        uint32_t taken = 0;
+        for (int i = 0; i < n && taken < quota; ++i)
+            if (order_key(sl[i]) == x) { push(x, i); ++taken; }
+    }
+    cluster_sync_all();
+    if (rank != 0) return;
+
+    // ---- the first CTA: sort and walk ----
+    const int nk = min((int)n_cand, kSmallSet);
+    int n2 = 1;
+    while (n2 < nk) n2 <<= 1;
+    for (int i = nk + tid; i < n2; i += kClThreads) cand[i] = 0ull;        // padding sorts last
+    __syncthreads();
+    for (int k = 2; k <= n2; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < n2; i += kClThreads) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const unsigned long long a = cand[i], b = cand[ixj];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (a < b) : (a > b)) { cand[i] = b; cand[ixj] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    if (tid == 0) {
+        auto prob_of = [&](unsigned long long c) { return expf((value_of_key((uint32_t)(c >> 32)) - maxv) / temp) / z; };
+        int cut = nk;
+        if (top_p < 1.0f) {
+            float cum = 0.f;
+            for (int i = 0; i < nk; ++i) {
+                cum += prob_of(cand[i]);
+                if (cum >= top_p) { cut = i + 1; break; }
+            }
+        }
+        float total = 0.f;
+        for (int i = 0; i < cut; ++i) total += prob_of(cand[i]);
+        const float rr = uniforms[row] * total;
+        float cdf = 0.f;
+        int pick = cut - 1;
+        for (int i = 0; i < cut; ++i) {
+            cdf += prob_of(cand[i]);
+            if (rr < cdf) { pick = i; break; }
+        }
+        out[row] = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
+    }
+}
+
 // Arg max alone (first maximum wins), for the greedy loop: reads, never writes, the logits.
 // A row is cut into chunks, one block each; a block leaves its (maximum, id) in `partial`
 // and takes a ticket; the block that takes a row's last ticket reduces the row's partials
@@ -438,9 +685,15 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int chunk, float*
     }
 }
 
+// Tests switch the cluster kernel off to put the one-CTA kernel through the same cases.
+static int g_cluster_sampler = 1;
+static bool cluster_sampler_enabled() { return g_cluster_sampler != 0; }
+
 }  // namespace hos
 
 using namespace hos;
+
+extern "C" void hos_sample_use_cluster(int on) { g_cluster_sampler = on ? 1 : 0; }
 
 // Chunks a row is cut into, and the floats of workspace the arg max needs: partial maxima
 // and ids, [B][chunks] each.  `tickets` is B ints that are zero before the first launch.
@@ -470,6 +723,23 @@ extern "C" int hos_sample(float* logits, int ld, int B, int V, const float* unif
     if (V > (1 << 24)) HOS_REFUSE("sample: vocabulary %d is beyond 2^24 (counts are kept in float)", V);
     if (top_k < 0) HOS_REFUSE("sample: top_k %d is negative", top_k);
     if (!(rep_penalty > 0.f)) HOS_REFUSE("sample: repetition penalty must be positive");
+    // temperature sampling from the top_k most probable (the usual case): a cluster of CTAs per row, each
+    // with its part of the row in shared memory
+    {
+        const int per = ((V + kClusterCtas - 1) / kClusterCtas + 3) / 4 * 4;
+        const size_t need = (size_t)per * sizeof(float);
+        if (temp > 0.f && top_k >= 1 && top_k <= kSmallSet && top_k < V && need <= 160 * 1024 && cluster_sampler_enabled()) {
+            static size_t attr_cluster = 0;
+            if (need > attr_cluster) {
+                if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess)
+                    HOS_REFUSE("sample: cannot get %zu bytes of shared memory", need);
+                attr_cluster = need;
+            }
+            launch_pdl(sample_cluster_kernel, dim3(B * kClusterCtas), dim3(kClThreads), need, stream, (const float*)logits, ld, V,
+                       uniforms, recent, recent_stride, recent_len, temp, top_k, top_p, rep_penalty, out, per);
+            return check_launch("sample");
+        }
+    }
     const size_t smem = (size_t)(kBins * kThreads + kBins + 32) * sizeof(float);
     static bool attr_set = false;
     if (!attr_set) {

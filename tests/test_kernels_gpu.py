@@ -306,11 +306,15 @@ def test_argmax_first_maximum_wins():
                                     dict(temp=0.9, top_k=50, top_p=0.6, rep=1.4),
                                     dict(temp=0.0, top_k=40, top_p=0.95, rep=1.5),
                                     dict(temp=2.0, top_k=1, top_p=1.0, rep=1.0)])
-def test_sampling_kernel_follows_the_plain_sampler(params):
+@pytest.mark.parametrize("kernel", ["cluster", "one_cta"])
+def test_sampling_kernel_follows_the_plain_sampler(params, kernel):
     """Same logits, same uniform draw -> the same token as the plain restatement of the
-    reference's sampler, ties and repeated 'recent' tokens included."""
+    reference's sampler, ties and repeated 'recent' tokens included.  Temperature sampling from
+    a top_k of up to 1024 runs as a cluster of 8 CTAs per row unless that is switched off; both
+    kernels go through every case."""
     from plain import gemma2_plain as P
     from hos_b200 import ops
+    _use_cluster_sampler(kernel == "cluster")
     V, B = 1003, 24
     g = torch.Generator().manual_seed(11)
     logits = torch.randn(B, V, generator=g) * 2.0
@@ -337,8 +341,42 @@ def test_sampling_kernel_follows_the_plain_sampler(params):
     ops.sample(dl, torch.tensor(us, device=DEV), out, params["temp"], params["top_k"], params["top_p"],
                params["rep"], torch.tensor(recent, dtype=torch.int32, device=DEV),
                torch.full((B,), 8, dtype=torch.int32, device=DEV))
+    _use_cluster_sampler(True)
     assert out.tolist() == want
     assert torch.equal(dl, keep)                              # the logits are handed back unchanged
+
+
+def _use_cluster_sampler(on: bool) -> None:
+    import ctypes
+    from hos_b200 import ops
+    f = ops.core().lib.hos_sample_use_cluster
+    f.restype, f.argtypes = None, [ctypes.c_int]
+    f(1 if on else 0)
+
+
+def test_cluster_sampler_on_a_large_vocabulary():
+    """256,000 logits per row (an eighth of a row per CTA, the vocabulary no multiple of 8 CTAs x 4):
+    the cluster kernel and the one-CTA kernel choose the same tokens, with a penalty on recent
+    tokens that lie in different CTAs' parts, a tie across the top_k cut and a top_k of 1024."""
+    from hos_b200 import ops
+    V, B = 255999, 12
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(B, V, generator=g) * 3.0).to(DEV)
+    logits[1, 70000] = logits[1, 200000] = logits[1, 5] = float(logits[1].topk(40).values[-1])   # ties at the 40th place
+    recent = torch.stack([torch.randint(0, V, (8,), generator=g) for _ in range(B)]).to(torch.int32)
+    recent[:, 0] = logits.argmax(-1).cpu().to(torch.int32)                  # the best token is penalised
+    us = torch.rand(B, generator=g).to(DEV)
+    rlen = torch.full((B,), 8, dtype=torch.int32, device=DEV)
+    for top_k, top_p, temp, rep in [(40, 0.95, 0.8, 1.1), (1024, 1.0, 1.5, 1.0), (1, 0.5, 0.3, 2.0), (40, 0.2, 1.0, 1.3)]:
+        outs = []
+        for cluster in (True, False):
+            _use_cluster_sampler(cluster)
+            out = torch.empty(B, dtype=torch.int32, device=DEV)
+            ops.sample(logits.clone(), us, out, temp, top_k, top_p, rep, recent.to(DEV), rlen)
+            outs.append(out.tolist())
+        _use_cluster_sampler(True)
+        assert outs[0] == outs[1], (top_k, top_p, temp, rep)
+        assert all(0 <= t < V for t in outs[0])
 
 
 def _plain_sample_with_u(P, logits, params, recent, u):
