@@ -43,19 +43,20 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     per_token = max(1, n_kv_heads * chunks)
     hi = max(1, n_tokens)
     lo = min(max(1, min_live), hi) if min_live else hi
-    lives = (lo, (lo + hi) // 2, hi) if lo < hi else (hi,)          # fewest, middle and most live rows
+    lives = (lo, (lo + hi) // 2, hi, hi) if lo < hi else (hi,)      # fewest, middle and most live rows (a full batch counts twice)
     best, best_cost = 1, None
     for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
-        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + (_MERGE_US if s > 1 else 0.0)
+        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + (_MERGE_US + _MERGE_PER_SHARE_US * s if s > 1 else 0.0)
         cost = sum(-(-live * per_token * s // SM_COUNT) * per_item for live in lives)
         if best_cost is None or cost < 0.97 * best_cost:          # more shares only for a clear gain
             best, best_cost = s, cost
     return best
 
 
-# measured: 8 sequences of 8192 keys take 130 / 76 / 65.5 / 72.6 us with 1 / 2 / 4 / 9 shares; at 64 sequences two
-# shares instead of one cost 27 us more per layer
-_ITEM_US, _PAGE_US, _MERGE_US = 7.0, 1.1, 4.0
+# Fitted to measurements at head size 256, 8192 keys: one sequence takes 43.0 / 29.7 / 24.7 / 26.6 us with
+# 4 / 8 / 16 / 32 shares (launch included), eight sequences 130 / 76 / 65.5 / 72.6 us with 1 / 2 / 4 / 9;
+# at 64 sequences two shares instead of one cost 27 us more per layer.
+_ITEM_US, _PAGE_US, _MERGE_US, _MERGE_PER_SHARE_US = 6.0, 0.9, 1.0, 0.275
 
 
 _ticket_store: Dict[object, torch.Tensor] = {}
