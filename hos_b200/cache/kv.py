@@ -14,7 +14,7 @@ device before a step runs.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 

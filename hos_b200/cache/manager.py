@@ -21,7 +21,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .. import ops
 from ..errors import CacheError
 from ..parts.base import CallStore, KVNeed, StateNeed
 from .kv import KVGroup, PAGE

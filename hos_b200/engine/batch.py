@@ -1,7 +1,7 @@
 """Turning a step's host-side description into the device tensors the kernels read."""
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import math
 import time
-from typing import List, Optional, Sequence, Tuple, Union
+from typing import Optional, Sequence, Tuple, Union
 
 import torch
 

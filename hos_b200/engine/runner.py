@@ -8,7 +8,7 @@ ended are simply absent from later steps; their slots go back with `release`.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 

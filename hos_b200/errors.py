@@ -4,7 +4,7 @@ aborts the process.  They mirror the reference's `HosError` variants
 reference's Python binding raises (py/src/lib.rs:23-25)."""
 from __future__ import annotations
 
-from typing import Dict, List, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 
 class HosError(ValueError):

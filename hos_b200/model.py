@@ -4,7 +4,7 @@ run order.  It knows nothing about any architecture: everything comes from the
 `ModelPlan` and the part registry."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional
 
 import torch
 

@@ -9,7 +9,6 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
-from ..errors import KernelError
 
 SM_COUNT = 148
 MAX_HEAD_DIM = 256

@@ -20,8 +20,8 @@ product (`h`, `y`) has the runtime's compute dtype; logits are float32.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
