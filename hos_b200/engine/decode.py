@@ -17,6 +17,7 @@ import os
 import weakref
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -49,6 +50,8 @@ class DecodeSession:
         # one int32 device buffer; two pinned host mirrors used in turn, each guarded by an event,
         # so that the host may run a step ahead of the device without overwriting a copy's source
         self._hosts = [torch.zeros(6 * b + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._hosts_np = [h.numpy() for h in self._hosts]
+        self._laid_out = [-1, -1]               # live rows each mirror's constant fields were written for
         self._copied = [None, None]
         self._turn = 0
         self._dev = torch.zeros(6 * b + 1, dtype=torch.int32, device=dev)
@@ -94,14 +97,21 @@ class DecodeSession:
         if self._copied[turn] is not None:
             self._copied[turn].synchronize()       # the copy that last read this mirror is done
         h = self._hosts[turn]
+        hn = self._hosts_np[turn]              # the same memory as a numpy array: no tensor per field
         b = self.b
-        h[0:b] = torch.tensor(list(tokens) + [-1] * pad, dtype=torch.int32)
-        lb = torch.tensor(list(lengths_before) + [0] * pad, dtype=torch.int32)
-        h[b:2 * b] = lb
-        h[2 * b:3 * b] = torch.tensor(list(range(n)) + [-1] * pad, dtype=torch.int32)
-        h[3 * b:4 * b + 1] = torch.arange(b + 1, dtype=torch.int32).clamp(max=n)
-        h[4 * b + 1:5 * b + 1] = torch.tensor(list(slots) + [0] * pad, dtype=torch.int32)
-        h[5 * b + 1:6 * b + 1] = lb + 1
+        hn[0:n] = tokens
+        hn[b:b + n] = lengths_before
+        hn[4 * b + 1:4 * b + 1 + n] = slots
+        np.add(hn[b:b + n], 1, out=hn[5 * b + 1:5 * b + 1 + n])
+        if self._laid_out[turn] != n:          # what depends on the number of live rows only
+            hn[n:b] = -1
+            hn[b + n:2 * b] = 0
+            hn[2 * b:2 * b + n] = np.arange(n, dtype=np.int32)
+            hn[2 * b + n:3 * b] = -1
+            hn[3 * b:4 * b + 1] = np.minimum(np.arange(b + 1, dtype=np.int32), n)
+            hn[4 * b + 1 + n:5 * b + 1] = 0
+            hn[5 * b + 1 + n:6 * b + 1] = 1
+            self._laid_out[turn] = n
         self._dev.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
