@@ -381,6 +381,245 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
+// ---- the same product on pairs of SMs (many tokens) ---------------------------------------------
+// Two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2): each loads its
+// own 128 token rows of A and HALF of the tile's 256 rows of W, the first CTA of the pair issues
+// one MMA of M = 256 that reads both CTAs' shared memory, and each CTA's tensor memory receives
+// the 128 x 256 accumulator of its own token rows.  Per k-step a CTA stages 32 KB instead of 48
+// and the tensor core reads 8 KB of operands per instruction instead of 12, which is what the
+// one-CTA kernel is bound by (shared-memory bandwidth: operand reads and TMA writes together).
+//
+// Who signals whom (all barriers lie at the same offsets in both CTAs):
+//   full[s]      the leader's only: its producer expects the bytes of BOTH CTAs' loads; every
+//                load names the leader's barrier (address with the pair bit cleared)
+//   empty[s]     one per CTA: the leader's commit arrives on both (multicast), so each
+//                producer knows when its own stage may be overwritten
+//   acc_full[a]  one per CTA, by the leader's multicast commit; each CTA's epilogue waits on its own
+//   acc_empty[a] the leader's only: the epilogue warps of both CTAs arrive on it (8 arrivals)
+// Tensor memory is allocated and freed by warp 1 of each CTA (the cta_group::2 forms); a
+// cluster barrier stands before the first remote arrival and before the release.
+constexpr uint32_t kPairBitMask = 0xFEFFFFFFu;          // clears the bit that tells the two CTAs of a pair apart
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(leader_bar) & kPairBitMask), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs when every MMA issued so far has finished.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+                 : "memory");
+}
+// An arrival on the LEADER's barrier at this offset, from either CTA of the pair.
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPairBitMask) : "memory");
+}
+
+struct PairCfg {
+    static constexpr int kABytes = GM * GK * 2;             // this CTA's 128 token rows
+    static constexpr int kBBytes = 128 * GK * 2;            // this CTA's half of the tile's 256 rows of W
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = 6;
+    static constexpr int kSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = 512;                   // two accumulators of 256 columns
+};
+
+template <int EPI, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes of [128 rows x 64]
+                    const __grid_constant__ CUtensorMap map_w,     // W: boxes of [128 rows x 64]
+                    GemmParams p) {
+    using Cfg = PairCfg;
+    constexpr int BN = 256;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + Cfg::kStages;
+    uint64_t* acc_full = empty + Cfg::kStages;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();               // 0: the leader of the pair
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    const int m_tiles = (p.M + 2 * GM - 1) / (2 * GM);     // tiles of 256 token rows
+    constexpr int n_span = EPI == kGEpiGated ? BN / 2 : BN;
+    const int n_tiles = (p.N + n_span - 1) / n_span;
+    const int k_blocks = (p.K + GK - 1) / GK;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&map_a);
+        prefetch_tmap(&map_w);
+        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    cluster_sync_all();                                    // both CTAs' barriers exist before anything arrives on them
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_smem, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+    pdl_enter();
+
+    auto tile_coords = [&](int tile, int& mt, int& nt) { mt = tile % m_tiles; nt = tile / m_tiles; };
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs, each its own halves) ----------------
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+                int mt, nt;
+                tile_coords(tile, mt, nt);
+                const int a_row = mt * 2 * GM + (int)rank * GM;
+                const int w_row = EPI == kGEpiGated ? (leader ? nt * 128 : p.gate_rows + nt * 128) : nt * BN + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    if (it >= Cfg::kStages && !mbar_wait_timed(&empty[s], ((it / Cfg::kStages) - 1) & 1)) { ok = false; break; }
+                    unsigned char* a_dst = stages + (size_t)s * Cfg::kStageBytes;
+                    if (leader) mbar_expect_tx(&full[s], 2 * Cfg::kStageBytes);       // both CTAs' bytes land here
+                    tma_load_2d_pair(a_dst, &map_a, kb * GK, a_row, &full[s]);
+                    tma_load_2d_pair(a_dst + Cfg::kABytes, &map_w, kb * GK, w_row, &full[s]);
+                }
+            }
+            if (!ok) atomicExch(&g_gemm_error, 1);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the leader's one thread, for both CTAs ----------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc(2 * GM, BN);
+            int it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local_tile) {
+                const int acc = local_tile & 1;
+                if (local_tile >= 2 && !mbar_wait_timed(&acc_empty[acc], ((local_tile >> 1) - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    if (!mbar_wait_timed(&full[s], (it / Cfg::kStages) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stages + (size_t)s * Cfg::kStageBytes);
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(a_addr + Cfg::kABytes);
+#pragma unroll
+                    for (int k = 0; k < GK / 16; ++k)
+                        umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[acc]);
+            }
+            if (!ok) atomicExch(&g_gemm_error, 1);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: warps 2..5 of each CTA, its own 128 token rows ----------------
+        const int quarter = warp & 3;
+        int local_tile = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local_tile) {
+            int mt, nt;
+            tile_coords(tile, mt, nt);
+            const int acc = local_tile & 1;
+            if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            const int r = quarter * 32 + lane;
+            const int m = mt * 2 * GM + (int)rank * GM + r;
+            OutT* orow = reinterpret_cast<OutT*>(p.out) + (size_t)m * p.ldo;
+            constexpr int COLS = (EPI == kGEpiGated) ? BN / 2 : BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < COLS; c0 += 32) {
+                uint32_t v[32], u[32];
+                tmem_ld_32x32(t_lane + c0, v);
+                if (EPI == kGEpiGated) tmem_ld_32x32(t_lane + BN / 2 + c0, u);
+                tmem_ld_wait();
+                const int n0 = nt * COLS + c0;
+                if (m < p.M) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(v[j]);
+                        if (EPI == kGEpiSoftcap) x = softcap_precise(x, p.cap);
+                        if (EPI == kGEpiGated) {
+                            const float a = p.act == 0 ? gelu_tanh(x) : x / (1.f + __expf(-x));
+                            x = a * __uint_as_float(u[j]);
+                        }
+                        f[j] = x;
+                    }
+                    if (n0 + 32 <= p.N && (p.ldo % 8) == 0) {
+                        if (sizeof(OutT) == 2) {
+                            uint4* dst = reinterpret_cast<uint4*>(orow + n0);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                dst[q] = make_uint4(pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
+                                                    pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(orow + n0);
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) dst[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < p.N) orow[n0 + j] = from_float<OutT>(f[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(&g_gemm_error, 1);
+    }
+    // ---- teardown: nobody of either CTA touches tensor memory or the other's barriers any more ----
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+}
+
 // Sum K-split partials [splits][M][N] (f32) in a fixed order into out[M][N].
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ out, int M, int N, int ldo,
@@ -451,6 +690,31 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
     return check_launch("gemm_tc");
 }
 
+// Whether products of many tokens run on pairs of SMs (HOS_GEMM_PAIR=0 keeps them on single SMs).
+static bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("HOS_GEMM_PAIR");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <int EPI, typename OutT>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, int total_tiles, cudaStream_t stream) {
+    auto kernel = gemm_tc_pair_kernel<EPI, OutT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmem) != cudaSuccess)
+            HOS_REFUSE("gemm_tc: cannot get %d bytes of shared memory", PairCfg::kSmem);
+        attr_set = true;
+    }
+    const int pairs_max = sm_count() / 2;
+    const int pairs = total_tiles < pairs_max ? total_tiles : pairs_max;
+    launch_pdl(kernel, dim3(2 * pairs), dim3(kGemmThreads), PairCfg::kSmem, stream, ma, mw, p);
+    return check_launch("gemm_tc (pairs of SMs)");
+}
+
 }  // namespace hos
 
 using namespace hos;
@@ -501,6 +765,17 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     while (k_splits > 1 && (k_splits - 1) * ((k_blocks + k_splits - 1) / k_splits) >= k_blocks) k_splits = --p.k_splits;
     int rc;
 #define HOS_GO(BN, EPI, SWAP, T, TILES) return launch<BN, EPI, SWAP, T>(mm, mn, p, (TILES), stream)
+    if (!swap && M >= 512 && pair_enabled()) {
+        // many tokens: tiles of 256 x 256 on pairs of SMs
+        if ((rc = make_map(&mm, A, M, K, lda, GM))) return rc;
+        if ((rc = make_map(&mn, W, w_rows, K, ldw, 128))) return rc;
+        const int m_tiles = (M + 2 * GM - 1) / (2 * GM);
+        if (epilogue == kGEpiGated) return launch_pair<kGEpiGated, bf16>(mm, mn, p, m_tiles * ((N + 127) / 128), stream);
+        const int tiles = m_tiles * ((N + 255) / 256);
+        if (epilogue == kGEpiSoftcap) return launch_pair<kGEpiSoftcap, float>(mm, mn, p, tiles, stream);
+        if (out_dtype == kBF16) return launch_pair<kGEpiNone, bf16>(mm, mn, p, tiles, stream);
+        return launch_pair<kGEpiNone, float>(mm, mn, p, tiles, stream);
+    }
     if (!swap) {
         const int m_tiles = (M + GM - 1) / GM;
         constexpr int BN = 256;
