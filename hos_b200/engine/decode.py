@@ -84,7 +84,7 @@ class DecodeSession:
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot,
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
                         max_len_after=self._max_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
-                        starts_host=(), min_live=smaller_bucket(self.b) + 1)
+                        starts_host=(), min_live=smaller_bucket(self.b) + 1, replayed=True)
 
     def feed(self, slots: Sequence[int], tokens: Sequence[int], lengths_before: Sequence[int]) -> None:
         """Host token ids, slots and each sequence's length before the step -> the static
@@ -176,3 +176,108 @@ class DecodeSession:
             self._graph_greedy.replay()
         else:
             self._forward_greedy()
+
+
+# ---- short prompts ---------------------------------------------------------------------------
+# A prompt of a few dozen tokens is bound by the host when its kernels are launched one by one
+# (about 16 us per launch).  Prompt steps of up to PROMPT_TOKENS tokens in all, of sequences that
+# start at position 0 and want the logits of their last token, are therefore captured too: one
+# graph per (token capacity, sequence capacity), the real token count, lengths and slots being
+# data.  Rows beyond the real tokens are padding; sequences beyond the real ones have length 0.
+PROMPT_TOKENS = 256
+PROMPT_TOKEN_BUCKETS = (16, 32, 64, 128, 256)
+PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
+
+
+def prompt_bucket(n_tokens: int, n_seqs: int):
+    """(token capacity, sequence capacity) of the session that takes such a prompt step, or None."""
+    if n_tokens > PROMPT_TOKENS or n_seqs > PROMPT_SEQ_BUCKETS[-1]:
+        return None
+    return (next(t for t in PROMPT_TOKEN_BUCKETS if n_tokens <= t),
+            next(q for q in PROMPT_SEQ_BUCKETS if n_seqs <= q))
+
+
+class PromptSession:
+    def __init__(self, runner, tokens_cap: int, seqs_cap: int, use_graph: Optional[bool] = None):
+        self._runner = weakref.ref(runner)
+        self.t, self.q = tokens_cap, seqs_cap
+        if use_graph is None:
+            use_graph = os.environ.get("HOS_NO_GRAPH", "") == ""
+        self.use_graph = use_graph
+        t, q = tokens_cap, seqs_cap
+        n = 3 * t + (q + 1) + 3 * q
+        self._hosts = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._hosts_np = [h.numpy() for h in self._hosts]
+        self._copied = [None, None]
+        self._turn = 0
+        self._dev = torch.zeros(n, dtype=torch.int32, device=runner.device)
+        d, o = self._dev, 3 * t
+        self.tokens, self.pos, self.seq = d[0:t], d[t:2 * t], d[2 * t:3 * t]
+        self.cu, self.slot, self.after, self.rows = d[o:o + q + 1], d[o + q + 1:o + 2 * q + 1], \
+            d[o + 2 * q + 1:o + 3 * q + 1], d[o + 3 * q + 1:o + 4 * q + 1]
+        self.logits: Optional[torch.Tensor] = None
+        self._graph = None
+        self._ready = False
+        self.n_live = 0
+
+    @property
+    def runner(self):
+        return self._runner()
+
+    def _info(self) -> StepInfo:
+        return StepInfo(n_tokens=self.t, n_seqs=self.q, tokens=self.tokens, token_pos=self.pos,
+                        token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot, seq_len_after=self.after,
+                        from_zero=True, single_token=False, max_new=self.t, max_len_after=self.t,
+                        slots_host=(), cu_host=(), starts_host=(), replayed=True)
+
+    def feed(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]]) -> None:
+        live = len(slots)
+        self.n_live = live
+        turn = self._turn
+        self._turn ^= 1
+        if self._copied[turn] is not None:
+            self._copied[turn].synchronize()
+        hn, t, q = self._hosts_np[turn], self.t, self.q
+        o = 3 * t
+        at = 0
+        cu = hn[o:o + q + 1]
+        for i, toks in enumerate(token_lists):
+            k = len(toks)
+            hn[at:at + k] = toks
+            hn[t + at:t + at + k] = np.arange(k, dtype=np.int32)
+            hn[2 * t + at:2 * t + at + k] = i
+            cu[i] = at
+            at += k
+        hn[at:t] = -1                      # padding rows
+        hn[t + at:2 * t] = 0
+        hn[2 * t + at:3 * t] = -1
+        cu[live:] = at                     # sequences beyond the real ones are empty
+        hn[o + q + 1:o + q + 1 + live] = slots
+        hn[o + q + 1 + live:o + 2 * q + 1] = 0
+        lens = np.diff(cu)
+        hn[o + 2 * q + 1:o + 3 * q + 1] = lens
+        hn[o + 3 * q + 1:o + 4 * q + 1] = np.maximum(cu[1:] - 1, 0)     # the last row of each sequence
+        self._dev.copy_(self._hosts[turn], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._copied[turn] = ev
+
+    def _forward(self) -> torch.Tensor:
+        r = self.runner
+        x = r.model.hidden(self._info(), r.cache)
+        return r.model.logits(x, self.rows)
+
+    def run(self) -> torch.Tensor:
+        """The step on what `feed` put in: float32 logits [real sequences, vocab] at each one's last
+        token (a view of a static buffer when graphs are on: use it before the next run)."""
+        self.runner.cache.flush()
+        if not self._ready:
+            self._graph, self.logits = DecodeSession._capture(self, self._forward)
+            self._ready = True
+            if self._graph is None:
+                return self.logits[: self.n_live]
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self.logits = self._forward()
+        return self.logits[: self.n_live]

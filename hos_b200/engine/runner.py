@@ -51,6 +51,7 @@ class Runner:
         self.vocab_size = self.plan.vocab_size
         self._sessions = {}
         self.use_sessions = self.model.graph_safe     # single-token steps run through DecodeSession
+        self.prompt_sessions = True                   # and short prompt steps through PromptSession
 
     @classmethod
     def from_folder(cls, model_dir: str, **kw) -> "Runner":
@@ -131,6 +132,24 @@ class Runner:
             sess.feed(slots, [t[0] for t in token_lists], starts)
             out = sess.run()
             return out.clone() if copy else out
+        if from_zero and self.use_sessions and self.prompt_sessions and all(len(w) == 1 and w[0] == len(t) - 1
+                                                                          for w, t in zip(want, token_lists)):
+            # a short prompt step: static buffers and a captured graph per capacity, as for decoding
+            from .decode import PromptSession, prompt_bucket
+            bucket = prompt_bucket(sum(len(t) for t in token_lists), len(slots))
+            if bucket is not None:
+                for toks in token_lists:
+                    for t in toks:
+                        if not (0 <= int(t) < self.vocab_size):
+                            raise HosError(f"token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+                for s, toks in zip(slots, token_lists):
+                    self.cache.extend(s, len(toks))
+                sess = self._sessions.get(("prompt",) + bucket)
+                if sess is None:
+                    sess = self._sessions[("prompt",) + bucket] = PromptSession(self, *bucket)
+                sess.feed(slots, token_lists)
+                out = sess.run()
+                return out.clone() if copy else out
         x, rows_t = self._hidden(slots, starts, token_lists, rows)
         return self.model.logits(x, rows_t)
 

@@ -107,14 +107,24 @@ def has_tc_prefill(head_dim: int) -> bool:
     return bool(f())
 
 
-def prefill_tc(rows: torch.Tensor, out, cu_seqlens, cu_host, n_heads, n_kv_heads, head_dim, scale, cap, window) -> None:
+def prompt_blocks(step, block: int):
+    """(sequences, blocks of `block` queries) a prompt kernel's grid has to cover.  From the host's
+    lists when the step has them; for a replayed step an upper bound (the kernels skip blocks
+    beyond the sequences' real ends, which they read on the device)."""
+    if step.replayed or not step.cu_host:
+        return step.n_seqs, (step.n_tokens + block - 1) // block + step.n_seqs
+    cu = step.cu_host
+    return len(cu) - 1, sum((cu[i + 1] - cu[i] + block - 1) // block for i in range(len(cu) - 1))
+
+
+def prefill_tc(rows: torch.Tensor, out, cu_seqlens, n_seqs: int, blocks: int, n_heads, n_kv_heads, head_dim, scale, cap,
+               window) -> None:
     """Attention of whole prompts from position 0 on the tcgen05 tensor cores; `rows` is the
-    fused projection output [N, (n_heads + 2 n_kv_heads) * head_dim] (head sizes 64, 128, 256)."""
+    fused projection output [N, (n_heads + 2 n_kv_heads) * head_dim] (head sizes 64, 128, 256).
+    `blocks`: at least the sum over sequences of ceil(length / 128)."""
     lib = lib_for(head_dim)
-    n_seqs = len(cu_host) - 1
-    tiles = sum((cu_host[i + 1] - cu_host[i] + 127) // 128 for i in range(n_seqs))
     lib.call("hos_attn_prefill_tc", ops._ptr(rows), rows.shape[0], rows.shape[1], ops._ptr(out), out.shape[1],
-             ops._ptr(cu_seqlens), n_seqs, tiles, n_heads, n_kv_heads, head_dim, float(scale), float(cap),
+             ops._ptr(cu_seqlens), n_seqs, blocks, n_heads, n_kv_heads, head_dim, float(scale), float(cap),
              int(window) if window else 0, ops._stream())
 
 
@@ -124,14 +134,13 @@ def prefill_tc_gave_up(head_dim: int) -> bool:
     return bool(f())
 
 
-def prefill(q, q_stride, k_rows, v_rows, kv_stride, out, cu_seqlens, cu_host, n_heads, n_kv_heads, head_dim,
-            scale, cap, window) -> None:
-    """Attention of whole prompts from position 0 over their own packed rows (mma.sync kernel)."""
+def prefill(q, q_stride, k_rows, v_rows, kv_stride, out, cu_seqlens, n_seqs: int, blocks: int, n_heads, n_kv_heads,
+            head_dim, scale, cap, window) -> None:
+    """Attention of whole prompts from position 0 over their own packed rows (mma.sync kernel).
+    `blocks`: at least the sum over sequences of ceil(length / 64)."""
     lib = lib_for(head_dim)
-    n_seqs = len(cu_host) - 1
-    tiles = sum((cu_host[i + 1] - cu_host[i] + 63) // 64 for i in range(n_seqs))
     lib.call("hos_attn_prefill", ops._ptr(q), q_stride, ops._ptr(k_rows), ops._ptr(v_rows), kv_stride,
-             ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens), n_seqs, tiles, n_heads, n_kv_heads, head_dim,
+             ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens), n_seqs, blocks, n_heads, n_kv_heads, head_dim,
              float(scale), float(cap), int(window) if window else 0, ops._stream())
 
 
@@ -142,14 +151,18 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
     if packed:
         if not enabled["prefill"]:
             return False
-        if step.n_tokens > step.cu_host[-1]:
+        if step.replayed or not step.cu_host:
+            att.zero_()                          # which rows are padding is known on the device only
+        elif step.n_tokens > step.cu_host[-1]:
             att[step.cu_host[-1]:].zero_()       # padding rows: a defined output
         if enabled["prefill_tc"] and qkv.is_contiguous() and has_tc_prefill(mixer.head_dim):
-            prefill_tc(qkv, att, step.cu_seqlens, step.cu_host, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+            n_seqs, blocks = prompt_blocks(step, 128)
+            prefill_tc(qkv, att, step.cu_seqlens, n_seqs, blocks, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                        mixer.scale, mixer.softcap, mixer.window)
             return True
+        n_seqs, blocks = prompt_blocks(step, 64)
         prefill(qkv, qkv.shape[1], qkv[:, mixer.q_dim:], qkv[:, mixer.q_dim + mixer.kv_dim:], qkv.shape[1],
-                att, step.cu_seqlens, step.cu_host, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                att, step.cu_seqlens, n_seqs, blocks, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                 mixer.scale, mixer.softcap, mixer.window)
         return True
     if not enabled["decode"]:

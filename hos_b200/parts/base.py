@@ -93,6 +93,8 @@ class StepInfo:
     cu_host: Sequence[int] = ()      # the same as cu_seqlens, on the host
     starts_host: Sequence[int] = ()  # each sequence's length before the step
     min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
+    replayed: bool = False           # the device arrays are refilled and the same launches replayed (a CUDA
+                                     # graph): n_tokens and n_seqs are capacities, the host lists are empty
 
 
 class CallStore:

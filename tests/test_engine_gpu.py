@@ -192,3 +192,44 @@ def test_perplexity_and_bench(tmp_path):
     assert b[0] == 28 and b[3] <= 12 and b[2] > 0
     eng.runner.cache.check()
     assert not eng.runner.cache.lengths                            # every slot was given back
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_short_prompts_replayed_as_graphs_match_whole_prompts(tmp_path, name, dtype):
+    """Prompt steps of up to 256 tokens run from static buffers as a replayed graph, one graph per
+    capacity: batches of other lengths and other numbers of sequences reuse it (the rows beyond the
+    real tokens are padding, the sequences beyond the real ones empty).  Every batch gives the plain
+    implementation's logits, the decode steps on top find what the prompt step stored, and slots
+    are reused from batch to batch."""
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(8)
+    r = runner_for(folder, dtype)
+    longest = TINY[name][0]["max_position_embeddings"] - 2
+    batches = [[5], [16], [17, 3], [1, 1, 1], [30, 31, 2, 1], [9, 100, 40], [60] * 4, [33] * 7, [2, 250]]
+    from hos_b200.engine.decode import prompt_bucket
+    buckets = set()
+    for lens in batches:
+        lens = [min(n, longest) for n in lens]
+        buckets.add(prompt_bucket(sum(lens), len(lens)))
+        seqs = [random_tokens(rng, n + 2, vocab) for n in lens]
+        want = [P.forward_logits(w, cfg, s) for s in seqs]
+        slots = r.admit(len(seqs))
+        got = r.step(slots, [s[:n] for s, n in zip(seqs, lens)])
+        assert_close(got, torch.stack([wl[n - 1] for wl, n in zip(want, lens)]), dtype, f"prompt step {lens}")
+        for t in range(2):
+            got = r.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+            assert_close(got, torch.stack([wl[n + t] for wl, n in zip(want, lens)]), dtype, f"decode {t} after {lens}")
+        for s in slots:
+            r.release(s)
+        r.cache.check()
+    used = {k[1:] for k in r._sessions if isinstance(k, tuple) and k[0] == "prompt"}
+    assert used == buckets and len(used) >= 5           # nine batches, fewer graphs
+    # the same steps launched kernel by kernel agree (other kernels for other row counts: within tolerance)
+    r2 = runner_for(folder, dtype)
+    r2.prompt_sessions = False
+    seqs = [random_tokens(rng, n, vocab) for n in (30, 31, 2, 1)]
+    s1, s2 = r.admit(4), r2.admit(4)
+    assert_close(r.step(s1, seqs), r2.step(s2, seqs), dtype, "graph against kernel by kernel")

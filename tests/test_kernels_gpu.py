@@ -491,7 +491,8 @@ def test_attention_prefill_kernel(cfg):
         cu_host.append(cu_host[-1] + l)
     cu = torch.tensor(cu_host, dtype=torch.int32, device=DEV)
     out = torch.full((N, nh * hd), 7.0, device=DEV, dtype=dt)
-    af.prefill(rows, stride, rows[:, nh * hd:], rows[:, (nh + nkv) * hd:], stride, out, cu, cu_host, nh, nkv, hd,
+    blocks = sum((l + 63) // 64 for l in seq_lens) + 3          # a grid larger than needed: the extra blocks leave at once
+    af.prefill(rows, stride, rows[:, nh * hd:], rows[:, (nh + nkv) * hd:], stride, out, cu, len(seq_lens), blocks, nh, nkv, hd,
                scale, cap, window)
     assert float((out[cu_host[-1]:] - 7.0).abs().sum()) == 0.0      # padding rows are not touched
     base = 0
@@ -757,7 +758,8 @@ def test_attention_prefill_tensor_core_kernel(cfg):
         cu_host.append(cu_host[-1] + l)
     cu = torch.tensor(cu_host, dtype=torch.int32, device=DEV)
     out = torch.full((N, nh * hd), 7.0, device=DEV, dtype=dt)
-    af.prefill_tc(rows, out, cu, cu_host, nh, nkv, hd, scale, cap, window)
+    blocks = sum((l + 127) // 128 for l in seq_lens) + 2        # a grid larger than needed: the extra blocks leave at once
+    af.prefill_tc(rows, out, cu, len(seq_lens), blocks, nh, nkv, hd, scale, cap, window)
     assert not af.prefill_tc_gave_up(hd)
     assert float((out[cu_host[-1]:] - 7.0).abs().sum()) == 0.0      # padding rows are not touched
     base = 0
