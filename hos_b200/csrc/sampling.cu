@@ -635,18 +635,52 @@ __device__ __forceinline__ void argmax_merge(float& best, int& best_i, float ov,
 
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int chunk, float* __restrict__ partial_val,
-              int* __restrict__ partial_idx, int* __restrict__ tickets, int* __restrict__ out) {
+              int* __restrict__ partial_idx, int* __restrict__ tickets, int* __restrict__ out,
+              const int* __restrict__ recent, int recent_stride, const int* __restrict__ recent_len, float rep_penalty) {
     pdl_enter();      // the kernels before this one are complete from here on
     __shared__ float sv[kArgmaxThreads / 32];
     __shared__ int si[kArgmaxThreads / 32];
     __shared__ int is_last;
+    __shared__ int pen_id[256];          // recent tokens that lie in this chunk, each once,
+    __shared__ float pen_val[256];       // with their logits after the penalty (once per occurrence)
+    __shared__ int n_pen;
     const int row = blockIdx.y, nchunks = gridDim.x;
     const float* l = logits + (size_t)row * ld;
     const int lo = blockIdx.x * chunk, hi = min(V, lo + chunk);
+    // The penalty is applied once per occurrence; a logit keeps its sign under it, so the order of the
+    // occurrences does not matter and each distinct token is handled by the thread of its first occurrence.
+    __shared__ int rec[256];
+    const int nrec = (recent != nullptr && rep_penalty != 1.0f) ? min(recent_len[row], 256) : 0;
+    if (threadIdx.x == 0) n_pen = 0;
+    if ((int)threadIdx.x < nrec) rec[threadIdx.x] = recent[(size_t)row * recent_stride + threadIdx.x];
+    __syncthreads();
+    if ((int)threadIdx.x < nrec) {
+        const int t = rec[threadIdx.x];
+        if (t >= lo && t < hi) {
+            int times = 0;
+            bool first = true;
+            for (int j = 0; j < nrec; ++j) {
+                if (rec[j] != t) continue;
+                if (j < (int)threadIdx.x) first = false;
+                ++times;
+            }
+            if (first) {
+                float v = l[t];
+                for (int k = 0; k < times; ++k) v = v > 0.f ? v / rep_penalty : v * rep_penalty;
+                const int at = atomicAdd(&n_pen, 1);
+                pen_id[at] = t;
+                pen_val[at] = v;
+            }
+        }
+    }
+    __syncthreads();
+    const int np = n_pen;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     for (int i = lo + threadIdx.x; i < hi; i += kArgmaxThreads) {
-        const float v = l[i];
+        float v = l[i];
+        for (int e = 0; e < np; ++e)
+            if (pen_id[e] == i) v = pen_val[e];
         if (v > best) { best = v; best_i = i; }     // ids rise within a thread: first maximum kept
     }
     auto block_reduce = [&]() {
@@ -701,16 +735,21 @@ extern "C" int hos_argmax_chunks(int V) {
     int c = (V + 4095) / 4096;
     return c < 1 ? 1 : (c > 256 ? 256 : c);
 }
+// recent, recent_len, rep_penalty: the repetition penalty of the sampler (once per occurrence of a recent
+// token), applied on the fly; recent == NULL or rep_penalty == 1: none.  The logits are not written.
 extern "C" int hos_argmax(const float* logits, int ld, int B, int V, int* out, float* workspace, int* tickets,
+                          const int* recent, int recent_stride, const int* recent_len, float rep_penalty,
                           cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) HOS_REFUSE("argmax: empty vocabulary");
     if (B > 65535) HOS_REFUSE("argmax: %d rows are more than one launch takes", B);
+    if (!(rep_penalty > 0.f)) HOS_REFUSE("argmax: repetition penalty must be positive");
     const int chunks = hos_argmax_chunks(V);
     const int chunk = (V + chunks - 1) / chunks;
     dim3 grid(chunks, B);
     launch_pdl(argmax_kernel, dim3(grid), dim3(kArgmaxThreads), 0, stream, logits, ld, V, chunk, workspace,
-                                                      reinterpret_cast<int*>(workspace + (size_t)B * chunks), tickets, out);
+                                                      reinterpret_cast<int*>(workspace + (size_t)B * chunks), tickets, out,
+                                                      recent, recent_stride, recent_len, rep_penalty);
     return check_launch("argmax");
 }
 

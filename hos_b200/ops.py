@@ -330,10 +330,20 @@ def attn_plain(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, tok
 _argmax_state = {}
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+def argmax(logits: torch.Tensor, out: torch.Tensor, rep_penalty: float = 1.0,
+           recent: Optional[torch.Tensor] = None, recent_len: Optional[torch.Tensor] = None) -> None:
+    """out[b] = the first maximum of row b.  With `recent` ([B, n] token ids, recent_len[b] of them
+    valid) and a penalty other than 1 the sampler's repetition penalty is applied on the fly."""
     _check(logits, "logits", torch.float32, 2)
     _check(out, "tokens", torch.int32, 1)
     b, v = logits.shape
+    stride = 0
+    if recent is not None:
+        _check(recent, "recent tokens", torch.int32, 2)
+        _check(recent_len, "recent counts", torch.int32, 1)
+        if recent.shape[0] != b or recent_len.shape[0] != b:
+            raise KernelError("argmax: one row of recent tokens per row of logits is needed")
+        stride = recent.shape[1]
     lib = core()
     f = lib.lib.hos_argmax_chunks
     f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int]
@@ -343,7 +353,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     if st is None:       # partial maxima and ids, and the tickets (zero between launches)
         st = _argmax_state[key] = (torch.empty(2 * b * chunks, dtype=torch.float32, device=logits.device),
                                    torch.zeros(b, dtype=torch.int32, device=logits.device))
-    lib.call("hos_argmax", _ptr(logits), v, b, v, _ptr(out), _ptr(st[0]), _ptr(st[1]), _stream())
+    lib.call("hos_argmax", _ptr(logits), v, b, v, _ptr(out), _ptr(st[0]), _ptr(st[1]), _ptr(recent), stride,
+             _ptr(recent_len), float(rep_penalty), _stream())
 
 
 def sample(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor, temp: float, top_k: int,

@@ -79,27 +79,25 @@ class Sampler:
         b = logits.shape[0]
         out = torch.empty((b,), dtype=torch.int32, device=logits.device)
         penal = p.rep_penalty != 1.0 and p.repeat_last_n > 0
-        if p.temp <= 0.0 and not penal:
-            ops.argmax(logits, out)
+        recent_t = recent_len = None
+        if penal:
+            n = min(p.repeat_last_n, 256)
+            rows, lens = [], []
+            for k in keys:
+                r = self._recent[k][-n:]
+                lens.append(len(r))
+                rows.append(r + [-1] * (n - len(r)))
+            both = torch.tensor([row + [ln] for row, ln in zip(rows, lens)], dtype=torch.int32).to(logits.device)
+            recent_t, recent_len = both[:, :n].contiguous(), both[:, n].contiguous()
+        if p.temp <= 0.0:
+            # greedy: the chunked arg max, with the penalty applied on the fly if there is one
+            ops.argmax(logits, out, p.rep_penalty if penal else 1.0, recent_t, recent_len)
         else:
             us = []
             for k in keys:
-                if p.temp > 0.0:
-                    self._rng[k], u = next_rand(self._rng[k])
-                else:
-                    u = 0.0
+                self._rng[k], u = next_rand(self._rng[k])
                 us.append(u)
             uniforms = torch.tensor(us, dtype=torch.float32).to(logits.device)
-            recent_t = recent_len = None
-            if penal:
-                n = min(p.repeat_last_n, 256)
-                rows, lens = [], []
-                for k in keys:
-                    r = self._recent[k][-n:]
-                    lens.append(len(r))
-                    rows.append(r + [-1] * (n - len(r)))
-                recent_t = torch.tensor(rows, dtype=torch.int32).to(logits.device)
-                recent_len = torch.tensor(lens, dtype=torch.int32).to(logits.device)
             ops.sample(logits, uniforms, out, p.temp, p.top_k, p.top_p,
                        p.rep_penalty if penal else 1.0, recent_t, recent_len)
         toks = out.tolist()

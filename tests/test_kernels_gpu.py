@@ -300,6 +300,37 @@ def test_argmax_first_maximum_wins():
     assert out.tolist()[4] == int(logits[4].argmax())
 
 
+@pytest.mark.parametrize("rep", [1.5, 0.7])
+def test_argmax_with_the_repetition_penalty_on_the_fly(rep):
+    """Greedy choice under the sampler's penalty (once per occurrence of a recent token, logits
+    untouched): against the plain sampler, with recent tokens that repeat, that hold the maximum,
+    that have negative logits, that crowd into one chunk, and ids outside the vocabulary."""
+    from plain import gemma2_plain as P
+    from hos_b200 import ops
+    V, B = 20011, 9
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(B, V, generator=g) * 2.0
+    recent = []
+    for b in range(B):
+        top = [int(t) for t in logits[b].topk(6).indices]
+        r = top[:4] + [top[0]] * 2 + [int(x) for x in torch.randint(0, V, (5,), generator=g)]
+        if b == 2:
+            r = list(range(300, 311))                        # eleven neighbours: one chunk holds them all
+            logits[b, 300:311] = 9.0
+        recent.append(r[:11])
+    want = [_plain_sample_with_u(P, logits[b], dict(temp=0.0, top_k=0, top_p=1.0, rep=rep), recent[b], 0.0)[0]
+            for b in range(B)]
+    rt = torch.tensor([r + [V + 5] for r in recent], dtype=torch.int32, device=DEV)     # a 12th entry beyond the count
+    dl = logits.to(DEV).contiguous()
+    keep = dl.clone()
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    ops.argmax(dl, out, rep, rt, torch.full((B,), 11, dtype=torch.int32, device=DEV))
+    assert out.tolist() == want
+    assert torch.equal(dl, keep)
+    if rep > 1:
+        assert out.tolist() != [int(t) for t in logits.argmax(-1)]          # the penalty did change choices
+
+
 @pytest.mark.parametrize("params", [dict(temp=1.0, top_k=0, top_p=1.0, rep=1.0),
                                     dict(temp=0.7, top_k=5, top_p=1.0, rep=1.0),
                                     dict(temp=1.3, top_k=0, top_p=0.8, rep=1.0),
