@@ -388,6 +388,8 @@ constexpr int kClusterCtas = 8;
 constexpr int kClThreads = 1024;
 constexpr int kClBins = 256;
 constexpr int kSubHists = 8;
+constexpr int kMassSub = 4;            // copies of the mass histogram (64-bit bins)
+constexpr int kMassBytes = (2 * kMassSub + 2 * kClusterCtas) * kClBins * 8;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -488,6 +490,168 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, const flo
     z = 0.f;
 #pragma unroll
     for (int r = 0; r < kClusterCtas; ++r) z += all[r];        // the same order in every CTA
+
+    if (top_k <= 0 || top_k >= V) {
+        // ---- no top_k: the whole row is kept (or its top_p prefix).  Probabilities are taken as integers,
+        // p * 2^40, so that their sums do not depend on the order of addition: every CTA, every pass and
+        // every run sees the same totals, and the radix selection by probability mass is exact in them.
+        // per-CTA histograms are kept as three 32-bit sums of 14-bit limbs of the masses (a CTA holds fewer
+        // than 2^17 tokens, so no limb sum overflows): 32-bit shared-memory atomics are native, 64-bit ones are not
+        unsigned long long* msub = reinterpret_cast<unsigned long long*>(sl + per);            // [kMassSub][kClBins] (as 3 x u32 + pad)
+        unsigned long long* xmass = msub + kMassSub * kClBins * 2;                              // [2][kClusterCtas][kClBins]
+        uint32_t* limb = reinterpret_cast<uint32_t*>(msub);                                     // [kMassSub][kClBins][4]
+        __shared__ unsigned long long xq[2][kClusterCtas];
+        __shared__ unsigned long long msel[3];
+        auto mass_of = [&](float logit) { return (unsigned long long)(expf((logit - maxv) / temp) * 1099511627776.0f); };
+        int qround = 0;
+        auto share_q = [&](unsigned long long mine, unsigned long long (&allq)[kClusterCtas]) {
+            const int buf = qround & 1;
+            ++qround;
+            if (tid < kClusterCtas) remote_store64(remote_addr(&xq[buf][rank], (uint32_t)tid), mine);
+            cluster_sync_all();
+#pragma unroll
+            for (int r = 0; r < kClusterCtas; ++r) allq[r] = xq[buf][r];
+        };
+        auto block_sum_q = [&](unsigned long long v) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            __syncthreads();
+            if ((tid & 31) == 0) msub[tid >> 5] = v;
+            __syncthreads();
+            unsigned long long t = 0;
+            for (int w = 0; w < kClThreads / 32; ++w) t += msub[w];
+            __syncthreads();
+            return t;
+        };
+        unsigned long long allq[kClusterCtas];
+        unsigned long long zq = 0;
+        for (int i = tid; i < n; i += kClThreads) zq += mass_of(sl[i]);
+        share_q(block_sum_q(zq), allq);
+        zq = 0;
+#pragma unroll
+        for (int r = 0; r < kClusterCtas; ++r) zq += allq[r];
+
+        int pass_no = 0;
+        // Selection by mass in the order "higher probability first, lower id first among equals":
+        // strict: above <= target < above + mass(equals);  else: above < target <= above + mass(equals).
+        // Returns the key, the mass above it and the number of tokens that have it.
+        auto select = [&](unsigned long long target, bool strict, uint32_t& x, unsigned long long& above, uint32_t& n_equal) {
+            uint32_t prefix = 0, mask = 0;
+            above = 0;
+            for (int pass = 0; pass < 4; ++pass, ++pass_no) {
+                const int shift = 24 - 8 * pass, buf = pass_no & 1;
+                for (int i = tid; i < kMassSub * kClBins * 4; i += kClThreads) limb[i] = 0;
+                __syncthreads();
+                uint32_t* mine = limb + (tid % kMassSub) * kClBins * 4;
+                for (int i = tid; i < n; i += kClThreads) {
+                    const float v = sl[i];
+                    const uint32_t key = order_key(v);
+                    if ((key & mask) == prefix) {
+                        const unsigned long long q = mass_of(v);
+                        uint32_t* bin = mine + ((key >> shift) & 255u) * 4;
+                        atomicAdd(bin, (uint32_t)(q & 0x3FFFu));
+                        atomicAdd(bin + 1, (uint32_t)((q >> 14) & 0x3FFFu));
+                        atomicAdd(bin + 2, (uint32_t)(q >> 28));
+                    }
+                }
+                __syncthreads();
+                if (tid < kClBins) {
+                    unsigned long long h = 0;
+#pragma unroll
+                    for (int c = 0; c < kMassSub; ++c) {
+                        const uint32_t* bin = limb + (c * kClBins + tid) * 4;
+                        h += (unsigned long long)bin[0] + ((unsigned long long)bin[1] << 14) + ((unsigned long long)bin[2] << 28);
+                    }
+#pragma unroll
+                    for (uint32_t r = 0; r < kClusterCtas; ++r)
+                        remote_store64(remote_addr(&xmass[(buf * kClusterCtas + rank) * kClBins + tid], r), h);
+                }
+                cluster_sync_all();
+                if (tid < kClBins) {
+                    unsigned long long t = 0;
+#pragma unroll
+                    for (int r = 0; r < kClusterCtas; ++r) t += xmass[(buf * kClusterCtas + r) * kClBins + tid];
+                    msub[tid] = t;                         // the totals of this pass (the copies are spent)
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    unsigned long long cum = above;
+                    int b = kClBins - 1;
+                    for (; b > 0; --b) {
+                        const unsigned long long mb = msub[b];
+                        if (strict ? (target < cum + mb) : (target <= cum + mb && mb > 0)) break;
+                        cum += mb;
+                    }
+                    msel[0] = (unsigned long long)b;
+                    msel[1] = cum;
+                }
+                __syncthreads();
+                prefix |= (uint32_t)msel[0] << shift;
+                mask |= 255u << shift;
+                above = msel[1];
+                __syncthreads();
+            }
+            x = prefix;
+            // how many tokens have this key, over all CTAs (their masses are equal)
+            uint32_t c = 0;
+            for (int i = tid; i < n; i += kClThreads) c += (order_key(sl[i]) == x);
+            unsigned long long allc[kClusterCtas];
+            share_q(block_sum_q(c), allc);
+            n_equal = 0;
+#pragma unroll
+            for (int r = 0; r < kClusterCtas; ++r) { n_equal += (uint32_t)allc[r]; xeq[r] = (uint32_t)allc[r]; }
+        };
+
+        uint32_t x = 0, n_equal = 0;
+        unsigned long long above = 0;
+        unsigned long long kept_mass = zq;
+        if (top_p < 1.0f) {
+            // the shortest prefix whose mass reaches top_p of the whole
+            const unsigned long long target = (unsigned long long)((double)top_p * (double)zq);
+            select(target > 0 ? target : 1, false, x, above, n_equal);
+            const unsigned long long q_eq = mass_of(value_of_key(x));
+            unsigned long long j = q_eq > 0 ? ((target > above ? target - above : 0) + q_eq - 1) / q_eq : 1;
+            j = j < 1 ? 1 : (j > n_equal ? n_equal : j);
+            kept_mass = above + j * q_eq;
+        }
+        const unsigned long long rr = (unsigned long long)((double)uniforms[row] * (double)kept_mass);
+        select(rr < kept_mass ? rr : kept_mass - 1, true, x, above, n_equal);
+        const unsigned long long q_eq = mass_of(value_of_key(x));
+        unsigned long long j = q_eq > 0 ? (rr - above) / q_eq + 1 : 1;          // the j-th of the equals, by rising id
+        j = j < 1 ? 1 : (j > n_equal ? n_equal : j);
+        // which CTA holds the j-th equal, and which of its own it is
+        uint32_t before = 0, owner = 0;
+        for (uint32_t r = 0; r < kClusterCtas; ++r) {
+            if (j <= before + xeq[r]) { owner = r; break; }
+            before += xeq[r];
+            owner = r;
+        }
+        if (rank == owner) {
+            // this CTA's tokens with that key, collected (few as a rule), then the one with j' - 1 smaller ids among them
+            int* ids = reinterpret_cast<int*>(msub);
+            __shared__ uint32_t n_ids;
+            const uint32_t mine_eq = xeq[rank], want_i = (uint32_t)(j - before);       // 1-based among this CTA's equals
+            if (tid == 0) n_ids = 0;
+            __syncthreads();
+            if (mine_eq <= 2048) {
+                for (int i = tid; i < n; i += kClThreads)
+                    if (order_key(sl[i]) == x) ids[atomicAdd(&n_ids, 1u)] = lo + i;
+                __syncthreads();
+                for (uint32_t c = tid; c < mine_eq; c += kClThreads) {
+                    const int id = ids[c];
+                    uint32_t smaller = 0;
+                    for (uint32_t d = 0; d < mine_eq; ++d) smaller += (ids[d] < id);
+                    if (smaller == want_i - 1) out[row] = id;
+                }
+            } else if (tid == 0) {                              // a row of ties: walk it
+                uint32_t seen = 0;
+                for (int i = 0; i < n; ++i)
+                    if (order_key(sl[i]) == x && ++seen == want_i) { out[row] = lo + i; break; }
+            }
+        }
+        cluster_sync_all();
+        return;
+    }
 
     // ---- the top_k-th key by radix selection over all parts, 8 bits a pass ----
     uint32_t prefix = 0, mask = 0, want = (uint32_t)top_k;
@@ -762,12 +926,14 @@ extern "C" int hos_sample(float* logits, int ld, int B, int V, const float* unif
     if (V > (1 << 24)) HOS_REFUSE("sample: vocabulary %d is beyond 2^24 (counts are kept in float)", V);
     if (top_k < 0) HOS_REFUSE("sample: top_k %d is negative", top_k);
     if (!(rep_penalty > 0.f)) HOS_REFUSE("sample: repetition penalty must be positive");
-    // temperature sampling from the top_k most probable (the usual case): a cluster of CTAs per row, each
-    // with its part of the row in shared memory
+    // temperature sampling (from the top_k most probable, up to 1024 of them, or from the whole row or its
+    // top_p prefix): a cluster of CTAs per row, each with its part of the row in shared memory
     {
         const int per = ((V + kClusterCtas - 1) / kClusterCtas + 3) / 4 * 4;
-        const size_t need = (size_t)per * sizeof(float);
-        if (temp > 0.f && top_k >= 1 && top_k <= kSmallSet && top_k < V && need <= 160 * 1024 && cluster_sampler_enabled()) {
+        size_t need = (size_t)per * sizeof(float);
+        const bool no_top_k = top_k <= 0 || top_k >= V;
+        if (no_top_k) need += kMassBytes;
+        if (temp > 0.f && (no_top_k || top_k <= kSmallSet) && need <= 190 * 1024 && cluster_sampler_enabled()) {
             static size_t attr_cluster = 0;
             if (need > attr_cluster) {
                 if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) != cudaSuccess)

@@ -388,7 +388,8 @@ def _use_cluster_sampler(on: bool) -> None:
 def test_cluster_sampler_on_a_large_vocabulary():
     """256,000 logits per row (an eighth of a row per CTA, the vocabulary no multiple of 8 CTAs x 4):
     the cluster kernel and the one-CTA kernel choose the same tokens, with a penalty on recent
-    tokens that lie in different CTAs' parts, a tie across the top_k cut and a top_k of 1024."""
+    tokens that lie in different CTAs' parts, a tie across the top_k cut, a top_k of 1024, and
+    without top_k (the whole row, and its top_p prefix: selection by probability mass)."""
     from hos_b200 import ops
     V, B = 255999, 12
     g = torch.Generator().manual_seed(5)
@@ -398,7 +399,8 @@ def test_cluster_sampler_on_a_large_vocabulary():
     recent[:, 0] = logits.argmax(-1).cpu().to(torch.int32)                  # the best token is penalised
     us = torch.rand(B, generator=g).to(DEV)
     rlen = torch.full((B,), 8, dtype=torch.int32, device=DEV)
-    for top_k, top_p, temp, rep in [(40, 0.95, 0.8, 1.1), (1024, 1.0, 1.5, 1.0), (1, 0.5, 0.3, 2.0), (40, 0.2, 1.0, 1.3)]:
+    for top_k, top_p, temp, rep in [(40, 0.95, 0.8, 1.1), (1024, 1.0, 1.5, 1.0), (1, 0.5, 0.3, 2.0), (40, 0.2, 1.0, 1.3),
+                                    (0, 1.0, 1.0, 1.0), (0, 0.9, 0.7, 1.2), (0, 0.3, 2.0, 1.0)]:
         outs = []
         for cluster in (True, False):
             _use_cluster_sampler(cluster)
