@@ -30,7 +30,16 @@ TINY_C = dict(
     max_position_embeddings=512, query_pre_attn_scalar=40, attn_logit_softcapping=30.0,
     final_logit_softcapping=0.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# A fourth one with a head size of 64: the cache's permuted layout, the tcgen05 prompt attention and
+# the tensor-core decode attention inside the engine (the sizes above use the other kernels).
+TINY_D = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2",
+    num_hidden_layers=2, hidden_size=136, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+    intermediate_size=264, vocab_size=1000, rope_theta=20000.0, sliding_window=70,
+    max_position_embeddings=1024, query_pre_attn_scalar=50, attn_logit_softcapping=40.0,
+    final_logit_softcapping=25.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 # Tolerances on logits against the plain float32 implementation.  Fixed up front:
 # float32 differs by summation order only; bfloat16 rounds every activation that a

@@ -233,3 +233,26 @@ def test_short_prompts_replayed_as_graphs_match_whole_prompts(tmp_path, name, dt
     seqs = [random_tokens(rng, n, vocab) for n in (30, 31, 2, 1)]
     s1, s2 = r.admit(4), r2.admit(4)
     assert_close(r.step(s1, seqs), r2.step(s2, seqs), dtype, "graph against kernel by kernel")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_64_whole_prompts_then_decoding(tmp_path, dtype):
+    """Config D (head size 64, a window of 70 keys in a ring of two pages): prompts that span
+    several blocks of 128 queries in one batch (the tcgen05 prompt attention in bfloat16), then
+    150 single-token steps that wrap the ring, all positions against the plain implementation."""
+    folder = make_folder(tmp_path, "D")
+    w, cfg = plain_model(folder)
+    rng = random.Random(12)
+    lens, extra = [300, 129, 5], 150
+    seqs = [random_tokens(rng, n + extra, 1000) for n in lens]
+    want = [P.forward_logits(w, cfg, s) for s in seqs]
+    r = runner_for(folder, dtype)
+    slots = r.admit(3)
+    got = r.step(slots, [s[:n] for s, n in zip(seqs, lens)], [list(range(n)) for n in lens])
+    assert_close(got, torch.cat([wl[:n] for wl, n in zip(want, lens)]), dtype, "whole prompts")
+    for t in range(extra):
+        got = r.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+        assert_close(got, torch.stack([wl[n + t] for wl, n in zip(want, lens)]), dtype, f"decode step {t}")
+    for s in slots:
+        r.release(s)
+    r.cache.check()

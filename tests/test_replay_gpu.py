@@ -15,7 +15,9 @@ pytestmark = pytest.mark.gpu
 # lengths chosen around what is special: 1 token, the window's size and one more, a page (64)
 # and one more, and long enough that the window's ring of 64 positions wraps
 LENGTHS = {"A": [1, 5, 8, 9, 33, 64, 65, 97], "B": [1, 9, 16, 17, 23, 40, 80, 128],
-           "C": [2, 40, 41, 63, 129, 200, 333, 150]}
+           "C": [2, 40, 41, 63, 129, 200, 333, 150],
+           # head size 64 (permuted cache tiles, tcgen05 prompt attention): a window of 70 in a ring of two pages
+           "D": [1, 64, 70, 71, 128, 129, 260, 400]}
 
 
 def build(name):
@@ -38,7 +40,7 @@ def build(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_matches_the_plain_implementation(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name)
     w, cfg = plain_model(folder)
