@@ -39,7 +39,14 @@ TINY_D = dict(
     max_position_embeddings=1024, query_pre_attn_scalar=50, attn_logit_softcapping=40.0,
     final_logit_softcapping=25.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# Head sizes 128 and 256 (what the 27B and the 2B/9B checkpoints have), small everywhere else.
+TINY_E = dict(TINY_D, num_attention_heads=3, num_key_value_heads=1, head_dim=128, hidden_size=72,
+              intermediate_size=200, query_pre_attn_scalar=144, sliding_window=100, vocab_size=777)
+TINY_F = dict(TINY_D, num_attention_heads=2, num_key_value_heads=2, head_dim=256, hidden_size=104,
+              intermediate_size=168, query_pre_attn_scalar=256, sliding_window=130, vocab_size=600,
+              attn_logit_softcapping=50.0, final_logit_softcapping=30.0)
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4), "F": (TINY_F, 5)}
 
 # Tolerances on logits against the plain float32 implementation.  Fixed up front:
 # float32 differs by summation order only; bfloat16 rounds every activation that a

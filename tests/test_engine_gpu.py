@@ -236,15 +236,17 @@ def test_short_prompts_replayed_as_graphs_match_whole_prompts(tmp_path, name, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_head_size_64_whole_prompts_then_decoding(tmp_path, dtype):
-    """Config D (head size 64, a window of 70 keys in a ring of two pages): prompts that span
-    several blocks of 128 queries in one batch (the tcgen05 prompt attention in bfloat16), then
-    150 single-token steps that wrap the ring, all positions against the plain implementation."""
-    folder = make_folder(tmp_path, "D")
+@pytest.mark.parametrize("name", ["D", "E", "F"])
+def test_head_sizes_64_128_256_whole_prompts_then_decoding(tmp_path, name, dtype):
+    """Configs D, E, F (head sizes 64, 128, 256; a window in a ring of two or three pages): prompts
+    that span several blocks of 128 queries in one batch (the tcgen05 prompt attention in
+    bfloat16), then 150 single-token steps that wrap the ring, all positions against the plain
+    implementation."""
+    folder = make_folder(tmp_path, name)
     w, cfg = plain_model(folder)
     rng = random.Random(12)
     lens, extra = [300, 129, 5], 150
-    seqs = [random_tokens(rng, n + extra, 1000) for n in lens]
+    seqs = [random_tokens(rng, n + extra, TINY[name][0]["vocab_size"]) for n in lens]
     want = [P.forward_logits(w, cfg, s) for s in seqs]
     r = runner_for(folder, dtype)
     slots = r.admit(3)
