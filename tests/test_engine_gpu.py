@@ -258,3 +258,33 @@ def test_head_sizes_64_128_256_whole_prompts_then_decoding(tmp_path, name, dtype
     for s in slots:
         r.release(s)
     r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_seqs", [20, 40, 70])
+def test_many_sequences_decode_together(tmp_path, n_seqs, dtype):
+    """20, 40 and 70 sequences in one batch (the row counts at which the products change
+    kernels: up to 32 rows, up to 64, more), prompts of unequal lengths in one step, then
+    single-token steps during which sequences leave the batch one by one."""
+    folder = make_folder(tmp_path, "D")
+    w, cfg = plain_model(folder)
+    rng = random.Random(n_seqs)
+    lens = [rng.randrange(1, 12) for _ in range(n_seqs)]
+    total = [n + rng.randrange(2, 7) for n in lens]
+    seqs = [random_tokens(rng, t, 1000) for t in total]
+    want = [P.forward_logits(w, cfg, s) for s in seqs]
+    r = runner_for(folder, dtype, max_tokens=64 * 128)          # a page, and so a slot, for each of them
+    slots = r.admit(n_seqs)
+    got = r.step(slots, [s[:n] for s, n in zip(seqs, lens)])
+    assert_close(got, torch.stack([wl[n - 1] for wl, n in zip(want, lens)]), dtype, "prompt step")
+    pos = list(lens)
+    live = list(range(n_seqs))
+    while live:
+        got = r.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live])
+        assert_close(got, torch.stack([want[i][pos[i]] for i in live]), dtype, f"decode with {len(live)} live")
+        for i in live:
+            pos[i] += 1
+        for i in [i for i in live if pos[i] == total[i]]:
+            r.release(slots[i])
+        live = [i for i in live if pos[i] < total[i]]
+    r.cache.check()
