@@ -160,8 +160,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // which sequence and which block of 128 queries (long blocks first: late queries have most keys)
-    int seq = 0, tile = blockIdx.x, row0 = 0, len = 0, nt = 0;
+    // which sequence and which block of 128 queries.  Long blocks first (late queries have most keys), and the
+    // heads are the fast index of the grid: every head's longest walk starts in the first wave, and the heads
+    // that share keys run side by side.
+    int seq = 0, tile = blockIdx.y, row0 = 0, len = 0, nt = 0;
     for (; seq < a.n_seqs; ++seq) {
         row0 = a.cu_seqlens[seq];
         len = a.cu_seqlens[seq + 1] - row0;
@@ -171,7 +173,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
     }
     if (seq >= a.n_seqs) return;
     const int q0 = (nt - 1 - tile) * TQ;
-    const int head = blockIdx.y, kvh = head / (a.n_heads / a.n_kv_heads);
+    const int head = blockIdx.x, kvh = head / (a.n_heads / a.n_kv_heads);
     const int last_q = min(len - 1, q0 + TQ - 1);
     const int first_key = a.window > 0 ? max(0, q0 + 1 - a.window) : 0;
     const int kt_lo = first_key / TK, kt_hi = last_q / TK;
@@ -276,9 +278,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = q0 + r;
-        const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
-        const float kLog2e = 1.4426950408889634f;
-        float m_ref = -INFINITY, l_run = 0.f;                    // l_run: this thread's keys only
+        // The walk works on t = tanh(s * scale / cap) (or t = s without a cap): the logit is c * t with c = cap
+        // (or scale), so the maximum is taken over t and a probability is exp2(t * c log2e - m * c log2e):
+        // per score one multiply, tanh, maximum; one fused multiply-add, exp2, add.
+        const bool capped = a.cap > 0.f;
+        const float pre = capped ? a.scale / a.cap : 1.f;       // what the raw score is multiplied with before tanh
+        const float c_logit = capped ? a.cap : a.scale;         // logit = c_logit * t
+        const float c2 = c_logit * 1.4426950408889634f;
+        const float slack_t = kRescaleSlack / c_logit;
+        float m_ref = -INFINITY, l_run = 0.f;                    // m_ref in units of t; l_run: this thread's keys only
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1, pb = j & 1;
@@ -295,21 +303,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[sb]);            // this warp has its part of the S buffer
-            const int k0 = (kt_lo + j) * TK + 32 * half;
+            const int kt0 = (kt_lo + j) * TK;                    // first key of the tile
+            const int k0 = kt0 + 32 * half;
             float m_half = -INFINITY;
+            if (capped) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int key = k0 + i;
-                float s = sc[i] * a.scale;
-                if (a.cap > 0.f) {
-                    float th;
-                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(s * inv_cap));
-                    s = a.cap * th;
+                for (int i = 0; i < 32; ++i) asm("tanh.approx.f32 %0, %1;" : "=f"(sc[i]) : "f"(sc[i] * pre));
+            }
+            // a tile that every query of the block sees whole needs no mask (all but the last one or two of a walk,
+            // and the first ones under a window)
+            const bool whole = kt0 + TK - 1 <= q0 && (a.window <= 0 || kt0 > q0 + TQ - 1 - a.window);
+            if (whole) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, sc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = k0 + i;
+                    const bool vis = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+                    sc[i] = vis ? sc[i] : -INFINITY;
+                    m_half = fmaxf(m_half, sc[i]);
                 }
-                const bool vis = key <= qpos && (a.window <= 0 || key > qpos - a.window);
-                s = vis ? s : -INFINITY;
-                sc[i] = s;
-                m_half = fmaxf(m_half, s);
             }
             // the row's maximum over both halves
             xchg[half * TQ + r] = m_half;
@@ -318,16 +332,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             asm volatile("bar.sync 1, 256;" ::: "memory");       // both have read before the next tile writes
             // raise the reference maximum only when it is exceeded by a margin (both threads of a row decide alike)
             float factor = 1.f;
-            if (m_tile > m_ref + kRescaleSlack || (m_ref == -INFINITY && m_tile > -INFINITY)) {
-                factor = m_ref == -INFINITY ? 0.f : __expf(m_ref - m_tile);
+            if (m_tile > m_ref + slack_t || (m_ref == -INFINITY && m_tile > -INFINITY)) {
+                factor = m_ref == -INFINITY ? 0.f : __expf((m_ref - m_tile) * c_logit);
                 m_ref = m_tile;
             }
-            const float m_use2 = (m_ref == -INFINITY ? 0.f : m_ref) * kLog2e;
+            const float m_use2 = (m_ref == -INFINITY ? 0.f : m_ref) * c2;
             float psum = 0.f;
             uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                const float p0 = exp2f(fmaf(sc[i], kLog2e, -m_use2)), p1 = exp2f(fmaf(sc[i + 1], kLog2e, -m_use2));
+                float p0, p1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(sc[i], c2, -m_use2)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(sc[i + 1], c2, -m_use2)));
                 psum += p0 + p1;
                 packed[i / 2] = pack_bf16(p0, p1);
             }
@@ -456,7 +472,7 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     if (head_dim != THD) HOS_REFUSE("attn_prefill_tc: built for head_dim %d, asked for %d", THD, head_dim);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         HOS_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
-    if (n_heads > 65535) HOS_REFUSE("attn_prefill_tc: %d heads are more than one launch takes", n_heads);
+    if (n_q_tiles > 65535) HOS_REFUSE("attn_prefill_tc: %d blocks of queries are more than one launch takes", n_q_tiles);
     if (row_stride != (n_heads + 2 * n_kv_heads) * THD)
         HOS_REFUSE("attn_prefill_tc: a row of %d elements is not q, k and v heads of %d", row_stride, THD);
     if ((row_stride % 8) || ((uintptr_t)rows % 16) || (out_stride % 8) || ((uintptr_t)out % 16))
@@ -476,7 +492,7 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
     a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
     a.scale = scale; a.cap = cap; a.window = window;
-    dim3 grid(n_q_tiles, n_heads);
+    dim3 grid(n_heads, n_q_tiles);
     launch_pdl(attn_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, stream, mq, mkv, a);
     return check_launch("attn_prefill_tc");
 #else
