@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "tcgen05_pair.cuh"
 
 #ifndef HOS_HEAD_DIM
 #define HOS_HEAD_DIM 64
@@ -413,6 +414,323 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColsTc) : "memory");
 }
 
+// ---- the same walk on pairs of SMs (head sizes 128 and 256) ----------------------------------------
+// With one CTA per block of queries every CTA streams all of its keys and values from L2, and at
+// head size 256 that traffic (64 KB per 128 x 64 tile) is what bounds the kernel once the SMs are
+// full.  Here the two query heads that share a kv head (an even number of heads per group) run as a
+// pair of CTAs on the same block of 128 queries: one MMA of M = 256 (tcgen05 cta_group::2) covers
+// both heads' queries, each CTA loads half of every key tile (64 of its 128 keys) and half of every
+// value tile (half of the head's dimensions), so a key or value byte is fetched once for 256 query
+// rows, and the tiles are 128 keys wide (S: 128 columns of tensor memory, twice, beside O).
+// Each CTA's softmax warps work on their own head exactly as in the one-CTA kernel, a thread on 64
+// keys of a tile.  Who signals whom (barriers at the same offsets in both CTAs):
+//   q_full, k_full[s], v_full[s]   the leader's; its producer expects both CTAs' bytes
+//   k_empty[s], v_empty[s], s_full[b], pv_done[b]   one per CTA, by the leader's multicast commit
+//   s_empty[b], p_full[b]          the leader's; the 16 softmax warps of both CTAs arrive on it
+#if (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+constexpr int PK = 128;                                       // keys per tile
+constexpr int kPairKBlockBytes = 64 * 128;                    // this CTA's 64 keys, one column block
+constexpr int kPairKBytes = CBLK * kPairKBlockBytes;
+constexpr int kPairVBlockBytes = PK * 128;                    // 128 keys, one column block of 64 dimensions
+constexpr int kPairVBytes = (CBLK / 2) * kPairVBlockBytes;    // this CTA's half of the head's dimensions
+constexpr int kPairStageBytes = kPairKBytes + kPairVBytes;
+constexpr int kPairStages = 2;
+constexpr int kPairPBlockBytes = TQ * 128;                    // 128 rows x 64 keys
+constexpr int kPairPBytes = 2 * kPairPBlockBytes;
+constexpr int kPairPBufs = THD == 256 ? 1 : 2;                // what shared memory has room for
+constexpr int kPairSmem = kQBytesTc + kPairStages * kPairStageBytes + kPairPBufs * kPairPBytes + kXchgBytes + 160 + 976;
+constexpr int kPairColS = 0, kPairColO = 2 * PK;
+constexpr int kPairTmemCols = 512;
+static_assert(kPairSmem <= 232448, "the pair kernel's shared memory");
+static_assert(kPairColO + THD <= kPairTmemCols, "the pair kernel's tensor memory");
+
+__device__ __forceinline__ bool tc_wait_cluster(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait_cluster(bar, parity))
+        if (clock64() - t0 > kTcWaitCycles) return false;
+    return true;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
+                         const __grid_constant__ CUtensorMap map_k,      // boxes of [64 rows x 64 columns]
+                         PrefillTcArgs a) {
+    pdl_enter();      // the kernels before this one are complete from here on
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* kv_s = q_s + kQBytesTc;                       // stage s: this CTA's keys, then its part of the values
+    unsigned char* p_s = kv_s + kPairStages * kPairStageBytes;
+    float* xchg = reinterpret_cast<float*>(p_s + kPairPBufs * kPairPBytes);    // [2 halves][128 rows]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kPairPBufs * kPairPBytes + kXchgBytes);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 3;
+    uint64_t* s_full = bars + 5;
+    uint64_t* s_empty = bars + 7;
+    uint64_t* p_full = bars + 9;
+    uint64_t* pv_done = bars + 11;
+    uint64_t* v_full = bars + 13;
+    uint64_t* v_empty = bars + 15;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 17);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    // which sequence and which block of 128 queries: the same for both CTAs of a pair (they differ in the head)
+    int seq = 0, tile = blockIdx.y, row0 = 0, len = 0, nt = 0;
+    for (; seq < a.n_seqs; ++seq) {
+        row0 = a.cu_seqlens[seq];
+        len = a.cu_seqlens[seq + 1] - row0;
+        nt = (len + TQ - 1) / TQ;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (seq >= a.n_seqs) return;                                 // both CTAs of the pair alike
+    const int q0 = (nt - 1 - tile) * TQ;
+    const int head = blockIdx.x, kvh = head / (a.n_heads / a.n_kv_heads);
+    const int last_q = min(len - 1, q0 + TQ - 1);
+    const int first_key = a.window > 0 ? max(0, q0 + 1 - a.window) : 0;
+    const int kt_lo = first_key / PK, kt_hi = last_q / PK;
+    const int n_tiles = kt_hi - kt_lo + 1;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 16);
+            mbar_init(&p_full[s], 16); mbar_init(&pv_done[s], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    cluster_sync_all();                                          // both CTAs' barriers exist before anything arrives on them
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_smem, kPairTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs, each its own halves) ----------------
+        if (lane == 0) {
+            bool ok = true;
+            if (leader) mbar_expect_tx(q_full, 2 * kQBytesTc);
+            for (int c = 0; c < CBLK; ++c)
+                tma_load_2d_pair(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % kPairStages;
+                unsigned char* kd = kv_s + (size_t)s * kPairStageBytes;
+                unsigned char* vd = kd + kPairKBytes;
+                const int krow = row0 + (kt_lo + j) * PK;
+                if (j >= kPairStages && !tc_wait(&k_empty[s], ((j / kPairStages) - 1) & 1)) { ok = false; break; }
+                if (leader) mbar_expect_tx(&k_full[s], 2 * kPairKBytes);
+                for (int c = 0; c < CBLK; ++c)          // keys 64 rank .. 64 rank + 63 of the tile, all dimensions
+                    tma_load_2d_pair(kd + c * kPairKBlockBytes, &map_k, a.k_col0 + kvh * THD + 64 * c, krow + 64 * (int)rank,
+                                     &k_full[s]);
+                if (j >= kPairStages && !tc_wait(&v_empty[s], ((j / kPairStages) - 1) & 1)) { ok = false; break; }
+                if (leader) mbar_expect_tx(&v_full[s], 2 * kPairVBytes);
+                for (int c = 0; c < CBLK / 2; ++c)      // all 128 keys, this CTA's half of the dimensions
+                    tma_load_2d_pair(vd + c * kPairVBlockBytes, &map_q, a.v_col0 + kvh * THD + (THD / 2) * (int)rank + 64 * c, krow,
+                                     &v_full[s]);
+            }
+            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: one thread of the leader, for both CTAs ----------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc_s = tc_idesc(2 * TQ, PK, 0);        // S = Q K^T: both K-major
+            constexpr uint32_t idesc_o = tc_idesc(2 * TQ, THD, 1);       // O = P V: V is MN-major
+            bool ok = tc_wait(q_full, 0);
+            tc_fence_after_sync();
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % kPairStages, sb = j & 1;
+                if (!tc_wait(&k_full[s], (j / kPairStages) & 1)) return false;
+                if (j >= 2 && !tc_wait_cluster(&s_empty[sb], ((j >> 1) - 1) & 1)) return false;
+                tc_fence_after_sync();
+                const uint32_t k_addr = smem_u32(kv_s + (size_t)s * kPairStageBytes);
+#pragma unroll
+                for (int kk = 0; kk < THD / 16; ++kk) {
+                    const uint64_t ad = desc_kmajor(smem_u32(q_s) + (kk / 4) * kQBlockBytes) + 2 * (kk % 4);
+                    const uint64_t bd = desc_kmajor(k_addr + (kk / 4) * kPairKBlockBytes) + 2 * (kk % 4);
+                    umma_bf16_pair(tmem_base + kPairColS + sb * PK, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit_pair(&s_full[sb]);
+                umma_commit_pair(&k_empty[s]);      // the keys of this stage have been read
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }      // the next S runs under this tile's softmax
+                const int pb = j % kPairPBufs;
+                if (!tc_wait_cluster(&p_full[pb], (j / kPairPBufs) & 1)) { ok = false; break; }
+                const int s = j % kPairStages;
+                if (!tc_wait(&v_full[s], (j / kPairStages) & 1)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t v_addr = smem_u32(kv_s + (size_t)s * kPairStageBytes + kPairKBytes);
+#pragma unroll
+                for (int ks = 0; ks < PK / 16; ++ks) {
+                    const uint64_t ad = desc_kmajor(smem_u32(p_s) + pb * kPairPBytes + (ks / 4) * kPairPBlockBytes) + 2 * (ks % 4);
+                    const uint64_t bd = desc_mnmajor(v_addr + ks * 16 * 128, kPairVBlockBytes);
+                    umma_bf16_pair(tmem_base + kPairColO, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit_pair(&v_empty[s]);      // the values of this stage have been read
+                umma_commit_pair(&pv_done[pb]);     // this P buffer has been read, O holds tile j
+            }
+            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax, correction, epilogue: two threads per query row, 64 keys each ----------------
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                        // which 64 of the tile's 128 keys
+        const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int qpos = q0 + r;
+        const bool capped = a.cap > 0.f;
+        const float pre = capped ? a.scale / a.cap : 1.f;
+        const float c_logit = capped ? a.cap : a.scale;          // logit = c_logit * t
+        const float c2 = c_logit * 1.4426950408889634f;
+        const float slack_t = kRescaleSlack / c_logit;
+        float m_ref = -INFINITY, l_run = 0.f;                    // m_ref in units of t; l_run: this thread's keys only
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int sb = j & 1, pb = j % kPairPBufs;
+            if (!tc_wait(&s_full[sb], (j >> 1) & 1)) { ok = false; break; }
+            tc_fence_after_sync();
+            float sc[64];
+            {
+                uint32_t v0[32], v1[32];
+                tc_ld32(t_lane + kPairColS + sb * PK + 64 * half, v0);
+                tc_ld32(t_lane + kPairColS + sb * PK + 64 * half + 32, v1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(v0[i]); sc[32 + i] = __uint_as_float(v1[i]); }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&s_empty[sb]);     // this warp has its part of the S buffer
+            const int kt0 = (kt_lo + j) * PK;                    // first key of the tile
+            const int k0 = kt0 + 64 * half;
+            if (capped) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) asm("tanh.approx.f32 %0, %1;" : "=f"(sc[i]) : "f"(sc[i] * pre));
+            }
+            float m_half = -INFINITY;
+            const bool whole = kt0 + PK - 1 <= q0 && (a.window <= 0 || kt0 > q0 + TQ - 1 - a.window);
+            if (whole) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) m_half = fmaxf(m_half, sc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int key = k0 + i;
+                    const bool vis = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+                    sc[i] = vis ? sc[i] : -INFINITY;
+                    m_half = fmaxf(m_half, sc[i]);
+                }
+            }
+            xchg[half * TQ + r] = m_half;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float m_tile = fmaxf(m_half, xchg[(half ^ 1) * TQ + r]);
+            asm volatile("bar.sync 1, 256;" ::: "memory");       // both have read before the next tile writes
+            float factor = 1.f;
+            if (m_tile > m_ref + slack_t || (m_ref == -INFINITY && m_tile > -INFINITY)) {
+                factor = m_ref == -INFINITY ? 0.f : __expf((m_ref - m_tile) * c_logit);
+                m_ref = m_tile;
+            }
+            const float m_use2 = (m_ref == -INFINITY ? 0.f : m_ref) * c2;
+            float psum = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                float p0, p1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(sc[i], c2, -m_use2)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(sc[i + 1], c2, -m_use2)));
+                psum += p0 + p1;
+                packed[i / 2] = pack_bf16(p0, p1);
+            }
+            l_run = l_run * factor + psum;
+            // this P buffer is free once the product that read it last is done
+            if (j >= kPairPBufs && !tc_wait(&pv_done[pb], ((j / kPairPBufs) - 1) & 1)) { ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O is touched only between products: wait for the one of the tile before
+                if (!tc_wait(&pv_done[(j - 1) % kPairPBufs], ((j - 1) / kPairPBufs) & 1)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = half * (THD / 2); c < (half + 1) * (THD / 2); c += 32) {
+                    uint32_t o[32];
+                    tc_ld32(t_lane + kPairColO + c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tc_st32(t_lane + kPairColO + c, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            // P row r, this thread's 64 keys = column block `half`: chunk c of 16 bytes at position c ^ (r & 7)
+            {
+                unsigned char* prow = p_s + (size_t)pb * kPairPBytes + (size_t)half * kPairPBlockBytes + (size_t)r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
+            // The proxy fence makes this thread's P visible to the tensor core of its own SM, which is the one that
+            // reads it (the A rows of an MMA on a pair come from each CTA's own shared memory); the arrival on the
+            // leader's barrier is the plain one: with release semantics over the cluster this step took 1,400 cycles
+            // instead of 490 per tile.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&p_full[pb]);
+        }
+        // ---- epilogue: O / l -> bfloat16 -> global; each thread half of its row ----
+        if (ok && !tc_wait(&pv_done[(n_tiles - 1) % kPairPBufs], ((n_tiles - 1) / kPairPBufs) & 1)) ok = false;
+        if (ok) {
+            tc_fence_after_sync();
+            asm volatile("bar.sync 1, 256;" ::: "memory");      // every reader of xchg's maxima is done
+            xchg[half * TQ + r] = l_run;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float l_row = l_run + xchg[(half ^ 1) * TQ + r];
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+            bf16* orow = a.out + (size_t)(row0 + qpos) * a.out_stride + (size_t)head * THD;
+#pragma unroll 1
+            for (int c = half * (THD / 2); c < (half + 1) * (THD / 2); c += 32) {
+                uint32_t o[32];
+                tc_ld32(t_lane + kPairColO + c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (qpos < len) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        dst[q4] = make_uint4(
+                            pack_bf16(__uint_as_float(o[8 * q4]) * inv, __uint_as_float(o[8 * q4 + 1]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 2]) * inv, __uint_as_float(o[8 * q4 + 3]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 4]) * inv, __uint_as_float(o[8 * q4 + 5]) * inv),
+                            pack_bf16(__uint_as_float(o[8 * q4 + 6]) * inv, __uint_as_float(o[8 * q4 + 7]) * inv));
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(&g_prefill_tc_error, 1);
+    }
+    // ---- teardown: nobody of either CTA touches tensor memory or the other's barriers any more ----
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, kPairTmemCols);
+}
+#endif   // head sizes with the pair kernel
+
 typedef CUresult (*TcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -445,6 +763,17 @@ static int tc_make_map(CUtensorMap* map, const void* ptr, long long rows, int co
 }  // namespace hos
 
 using namespace hos;
+
+// Whether prompts of models whose query heads share keys two by two run on pairs of SMs (head sizes
+// 128 and 256).  Default on; HOS_ATTN_PAIR=0 in the environment or hos_attn_prefill_pair(0) switch it off.
+static int& pair_state() {
+    static int on = !(getenv("HOS_ATTN_PAIR") && getenv("HOS_ATTN_PAIR")[0] == '0');
+    return on;
+}
+extern "C" int hos_attn_prefill_pair(int on) {
+    pair_state() = on ? 1 : 0;
+    return 0;
+}
 
 // 1 if this library has the tensor-core prompt kernel (head sizes 64, 128, 256).
 extern "C" int hos_attn_prefill_tc_available() { return kHasTcPrefill ? 1 : 0; }
@@ -493,6 +822,19 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
     a.scale = scale; a.cap = cap; a.window = window;
     dim3 grid(n_heads, n_q_tiles);
+#if (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+    // pairs of SMs when two query heads share their keys (and nothing switched it off)
+    if (pair_state() != 0 && (n_heads / n_kv_heads) % 2 == 0) {
+        static bool pair_attr_set = false;
+        if (!pair_attr_set) {
+            if (cudaFuncSetAttribute(attn_prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess)
+                HOS_REFUSE("attn_prefill_tc: cannot get %d bytes of shared memory", kPairSmem);
+            pair_attr_set = true;
+        }
+        launch_pdl(attn_prefill_pair_kernel, dim3(grid), dim3(kTcThreads), kPairSmem, stream, mq, mkv, a);
+        return check_launch("attn_prefill_tc (pairs of SMs)");
+    }
+#endif
     launch_pdl(attn_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, stream, mq, mkv, a);
     return check_launch("attn_prefill_tc");
 #else

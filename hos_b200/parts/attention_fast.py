@@ -4,6 +4,7 @@ csrc/attention_prefill.cu).  They are compiled per head size (a multiple of 16, 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -15,7 +16,9 @@ MAX_HEAD_DIM = 256
 MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
-enabled = {"decode": True, "prefill": True, "prefill_tc": True}     # tests switch a kernel off to compare with the plain one
+enabled = {"decode": True, "prefill": True, "prefill_tc": True,
+           "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0"}
+_pair_state: Dict[int, bool] = {}     # tests switch a kernel off to compare with the plain one
 
 
 def supports(head_dim: int) -> bool:
@@ -118,11 +121,16 @@ def prompt_blocks(step, block: int):
 
 
 def prefill_tc(rows: torch.Tensor, out, cu_seqlens, n_seqs: int, blocks: int, n_heads, n_kv_heads, head_dim, scale, cap,
-               window) -> None:
+               window, pairs: bool = True) -> None:
     """Attention of whole prompts from position 0 on the tcgen05 tensor cores; `rows` is the
     fused projection output [N, (n_heads + 2 n_kv_heads) * head_dim] (head sizes 64, 128, 256).
-    `blocks`: at least the sum over sequences of ceil(length / 128)."""
+    `blocks`: at least the sum over sequences of ceil(length / 128).  `pairs`: two query heads that
+    share their keys may run as one pair of SMs (head sizes 128 and 256, an even group)."""
     lib = lib_for(head_dim)
+    want = bool(pairs and enabled["prefill_pair"])
+    if _pair_state.get(head_dim) != want:
+        lib.call("hos_attn_prefill_pair", 1 if want else 0)
+        _pair_state[head_dim] = want
     lib.call("hos_attn_prefill_tc", ops._ptr(rows), rows.shape[0], rows.shape[1], ops._ptr(out), out.shape[1],
              ops._ptr(cu_seqlens), n_seqs, blocks, n_heads, n_kv_heads, head_dim, float(scale), float(cap),
              int(window) if window else 0, ops._stream())

@@ -761,12 +761,15 @@ def test_qkv_projection_with_rotation_and_cache_write_fused(cfg):
                                  dict(nh=2, nkv=2, hd=64, window=70, cap=30.0),
                                  dict(nh=4, nkv=2, hd=128, window=100, cap=50.0),
                                  dict(nh=8, nkv=4, hd=256, window=200, cap=50.0),
-                                 dict(nh=2, nkv=1, hd=256, window=None, cap=50.0)])
-def test_attention_prefill_tensor_core_kernel(cfg):
-    """The tcgen05 prompt kernel over packed rows of unequal sequences (1 to 517 tokens; blocks
+                                 dict(nh=2, nkv=1, hd=256, window=None, cap=50.0),
+                                 dict(nh=8, nkv=2, hd=128, window=None, cap=0.0)])
+@pytest.mark.parametrize("pairs", [True, False])
+def test_attention_prefill_tensor_core_kernel(cfg, pairs):
+    """The tcgen05 prompt kernels over packed rows of unequal sequences (1 to 517 tokens; blocks
     of 128 queries that are full, partial, and cut by the window), every position against
     float64.  One logit is made large early in a sequence so that the running maximum has to
-    be raised, and O rescaled, in the middle of a walk."""
+    be raised, and O rescaled, in the middle of a walk.  `pairs`: the kernel on pairs of SMs
+    (head sizes 128 and 256 with an even number of query heads per kv head) or the one-CTA kernel."""
     from hos_b200.parts import attention_fast as af
     dt = torch.bfloat16
     nh, nkv, hd, window, cap = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], cfg["cap"]
@@ -792,7 +795,7 @@ def test_attention_prefill_tensor_core_kernel(cfg):
     cu = torch.tensor(cu_host, dtype=torch.int32, device=DEV)
     out = torch.full((N, nh * hd), 7.0, device=DEV, dtype=dt)
     blocks = sum((l + 127) // 128 for l in seq_lens) + 2        # a grid larger than needed: the extra blocks leave at once
-    af.prefill_tc(rows, out, cu, len(seq_lens), blocks, nh, nkv, hd, scale, cap, window)
+    af.prefill_tc(rows, out, cu, len(seq_lens), blocks, nh, nkv, hd, scale, cap, window, pairs=pairs)
     assert not af.prefill_tc_gave_up(hd)
     assert float((out[cu_host[-1]:] - 7.0).abs().sum()) == 0.0      # padding rows are not touched
     base = 0
