@@ -22,6 +22,8 @@
 // a few 1e-3 in a logit of ordinary size, 0.024 at the cap of 50), the 32-bit path and the
 // decode kernel use the exact form.  Every mbarrier wait is bounded in time.
 //
+// A second kernel further down runs the same walk on pairs of SMs for head sizes 128 and 256.
+//
 // Compiled per head size: -DHOS_HEAD_DIM=N; the kernel exists for N in {64, 128, 256}.
 #include <cuda.h>
 #include "common.cuh"
