@@ -46,7 +46,8 @@ inline int check_launch(const char* what) {
 // lets the kernel after it be set up in turn.  Both are no-ops for a kernel launched the
 // ordinary way.  Measured on Gemma-2 2B sizes the attribute gains 3% on a
 // 2,048-token prompt and loses 5% on a decode step at batch 8 (the step's kernels are short and
-// the graph replays them back to back anyway); issuing the first weight loads of the few-rows
+// the graph replays them back to back anyway, and the loss is the same 5% whether a kernel lets its
+// successor go at its start or only after its main loop); issuing the first weight loads of the few-rows
 // products before the wait changed nothing at batch 8 and gained 3% at batch 1.  So the engine
 // switches it on for prompt steps and off for single-token steps (hos_set_pdl); HOS_PDL=0 or 1 in
 // the environment fixes it for all.  One pair uses it always: the decode attention kernel fetches
