@@ -51,6 +51,7 @@ struct DecodeArgs {
     const int* token_pos;
     const int* token_seq;
     const int* seq_slot;
+    const int* token_slot;    // seq_slot[token_seq[n]] for every token, or null: one dependent load less before the first copy
     PagedKV cache;
     int n_tokens, n_heads, n_splits;
     int stages, merge_rows;
@@ -71,7 +72,7 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;
 // What an item is and which pages it covers: the same arithmetic on both sides of the pipe.
 struct Item {
     int n, y, kvh, head0, n_rows, split;     // y: (kv head, chunk of 16 query heads) of the token
-    int seq, pos, lo, lp_begin, n_tiles;
+    int seq, pos, slot, lo, lp_begin, n_tiles;
 };
 __device__ __forceinline__ Item make_item(const DecodeArgs& a, int index, int group, int chunks) {
     Item it;
@@ -84,10 +85,13 @@ __device__ __forceinline__ Item make_item(const DecodeArgs& a, int index, int gr
     const int chunk = y % chunks;
     it.head0 = it.kvh * group + chunk * kMaxHeadsPerCta;
     it.n_rows = min(kMaxHeadsPerCta, group - chunk * kMaxHeadsPerCta);
+    // the three look-ups go out together; only the slot of a step that gives none waits for the sequence
     it.seq = a.token_seq[it.n];
-    it.pos = 0; it.lo = 0; it.lp_begin = 0; it.n_tiles = 0;
-    if (it.seq < 0) return it;
     it.pos = a.token_pos[it.n];
+    it.slot = a.token_slot != nullptr ? a.token_slot[it.n] : -1;
+    it.lo = 0; it.lp_begin = 0; it.n_tiles = 0;
+    if (it.seq < 0) { it.pos = 0; return it; }
+    if (a.token_slot == nullptr) it.slot = a.seq_slot[it.seq];
     it.lo = a.window > 0 ? max(0, it.pos + 1 - a.window) : 0;
     const int lp_lo = it.lo / kPageTokens, lp_hi = it.pos / kPageTokens;
     const int n_lp = lp_hi - lp_lo + 1;
@@ -139,7 +143,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             for (int index = blockIdx.x; index < total_items && ok; index += gridDim.x) {
                 const Item it = make_item(a, index, group, chunks);
                 if (it.n_tiles == 0) continue;
-                const int* table = a.cache.page_table + (size_t)a.seq_slot[it.seq] * a.cache.table_stride;
+                const int* table = a.cache.page_table + (size_t)it.slot * a.cache.table_stride;
                 for (int tile = 0; tile < it.n_tiles; ++tile, ++t) {
                     const int s = t % stages;
                     if (!waited && (t >= stages || (it.lp_begin + tile + 1) * kPageTokens > it.pos + 1 - a.max_new)) {
@@ -426,7 +430,7 @@ extern "C" int hos_attn_decode_error() {
 
 extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_stride, float* workspace,
                                int* tickets, const int* token_pos, const int* token_seq, const int* seq_slot,
-                               void* k_pages, void* v_pages, const int* page_table, int table_stride,
+                               const int* token_slot, void* k_pages, void* v_pages, const int* page_table, int table_stride,
                                int ring_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                float scale, float cap, int window, int n_splits, int max_new, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -462,7 +466,7 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     a.part_o = workspace;
     a.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * n_splits * HD : nullptr;
     a.tickets = tickets;
-    a.token_pos = token_pos; a.token_seq = token_seq; a.seq_slot = seq_slot;
+    a.token_pos = token_pos; a.token_seq = token_seq; a.seq_slot = seq_slot; a.token_slot = token_slot;
     a.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
     a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_splits = n_splits;
     a.scale = scale; a.cap = cap; a.window = window; a.max_new = max_new;
@@ -517,7 +521,7 @@ extern "C" int hos_attn_decode_noalloc(const void* q, int q_stride, void* out, i
         cudaError_t e = cudaMemsetAsync(tickets, 0, (size_t)pairs * sizeof(int), stream);
         if (e != cudaSuccess) HOS_REFUSE("attn_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
     }
-    return hos_attn_decode(q, q_stride, out, out_stride, workspace, tickets, token_pos, token_seq, seq_slot, k_pages,
+    return hos_attn_decode(q, q_stride, out, out_stride, workspace, tickets, token_pos, token_seq, seq_slot, nullptr, k_pages,
                            v_pages, page_table, table_stride, ring_pages, n_tokens, n_heads, n_kv_heads, head_dim,
                            scale, cap, window, n_splits, /*max_new: nothing is fetched ahead*/ 1 << 30, stream);
 }

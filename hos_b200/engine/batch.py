@@ -25,9 +25,9 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
     cu = np.zeros(b + 1, dtype=np.int64)
     np.cumsum(news, out=cu[1:])
     n_extra = len(extra) if extra is not None else 0
-    flat = np.empty(3 * nn + (b + 1) + 2 * b + n_extra, dtype=np.int32)
-    tokens, pos, seq = flat[:nn], flat[nn:2 * nn], flat[2 * nn:3 * nn]
-    tokens[n:], pos[n:], seq[n:] = -1, 0, -1                     # padding rows
+    flat = np.empty(4 * nn + (b + 1) + 2 * b + n_extra, dtype=np.int32)
+    tokens, pos, seq, tslot = flat[:nn], flat[nn:2 * nn], flat[2 * nn:3 * nn], flat[3 * nn:4 * nn]
+    tokens[n:], pos[n:], seq[n:], tslot[n:] = -1, 0, -1, 0       # padding rows
     for i, (toks, start) in enumerate(zip(token_lists, starts)):
         lo, hi = int(cu[i]), int(cu[i + 1])
         if hi == lo:
@@ -41,7 +41,8 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
         tokens[lo:hi] = ids
         pos[lo:hi] = np.arange(start, start + hi - lo)
         seq[lo:hi] = i
-    o = 3 * nn
+        tslot[lo:hi] = slots[i]
+    o = 4 * nn
     flat[o:o + b + 1] = cu
     flat[o + b + 1:o + 2 * b + 1] = np.asarray(slots, dtype=np.int64)
     lens_after = [s + k for s, k in zip(starts, news)]
@@ -57,7 +58,7 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
         dev = host.to(device)
     info = StepInfo(
         n_tokens=nn, n_seqs=b, tokens=dev[:nn], token_pos=dev[nn:2 * nn], token_seq=dev[2 * nn:3 * nn],
-        cu_seqlens=dev[o:o + b + 1], seq_slot=dev[o + b + 1:o + 2 * b + 1],
+        token_slot=dev[3 * nn:4 * nn], cu_seqlens=dev[o:o + b + 1], seq_slot=dev[o + b + 1:o + 2 * b + 1],
         seq_len_after=dev[o + 2 * b + 1:o + 3 * b + 1],
         from_zero=all(s == 0 for s in starts),
         single_token=all(k == 1 for k in news),

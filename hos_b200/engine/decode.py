@@ -84,7 +84,8 @@ class DecodeSession:
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot,
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
                         max_len_after=self._max_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
-                        starts_host=(), min_live=smaller_bucket(self.b) + 1, replayed=True)
+                        starts_host=(), token_slot=self.slot,      # row n is sequence n here
+                        min_live=smaller_bucket(self.b) + 1, replayed=True)
 
     def feed(self, slots: Sequence[int], tokens: Sequence[int], lengths_before: Sequence[int]) -> None:
         """Host token ids, slots and each sequence's length before the step -> the static

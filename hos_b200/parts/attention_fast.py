@@ -75,11 +75,12 @@ def _tickets(device, n: int) -> torch.Tensor:
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
            window: Optional[int], max_len: int, n_splits: Optional[int] = None,
-           max_new: Optional[int] = None, min_live: int = 0) -> None:
+           max_new: Optional[int] = None, min_live: int = 0, token_slot=None) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
     position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
     the kernel may fetch keys that lie below them while the kernel before it (which writes the
-    step's new keys) still runs.  None: it fetches nothing ahead."""
+    step's new keys) still runs.  None: it fetches nothing ahead.  `token_slot`: each token's cache slot
+    (seq_slot[token_seq]) if the step has it: the kernel then finds its first page one look-up sooner."""
     hd, nkv = cache.head_dim, cache.n_kv_heads
     lib = lib_for(hd)
     if n_splits is None:
@@ -89,7 +90,8 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
         tickets = _tickets(q.device, n_tokens * nkv * ((n_heads // nkv + 15) // 16))
     lib.call("hos_attn_decode", ops._ptr(q), q_stride, ops._ptr(out), out.shape[1], ops._ptr(ws),
-             ops._ptr(tickets), ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(cache.k_pages),
+             ops._ptr(tickets), ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(token_slot),
+             ops._ptr(cache.k_pages),
              ops._ptr(cache.v_pages), ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages,
              n_tokens, n_heads, nkv, hd, float(scale), float(cap), int(window) if window else 0,
              int(n_splits), int(max_new) if max_new else 1 << 30, ops._stream())
@@ -177,5 +179,5 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
         return False
     decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
            mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new,
-           min_live=getattr(step, "min_live", 0))
+           min_live=getattr(step, "min_live", 0), token_slot=getattr(step, "token_slot", None))
     return True

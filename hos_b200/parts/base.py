@@ -92,6 +92,7 @@ class StepInfo:
     slots_host: Sequence[int] = ()   # the same as seq_slot, on the host
     cu_host: Sequence[int] = ()      # the same as cu_seqlens, on the host
     starts_host: Sequence[int] = ()  # each sequence's length before the step
+    token_slot: Optional[torch.Tensor] = None   # int32 [N] seq_slot[token_seq] for every row (anything for padding), if at hand
     min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
     replayed: bool = False           # the device arrays are refilled and the same launches replayed (a CUDA
                                      # graph): n_tokens and n_seqs are capacities, the host lists are empty
