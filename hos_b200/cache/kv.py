@@ -72,13 +72,22 @@ class KVGroup:
             self.pages.give_back(page)
 
     def flush(self) -> None:
+        """Changed rows of the table go to the device: staged in pinned memory (the host may change the
+        table again before the copy runs), one asynchronous copy per run of neighbouring rows, no kernel."""
         if not self._dirty:
             return
         rows = sorted(self._dirty)
-        idx = torch.tensor(rows, dtype=torch.long)
-        self.table_dev[idx.to(self.table_dev.device)] = self.table_host[idx].to(
-            self.table_dev.device, non_blocking=False)
         self._dirty.clear()
+        on_gpu = self.table_dev.device.type == "cuda"
+        staged = torch.empty((len(rows), self.table_stride), dtype=torch.int32, pin_memory=on_gpu)
+        torch.index_select(self.table_host, 0, torch.tensor(rows, dtype=torch.long), out=staged)
+        at = 0
+        while at < len(rows):
+            end = at + 1
+            while end < len(rows) and rows[end] == rows[end - 1] + 1:
+                end += 1
+            self.table_dev[rows[at]:rows[at] + end - at].copy_(staged[at:end], non_blocking=on_gpu)
+            at = end
 
     def view(self, entry: int) -> ops.PagedKVArgs:
         return ops.PagedKVArgs(self.k[entry], self.v[entry], self.table_dev, self.ring_pages,
