@@ -23,8 +23,19 @@ namespace hos {
 
 constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
-constexpr int kUnroll = 8;          // k-blocks of 32 whose loads are issued before any is used: fewer with more token tiles (registers)
-template <int MT> struct Unroll { static constexpr int value = MT == 1 ? 8 : (MT == 2 ? 4 : 2); };
+// A warp walks its share of K in rounds: the loads of U k-blocks of 32 are written before any is used, and a
+// round costs a memory latency however few blocks it holds.  So U is chosen (unroll_for, on the host) to deal
+// the blocks evenly over the fewest rounds: at K = 2304 a warp has 9 or 18 blocks, which 8 at a time walked in
+// 2 or 3 rounds (8 + 1, 8 + 8 + 2) and 9 at a time walks in 1 or 2 (a decode step at 8 sequences 2.243 ->
+// 2.19 ms, at 32 sequences 4.75 -> 4.57 ms).  The compiler keeps within 128 registers by issuing some of a
+// round's loads between its products; with more than 8 rows more than 9 blocks at a time do not pay.
+static int unroll_for(int blocks_per_warp, int token_tiles) {
+    const int most = token_tiles == 1 ? 12 : 9;
+    const int rounds = (blocks_per_warp + most - 1) / most;
+    const int need = rounds > 0 ? (blocks_per_warp + rounds - 1) / rounds : 1;
+    if (token_tiles > 1) return need <= 8 ? 8 : 9;
+    return need <= 7 ? 7 : (need <= 8 ? 8 : (need <= 9 ? 9 : (need <= 10 ? 10 : 12)));
+}
 constexpr int kMaxTokenTiles = 4;       // token tiles of 8: up to 32 rows
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
@@ -37,7 +48,7 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
 }
 
 // MT: token tiles of 8 (M <= 8 MT).  GATED: rows come in gate/up pairs.
-template <int MT, bool GATED, typename OutT>
+template <int MT, int kUnroll, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
@@ -151,7 +162,7 @@ struct QkvRopeArgs {
     int n_heads, rotary_dim, style, write_cache;
 };
 
-template <int MT>
+template <int MT, int kUnroll>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* __restrict__ out,
                        int M, int K, int lda, int ldw, int ldo, QkvRopeArgs q) {
@@ -293,15 +304,28 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     if (k_splits > 1 && (epilogue != 0 || out_dtype != kF32))
         HOS_REFUSE("gemm_skinny: partial sums over a split K are 32-bit and take no epilogue");
     const unsigned grid = (unsigned)((N + 15) / 16);
-#define HOS_SK(MT, G, T)                                                                                     \
-    launch_pdl(gemm_skinny_kernel<MT, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+    const int k_ways = epilogue == 2 ? kSkinnyWarps / 2 : kSkinnyWarps;
+    const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
+    const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
+#define HOS_SK(MT, U, G, T)                                                                                     \
+    launch_pdl(gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
+#define HOS_SK_U(MT, G, T)                              \
+    do {                                                \
+        if (unroll == 8) HOS_SK(MT, 8, G, T);           \
+        else HOS_SK(MT, 9, G, T);                       \
+    } while (0)
 #define HOS_SK_M(G, T)                                  \
     do {                                                \
-        if (M <= 8) HOS_SK(1, G, T);                    \
-        else if (M <= 16) HOS_SK(2, G, T);              \
-        else if (M <= 24) HOS_SK(3, G, T);              \
-        else HOS_SK(4, G, T);                           \
+        if (M <= 8) {                                   \
+            if (unroll == 7) HOS_SK(1, 7, G, T);        \
+            else if (unroll == 8) HOS_SK(1, 8, G, T);   \
+            else if (unroll == 9) HOS_SK(1, 9, G, T);   \
+            else if (unroll == 10) HOS_SK(1, 10, G, T); \
+            else HOS_SK(1, 12, G, T);                   \
+        } else if (M <= 16) HOS_SK_U(2, G, T);          \
+        else if (M <= 24) HOS_SK_U(3, G, T);            \
+        else HOS_SK_U(4, G, T);                         \
     } while (0)
     if (epilogue == 2) {
         HOS_SK_M(true, bf16);
@@ -312,6 +336,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     } else {
         HOS_REFUSE("gemm_skinny: unknown output dtype %d", out_dtype);
     }
+#undef HOS_SK_U
 #undef HOS_SK_M
 #undef HOS_SK
     return check_launch("gemm_skinny");
@@ -339,13 +364,25 @@ extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int 
     q.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
     q.n_heads = n_heads; q.rotary_dim = rotary_dim; q.style = style; q.write_cache = write_cache;
     const unsigned grid = (unsigned)((n_heads + 2 * n_kv_heads) * (head_dim / 16));
-#define HOS_QR(MT)                                                                                                      \
-    launch_pdl(qkv_rope_skinny_kernel<MT>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, \
+    const int unroll = unroll_for(((K + 31) / 32 + kSkinnyWarps - 1) / kSkinnyWarps, (M + 7) / 8);
+#define HOS_QR(MT, U)                                                                                                      \
+    launch_pdl(qkv_rope_skinny_kernel<MT, U>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, \
                (bf16*)out, M, K, lda, ldw, ldo, q)
-    if (M <= 8) HOS_QR(1);
-    else if (M <= 16) HOS_QR(2);
-    else if (M <= 24) HOS_QR(3);
-    else HOS_QR(4);
+#define HOS_QR_U(MT)                     \
+    do {                                 \
+        if (unroll == 8) HOS_QR(MT, 8);  \
+        else HOS_QR(MT, 9);              \
+    } while (0)
+    if (M <= 8) {
+        if (unroll == 7) HOS_QR(1, 7);
+        else if (unroll == 8) HOS_QR(1, 8);
+        else if (unroll == 9) HOS_QR(1, 9);
+        else if (unroll == 10) HOS_QR(1, 10);
+        else HOS_QR(1, 12);
+    } else if (M <= 16) HOS_QR_U(2);
+    else if (M <= 24) HOS_QR_U(3);
+    else HOS_QR_U(4);
+#undef HOS_QR_U
 #undef HOS_QR
     return check_launch("qkv_rope_skinny");
 }
