@@ -293,6 +293,20 @@ __global__ void residual_add_kernel(const TY* __restrict__ y, float* __restrict_
     if (i < n) x[i] += to_float(y[i]);
 }
 
+// ---- the angles of a step, once for all layers -------------------------------------------------
+// out[n][i] = (cos, sin) of position[n] * inv_freq[i], in 32-bit: what the q/k/v projection of many tokens
+// reads in its epilogue instead of taking a sine and a cosine per head.
+__global__ void rope_table_kernel(const int* __restrict__ token_pos, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ out, int N, int half) {
+    pdl_enter();      // the kernels before this one are complete from here on
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)N * half) return;
+    const int n = (int)(idx / half), i = (int)(idx % half);
+    float sn, cs;
+    sincosf((float)token_pos[n] * inv_freq[i], &sn, &cs);
+    out[idx] = make_float2(cs, sn);
+}
+
 // ---- rotary encoding + cache write --------------------------------------------------
 // One block per token.  The q and k heads of the fused projection row are rotated
 // (angle = position * inv_freq[i], sincosf in 32-bit, once per pair and token), the row is
@@ -712,6 +726,15 @@ extern "C" int hos_rope_kv_write(const void* src, int src_dtype, int n_parts, vo
     else HOS_REFUSE("rope: unknown dtype %d", dtype);
 #undef HOS_ROPE
     return check_launch("rope_kv_write");
+}
+
+extern "C" int hos_rope_table(const int* token_pos, const float* inv_freq, float* out, int N, int half,
+                              cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return 0;
+    const size_t n = (size_t)N * half;
+    launch_pdl(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, token_pos, inv_freq,
+               reinterpret_cast<float2*>(out), N, half);
+    return check_launch("rope_table");
 }
 
 extern "C" int hos_gated_act(const void* gu, void* out, int dtype, int N, int F, int act,

@@ -25,6 +25,7 @@
 // the roles leave their loops, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 #include "common.cuh"
+#include "kv_layout.cuh"
 #include "mma_utils.cuh"
 #include "tcgen05_pair.cuh"
 
@@ -35,7 +36,7 @@ constexpr int GK = 64;             // K elements per stage: 128 bytes, one swizz
 constexpr int kGemmThreads = 192;
 constexpr long long kWaitCycles = 1ll << 31;     // about a second
 
-enum { kGEpiNone = 0, kGEpiSoftcap = 1, kGEpiGated = 2 };
+enum { kGEpiNone = 0, kGEpiSoftcap = 1, kGEpiGated = 2, kGEpiRope = 3 };
 
 __device__ int g_gemm_error = 0;
 
@@ -122,6 +123,19 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// What the rotary epilogue of the q/k/v projection needs (kGEpiRope): the output's columns are q heads, then k
+// heads, then v heads of head_dim each; q and k heads are rotated (rotate-half over the whole head: the pair
+// (i, i + head_dim/2) by position * inv_freq[i]), and keys and values go to the tokens' places in the paged cache.
+struct RopeEpi {
+    const int* token_pos;
+    const int* token_seq;
+    const int* seq_slot;
+    const int* seq_len_after;
+    const float2* angles;      // [M][head_dim / 2] (cos, sin)
+    PagedKV cache;
+    int n_heads, n_kv_heads, write_cache;
+};
+
 struct GemmParams {
     void* out;            // [M, N] row-major (bf16 or f32); with K splits: f32 partials [splits][M][N]
     int M, N, K;          // the product's logical sizes: rows of A, rows of W (per half if gated), K
@@ -130,6 +144,7 @@ struct GemmParams {
     int gate_rows;        // gated: row of W where the up rows begin
     float cap;
     int act;
+    RopeEpi rope;         // kGEpiRope only
 };
 
 template <int BN, bool SWAP>
@@ -523,6 +538,73 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
             const int m = mt * 2 * GM + (int)rank * GM + r;
             OutT* orow = reinterpret_cast<OutT*>(p.out) + (size_t)m * p.ldo;
             constexpr int COLS = (EPI == kGEpiGated) ? BN / 2 : BN;
+            if constexpr (EPI == kGEpiRope) {
+                // A tile holds whole heads (head_dim divides 256).  A thread has one token's row: it rotates the
+                // pairs (i, i + head_dim/2) of q and k heads, writes the row, and puts keys and values into the cache.
+                const RopeEpi& q = p.rope;
+                const int hd = q.cache.head_dim, half = hd >> 1;
+                const bool in_rows = m < p.M;
+                const int seq = in_rows ? q.token_seq[m] : -1;
+                const int pos = in_rows ? q.token_pos[m] : 0;
+                const int first_head = nt * BN / hd;
+                int page = -1;
+                if (seq >= 0 && q.write_cache && first_head + BN / hd > q.n_heads &&
+                    !(q.cache.ring_pages > 0 && pos + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq]))
+                    page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
+                                              kv_table_entry(q.cache, pos / kPageTokens)];
+                const int rr = pos % kPageTokens;
+#pragma unroll 1
+                for (int col0 = 0; col0 < BN && nt * BN + col0 < p.N; col0 += hd) {
+                    const int head = first_head + col0 / hd;
+                    const bool is_v = head >= q.n_heads + q.n_kv_heads;
+                    bf16* tile = nullptr;
+                    if (head >= q.n_heads && page >= 0)
+                        tile = (bf16*)(is_v ? q.cache.v_pages : q.cache.k_pages) +
+                               kv_tile_offset(q.cache, page, is_v ? head - q.n_heads - q.n_kv_heads : head - q.n_heads);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < half; c0 += 32) {
+                        uint32_t lo[32], hi[32];
+                        tmem_ld_32x32(t_lane + col0 + c0, lo);
+                        tmem_ld_32x32(t_lane + col0 + half + c0, hi);
+                        tmem_ld_wait();
+                        if (in_rows) {
+                        if (!is_v && seq >= 0) {
+                            const float4* ang = reinterpret_cast<const float4*>(q.angles + (size_t)m * half + c0);
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float4 a2 = __ldg(ang + j / 2);          // (cos, sin) of two pairs
+                                const float x0 = __uint_as_float(lo[j]), x1 = __uint_as_float(hi[j]);
+                                lo[j] = __float_as_uint(x0 * a2.x - x1 * a2.y);
+                                hi[j] = __float_as_uint(x0 * a2.y + x1 * a2.x);
+                                const float y0 = __uint_as_float(lo[j + 1]), y1 = __uint_as_float(hi[j + 1]);
+                                lo[j + 1] = __float_as_uint(y0 * a2.z - y1 * a2.w);
+                                hi[j + 1] = __float_as_uint(y0 * a2.w + y1 * a2.z);
+                            }
+                        }
+                        bf16* dst = reinterpret_cast<bf16*>(orow) + nt * BN + col0 + c0;
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const uint4 a = make_uint4(
+                                pack_bf16(__uint_as_float(lo[8 * q4]), __uint_as_float(lo[8 * q4 + 1])),
+                                pack_bf16(__uint_as_float(lo[8 * q4 + 2]), __uint_as_float(lo[8 * q4 + 3])),
+                                pack_bf16(__uint_as_float(lo[8 * q4 + 4]), __uint_as_float(lo[8 * q4 + 5])),
+                                pack_bf16(__uint_as_float(lo[8 * q4 + 6]), __uint_as_float(lo[8 * q4 + 7])));
+                            const uint4 b = make_uint4(
+                                pack_bf16(__uint_as_float(hi[8 * q4]), __uint_as_float(hi[8 * q4 + 1])),
+                                pack_bf16(__uint_as_float(hi[8 * q4 + 2]), __uint_as_float(hi[8 * q4 + 3])),
+                                pack_bf16(__uint_as_float(hi[8 * q4 + 4]), __uint_as_float(hi[8 * q4 + 5])),
+                                pack_bf16(__uint_as_float(hi[8 * q4 + 6]), __uint_as_float(hi[8 * q4 + 7])));
+                            *reinterpret_cast<uint4*>(dst + 8 * q4) = a;
+                            *reinterpret_cast<uint4*>(dst + half + 8 * q4) = b;
+                            if (tile != nullptr) {
+                                *reinterpret_cast<uint4*>(tile + kv_elem_offset(rr, c0 + 8 * q4, hd)) = a;
+                                *reinterpret_cast<uint4*>(tile + kv_elem_offset(rr, half + c0 + 8 * q4, hd)) = b;
+                            }
+                        }
+                        }
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < COLS; c0 += 32) {
                 uint32_t v[32], u[32];
@@ -560,6 +642,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                             if (n0 + j < p.N) orow[n0 + j] = from_float<OutT>(f[j]);
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -785,4 +868,43 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     if (bn == 32) HOS_GO(32, kGEpiNone, true, float, tiles);
     HOS_GO(64, kGEpiNone, true, float, tiles);
 #undef HOS_GO
+}
+
+// The q/k/v projection of many tokens with the rotary encoding and the cache write in its epilogue (pairs of
+// SMs): out[M, N] = A . W^T, N = (n_heads + 2 n_kv_heads) * head_dim (n_kv_heads = 0: q heads only), q and k heads
+// rotated over the whole head (rotate-half) by the angles[M][head_dim / 2] (cos, sin) of hos_rope_table, keys and
+// values stored at the tokens' places if write_cache.
+// head_dim 64, 128 or 256; at least 512 rows; bfloat16 output whose rows are 16-byte aligned.
+extern "C" int hos_gemm_tc_qkv_rope(const void* A, const void* W, void* out, int M, int N, int K, int lda, int ldw, int ldo,
+                                    int n_heads, int n_kv_heads, int head_dim, const int* token_pos, const int* token_seq,
+                                    const int* seq_slot, const int* seq_len_after, const float* angles, void* k_pages,
+                                    void* v_pages, const int* page_table, int table_stride, int ring_pages,
+                                    int write_cache, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M < 512) HOS_REFUSE("gemm_tc_qkv_rope: %d rows are fewer than the 512 this kernel is for", M);
+    if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
+        HOS_REFUSE("gemm_tc_qkv_rope: K and the leading dimensions must be multiples of 8 elements and the operands "
+                   "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+        HOS_REFUSE("gemm_tc_qkv_rope: head_dim %d is not 64, 128 or 256", head_dim);
+    if (n_heads <= 0 || n_kv_heads < 0 || N != (n_heads + 2 * n_kv_heads) * head_dim)
+        HOS_REFUSE("gemm_tc_qkv_rope: %d columns are not %d + 2 x %d heads of %d", N, n_heads, n_kv_heads, head_dim);
+    if ((ldo % 8) || ((uintptr_t)out % 16)) HOS_REFUSE("gemm_tc_qkv_rope: output rows must be 16-byte aligned");
+    if (angles == nullptr || ((uintptr_t)angles % 16) || token_pos == nullptr || token_seq == nullptr)
+        HOS_REFUSE("gemm_tc_qkv_rope: positions, sequences and the table of angles (16-byte aligned) are needed");
+    if (write_cache && (n_kv_heads == 0 || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
+                        seq_slot == nullptr || seq_len_after == nullptr))
+        HOS_REFUSE("gemm_tc_qkv_rope: the cache write needs kv heads, pages, a page table, slots and lengths");
+    GemmParams p;
+    p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.k_splits = 1; p.gate_rows = N; p.cap = 0.f; p.act = 0;
+    p.rope.token_pos = token_pos; p.rope.token_seq = token_seq; p.rope.seq_slot = seq_slot;
+    p.rope.seq_len_after = seq_len_after; p.rope.angles = reinterpret_cast<const float2*>(angles);
+    p.rope.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
+    p.rope.n_heads = n_heads; p.rope.n_kv_heads = n_kv_heads; p.rope.write_cache = write_cache;
+    CUtensorMap mm, mn;
+    int rc;
+    if ((rc = make_map(&mm, A, M, K, lda, GM))) return rc;
+    if ((rc = make_map(&mn, W, N, K, ldw, 128))) return rc;
+    const int m_tiles = (M + 2 * GM - 1) / (2 * GM);
+    return launch_pair<kGEpiRope, bf16>(mm, mn, p, m_tiles * ((N + 255) / 256), stream);
 }

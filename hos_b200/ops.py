@@ -225,6 +225,16 @@ def norm_add_norm(y: torch.Tensor, w_post: torch.Tensor, eps_post: float, add_on
                 _ptr(h), dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
 
 
+def rope_table(token_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """float32 [N, len(inv_freq), 2]: (cos, sin) of position * inv_freq, taken in 32-bit."""
+    _check(token_pos, "positions", torch.int32, 1)
+    _check(inv_freq, "inverse frequencies", torch.float32, 1)
+    out = torch.empty((token_pos.shape[0], inv_freq.shape[0], 2), dtype=torch.float32, device=token_pos.device)
+    core().call("hos_rope_table", _ptr(token_pos), _ptr(inv_freq), _ptr(out), token_pos.shape[0], inv_freq.shape[0],
+                _stream())
+    return out
+
+
 def residual_add(y: torch.Tensor, x: torch.Tensor) -> None:
     _check(y, "branch output")
     _check(x, "residual stream", torch.float32)

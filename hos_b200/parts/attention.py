@@ -84,12 +84,17 @@ class SoftmaxAttention(Mixer):
         inv_freq, rotary_dim, style = self.position.kernel_args() if self.position else (None, 0, 0)
         w = self.w_qkv if store.owns_kv else self.w_q
         n_kv = self.n_kv_heads if store.owns_kv else 0
-        from . import gemm_skinny
+        from . import gemm_skinny, gemm_tc
         if not linear.plain_forced() and gemm_skinny.can_fuse_qkv_rope(h, w, self.head_dim, rotary_dim):
             # a handful of rows: projection, rotation and cache write in one kernel
             qkv = torch.empty((n, w.shape[0]), dtype=h.dtype, device=h.device)
             gemm_skinny.qkv_rope(h, w, qkv, self.n_heads, n_kv, self.head_dim, step, inv_freq, rotary_dim, style,
                                  cache if store.owns_kv else None)
+        elif not linear.plain_forced() and gemm_tc.can_fuse_qkv_rope(h, w, self.head_dim, rotary_dim, style, inv_freq):
+            # many rows: the same on the tensor cores (tiles of 256 columns hold whole heads)
+            qkv = torch.empty((n, w.shape[0]), dtype=h.dtype, device=h.device)
+            gemm_tc.qkv_rope(h, w, qkv, self.n_heads, n_kv, self.head_dim, step, inv_freq,
+                             cache if store.owns_kv else None)
         elif store.owns_kv:
             qkv = linear.matmul_or_partials(h, w)
             parts = None

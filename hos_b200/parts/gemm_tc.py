@@ -87,3 +87,50 @@ def gave_up() -> bool:
     f.restype = ctypes.c_int
     f.argtypes = []
     return bool(f())
+
+
+PAIR_MIN_ROWS = 512      # from here on the product runs on pairs of SMs
+
+
+def can_fuse_qkv_rope(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int, style: int, inv_freq) -> bool:
+    """Whether the q/k/v projection of many tokens can rotate q and k and store keys and values in its own
+    epilogue: the product's rules, at least 512 rows, the whole head rotated with the rotate-half pairing,
+    a head size that divides the tile's 256 columns."""
+    if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] < PAIR_MIN_ROWS:
+        return False
+    if inv_freq is None or rotary_dim != head_dim or style != 0 or head_dim not in (64, 128, 256):
+        return False
+    k = x.shape[1]
+    if k % 8 != 0 or x.stride(1) != 1 or w.stride(1) != 1 or x.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    return x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def step_angles(step, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of every token's position times every inverse frequency, float32 [N, len(inv_freq), 2]:
+    taken once per step and set of frequencies and kept on the step, so that all layers share it."""
+    kept = getattr(step, "_angles", None)
+    if kept is None:
+        kept = {}
+        try:
+            step._angles = kept
+        except AttributeError:
+            pass
+    key = (inv_freq.data_ptr(), inv_freq.shape[0])
+    table = kept.get(key)
+    if table is None or getattr(step, "replayed", False):
+        table = kept[key] = ops.rope_table(step.token_pos, inv_freq)
+    return table
+
+
+def qkv_rope(x, w, out, n_heads: int, n_kv_heads: int, head_dim: int, step, inv_freq, cache) -> None:
+    """out[M, (n_heads + 2 n_kv_heads) * head_dim] = x . w^T with q and k heads rotated and, if `cache` is given,
+    keys and values stored at the tokens' places.  n_kv_heads = 0: q heads only."""
+    m, k = x.shape
+    angles = step_angles(step, inv_freq)
+    lib().call("hos_gemm_tc_qkv_rope", ops._ptr(x), ops._ptr(w), ops._ptr(out), m, out.shape[1], k, x.stride(0),
+               w.stride(0), out.stride(0), n_heads, n_kv_heads, head_dim, ops._ptr(step.token_pos),
+               ops._ptr(step.token_seq), ops._ptr(step.seq_slot), ops._ptr(step.seq_len_after), ops._ptr(angles),
+               ops._ptr(cache.k_pages) if cache else None, ops._ptr(cache.v_pages) if cache else None,
+               ops._ptr(cache.page_table) if cache else None, cache.table_stride if cache else 0,
+               cache.ring_pages if cache else 0, 1 if cache else 0, ops._stream())

@@ -17,6 +17,9 @@ from ..registry import register_part
 from .base import Part
 
 
+_shared = {}
+
+
 class Rotary(Part):
     graph_safe = True
 
@@ -30,11 +33,14 @@ class Rotary(Part):
         if self.rotary_dim % 2 != 0 or self.rotary_dim <= 0:
             raise SpecError(f"arch spec error: rotary_dim {self.rotary_dim} must be positive and even")
         self.style = ops.ROPE_STYLES[style]
-        half = self.rotary_dim // 2
-        i = torch.arange(half, dtype=torch.float32)
-        exponent = 2.0 * i / float(self.rotary_dim)
-        self.inv_freq = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent)) \
-            .to(rt.device).contiguous()
+        key = (str(rt.device), self.theta, self.rotary_dim)
+        if key not in _shared:          # layers with the same frequencies share one tensor (and what is derived from it)
+            half = self.rotary_dim // 2
+            i = torch.arange(half, dtype=torch.float32)
+            exponent = 2.0 * i / float(self.rotary_dim)
+            _shared[key] = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent)) \
+                .to(rt.device).contiguous()
+        self.inv_freq = _shared[key]
 
     def kernel_args(self):
         """(inverse frequencies [rotary_dim/2] float32 on the device, rotary_dim, style code)."""

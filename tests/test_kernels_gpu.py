@@ -757,6 +757,64 @@ def test_qkv_projection_with_rotation_and_cache_write_fused(cfg):
         assert float(ca.k_pages.abs().sum()) > 0
 
 
+@pytest.mark.parametrize("cfg", [dict(nh=3, nkv=1, hd=64, K=264, ring=0),
+                                 dict(nh=4, nkv=2, hd=128, K=520, ring=3),
+                                 dict(nh=2, nkv=1, hd=256, K=136, ring=0),
+                                 dict(nh=5, nkv=0, hd=64, K=72, ring=0)])
+def test_qkv_projection_of_many_tokens_with_rotation_and_cache_write_fused(cfg):
+    """The tensor-core q/k/v projection of 600 tokens that rotates and stores in its epilogue, against a
+    float64 product and rotation, and its cache against the separate rotate-and-store kernel given the
+    same rows: tiles that hold four, two and one head and a last tile that is partly empty, three
+    sequences at far positions, a ring whose oldest tokens must not be stored, padding rows, q heads alone."""
+    from types import SimpleNamespace
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc
+    nh, nkv, hd, K, ring = (cfg[k] for k in ("nh", "nkv", "hd", "K", "ring"))
+    M = 600
+    torch.manual_seed(13)
+    width = (nh + 2 * nkv) * hd
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(width, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    lens = [250, 200, 140]                      # 590 real rows, 10 padding rows
+    starts = [0, 3000, 100]
+    pos = torch.cat([torch.arange(s, s + l) for s, l in zip(starts, lens)] + [torch.zeros(10, dtype=torch.long)]).to(torch.int32).to(DEV)
+    seq = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)] + [torch.full((10,), -1)]).to(torch.int32).to(DEV)
+    slot = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    len_after = torch.tensor([s + l for s, l in zip(starts, lens)], dtype=torch.int32, device=DEV)
+    inv = (1.0 / torch.pow(torch.tensor(5000.0), 2.0 * torch.arange(hd // 2).float() / hd)).to(DEV)
+    n_entries = ring if ring else 64
+    table = torch.randperm(3 * n_entries, device=DEV).view(3, n_entries).to(torch.int32)
+    step = SimpleNamespace(token_pos=pos, token_seq=seq, seq_slot=slot, seq_len_after=len_after)
+
+    def caches():
+        kp = torch.zeros(3 * n_entries, max(nkv, 1), 64, hd, device=DEV, dtype=torch.bfloat16)
+        return ops.PagedKVArgs(kp, torch.zeros_like(kp), table, ring, max(nkv, 1), hd)
+
+    assert gemm_tc.can_fuse_qkv_rope(x, w, hd, hd, 0, inv)
+    out = torch.full((M, width), 7.0, device=DEV, dtype=torch.bfloat16)
+    ca = caches()
+    gemm_tc.qkv_rope(x, w, out, nh, nkv, hd, step, inv, ca if nkv else None)
+    assert not gemm_tc.gave_up()
+    y = (x.double() @ w.double().T).view(M, nh + 2 * nkv, hd)
+    want = y.clone()
+    ang = pos.double()[:, None] * inv.double()[None, :]
+    c, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = y[:, :nh + nkv, :hd // 2], y[:, :nh + nkv, hd // 2:]
+    want[:, :nh + nkv, :hd // 2], want[:, :nh + nkv, hd // 2:] = a * c - b * sn, a * sn + b * c
+    live = seq >= 0
+    close(out.view(M, -1, hd)[live], want.to(torch.bfloat16)[live], torch.bfloat16)
+    assert bool(torch.isfinite(out.float()).all())            # padding rows hold the plain product
+    close(out.view(M, -1, hd)[~live], y.to(torch.bfloat16)[~live], torch.bfloat16)
+    if nkv:
+        # the separate kernel stores the fused kernel's own rows: the caches must be equal bit for bit
+        cb = caches()
+        rows = out.clone()
+        rows[~live] = 0
+        ops.rope_kv_write(rows, nh, pos, seq, slot, len_after, None, 0, 0, cb, nkv, hd)   # no rotation: store only
+        assert torch.equal(ca.k_pages, cb.k_pages) and torch.equal(ca.v_pages, cb.v_pages)
+        assert float(ca.k_pages.abs().sum()) > 0
+
+
 @pytest.mark.parametrize("cfg", [dict(nh=3, nkv=1, hd=64, window=None, cap=0.0),
                                  dict(nh=2, nkv=2, hd=64, window=70, cap=30.0),
                                  dict(nh=4, nkv=2, hd=128, window=100, cap=50.0),
