@@ -34,6 +34,7 @@ namespace hos {
 constexpr int GM = 128;            // rows of the M operand per tile (UMMA M)
 constexpr int GK = 64;             // K elements per stage: 128 bytes, one swizzle atom
 constexpr int kGemmThreads = 192;
+constexpr int kPairThreads = 320;         // the kernel on pairs of SMs: TMA warp, MMA warp, 8 epilogue warps
 constexpr long long kWaitCycles = 1ll << 31;     // about a second
 
 enum { kGEpiNone = 0, kGEpiSoftcap = 1, kGEpiGated = 2, kGEpiRope = 3 };
@@ -411,7 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
 //   empty[s]     one per CTA: the leader's commit arrives on both (multicast), so each
 //                producer knows when its own stage may be overwritten
 //   acc_full[a]  one per CTA, by the leader's multicast commit; each CTA's epilogue waits on its own
-//   acc_empty[a] the leader's only: the epilogue warps of both CTAs arrive on it (8 arrivals)
+//   acc_empty[a] the leader's only: the epilogue warps of both CTAs arrive on it (16 arrivals)
 // Tensor memory is allocated and freed by warp 1 of each CTA (the cta_group::2 forms); a
 // cluster barrier stands before the first remote arrival and before the release.
 struct PairCfg {
@@ -424,7 +425,7 @@ struct PairCfg {
 };
 
 template <int EPI, typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes of [128 rows x 64]
                     const __grid_constant__ CUtensorMap map_w,     // W: boxes of [128 rows x 64]
                     GemmParams p) {
@@ -455,7 +456,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
         prefetch_tmap(&map_a);
         prefetch_tmap(&map_w);
         for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 16); }
         mbar_fence_init();
     }
     __syncthreads();
@@ -523,8 +524,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue: warps 2..5 of each CTA, its own 128 token rows ----------------
+        // ---------------- epilogue: warps 2..9 of each CTA, its own 128 token rows; warps w and w + 4 share a
+        // quarter of the tensor-memory lanes and take half of the tile's columns each ----------------
         const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
         int local_tile = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local_tile) {
@@ -553,8 +556,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                     page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
                                               kv_table_entry(q.cache, pos / kPageTokens)];
                 const int rr = pos % kPageTokens;
+                // the two warps of a lane quarter share the work: whole heads if the tile holds several, else halves
+                // of the one head's pairs
+                const int heads_in_tile = BN / hd;
+                const int col_begin = heads_in_tile > 1 ? col_half * (BN / 2) : 0, col_end = heads_in_tile > 1 ? col_begin + BN / 2 : BN;
+                const int pair_begin = heads_in_tile > 1 ? 0 : col_half * (half / 2), pair_end = heads_in_tile > 1 ? half : pair_begin + half / 2;
 #pragma unroll 1
-                for (int col0 = 0; col0 < BN && nt * BN + col0 < p.N; col0 += hd) {
+                for (int col0 = col_begin; col0 < col_end && nt * BN + col0 < p.N; col0 += hd) {
                     const int head = first_head + col0 / hd;
                     const bool is_v = head >= q.n_heads + q.n_kv_heads;
                     bf16* tile = nullptr;
@@ -562,7 +570,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                         tile = (bf16*)(is_v ? q.cache.v_pages : q.cache.k_pages) +
                                kv_tile_offset(q.cache, page, is_v ? head - q.n_heads - q.n_kv_heads : head - q.n_heads);
 #pragma unroll 1
-                    for (int c0 = 0; c0 < half; c0 += 32) {
+                    for (int c0 = pair_begin; c0 < pair_end; c0 += 32) {
                         uint32_t lo[32], hi[32];
                         tmem_ld_32x32(t_lane + col0 + c0, lo);
                         tmem_ld_32x32(t_lane + col0 + half + c0, hi);
@@ -606,7 +614,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                 }
             } else {
 #pragma unroll 1
-            for (int c0 = 0; c0 < COLS; c0 += 32) {
+            for (int c0 = col_half * (COLS / 2); c0 < (col_half + 1) * (COLS / 2); c0 += 32) {
                 uint32_t v[32], u[32];
                 tmem_ld_32x32(t_lane + c0, v);
                 if (EPI == kGEpiGated) tmem_ld_32x32(t_lane + BN / 2 + c0, u);
@@ -748,7 +756,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const GemmP
     }
     const int pairs_max = sm_count() / 2;
     const int pairs = total_tiles < pairs_max ? total_tiles : pairs_max;
-    launch_pdl(kernel, dim3(2 * pairs), dim3(kGemmThreads), PairCfg::kSmem, stream, ma, mw, p);
+    launch_pdl(kernel, dim3(2 * pairs), dim3(kPairThreads), PairCfg::kSmem, stream, ma, mw, p);
     return check_launch("gemm_tc (pairs of SMs)");
 }
 
