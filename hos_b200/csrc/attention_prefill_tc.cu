@@ -110,6 +110,63 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- tanh and exp2 shared between the MUFU unit and the FMA pipe ----------------------------------
+// Per score the softmax needs a tanh (soft-cap) and an exp2, and the special-function unit takes 16 a clock
+// per SM: with two softmax warps on a scheduler that unit, not the issue slots, sets the pace.  So a fixed
+// share of a thread's scores (by index, no divergence) goes through polynomials on the FMA pipe instead:
+//   tanh(x) = x + x^3 (a + x^2 (b + x^2 c)) for |x| <= 0.55, relative error 1.3e-6 (tanh.approx: 5e-4); a thread
+//   whose polynomial scores are not all that small (a warp vote) takes the unit for all of them;
+//   2^x = 2^n p(f), n = round(x), f = x - n in [-0.5, 0.5], p of degree 3 with relative error 7.5e-5 (the
+//   result is rounded to bfloat16, 4e-3, for the product with V and summed as it stands), n added to the
+//   exponent bits.
+constexpr float kTanhPolyMax = 0.55f;
+__device__ __forceinline__ float tanh_poly(float x) {
+    const float x2 = x * x;
+    float q = fmaf(-0.043099623f, x2, 0.13152355f);
+    q = fmaf(q, x2, -0.33324513f);
+    return fmaf(q * x2, x, x);
+}
+__device__ __forceinline__ float tanh_unit(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+__device__ __forceinline__ float exp2_unit(float x) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(x));
+    return p;
+}
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.f);                                    // also what a masked score (-inf) becomes: 2^-125
+    const float xr = x + 12582912.f;                         // 1.5 * 2^23: the low mantissa bits now hold round(x)
+    const float f = x - (xr - 12582912.f);
+    float p = fmaf(0.055171646f, f, 0.24261113f);
+    p = fmaf(p, f, 0.69326097f);
+    p = fmaf(p, f, 0.99992806f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+// Shares measured at head size 256, 8,192 tokens (us per launch; none: 258.9): tanh 3/8 alone 244.6, exp2 2/8 alone
+// 251.8, 3/8 + 2/8 240.5, 4/8 + 2/8 240.1, 4/8 + 3/8 243.0, 5/8 + 3/8 253.3.
+__device__ __forceinline__ bool tanh_by_poly(int i) { return (i & 7) < 4; }
+__device__ __forceinline__ bool exp2_by_poly(int i) { return ((i >> 1) & 7) < 2; }
+// t[i] = tanh(t[i] * pre) for a thread's N scores
+template <int N>
+__device__ __forceinline__ void tanh_scores(float (&t)[N], float pre) {
+    float big = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        t[i] *= pre;
+        if (tanh_by_poly(i)) big = fmaxf(big, fabsf(t[i]));
+    }
+    if (__any_sync(0xffffffffu, !(big <= kTanhPolyMax))) {          // a large (or not-a-number) score: the unit for all
+#pragma unroll
+        for (int i = 0; i < N; ++i) t[i] = tanh_unit(t[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) t[i] = tanh_by_poly(i) ? tanh_poly(t[i]) : tanh_unit(t[i]);
+    }
+}
+
 // K-major tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
@@ -309,10 +366,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             const int kt0 = (kt_lo + j) * TK;                    // first key of the tile
             const int k0 = kt0 + 32 * half;
             float m_half = -INFINITY;
-            if (capped) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) asm("tanh.approx.f32 %0, %1;" : "=f"(sc[i]) : "f"(sc[i] * pre));
-            }
+            if (capped) tanh_scores<32>(sc, pre);
             // a tile that every query of the block sees whole needs no mask (all but the last one or two of a walk,
             // and the first ones under a window)
             const bool whole = kt0 + TK - 1 <= q0 && (a.window <= 0 || kt0 > q0 + TQ - 1 - a.window);
@@ -344,9 +398,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float p0, p1;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(sc[i], c2, -m_use2)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(sc[i + 1], c2, -m_use2)));
+                const float e0 = fmaf(sc[i], c2, -m_use2), e1 = fmaf(sc[i + 1], c2, -m_use2);
+                const float p0 = exp2_by_poly(i) ? exp2_poly(e0) : exp2_unit(e0);
+                const float p1 = exp2_by_poly(i + 1) ? exp2_poly(e1) : exp2_unit(e1);
                 psum += p0 + p1;
                 packed[i / 2] = pack_bf16(p0, p1);
             }
@@ -623,10 +677,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
             if (lane == 0) mbar_arrive_leader(&s_empty[sb]);     // this warp has its part of the S buffer
             const int kt0 = (kt_lo + j) * PK;                    // first key of the tile
             const int k0 = kt0 + 64 * half;
-            if (capped) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) asm("tanh.approx.f32 %0, %1;" : "=f"(sc[i]) : "f"(sc[i] * pre));
-            }
+            if (capped) tanh_scores<64>(sc, pre);
             float m_half = -INFINITY;
             const bool whole = kt0 + PK - 1 <= q0 && (a.window <= 0 || kt0 > q0 + TQ - 1 - a.window);
             if (whole) {
@@ -655,9 +706,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
             uint32_t packed[32];
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
-                float p0, p1;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(sc[i], c2, -m_use2)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(sc[i + 1], c2, -m_use2)));
+                const float e0 = fmaf(sc[i], c2, -m_use2), e1 = fmaf(sc[i + 1], c2, -m_use2);
+                const float p0 = exp2_by_poly(i) ? exp2_poly(e0) : exp2_unit(e0);
+                const float p1 = exp2_by_poly(i + 1) ? exp2_poly(e1) : exp2_unit(e1);
                 psum += p0 + p1;
                 packed[i / 2] = pack_bf16(p0, p1);
             }
