@@ -58,6 +58,7 @@ struct DecodeArgs {
     float scale, cap;
     int window;
     int max_new;          // most new tokens any sequence brings in this step: what lies below them is old
+    int cluster_merge;    // 1: the shares of a (token, kv head) are the CTAs of one cluster and merge through shared memory
 };
 
 __device__ __forceinline__ bool wait_timed(uint64_t* bar, uint32_t parity) {
@@ -68,6 +69,18 @@ __device__ __forceinline__ bool wait_timed(uint64_t* bar, uint32_t parity) {
     return true;
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A 32-bit float at the same shared-memory address in CTA `rank` of this cluster.
+__device__ __forceinline__ float ld_cluster(const float* p, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 
 // What an item is and which pages it covers: the same arithmetic on both sides of the pipe.
 struct Item {
@@ -111,7 +124,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
     float* mml = mo + 4 * a.merge_rows * HD;                                    // [4][merge_rows][2]
     float* wm = mml + 4 * a.merge_rows * 2;                                     // [merge_rows][kMaxSplits] share weights
     float* wl = wm + a.merge_rows * kMaxSplits;                                 // [merge_rows][kMaxSplits]
-    uint64_t* full = reinterpret_cast<uint64_t*>(wl + a.merge_rows * kMaxSplits);   // [stages]
+    float* res = wl + a.merge_rows * kMaxSplits;                                // [merge_rows][HD + 2]: this share's result, for the cluster
+    uint64_t* full = reinterpret_cast<uint64_t*>(res + a.merge_rows * (HD + 2));   // [stages]
     uint64_t* empty = full + kMaxStages;                                        // [stages]
     __shared__ int last_flag;
 
@@ -161,6 +175,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             }
             if (!ok) atomicExch(&g_decode_error, 1);
         }
+        if (a.cluster_merge) {
+            // one item per CTA; the whole cluster meets twice around the merge unless its token is padding
+            __syncwarp();
+            if (blockIdx.x < total_items && a.token_seq[blockIdx.x / (total_items / a.n_tokens)] >= 0) {
+                cluster_barrier();
+                cluster_barrier();
+            }
+        }
         return;
     }
 
@@ -203,7 +225,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
 
         for (int tile = 0; tile < it.n_tiles; ++tile, ++t) {
             const int s = t % stages;
-            if (!wait_timed(&full[s], (t / stages) & 1)) { gave_up = true; break; }
+            if (!wait_timed(&full[s], (t / stages) & 1)) { gave_up = true; break; }      // (the whole CTA: the barrier is one)
             const bf16* k_s = stage_base + (size_t)s * (kStageBytes / 2);
             const bf16* v_s = k_s + kTileBytes / 2;
             const uint32_t k_base = smem_u32(k_s), v_base = smem_u32(v_s);
@@ -282,7 +304,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);      // this warp is done with the stage
         }
-        if (gave_up) break;
+        if (gave_up && !a.cluster_merge) break;      // in a cluster the others wait for this CTA at the barriers below
 
         // ---- merge the four warps (each saw other keys) through shared memory ----
 #pragma unroll
@@ -324,6 +346,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             const int head = it.head0 + r;
             if (a.n_splits == 1) {
                 a.out[(size_t)n * a.out_stride + (size_t)head * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+            } else if (a.cluster_merge) {
+                res[r * (HD + 2) + d] = acc;
+                if (d == 0) {
+                    res[r * (HD + 2) + HD] = M;
+                    res[r * (HD + 2) + HD + 1] = L;
+                }
             } else {
                 a.part_o[part_index(head) * HD + d] = acc;
                 if (d == 0) {
@@ -333,6 +361,29 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             }
         }
         if (a.n_splits == 1) continue;
+        if (a.cluster_merge) {
+            // ---- the shares of this (token, kv head) are the CTAs of this cluster: every one of them merges a
+            // slice of the columns, reading the others' results from their shared memory ----
+            cluster_barrier();
+            const int per_rank = (HD + a.n_splits - 1) / a.n_splits;
+            const int d0 = it.split * per_rank, d1 = min(HD, d0 + per_rank);
+            for (int idx = tid; idx < it.n_rows * (d1 - d0); idx += kConsumers) {
+                const int r = idx / (d1 - d0), d = d0 + idx % (d1 - d0);
+                float M = -INFINITY;
+                for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, ld_cluster(res + r * (HD + 2) + HD, s));
+                float L = 0.f, acc = 0.f;
+                for (int s = 0; s < a.n_splits; ++s) {
+                    const float ms = ld_cluster(res + r * (HD + 2) + HD, s);
+                    const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+                    L += ld_cluster(res + r * (HD + 2) + HD + 1, s) * f;
+                    if (f != 0.f) acc += ld_cluster(res + r * (HD + 2) + d, s) * f;
+                }
+                a.out[(size_t)n * a.out_stride + (size_t)(it.head0 + r) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+            }
+            cluster_barrier();                 // nobody leaves while its results are still being read
+            if (gave_up) break;
+            continue;
+        }
 
         // ---- the share is written: take a ticket; the last share of (token, kv head) merges all ----
         __threadfence();
@@ -409,6 +460,18 @@ using namespace hos;
 extern "C" const char* hos_last_error() { return error_buffer(); }
 extern "C" int hos_attn_head_dim() { return HD; }
 
+// Whether few shares merge as a cluster (default) or through the workspace: HOS_ATTN_CLUSTER=0 or
+// hos_attn_decode_cluster(0) keep the workspace.
+static int& cluster_merge_state() {
+    static int on = !(getenv("HOS_ATTN_CLUSTER") && getenv("HOS_ATTN_CLUSTER")[0] == '0');
+    return on;
+}
+static bool cluster_merge_enabled() { return cluster_merge_state() != 0; }
+extern "C" int hos_attn_decode_cluster(int on) {
+    cluster_merge_state() = on ? 1 : 0;
+    return 0;
+}
+
 // Floats of workspace the kernel needs for these sizes (0 when one share is enough), and the
 // ints of tickets (which must be zero before the first launch; the kernel leaves them zero).
 extern "C" long long hos_attn_decode_workspace(int n_tokens, int n_heads, int n_splits) {
@@ -426,6 +489,53 @@ extern "C" int hos_attn_decode_error() {
     cudaMemcpyFromSymbol(&v, g_decode_error, sizeof(int));
     if (v) cudaMemcpyToSymbol(g_decode_error, &zero, sizeof(int));
     return v;
+}
+
+// How many clusters of `size` CTAs with `smem` bytes each run on the GPU at once (0: such clusters cannot be had).
+static int clusters_that_fit(int size, int smem) {
+    static int known[17][2] = {};             // [cluster size]: (smem asked about, answer)
+    if (size < 1 || size > 16) return 0;
+    if (known[size][0] == smem) return known[size][1];
+    static bool wide = false;
+    if (size > 8 && !wide) {
+        wide = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        cudaGetLastError();
+    }
+    static int attr_smem = 0;
+    if (smem > attr_smem &&
+        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess)
+        attr_smem = smem;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)size);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = size; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if ((size > 8 && !wide) || cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel, &cfg) != cudaSuccess) n = 0;
+    cudaGetLastError();
+    known[size][0] = smem;
+    known[size][1] = n;
+    return n;
+}
+static int decode_smem(int group, int* stages_out) {
+    const int merge_rows = group < kMaxHeadsPerCta ? group : kMaxHeadsPerCta;
+    const int fixed = kQBytes + 5 * merge_rows * (HD + 2) * 4 + 2 * merge_rows * kMaxSplits * 4 + 2 * kMaxStages * 8 + 128;
+    int stages = (kSmemBudget - fixed) / kStageBytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages_out) *stages_out = stages;
+    return stages * kStageBytes + fixed;
+}
+// Clusters of n_splits CTAs of this kernel that run at once for these heads (0: none): what the choice of the
+// number of shares needs to know about the cluster merge.
+extern "C" int hos_attn_decode_clusters(int n_heads, int n_kv_heads, int n_splits) {
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits < 2 || n_splits > 16) return 0;
+    int stages = 0;
+    const int smem = decode_smem(n_heads / n_kv_heads, &stages);
+    return stages < 2 ? 0 : clusters_that_fit(n_splits, smem);
 }
 
 extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_stride, float* workspace,
@@ -449,12 +559,10 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     if (items > (1ll << 30)) HOS_REFUSE("attn_decode: too many work items");
     DecodeArgs a;
     a.merge_rows = group < kMaxHeadsPerCta ? group : kMaxHeadsPerCta;
-    const int fixed = kQBytes + 4 * a.merge_rows * (HD + 2) * 4 + 2 * a.merge_rows * kMaxSplits * 4 + 2 * kMaxStages * 8 + 128;
-    int stages = (kSmemBudget - fixed) / kStageBytes;
-    if (stages > kMaxStages) stages = kMaxStages;
+    int stages = 0;
+    const int smem = decode_smem(group, &stages);
     if (stages < 2) HOS_REFUSE("attn_decode: shared memory holds fewer than two stages for head_dim %d", HD);
     a.stages = stages;
-    const int smem = stages * kStageBytes + fixed;
     static int attr_smem = 0;
     if (smem > attr_smem) {
         if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -470,6 +578,29 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     a.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
     a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_splits = n_splits;
     a.scale = scale; a.cap = cap; a.window = window; a.max_new = max_new;
+    a.cluster_merge = 0;
+    // Few items (one wave): the shares of a (token, kv head) run as one cluster and merge through shared memory
+    // instead of through a workspace, a ticket and a last arrival; only if all the clusters fit on the GPU at once.
+    if (n_splits > 1 && n_splits <= 16 && items <= sm_count() && cluster_merge_enabled()) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)items);
+        cfg.blockDim = dim3(kDecodeThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = n_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        const int fit = clusters_that_fit(n_splits, smem);
+        if ((long long)fit * n_splits >= items) {
+            a.cluster_merge = 1;
+            cfg.numAttrs = 2;
+            cudaLaunchKernelEx(&cfg, attn_decode_kernel, a);
+            return check_launch("attn_decode (clusters)");
+        }
+    }
     const int grid = items < sm_count() ? (int)items : sm_count();
     launch_ahead(true, attn_decode_kernel, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
     return check_launch("attn_decode");

@@ -17,8 +17,10 @@ MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
 enabled = {"decode": True, "prefill": True, "prefill_tc": True,
-           "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0"}
-_pair_state: Dict[int, bool] = {}     # tests switch a kernel off to compare with the plain one
+           "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0",
+           "decode_cluster": os.environ.get("HOS_ATTN_CLUSTER", "1") != "0"}
+_pair_state: Dict[int, bool] = {}
+_cluster_state: Dict[int, bool] = {}     # tests switch a kernel off to compare with the plain one
 
 
 def supports(head_dim: int) -> bool:
@@ -33,12 +35,14 @@ def lib_for(head_dim: int) -> ops.Library:
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int],
-                  min_live: int = 0) -> int:
+                  min_live: int = 0, clusters_fit=None) -> int:
     """How many shares the keys of one (token, kv head) are cut into.  The kernel's CTAs (one per
     SM) take items one after another; an item costs a fixed part (look-ups, first loads, the merge)
     and a part per page.  The number of shares is the one that makes the step shortest by that
     model (constants measured at head size 256), for all `n_tokens` rows live and, if the step is
-    a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well."""
+    a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well.
+    `clusters_fit(s)`: how many clusters of s CTAs of the kernel run at once (None: no cluster merge); with
+    all of a step's clusters on the GPU at once the shares merge through shared memory, which is cheaper."""
     chunks = (group + 15) // 16
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
@@ -48,7 +52,14 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     lives = (lo, (lo + hi) // 2, hi, hi) if lo < hi else (hi,)      # fewest, middle and most live rows (a full batch counts twice)
     best, best_cost = 1, None
     for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
-        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + (_MERGE_US + _MERGE_PER_SHARE_US * s if s > 1 else 0.0)
+        if s == 1:
+            merge = 0.0
+        elif clusters_fit is not None and s <= CLUSTER_SHARES and hi * per_token * s <= SM_COUNT \
+                and clusters_fit(s) >= hi * per_token:
+            merge = _CLUSTER_MERGE_US + _CLUSTER_MERGE_PER_SHARE_US * s      # the shares are one cluster
+        else:
+            merge = _MERGE_US + _MERGE_PER_SHARE_US * s
+        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + merge
         cost = sum(-(-live * per_token * s // SM_COUNT) * per_item for live in lives)
         if best_cost is None or cost < 0.97 * best_cost:          # more shares only for a clear gain
             best, best_cost = s, cost
@@ -59,6 +70,24 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
 # 4 / 8 / 16 / 32 shares (launch included), eight sequences 130 / 76 / 65.5 / 72.6 us with 1 / 2 / 4 / 9;
 # at 64 sequences two shares instead of one cost 27 us more per layer.
 _ITEM_US, _PAGE_US, _MERGE_US, _MERGE_PER_SHARE_US = 6.0, 0.9, 1.0, 0.275
+# Up to 16 shares of at most one wave of items merge as a cluster through shared memory: 2.3 to 2.8 us less
+# than through the workspace (one sequence, 8,192 keys, 16 shares: 17.4 -> 14.6 us; a window of 4,096: 13.5 -> 10.7).
+CLUSTER_SHARES = 16
+_CLUSTER_MERGE_US, _CLUSTER_MERGE_PER_SHARE_US = 0.3, 0.03
+
+
+_fit_known: Dict[tuple, int] = {}
+
+
+def clusters_fit(head_dim: int, n_heads: int, n_kv_heads: int, n_splits: int) -> int:
+    """Clusters of n_splits CTAs of the decode kernel that run on the GPU at once (asked once per shape)."""
+    key = (head_dim, n_heads, n_kv_heads, n_splits)
+    n = _fit_known.get(key)
+    if n is None:
+        f = lib_for(head_dim).lib.hos_attn_decode_clusters
+        f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        n = _fit_known[key] = int(f(n_heads, n_kv_heads, n_splits))
+    return n
 
 
 _ticket_store: Dict[object, torch.Tensor] = {}
@@ -75,16 +104,23 @@ def _tickets(device, n: int) -> torch.Tensor:
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
            window: Optional[int], max_len: int, n_splits: Optional[int] = None,
-           max_new: Optional[int] = None, min_live: int = 0, token_slot=None) -> None:
+           max_new: Optional[int] = None, min_live: int = 0, token_slot=None, cluster: bool = True) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
     position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
     the kernel may fetch keys that lie below them while the kernel before it (which writes the
     step's new keys) still runs.  None: it fetches nothing ahead.  `token_slot`: each token's cache slot
-    (seq_slot[token_seq]) if the step has it: the kernel then finds its first page one look-up sooner."""
+    (seq_slot[token_seq]) if the step has it: the kernel then finds its first page one look-up sooner.
+    `cluster`: up to 16 shares of at most one wave of work items may run as clusters that merge through
+    shared memory (False: always through the workspace)."""
     hd, nkv = cache.head_dim, cache.n_kv_heads
     lib = lib_for(hd)
+    want = bool(cluster and enabled["decode_cluster"])
+    if _cluster_state.get(hd) != want:
+        lib.call("hos_attn_decode_cluster", 1 if want else 0)
+        _cluster_state[hd] = want
     if n_splits is None:
-        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live)
+        fit = (lambda s: clusters_fit(hd, n_heads, nkv, s)) if want else None
+        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit)
     ws = tickets = None
     if n_splits > 1:
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)

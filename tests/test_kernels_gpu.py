@@ -490,6 +490,12 @@ def test_attention_decode_kernel(cfg, n_splits):
     af.decode(q, nh * hd, out2, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), cache, len(items),
               nh, scale, cap, window, 517, max_new=1)
     close(out2, out, dt)
+    # shares that merge through the workspace and a ticket (what runs when the clusters would not fit at once)
+    out3 = torch.empty_like(q)
+    af.decode(q, nh * hd, out3, pos, seq, torch.tensor(slots, dtype=torch.int32, device=DEV), cache, len(items),
+              nh, scale, cap, window, 517, n_splits=n_splits, cluster=False)
+    assert not af.decode_gave_up(hd)
+    close(out3, out, dt)
 
 
 @pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=8, cap=50.0),
