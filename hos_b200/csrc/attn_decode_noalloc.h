@@ -26,6 +26,8 @@
 //    start at zero, are cleared on the caller's stream before every launch.  Two calls whose
 //    kernels overlap on the GPU (different streams without an order between them) race on it:
 //    keep calls on one stream or order them yourself.
+//  * Where the shares of a step run as clusters that merge through shared memory (up to 16 shares, all
+//    clusters on the GPU at once) the scratch array is not touched at all.
 #pragma once
 #include <cuda_runtime.h>
 

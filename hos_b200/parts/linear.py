@@ -1,5 +1,5 @@
 """The matrix product that every part calls: y = x . W^T, W stored [out, in] as the
-checkpoint has it (src/model.rs:179-180).  Chooses the kernel: in bfloat16, for up to 16
+checkpoint has it (src/model.rs:179-180).  Chooses the kernel: in bfloat16, for up to 32
 rows the register-streaming kernel, else the tcgen05/TMA kernel, when the sizes meet their
 alignment rules; otherwise (and always in the 32-bit path) the plain CUDA-core kernel.  All
 accumulate in 32-bit."""
