@@ -1,0 +1,53 @@
+"""The choice of how many shares the decode attention cuts a sequence's keys into
+(hos_b200/parts/attention_fast.py: decode_splits): pure arithmetic, checked without a GPU."""
+import pytest
+
+from hos_b200.parts import attention_fast as af
+
+
+@pytest.mark.parametrize("window", [None, 4096, 100])
+@pytest.mark.parametrize("n_tokens", [1, 2, 3, 8, 17, 64, 200])
+@pytest.mark.parametrize("max_len", [1, 64, 65, 1000, 8192, 100000])
+def test_shares_are_within_bounds(n_tokens, max_len, window):
+    for fit in (None, lambda s: 0, lambda s: 1000):
+        s = af.decode_splits(n_tokens, 4, 2, max_len, window, 0, fit)
+        span = min(max_len, window) if window else max_len
+        pages = (span + 63) // 64 + (1 if window else 0)
+        assert 1 <= s <= af.MAX_SPLITS
+        assert s <= max(1, (pages + 1) // 2)          # a share holds two pages or more (or there is one share)
+
+
+def test_one_page_is_never_cut():
+    assert af.decode_splits(1, 4, 2, 60, None) == 1
+    assert af.decode_splits(64, 1, 8, 64, None) == 1
+
+
+def test_few_sequences_are_cut_finely_and_many_not_at_all():
+    # (in between the choice follows how the items fill waves of 148 CTAs, so it need not fall steadily)
+    assert af.decode_splits(1, 4, 2, 8192, None) >= 8
+    assert 2 <= af.decode_splits(8, 4, 2, 8192, None) <= 8
+    assert af.decode_splits(32, 4, 2, 8192, None) == 1         # 128 items: one wave as they are
+    assert af.decode_splits(64, 4, 2, 8192, None) == 1
+
+
+def test_clusters_that_do_not_fit_change_nothing():
+    for n in (1, 2, 4, 8):
+        for window in (None, 4096):
+            assert af.decode_splits(n, 4, 2, 8192, window, 0, lambda s: 0) == af.decode_splits(n, 4, 2, 8192, window)
+
+
+def test_a_cluster_is_preferred_only_where_it_fits():
+    # one sequence, four kv heads: 4 s CTAs.  With room for every cluster the cheaper merge allows up to 16 shares;
+    # with room for clusters of at most 8 CTAs the choice stays at a size that fits or goes back to the workspace.
+    roomy = af.decode_splits(1, 4, 2, 8192, None, 0, lambda s: 1000)
+    assert 8 <= roomy <= af.CLUSTER_SHARES
+    asked = []
+    tight = af.decode_splits(1, 4, 2, 8192, None, 0, lambda s: (asked.append(s), 4 if s <= 8 else 0)[1])
+    assert asked and max(asked) <= af.CLUSTER_SHARES          # never asks about clusters that cannot exist
+    assert tight >= 8
+
+
+def test_a_replayed_step_weighs_fewer_live_rows_too():
+    full = af.decode_splits(12, 4, 2, 8192, None, 0)
+    part = af.decode_splits(12, 4, 2, 8192, None, 9)
+    assert part >= full                                # fewer live rows never argue for fewer shares
