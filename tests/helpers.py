@@ -46,7 +46,13 @@ TINY_F = dict(TINY_D, num_attention_heads=2, num_key_value_heads=2, head_dim=256
               intermediate_size=168, query_pre_attn_scalar=256, sliding_window=130, vocab_size=600,
               attn_logit_softcapping=50.0, final_logit_softcapping=30.0)
 
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4), "F": (TINY_F, 5)}
+# Two query heads per kv head at head size 128: the prompt attention on pairs of SMs.
+TINY_G = dict(TINY_D, num_attention_heads=4, num_key_value_heads=2, head_dim=128, hidden_size=88,
+              intermediate_size=184, query_pre_attn_scalar=100, sliding_window=150, vocab_size=900,
+              attn_logit_softcapping=30.0, final_logit_softcapping=0.0, rms_norm_eps=1e-5)
+
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4), "F": (TINY_F, 5),
+        "G": (TINY_G, 6)}
 
 # Tolerances on logits against the plain float32 implementation.  Fixed up front:
 # float32 differs by summation order only; bfloat16 rounds every activation that a

@@ -236,20 +236,21 @@ def test_short_prompts_replayed_as_graphs_match_whole_prompts(tmp_path, name, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["D", "E", "F"])
+@pytest.mark.parametrize("name", ["D", "E", "F", "G"])
 def test_head_sizes_64_128_256_whole_prompts_then_decoding(tmp_path, name, dtype):
-    """Configs D, E, F (head sizes 64, 128, 256; a window in a ring of two or three pages): prompts
-    that span several blocks of 128 queries in one batch (the tcgen05 prompt attention in
-    bfloat16), then 150 single-token steps that wrap the ring, all positions against the plain
-    implementation."""
+    """Configs D to G (head sizes 64, 128, 256; one, two or three query heads per kv head; a window in a
+    ring of two or three pages): prompts of 644 tokens in all that span several blocks of 128 queries
+    in one batch (in bfloat16 the products on pairs of SMs with rotation and cache write in the q/k/v
+    product's epilogue, the tcgen05 prompt attention, on pairs of SMs for G), then 150 single-token
+    steps that wrap the ring, all positions against the plain implementation."""
     folder = make_folder(tmp_path, name)
     w, cfg = plain_model(folder)
     rng = random.Random(12)
-    lens, extra = [300, 129, 5], 150
+    lens, extra = [300, 129, 5, 210], 150
     seqs = [random_tokens(rng, n + extra, TINY[name][0]["vocab_size"]) for n in lens]
     want = [P.forward_logits(w, cfg, s) for s in seqs]
     r = runner_for(folder, dtype)
-    slots = r.admit(3)
+    slots = r.admit(len(lens))
     got = r.step(slots, [s[:n] for s, n in zip(seqs, lens)], [list(range(n)) for n in lens])
     assert_close(got, torch.cat([wl[:n] for wl, n in zip(want, lens)]), dtype, "whole prompts")
     for t in range(extra):
