@@ -8,9 +8,13 @@
 // and across item boundaries, so that the memory pipe does not drain while an item is
 // finished.  Four consumer warps take 16 keys of a tile each: S = Q K^T (m16n8k16, bf16, 32-bit
 // accumulators), scale, soft-cap, mask, running max/sum in 32-bit, O += P V.  The four warps'
-// partial results are merged through shared memory.  A share that is not alone writes its
-// unnormalised result and (max, sum) to the workspace and takes a ticket; the CTA that takes
-// the last ticket of a (token, kv head) merges the shares and writes the output.  Unused MMA
+// partial results are merged through shared memory.  The shares of a (token, kv head) are then
+// merged in one of two ways.  When there are at most 16 of them and all of a launch's items run
+// at once, the launch is made of clusters, one per (token, kv head): every CTA leaves its
+// unnormalised result and (max, sum) in its own shared memory, the cluster meets at a barrier,
+// and every CTA merges a slice of the columns, reading the others' results through distributed
+// shared memory.  Otherwise a share writes its result to the workspace and takes a ticket; the
+// CTA that takes the last ticket of a (token, kv head) merges the shares.  Unused MMA
 // rows (fewer than 16 heads per kv head) cost nothing that matters: the kernel is bound by
 // the cache's bytes.
 //
