@@ -236,6 +236,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the timed prompt (default: the contract's 2,048)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -289,7 +291,7 @@ def main() -> int:
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "sliding_window": cfg.sliding_window, "decode_ends_at": args.ctx,
             "cache_fill": "random keys and values", "l2": "inputs larger than L2 (weights %.1f GB per step)" % (wbytes / 1e9),
-            "peaks": pk_src, "prefill_tokens": PREFILL_TOKENS},
+            "peaks": pk_src, "prefill_tokens": args.prefill_tokens},
         "clocks": clock_rec,
         "e2e": {"value": args.batch * 1e3 / ms_e2e, "unit": "tok/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -298,9 +300,9 @@ def main() -> int:
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes, "of": pk_src},
     }
     if not args.no_prefill:
-        ms = measure_prefill(eng, PREFILL_TOKENS, rng)
-        fl = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
-        line["prefill"] = {"value": PREFILL_TOKENS * 1e3 / ms, "tokens": PREFILL_TOKENS, "ms": ms,
+        ms = measure_prefill(eng, args.prefill_tokens, rng)
+        fl = prefill_flops(cfg, args.layers, args.prefill_tokens)
+        line["prefill"] = {"value": args.prefill_tokens * 1e3 / ms, "tokens": args.prefill_tokens, "ms": ms,
                            "frac": fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "tflop": fl / 1e12,
                            "peak_tflops": pk["bf16_tflops"], "of": pk_src}
     if not args.no_points:
