@@ -450,7 +450,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
     constexpr int n_span = EPI == kGEpiGated ? BN / 2 : BN;
     const int n_tiles = (p.N + n_span - 1) / n_span;
     const int k_blocks = (p.K + GK - 1) / GK;
-    const int total_tiles = m_tiles * n_tiles;
+    const int kb_per_split = (k_blocks + p.k_splits - 1) / p.k_splits;      // K may be split over tiles: 32-bit partial sums
+    const int total_tiles = m_tiles * n_tiles * p.k_splits;
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&map_a);
@@ -471,7 +472,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
     const uint32_t tmem_base = *tmem_base_smem;
     pdl_enter();
 
-    auto tile_coords = [&](int tile, int& mt, int& nt) { mt = tile % m_tiles; nt = tile / m_tiles; };
+    auto tile_coords = [&](int tile, int& mt, int& nt, int& ks) {
+        ks = tile % p.k_splits;
+        const int t = tile / p.k_splits;
+        mt = t % m_tiles;
+        nt = t / m_tiles;
+    };
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs, each its own halves) ----------------
@@ -479,11 +485,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
             int it = 0;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-                int mt, nt;
-                tile_coords(tile, mt, nt);
+                int mt, nt, ks;
+                tile_coords(tile, mt, nt, ks);
+                const int kb0 = ks * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
                 const int a_row = mt * 2 * GM + (int)rank * GM;
                 const int w_row = EPI == kGEpiGated ? (leader ? nt * 128 : p.gate_rows + nt * 128) : nt * BN + (int)rank * 128;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     if (it >= Cfg::kStages && !mbar_wait_timed(&empty[s], ((it / Cfg::kStages) - 1) & 1)) { ok = false; break; }
                     unsigned char* a_dst = stages + (size_t)s * Cfg::kStageBytes;
@@ -506,7 +513,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                 if (local_tile >= 2 && !mbar_wait_timed(&acc_empty[acc], ((local_tile >> 1) - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int ks = tile % p.k_splits;
+                const int kb0 = ks * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     if (!mbar_wait_timed(&full[s], (it / Cfg::kStages) & 1)) { ok = false; break; }
                     tc_fence_after();
@@ -515,7 +524,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                     const uint64_t b_desc = umma_desc_sw128(a_addr + Cfg::kABytes);
 #pragma unroll
                     for (int k = 0; k < GK / 16; ++k)
-                        umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty[s]);
                 }
                 if (ok) umma_commit_pair(&acc_full[acc]);
@@ -531,15 +540,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
         int local_tile = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local_tile) {
-            int mt, nt;
-            tile_coords(tile, mt, nt);
+            int mt, nt, ks;
+            tile_coords(tile, mt, nt, ks);
             const int acc = local_tile & 1;
             if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
             const int r = quarter * 32 + lane;
             const int m = mt * 2 * GM + (int)rank * GM + r;
-            OutT* orow = reinterpret_cast<OutT*>(p.out) + (size_t)m * p.ldo;
+            OutT* orow = reinterpret_cast<OutT*>(p.out) + (p.k_splits > 1 ? (size_t)ks * p.M * p.ldo : 0) + (size_t)m * p.ldo;
             constexpr int COLS = (EPI == kGEpiGated) ? BN / 2 : BN;
             if constexpr (EPI == kGEpiRope) {
                 // A tile holds whole heads (head_dim divides 256).  A thread has one token's row: it rotates the
@@ -798,8 +807,9 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     if (epilogue == kGEpiGated && out_dtype != kBF16) HOS_REFUSE("gemm_tc: the gated epilogue writes bfloat16");
     if (k_splits < 1) k_splits = 1;
     const bool swap = M <= 64;
-    if (k_splits > 1 && (!swap || epilogue != kGEpiNone || workspace == nullptr))
-        HOS_REFUSE("gemm_tc: K splits need the swapped orientation, no epilogue and a workspace");
+    const bool pairs = !swap && M >= 512 && pair_enabled();
+    if (k_splits > 1 && (!(swap || pairs) || epilogue != kGEpiNone || workspace == nullptr))
+        HOS_REFUSE("gemm_tc: K splits need up to 64 or at least 512 rows, no epilogue and a workspace");
     const int w_rows = epilogue == kGEpiGated ? 2 * N : N;
     GemmParams p;
     p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.k_splits = k_splits; p.gate_rows = N; p.cap = cap; p.act = act;
@@ -810,11 +820,25 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     while (k_splits > 1 && (k_splits - 1) * ((k_blocks + k_splits - 1) / k_splits) >= k_blocks) k_splits = --p.k_splits;
     int rc;
 #define HOS_GO(BN, EPI, SWAP, T, TILES) return launch<BN, EPI, SWAP, T>(mm, mn, p, (TILES), stream)
-    if (!swap && M >= 512 && pair_enabled()) {
+    if (pairs) {
         // many tokens: tiles of 256 x 256 on pairs of SMs
         if ((rc = make_map(&mm, A, M, K, lda, GM))) return rc;
         if ((rc = make_map(&mn, W, w_rows, K, ldw, 128))) return rc;
         const int m_tiles = (M + 2 * GM - 1) / (2 * GM);
+        if (k_splits > 1) {
+            // few tiles for the pairs of SMs (a prompt of some hundred tokens): K is split, the partial sums are 32-bit
+            p.out = workspace;
+            p.ldo = N;
+            if ((rc = launch_pair<kGEpiNone, float>(mm, mn, p, m_tiles * ((N + 255) / 256) * k_splits, stream))) return rc;
+            if (parts_used) *parts_used = k_splits;
+            if (!reduce_now) return 0;
+            const size_t n = (size_t)M * N;
+            if (out_dtype == kBF16)
+                launch_pdl(splitk_reduce_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, workspace, (bf16*)out, M, N, ldo, k_splits);
+            else
+                launch_pdl(splitk_reduce_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, workspace, (float*)out, M, N, ldo, k_splits);
+            return check_launch("gemm_tc split-K reduce");
+        }
         if (epilogue == kGEpiGated) return launch_pair<kGEpiGated, bf16>(mm, mn, p, m_tiles * ((N + 127) / 128), stream);
         const int tiles = m_tiles * ((N + 255) / 256);
         if (epilogue == kGEpiSoftcap) return launch_pair<kGEpiSoftcap, float>(mm, mn, p, tiles, stream);

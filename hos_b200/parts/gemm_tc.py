@@ -12,6 +12,7 @@ import torch
 from .. import ops
 
 SM_COUNT = 148
+PAIR_MIN_ROWS = 512      # from here on the product runs on pairs of SMs
 _lib: Optional[ops.Library] = None
 enabled = True          # tests switch it off to compare with the plain kernel
 
@@ -42,7 +43,14 @@ def can_take(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int)
 def k_splits_for(m: int, n: int, k: int, epilogue: int) -> int:
     """Swapped products whose output gives few tiles split K so that about every SM has work,
     keeping at least four 64-wide K blocks per share."""
-    if m > 64 or epilogue != ops.EPI_NONE:
+    if epilogue != ops.EPI_NONE:
+        return 1
+    if m >= PAIR_MIN_ROWS:
+        # pairs of SMs with tiles of 256 x 256: a prompt of some hundred tokens gives the o and down products
+        # fewer tiles than there are pairs; K is then split so that most pairs have one, 8 blocks of 64 or more each
+        tiles = ((m + 255) // 256) * ((n + 255) // 256)
+        return max(1, min((SM_COUNT // 2) // tiles, ((k + 63) // 64) // 8))
+    if m > 64:
         return 1
     tiles = (n + 127) // 128
     if tiles >= SM_COUNT // 2:
@@ -88,8 +96,6 @@ def gave_up() -> bool:
     f.argtypes = []
     return bool(f())
 
-
-PAIR_MIN_ROWS = 512      # from here on the product runs on pairs of SMs
 
 
 def can_fuse_qkv_rope(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int, style: int, inv_freq) -> bool:

@@ -876,3 +876,25 @@ def test_attention_prefill_tensor_core_kernel(cfg, pairs):
             want = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // g]
             close(out[base:base + l, h * hd:(h + 1) * hd], want.to(dt), dt)
         base += l
+
+
+@pytest.mark.parametrize("shape", [(600, 264, 1104, 3), (512, 2304, 2048, 4), (1030, 520, 4104, 2)])
+def test_product_on_pairs_of_sms_with_k_split(shape):
+    """A prompt of some hundred tokens: the product on pairs of SMs with K split over tiles, as 32-bit
+    partial sums for a consumer that adds them and reduced in place, against float64 (K that does not
+    divide evenly, a last tile of rows and of columns that is partly empty)."""
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc
+    M, N, K, splits = shape
+    torch.manual_seed(21)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    parts = gemm_tc.matmul_partials(x, w, k_splits=splits)
+    assert parts is not None and parts.shape[1:] == (M, N) and 2 <= parts.shape[0] <= splits
+    close(parts.sum(0), want.float(), torch.float32, scale=100.0)      # bf16 products, 32-bit sums: 1e-3
+    out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    gemm_tc.matmul(x, w, out, k_splits=splits)
+    close(out, want.to(torch.bfloat16), torch.bfloat16)
+    assert not gemm_tc.gave_up()
+    assert gemm_tc.k_splits_for(512, 2304, 9216, ops.EPI_NONE) > 1 and gemm_tc.k_splits_for(2048, 2304, 9216, ops.EPI_NONE) == 1
