@@ -163,3 +163,27 @@ def test_random_traffic_keeps_the_books():
         c.release(s)
     c.check()
     assert all(g.pages.n_held == 0 for g in c.groups)
+
+
+def test_changed_table_rows_reach_the_device_copy():
+    """`flush` copies the rows that changed, neighbours in one copy, others on their own: the device
+    copy of every table equals the host's afterwards, for slots taken in any order and reused."""
+    c = make(max_tokens=4096, max_seq_len=512)
+    rng = random.Random(3)
+    slots = c.admit([0] * 9)
+    for s in slots:
+        c.extend(s, rng.randrange(1, 400))
+    c.flush()
+    for g in c.groups:
+        assert torch.equal(g.table_dev, g.table_host) and not g._dirty
+    # rows 1, 2, 3 and 7 change (a run and a single row); 5 is given back and taken again
+    for s in (slots[1], slots[2], slots[3], slots[7]):
+        c.extend(s, 500)
+    c.release(slots[5])
+    again = c.admit([0])[0]
+    c.extend(again, 130)
+    c.flush()
+    for g in c.groups:
+        assert torch.equal(g.table_dev, g.table_host) and not g._dirty
+    c.flush()                                  # nothing changed: nothing to do
+    c.check()

@@ -51,3 +51,27 @@ def test_a_replayed_step_weighs_fewer_live_rows_too():
     full = af.decode_splits(12, 4, 2, 8192, None, 0)
     part = af.decode_splits(12, 4, 2, 8192, None, 9)
     assert part >= full                                # fewer live rows never argue for fewer shares
+
+
+def test_k_splits_of_the_products():
+    """How many shares of K the tensor-core product takes (hos_b200/parts/gemm_tc.py: k_splits_for): only
+    without an epilogue; few rows (the weights are the M operand) when the output gives few tiles; many
+    rows on pairs of SMs when a prompt of some hundred tokens gives fewer tiles than pairs; never
+    shares of fewer than a few blocks of K."""
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc
+    none, gated = ops.EPI_NONE, ops.EPI_GATED
+    assert gemm_tc.k_splits_for(8, 2304, 9216, gated) == 1 and gemm_tc.k_splits_for(600, 2304, 9216, gated) == 1
+    assert gemm_tc.k_splits_for(40, 2304, 9216, none) > 1              # 18 tiles of 128 features
+    assert gemm_tc.k_splits_for(40, 256000, 2304, none) == 1           # the head: tiles enough
+    assert gemm_tc.k_splits_for(100, 2304, 9216, none) == 1            # 65 to 511 rows: no split
+    assert gemm_tc.k_splits_for(512, 2304, 9216, none) == 4 and gemm_tc.k_splits_for(512, 2304, 2048, none) == 4
+    assert gemm_tc.k_splits_for(1024, 2304, 9216, none) == 2
+    assert gemm_tc.k_splits_for(2048, 2304, 9216, none) == 1 and gemm_tc.k_splits_for(8192, 2304, 2048, none) == 1
+    assert gemm_tc.k_splits_for(512, 2304, 512, none) == 1             # eight blocks of 64 are one share
+    for m in (512, 700, 1024, 1500):
+        for n, k in ((2304, 2048), (2304, 9216), (4608, 36864), (3584, 14336)):
+            s = gemm_tc.k_splits_for(m, n, k, none)
+            tiles = ((m + 255) // 256) * ((n + 255) // 256)
+            assert 1 <= s and tiles * s <= 74 or s == 1                 # at most one tile per pair of SMs
+            assert s == 1 or (k + 63) // 64 // s >= 8
