@@ -203,17 +203,21 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
     return ms_dev, ms_e2e, launches, h2d, d2h, mean_len
 
 
-def measure_prefill(eng, tokens, rng, reps=3):
+def measure_prefill(eng, tokens, rng, reps=3, pieces=1):
+    """Milliseconds of one prompt of `tokens` tokens (the best of `reps` runs after a warm-up
+    run), fed whole or as `pieces` steps of equal size that continue one another."""
     import torch
     r = eng.runner
     prompt = [rng.randrange(r.vocab_size) for _ in range(tokens)]
+    size = (tokens + pieces - 1) // pieces
     best = None
     for i in range(reps + 1):
         slot = r.admit(1)[0]
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        r.step([slot], [prompt])
+        for lo in range(0, tokens, size):
+            r.step([slot], [prompt[lo:lo + size]])
         e1.record()
         torch.cuda.synchronize()
         r.release(slot)
@@ -305,6 +309,8 @@ def main() -> int:
         line["prefill"] = {"value": args.prefill_tokens * 1e3 / ms, "tokens": args.prefill_tokens, "ms": ms,
                            "frac": fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "tflop": fl / 1e12,
                            "peak_tflops": pk["bf16_tflops"], "of": pk_src}
+        if args.prefill_tokens % 4 == 0:       # the same prompt as four steps that continue one another
+            line["prefill"]["ms_in_4_pieces"] = measure_prefill(eng, args.prefill_tokens, rng, pieces=4)
     if not args.no_points:
         pts = {}
         for b in (1, 64):

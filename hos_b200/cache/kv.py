@@ -28,10 +28,14 @@ PAGE = ops.PAGE_TOKENS
 
 class KVGroup:
     def __init__(self, need: KVNeed, n_entries: int, n_pages: int, n_slots: int,
-                 max_seq_len: int, dtype: torch.dtype, device: torch.device):
+                 max_seq_len: int, dtype: torch.dtype, device: torch.device, chunk_tokens: int = 1):
         self.need = need
         self.n_entries = n_entries
-        self.ring_pages = 0 if need.window is None else (need.window + PAGE - 1) // PAGE
+        # A step that continues a sequence by n tokens stores all n before any of them attends, so
+        # the ring must still hold the window of the first while it holds the last: window + n - 1
+        # positions.  `chunk_tokens` is the n the ring is made for (a sequence holds at most
+        # ceil(length / 64) pages in any case, so a longer ring costs nothing until it is filled).
+        self.ring_pages = 0 if need.window is None else (need.window + max(1, chunk_tokens) - 1 + PAGE - 1) // PAGE
         full_entries = (max_seq_len + PAGE - 1) // PAGE
         self.table_stride = max(1, min(full_entries, self.ring_pages) if self.ring_pages else full_entries)
         self.pages = IdPool(n_pages, "page")
@@ -44,6 +48,13 @@ class KVGroup:
         self.table_dev = torch.zeros((n_slots, self.table_stride), dtype=torch.int32, device=device)
         self._slot_pages: Dict[int, List[int]] = {}
         self._dirty: set = set()
+
+    def chunk_room(self):
+        """The most tokens a sequence may bring in one step that attends over this group's
+        storage (None: any number)."""
+        if self.ring_pages == 0:
+            return None
+        return self.ring_pages * PAGE - self.need.window + 1
 
     def pages_for(self, length: int) -> int:
         n = (length + PAGE - 1) // PAGE

@@ -30,8 +30,11 @@ from .pool import IdPool
 class CacheManager:
     def __init__(self, kv_needs: Sequence[Optional[KVNeed]], cache_from: Sequence[Optional[int]],
                  state_needs: Sequence[Sequence[StateNeed]], max_tokens: int, max_seq_len: int,
-                 dtype: torch.dtype, device: torch.device, max_slots: Optional[int] = None):
-        """kv_needs[i], cache_from[i], state_needs[i] describe entry i of the run order."""
+                 dtype: torch.dtype, device: torch.device, max_slots: Optional[int] = None,
+                 chunk_tokens: int = 1):
+        """kv_needs[i], cache_from[i], state_needs[i] describe entry i of the run order.
+        `chunk_tokens`: the most tokens one step adds to a sequence that is under way (a window
+        group's ring is made long enough for it; longer additions are cut by the step function)."""
         if max_tokens <= 0:
             raise CacheError("the cache must hold at least one token")
         self.device = torch.device(device)
@@ -50,7 +53,7 @@ class CacheManager:
         placed: Dict[int, Tuple[int, int]] = {}
         for need, entries in by_need.items():
             g = KVGroup(need, len(entries), self.n_pages, self.n_slots, self.max_seq_len, dtype,
-                        self.device)
+                        self.device, chunk_tokens)
             for j, e in enumerate(entries):
                 placed[e] = (len(self.groups), j)
             self.groups.append(g)
@@ -111,6 +114,31 @@ class CacheManager:
         for g in self.groups:
             g.grow(slot, new_len)
         self.lengths[slot] = max(self.lengths[slot], new_len)
+
+    def extend_all(self, slots: Sequence[int], new_lens: Sequence[int]) -> None:
+        """`extend` for the sequences of one step, all or nothing: if any of them cannot have
+        its pages (or would pass the longest sequence the cache holds), none is changed."""
+        for slot, n in zip(slots, new_lens):
+            if slot not in self.lengths:
+                raise CacheError(f"slot {slot} holds no sequence")
+            if n > self.max_seq_len:
+                raise CacheError(f"a sequence of {n} tokens is longer than the cache holds "
+                                 f"({self.max_seq_len})")
+        for g in self.groups:
+            more = sum(max(0, g.pages_for(n) - len(g._slot_pages[slot])) for slot, n in zip(slots, new_lens))
+            if more > g.pages.n_free:
+                raise CacheError(f"the cache has no free pages left for this step ({more} wanted, "
+                                 f"{g.pages.n_free} free of {g.pages.n})")
+        for slot, n in zip(slots, new_lens):
+            for g in self.groups:
+                g.grow(slot, n)
+            self.lengths[slot] = max(self.lengths[slot], n)
+
+    def chunk_room(self) -> Optional[int]:
+        """The most tokens one step may add to a sequence that is under way (None: any number):
+        the smallest room of the window groups' rings."""
+        rooms = [r for r in (g.chunk_room() for g in self.groups) if r is not None]
+        return min(rooms) if rooms else None
 
     def release(self, slot: int) -> None:
         if slot not in self.lengths:

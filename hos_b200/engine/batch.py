@@ -19,6 +19,11 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
     `extra` (a list of integers, e.g. the rows whose logits are wanted) the result is
     (StepInfo, extra as an int32 device tensor) and it rides in the same copy."""
     b = len(token_lists)
+    n_fresh = 0                       # the sequences that start at position 0 stand first
+    while n_fresh < b and starts[n_fresh] == 0:
+        n_fresh += 1
+    if any(s == 0 for s in starts[n_fresh:]):
+        raise HosError("the sequences of a step that start at position 0 must be listed first")
     news = [len(t) for t in token_lists]
     n = sum(news)
     nn = max(n, pad_to)
@@ -64,7 +69,8 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
         single_token=all(k == 1 for k in news),
         max_new=max(news) if news else 0,
         max_len_after=max(lens_after) if lens_after else 0,
-        slots_host=tuple(slots), cu_host=tuple(int(c) for c in cu), starts_host=tuple(starts))
+        slots_host=tuple(slots), cu_host=tuple(int(c) for c in cu), starts_host=tuple(starts),
+        fresh_seqs=n_fresh, fresh_tokens=int(cu[n_fresh]))
     if extra is not None:
         return info, dev[o + 3 * b + 1:]
     return info

@@ -1,10 +1,16 @@
 """The step function: a model, its cache, and `step()`.
 
 A step runs exactly the tokens it is given, as one batch, on top of what earlier
-steps left in the cache, and returns float32 logits at the wanted places.  The
-sequences of a step either all start at their first token (prompts of unequal
-lengths, packed into one batch) or all go on by one token.  Sequences that have
-ended are simply absent from later steps; their slots go back with `release`.
+steps left in the cache, and returns float32 logits at the wanted places.  Each
+sequence of a step brings its next tokens, one or many, whether it starts at its
+first token or goes on from where the cache left it (src/forward.rs:247-253: a
+prompt is run from any `start`; src/lib.rs:352-366: in chunks).  Two shapes have
+fast paths: prompts that all start at position 0 (short ones replayed as a CUDA
+graph), and sequences that all go on by one token (always replayed).  Everything
+else is the general case: the sequences that start at position 0 attend over their
+own rows, the others over the cache; a sequence that brings more tokens than the
+window rings have room for is fed in several passes.  Sequences that have ended
+are simply absent from later steps; their slots go back with `release`.
 """
 from __future__ import annotations
 
@@ -36,7 +42,10 @@ def _device() -> torch.device:
 class Runner:
     def __init__(self, config: ModelConfig, source, dtype: str = "bfloat16", max_tokens: int = 8192,
                  max_seq_len: Optional[int] = None, max_slots: Optional[int] = None,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, chunk_tokens: int = 512):
+        """`chunk_tokens`: the most tokens a step adds in one pass to a sequence that is under way
+        (layers that keep a window of keys make their ring of pages that much longer; a step
+        that brings more is run as several passes)."""
         if dtype not in DTYPES:
             raise HosError(f"dtype must be one of {sorted(DTYPES)}, found {dtype!r}")
         self.config = config
@@ -47,7 +56,7 @@ class Runner:
         tensors = load_tensors(self.model.weight_specs(), source, self.device)
         self.model.bind(tensors)
         del tensors
-        self.cache: CacheManager = self.model.new_cache(max_tokens, max_seq_len, max_slots)
+        self.cache: CacheManager = self.model.new_cache(max_tokens, max_seq_len, max_slots, chunk_tokens)
         self.vocab_size = self.plan.vocab_size
         self._sessions = {}
         self.use_sessions = self.model.graph_safe     # single-token steps run through DecodeSession
@@ -104,27 +113,18 @@ class Runner:
             starts.append(self.cache.lengths[s] if s in self.cache.lengths else self._no_slot(s))
         from_zero = all(st == 0 for st in starts)
         single = all(len(t) == 1 for t in token_lists)
-        if not (from_zero or single):
-            raise HosError("step: the sequences of a step either all start at their first token or "
-                           "all go on by one token")
         if want is None:
             want = [[len(t) - 1] for t in token_lists]
-        rows: List[int] = []
-        base = 0
         for toks, w in zip(token_lists, want):
             for j in w:
                 if not (0 <= j < len(toks)):
                     raise HosError(f"step: wanted place {j} is outside the {len(toks)} tokens brought")
-                rows.append(base + j)
-            base += len(toks)
-        if single and not from_zero and len(rows) == len(slots) and self.use_sessions:
+        last_only = all(len(w) == 1 and w[0] == len(t) - 1 for w, t in zip(want, token_lists))
+        if single and not from_zero and last_only and self.use_sessions:
             # decoding: static buffers and a captured graph, one per batch-size bucket
             from .decode import DecodeSession, bucket_for
-            for toks in token_lists:
-                if not (0 <= int(toks[0]) < self.vocab_size):
-                    raise HosError(f"token id {toks[0]} is outside the vocabulary (0..{self.vocab_size - 1})")
-            for s, st in zip(slots, starts):
-                self.cache.extend(s, st + 1)
+            self._check_ids(token_lists)
+            self.cache.extend_all(slots, [st + 1 for st in starts])
             bucket = bucket_for(len(slots))
             sess = self._sessions.get(bucket)
             if sess is None:
@@ -132,32 +132,86 @@ class Runner:
             sess.feed(slots, [t[0] for t in token_lists], starts)
             out = sess.run()
             return out.clone() if copy else out
-        if from_zero and self.use_sessions and self.prompt_sessions and all(len(w) == 1 and w[0] == len(t) - 1
-                                                                          for w, t in zip(want, token_lists)):
+        if from_zero and last_only and self.use_sessions and self.prompt_sessions:
             # a short prompt step: static buffers and a captured graph per capacity, as for decoding
             from .decode import PromptSession, prompt_bucket
             bucket = prompt_bucket(sum(len(t) for t in token_lists), len(slots))
             if bucket is not None:
-                for toks in token_lists:
-                    for t in toks:
-                        if not (0 <= int(t) < self.vocab_size):
-                            raise HosError(f"token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
-                for s, toks in zip(slots, token_lists):
-                    self.cache.extend(s, len(toks))
+                self._check_ids(token_lists)
+                self.cache.extend_all(slots, [len(t) for t in token_lists])
                 sess = self._sessions.get(("prompt",) + bucket)
                 if sess is None:
                     sess = self._sessions[("prompt",) + bucket] = PromptSession(self, *bucket)
                 sess.feed(slots, token_lists)
                 out = sess.run()
                 return out.clone() if copy else out
-        x, rows_t = self._hidden(slots, starts, token_lists, rows)
-        return self.model.logits(x, rows_t)
+        return self._general(slots, starts, token_lists, want)
 
-    def _hidden(self, slots, starts, token_lists, rows=()):
-        """The hidden rows of a step, and `rows` (indices into them) as a device tensor."""
+    def _check_ids(self, token_lists) -> None:
+        for toks in token_lists:
+            for t in toks:
+                if not (0 <= int(t) < self.vocab_size):
+                    raise HosError(f"token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+
+    def _general(self, slots, starts, token_lists, want) -> torch.Tensor:
+        """Any mix of sequences that start and sequences that go on by any number of tokens.
+        The sequences that start at position 0 are listed first (the mixers send them to the
+        kernels that attend over a step's own rows).  A sequence that goes on brings at most
+        `cache.chunk_room()` tokens per pass, so that in a ring of pages no key is overwritten
+        that a token of the same pass still reads; what is left over runs in further passes."""
+        self._check_ids(token_lists)
+        # all or nothing: every sequence gets its pages for the whole step before anything runs
+        self.cache.extend_all(slots, [st + len(t) for st, t in zip(starts, token_lists)])
+        room = self.cache.chunk_room()
+        order = sorted(range(len(slots)), key=lambda i: starts[i] != 0)     # stable: fresh ones first
+        first_row = [0] * len(slots)          # where each sequence's rows begin in the result
+        at = 0
+        for i, w in enumerate(want):
+            first_row[i] = at
+            at += len(w)
+        n_out = at
+        done = [0] * len(slots)               # tokens of each sequence already run
+        out = None
+        while True:
+            part = []                         # (sequence, first token, tokens) of this pass
+            for i in order:
+                left = len(token_lists[i]) - done[i]
+                if left <= 0:
+                    continue
+                take = left if (starts[i] == 0 and done[i] == 0) or room is None else min(left, room)
+                part.append((i, done[i], take))
+            if not part:
+                break
+            rows, dest = [], []
+            base = 0
+            for i, lo, k in part:
+                for j, place in enumerate(want[i]):
+                    if lo <= place < lo + k:
+                        rows.append(base + place - lo)
+                        dest.append(first_row[i] + j)
+                base += k
+            x, rows_t = self._hidden([slots[i] for i, _, _ in part], [starts[i] + lo for i, lo, _ in part],
+                                     [token_lists[i][lo:lo + k] for i, lo, k in part], rows, extend=False)
+            for i, lo, k in part:
+                done[i] = lo + k
+            if not rows:
+                continue
+            logits = self.model.logits(x, rows_t)
+            if len(dest) == n_out and dest == list(range(n_out)):
+                return logits                 # one pass gave every wanted row, in order
+            if out is None:
+                out = torch.empty((n_out, self.vocab_size), dtype=torch.float32, device=self.device)
+            out[torch.tensor(dest, dtype=torch.long, device=self.device)] = logits
+        if out is None:
+            out = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        return out
+
+    def _hidden(self, slots, starts, token_lists, rows=(), extend: bool = True):
+        """The hidden rows of one pass, and `rows` (indices into them) as a device tensor.  The
+        sequences that start at position 0 must come first."""
         info, rows_t = build_step(token_lists, starts, slots, self.device, self.vocab_size, extra=rows)
-        for s, st, toks in zip(slots, starts, token_lists):
-            self.cache.extend(s, st + len(toks))
+        if extend:
+            self.cache.extend_all(slots, [st + len(t) for st, t in zip(starts, token_lists)])
         self.cache.flush()
         # a step of many tokens: its kernels are long enough for the next one's set-up to hide under them
         ops.set_launch_ahead(info.n_tokens >= LAUNCH_AHEAD_MIN_TOKENS)

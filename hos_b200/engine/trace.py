@@ -6,8 +6,10 @@ that generation uses.
 
 Standard input carries one JSON object per line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
-`entries`: each request's next tokens and the places among them whose logits are
-wanted.  The requests of a step either all start or all go on by one token.
+`entries`: each request's next tokens (one or many, from the request's first token
+or from where its last step left it) and the places among them whose logits are
+wanted.  A request that is seen for the first time gets a slot, whether or not
+other requests of the step are under way.
 `end`: requests that are finished after this step; their slots and pages go back.
 For a step that wants something, DIR/<step>.f32 holds the logits at the wanted
 places, in the order of the entries and of `want`, little-endian float32
@@ -30,6 +32,9 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to 64")
+    ap.add_argument("--chunk-tokens", type=int, default=512,
+                    help="most tokens one pass adds to a request that is under way (more are run as several "
+                         "passes); layers with a window keep a ring of window + this many keys")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
 
@@ -38,7 +43,7 @@ def main(argv=None) -> int:
     # the cache alone bounds a request's length here: replay is not cut at the model's
     # max_position_embeddings, which generation takes as its context limit
     runner = Runner.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
-                                max_seq_len=args.max_tokens)
+                                max_seq_len=args.max_tokens, chunk_tokens=args.chunk_tokens)
     slots: Dict[str, int] = {}
 
     for line in sys.stdin:
@@ -49,8 +54,6 @@ def main(argv=None) -> int:
         step = obj["step"]
         entries = obj.get("entries", [])
         new = [e for e in entries if str(e["id"]) not in slots]
-        if new and len(new) != len(entries):
-            raise ValueError(f"step {step}: new requests may not join requests that are under way")
         if new:
             for e, s in zip(new, runner.admit(len(new))):
                 slots[str(e["id"])] = s

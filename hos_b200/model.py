@@ -51,7 +51,7 @@ class Model:
             p.bind(tensors)
 
     def new_cache(self, max_tokens: int, max_seq_len: Optional[int] = None,
-                  max_slots: Optional[int] = None) -> CacheManager:
+                  max_slots: Optional[int] = None, chunk_tokens: int = 1) -> CacheManager:
         kv_needs, cache_from, state_needs = [], [], []
         for call in self.schedule:
             mixer = self.layers[call.layer].mixer
@@ -60,7 +60,7 @@ class Model:
             state_needs.append(mixer.state_needs())
         return CacheManager(kv_needs, cache_from, state_needs, max_tokens,
                             max_seq_len or self.plan.max_positions, self.rt.dtype, self.rt.device,
-                            max_slots)
+                            max_slots, chunk_tokens)
 
     def hidden(self, step: StepInfo, cache: CacheManager) -> torch.Tensor:
         """The residual stream after the last entry of the run order, float32 [N, width]."""

@@ -9,9 +9,10 @@ scale, softcap (0 = off), window (None = all keys), and the position encoding
 (a PartSpec of category "position").  The mixer asks the cache for keys and
 values of [n_kv_heads, head_dim] per position, all of them or a window.
 
-A prompt that starts at position 0 attends over its own freshly projected rows
-and only stores to the cache; every other step stores first and then attends
-over the cache.  An entry of the run order that reads another entry's cache
+A sequence that starts at position 0 attends over its own freshly projected rows
+and only stores to the cache; a sequence that goes on (by one token or by many)
+stores first and then attends over the cache.  One step may hold both kinds: the
+rows of the first kind come first and go to one kernel, the rest to another.  An entry of the run order that reads another entry's cache
 projects q only and always attends over that cache.
 """
 from __future__ import annotations
@@ -108,16 +109,25 @@ class SoftmaxAttention(Mixer):
             ops.rope_kv_write(qkv, self.n_heads, step.token_pos, step.token_seq, step.seq_slot,
                               step.seq_len_after, inv_freq, rotary_dim, style, None, 0, self.head_dim)
         att = torch.empty((n, self.q_dim), dtype=h.dtype, device=h.device)
-        packed = step.from_zero and store.owns_kv
-        if not packed and cache.ring_pages > 0:
-            room = cache.ring_pages * ops.PAGE_TOKENS - int(self.window) + 1
-            if step.max_new > room:
-                raise KernelError(
-                    f"a step that continues sequences brings {step.max_new} tokens to a layer that "
-                    f"keeps a window of {self.window} keys in a ring of "
-                    f"{cache.ring_pages * ops.PAGE_TOKENS}: at most {room} fit without overwriting "
-                    f"keys that the step still reads")
-        self._attend(qkv, att, step, cache, packed)
+        if step.from_zero and store.owns_kv:
+            self._attend(qkv, att, step, cache, True)          # whole prompts: over the step's own rows
+        else:
+            # the sequences that start at position 0 come first and attend over their own rows;
+            # every other row attends over the cache, which holds the step's keys already
+            nf, sf = (step.fresh_tokens, step.fresh_seqs) if store.owns_kv else (0, 0)
+            if nf > 0:
+                self._attend(qkv[:nf], att[:nf], step.rows(0, nf, 0, sf), cache, True)
+            if nf < n:
+                rest = step if nf == 0 else step.rows(nf, n, sf, step.n_seqs)
+                if cache.ring_pages > 0:
+                    room = cache.ring_pages * ops.PAGE_TOKENS - int(self.window) + 1
+                    if rest.max_new > room:
+                        raise KernelError(
+                            f"a step that continues sequences brings {rest.max_new} tokens to a layer that "
+                            f"keeps a window of {self.window} keys in a ring of "
+                            f"{cache.ring_pages * ops.PAGE_TOKENS}: at most {room} fit without overwriting "
+                            f"keys that the step still reads")
+                self._attend(qkv[nf:], att[nf:], rest, cache, False)
         return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
 
     def _attend(self, qkv, att, step: StepInfo, cache, packed: bool) -> None:

@@ -96,6 +96,31 @@ class StepInfo:
     min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
     replayed: bool = False           # the device arrays are refilled and the same launches replayed (a CUDA
                                      # graph): n_tokens and n_seqs are capacities, the host lists are empty
+    fresh_seqs: int = 0              # a step that is not from_zero lists the sequences that start at position 0
+    fresh_tokens: int = 0            # first: that many sequences, that many rows (0: every row continues)
+
+    def rows(self, lo: int, hi: int, seq_lo: int, seq_hi: int) -> "StepInfo":
+        """The step as seen by rows lo..hi-1 alone, which are the sequences seq_lo..seq_hi-1: what a
+        mixer hands to a kernel that takes only a part of a step (the sequences that start at
+        position 0 to one kernel, the ones that go on to another).  Row arrays are cut;
+        `token_seq` keeps its values, so the per-sequence arrays `seq_slot` and `seq_len_after`
+        stay whole, while `cu_seqlens` and the host lists are cut to the part's sequences (the
+        part must begin at row 0 if a kernel is to use `cu_seqlens` as it is)."""
+        import dataclasses
+        cu = tuple(c - lo for c in self.cu_host[seq_lo:seq_hi + 1]) if self.cu_host else ()    # counted from the part's first row
+        starts = tuple(self.starts_host[seq_lo:seq_hi]) if self.starts_host else ()
+        news = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+        fresh = seq_lo == 0 and seq_hi <= self.fresh_seqs
+        return dataclasses.replace(
+            self, n_tokens=hi - lo, n_seqs=seq_hi - seq_lo, tokens=self.tokens[lo:hi],
+            token_pos=self.token_pos[lo:hi], token_seq=self.token_seq[lo:hi],
+            cu_seqlens=self.cu_seqlens[seq_lo:seq_hi + 1],
+            token_slot=self.token_slot[lo:hi] if self.token_slot is not None else None,
+            from_zero=fresh or self.from_zero, single_token=bool(news) and all(k == 1 for k in news),
+            max_new=max(news) if news else self.max_new,
+            max_len_after=max((s + k for s, k in zip(starts, news)), default=self.max_len_after),
+            slots_host=tuple(self.slots_host[seq_lo:seq_hi]) if self.slots_host else (), cu_host=cu,
+            starts_host=starts, fresh_seqs=seq_hi - seq_lo if fresh else 0, fresh_tokens=hi - lo if fresh else 0)
 
 
 class CallStore:

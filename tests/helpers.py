@@ -156,17 +156,49 @@ class Trace:
                 pos[m] += 1
             live = [m for m in live if pos[m] < len(members[m][2])]
 
+    def chunked(self, rid, key, tokens, sizes):
+        """One request fed in pieces of the given sizes (used round and round), every place wanted."""
+        at, i = 0, 0
+        while at < len(tokens):
+            k = min(sizes[i % len(sizes)], len(tokens) - at)
+            self.step([(rid, key, tokens[at:at + k], at, range(k))], end=[rid] if at + k == len(tokens) else [])
+            at, i = at + k, i + 1
+
+    def mixed(self, members, joins, sizes):
+        """members: [(id, key, tokens)]; member m joins at step joins[m] of this run and from then
+        on brings sizes[m][j] tokens in its j-th step (the list used round and round) until its
+        tokens end: requests that start, requests that go on by many tokens and requests that
+        go on by one share steps.  Every place is wanted."""
+        at = [0] * len(members)
+        turn = [0] * len(members)
+        t = 0
+        while any(at[m] < len(members[m][2]) for m in range(len(members))):
+            entries, ends = [], []
+            for m, (rid, key, toks) in enumerate(members):
+                if joins[m] > t or at[m] >= len(toks):
+                    continue
+                k = min(sizes[m][turn[m] % len(sizes[m])], len(toks) - at[m])
+                entries.append((rid, key, toks[at[m]:at[m] + k], at[m], range(k)))
+                at[m] += k
+                turn[m] += 1
+                if at[m] == len(toks):
+                    ends.append(rid)
+            if entries:
+                self.step(entries, end=ends)
+            t += 1
+
     def text(self) -> str:
         return "".join(json.dumps(s) + "\n" for s in self.steps)
 
 
-def run_trace(folder: str, dtype: str, trace: Trace, out_dir: str, timeout: int = 600) -> Dict[int, torch.Tensor]:
+def run_trace(folder: str, dtype: str, trace: Trace, out_dir: str, timeout: int = 600,
+              extra_args=()) -> Dict[int, torch.Tensor]:
     """Run bin/trace_run as a user would; returns {step: logits [wanted, vocab]}."""
     import subprocess
     import numpy as np
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-           "--out", out_dir, "--max-tokens", str(trace.max_tokens)]
+           "--out", out_dir, "--max-tokens", str(trace.max_tokens)] + [str(a) for a in extra_args]
     p = subprocess.run(cmd, input=trace.text().encode(), stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                        timeout=timeout)
     assert p.returncode == 0, f"trace_run failed ({p.returncode}):\n{p.stderr.decode()[-3000:]}"

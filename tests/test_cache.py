@@ -187,3 +187,38 @@ def test_changed_table_rows_reach_the_device_copy():
         assert torch.equal(g.table_dev, g.table_host) and not g._dirty
     c.flush()                                  # nothing changed: nothing to do
     c.check()
+
+
+def test_a_ring_is_made_for_the_tokens_a_step_adds():
+    # window 100: one more token per step needs 100 positions (2 pages, room 29);
+    # 130 more need 229 positions (4 pages, room 157)
+    c = make(chunk_tokens=1)
+    assert c.chunk_room() == 2 * 64 - 100 + 1
+    c = make(chunk_tokens=130)
+    ring = [g for g in c.groups if g.ring_pages][0]
+    assert ring.ring_pages == 4 and c.chunk_room() == 4 * 64 - 100 + 1 >= 130
+    # a window that is a multiple of the page: exactly one token of room, as decoding needs
+    c = make(window=128, chunk_tokens=1)
+    assert c.chunk_room() == 1
+    # no window anywhere: any number of tokens
+    needs = [KVNeed(2, 16, None)]
+    c = CacheManager(needs, [None], [[]], 256, 256, torch.float32, CPU)
+    assert c.chunk_room() is None
+
+
+def test_extending_the_sequences_of_a_step_is_all_or_nothing():
+    c = make(max_tokens=256, max_seq_len=256)                 # 4 pages per group
+    a, b, d = c.admit([0, 0, 0])
+    c.extend_all([a, b], [10, 70])                            # 1 + 2 pages
+    before = {s: (c.lengths[s], [list(g._slot_pages[s]) for g in c.groups]) for s in (a, b, d)}
+    with pytest.raises(CacheError, match="no free pages"):
+        c.extend_all([a, d], [20, 65])                        # a fits in its page, d wants 2 of the 1 left
+    with pytest.raises(CacheError, match="longer than the cache holds"):
+        c.extend_all([a, d], [20, 257])
+    with pytest.raises(CacheError, match="holds no sequence"):
+        c.extend_all([a, 99], [20, 5])
+    assert before == {s: (c.lengths[s], [list(g._slot_pages[s]) for g in c.groups]) for s in (a, b, d)}
+    c.check()
+    c.extend_all([a, d], [20, 64])
+    assert c.lengths[a] == 20 and c.lengths[d] == 64
+    c.check()

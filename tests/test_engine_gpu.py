@@ -106,8 +106,6 @@ def test_step_refuses_what_it_cannot_run(tmp_path):
     r = runner_for(folder, "float32", max_tokens=128)
     a, b = r.admit(2)
     r.step([a], [[1, 2, 3]])
-    with pytest.raises(HosError, match="either all start"):
-        r.step([a, b], [[4], [5, 6]])
     with pytest.raises(HosError, match="outside the vocabulary"):
         r.step([a], [[256]])
     with pytest.raises(HosError, match="appears twice"):
@@ -116,7 +114,18 @@ def test_step_refuses_what_it_cannot_run(tmp_path):
         r.step([a], [[1]], [[1]])
     with pytest.raises(CacheError):
         r.step([b], [list(range(65))])          # config A's context holds 64 positions
-    assert r.length(a) == 3                      # refused steps left the cache as it was
+    assert r.length(a) == 3 and r.length(b) == 0      # refused steps left the cache as it was
+    # all or nothing across the sequences of a step: the second one cannot be run, the first keeps its length
+    # (the same for a sequence that finds no free page: tests/test_cache.py)
+    pages_a = [len(g._slot_pages[a]) for g in r.cache.groups]
+    with pytest.raises(CacheError, match="longer than the cache holds"):
+        r.step([a, b], [[4], list(range(65))])
+    assert r.length(a) == 3 and r.length(b) == 0
+    assert [len(g._slot_pages[a]) for g in r.cache.groups] == pages_a
+    r.cache.check()
+    # a sequence that goes on by several tokens beside one that starts: one step
+    out = r.step([a, b], [[4, 5], [6, 7, 8]], [[0, 1], [2]])
+    assert out.shape == (3, 256) and r.length(a) == 5 and r.length(b) == 3
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -1,7 +1,9 @@
 """Trace replay on the GPU, through bin/trace_run as a user runs it, compared with
 the plain implementation: each request alone and whole; with its last 32 tokens one
 by one; in batches of unequal lengths whose shorter requests end earlier, one batch
-after another so that slots and pages are used again.  In 32-bit and in bfloat16."""
+after another so that slots and pages are used again; and fed in pieces of unequal
+sizes, alone and in steps that other requests share (some starting, some going on by
+one token, some by many).  In 32-bit and in bfloat16."""
 import random
 
 import pytest
@@ -46,5 +48,43 @@ def test_replay_matches_the_plain_implementation(tmp_path, name, dtype):
     w, cfg = plain_model(folder)
     reqs, trace = build(name)
     expected = {i: P.forward_logits(w, cfg, r) for i, r in enumerate(reqs)}
-    got = run_trace(folder, dtype, trace, str(tmp_path / "out"))
+    # a ring made for one more token per step: the shortest ring, which wraps soonest
+    got = run_trace(folder, dtype, trace, str(tmp_path / "out"), extra_args=["--chunk-tokens", 1])
+    check_trace(trace, got, expected, dtype)
+
+
+PIECES = [1, 7, 64, 100, 3, 33]
+
+
+def build_pieces(name):
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(200 + ord(name))
+    reqs = [random_tokens(rng, n, vocab) for n in LENGTHS[name]]
+    t = Trace()
+    for i, r in enumerate(reqs):                      # each request alone, in pieces
+        t.chunked(f"c{i}", i, r, PIECES[i % len(PIECES):] + PIECES[:i % len(PIECES)])
+    # requests that share steps: one is still fed in pieces while others go on by one token, and
+    # others join on the way (a step with sequences that start and sequences that go on)
+    order = sorted(range(len(reqs)), key=lambda i: -len(reqs[i]))
+    a = order[:4]
+    t.mixed([(f"m{i}", i, reqs[i]) for i in a], joins=[0, 0, 2, 3],
+            sizes=[[5, 40, 1, 1, 70], [len(reqs[a[1]]) // 2, 1], [9, 1, 1, 30], [1000]])
+    b = order[2:]
+    t.mixed([(f"n{i}", i, reqs[i]) for i in b], joins=[0, 1, 1, 2, 4, 5][:len(b)],
+            sizes=[[3, 1], [1], [64, 1, 1], [1000], [2, 65], [17]][:len(b)])
+    return reqs, t
+
+
+@pytest.mark.parametrize("chunk_tokens", [24, 512])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_replay_in_pieces_matches_the_plain_implementation(tmp_path, name, dtype, chunk_tokens):
+    """With --chunk-tokens 24 the rings of the window layers hold one or two pages, wrap all the
+    time, and pieces of 64 and 100 tokens are more than they have room for (the step function
+    feeds them in several passes); with 512 every piece runs in one pass."""
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    reqs, trace = build_pieces(name)
+    expected = {i: P.forward_logits(w, cfg, r) for i, r in enumerate(reqs)}
+    got = run_trace(folder, dtype, trace, str(tmp_path / "out"), extra_args=["--chunk-tokens", chunk_tokens])
     check_trace(trace, got, expected, dtype)
