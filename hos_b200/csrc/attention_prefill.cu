@@ -1,7 +1,12 @@
-// Attention of whole prompts that start at position 0 (prefill), bfloat16, flash style.
+// Attention of many tokens per sequence, bfloat16, flash style, in two forms.
 //
-// Queries, keys and values are the rows of this step's own fused projection output, packed
-// sequence after sequence (nothing is read from the cache).  One CTA (4 warps) takes 64
+// Whole prompts that start at position 0: queries, keys and values are the rows of this
+// step's own fused projection output, packed sequence after sequence (nothing is read from
+// the cache).  Sequences that go on by many tokens (a prompt fed in pieces, a second turn):
+// queries are the step's rows, keys and values are read from the paged cache, which holds
+// the step's own keys already; a key tile is a page (or half of one), copied as it lies.
+//
+// One CTA (4 warps) takes 64
 // consecutive queries of one sequence and one query head; key/value tiles of 64 rows (32 for
 // head sizes above 128, where two CTAs then share an SM) stream
 // through a two-stage cp.async pipeline into XOR-permuted shared memory.  Per tile each warp
@@ -11,6 +16,7 @@
 //
 // Compiled per head size: -DHOS_HEAD_DIM=N, N a multiple of 16 up to 256.
 #include "common.cuh"
+#include "kv_layout.cuh"
 #include "mma_utils.cuh"
 
 #ifndef HOS_HEAD_DIM
@@ -48,11 +54,22 @@ __device__ __forceinline__ void load_tile(bf16* tile, const bf16* src, int strid
     }
 }
 
+// A tile of `rows` keys (or values) that lies contiguous and permuted in the cache: copied as it is.
+__device__ __forceinline__ void load_tile_verbatim(bf16* tile, const bf16* src, int rows) {
+    for (int i = threadIdx.x; i < rows * (PHD / 8); i += 128) cp_async_16(tile + i * 8, src + i * 8, true);
+}
+
+// PAGED = false: sequences from position 0, keys and values in rows k, v (stride kv_stride).
+// PAGED = true: the rows of sequence s are cu_seqlens[s] - row_base .. of q and out, the first of
+// them at position token_pos[that row]; keys and values come from `cache` through the page table
+// row of seq_slot[s].
+template <bool PAGED>
 __global__ void __launch_bounds__(128, PHD > 128 ? 2 : 1)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k,
                     const bf16* __restrict__ v, int kv_stride, bf16* __restrict__ out, int out_stride,
                     const int* __restrict__ cu_seqlens, int n_seqs, int n_heads, int n_kv_heads,
-                    float scale, float cap, int window) {
+                    float scale, float cap, int window, int row_base, const int* __restrict__ token_pos,
+                    const int* __restrict__ seq_slot, PagedKV cache) {
     pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
@@ -61,30 +78,44 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     // which sequence and which block of 64 queries
     int seq = 0, tile_in_seq = blockIdx.x, row0 = 0, len = 0;
     for (; seq < n_seqs; ++seq) {
-        row0 = cu_seqlens[seq];
-        len = cu_seqlens[seq + 1] - row0;
+        row0 = cu_seqlens[seq] - row_base;
+        len = cu_seqlens[seq + 1] - row_base - row0;
         const int nt = (len + BQ - 1) / BQ;
         if (tile_in_seq < nt) break;
         tile_in_seq -= nt;
     }
     if (seq >= n_seqs) return;
     const int head = blockIdx.y, kvh = head / (n_heads / n_kv_heads);
-    const int q0 = tile_in_seq * BQ;                           // first query position of this CTA
+    const int q0 = tile_in_seq * BQ;                           // first query row of this CTA within its sequence
     const int q_rows = min(BQ, len - q0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int p0 = q0 + (PAGED ? token_pos[row0] : 0);         // and its position
 
-    const int last_q = q0 + q_rows - 1;
-    const int first_key = window > 0 ? max(0, q0 + 1 - window) : 0;
+    const int last_q = p0 + q_rows - 1;
+    const int first_key = window > 0 ? max(0, p0 + 1 - window) : 0;
     const int kt_lo = first_key / BKV, kt_hi = last_q / BKV;
     const int n_kt = kt_hi - kt_lo + 1;
 
-    const bf16* kbase = k + (size_t)row0 * kv_stride + (size_t)kvh * PHD;
-    const bf16* vbase = v + (size_t)row0 * kv_stride + (size_t)kvh * PHD;
+    const bf16* kbase = PAGED ? reinterpret_cast<const bf16*>(cache.k_pages) : k + (size_t)row0 * kv_stride + (size_t)kvh * PHD;
+    const bf16* vbase = PAGED ? reinterpret_cast<const bf16*>(cache.v_pages) : v + (size_t)row0 * kv_stride + (size_t)kvh * PHD;
+    const int* table = PAGED ? cache.page_table + (size_t)seq_slot[seq] * cache.table_stride : nullptr;
     load_tile(q_s, q + (size_t)(row0 + q0) * q_stride + (size_t)head * PHD, q_stride, BQ, q_rows);
     auto load_kv = [&](int kt, int stage) {
         const int key0 = kt * BKV;
-        load_tile(kv_s + (size_t)(2 * stage) * BKV * PHD, kbase + (size_t)key0 * kv_stride, kv_stride, BKV, len - key0);
-        load_tile(kv_s + (size_t)(2 * stage + 1) * BKV * PHD, vbase + (size_t)key0 * kv_stride, kv_stride, BKV, len - key0);
+        bf16* ks = kv_s + (size_t)(2 * stage) * BKV * PHD;
+        bf16* vs = kv_s + (size_t)(2 * stage + 1) * BKV * PHD;
+        if (PAGED) {
+            // rows key0 % 64 .. of the page's tile: contiguous, and permuted by (row & 7) as the tile in
+            // shared memory is (BKV is a multiple of 8).  Rows that no token has written yet hold zeros
+            // or older keys: the causal mask and the window's lower edge leave them out.
+            const int page = table[kv_table_entry(cache, key0 / kPageTokens)];
+            const size_t off = kv_tile_offset(cache, page, kvh) + (size_t)(key0 % kPageTokens) * PHD;
+            load_tile_verbatim(ks, kbase + off, BKV);
+            load_tile_verbatim(vs, vbase + off, BKV);
+        } else {
+            load_tile(ks, kbase + (size_t)key0 * kv_stride, kv_stride, BKV, len - key0);
+            load_tile(vs, vbase + (size_t)key0 * kv_stride, kv_stride, BKV, len - key0);
+        }
     };
     load_kv(kt_lo, 0);
     cp_async_commit();
@@ -95,7 +126,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 #pragma unroll
     for (int i = 0; i < PHD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     const uint32_t q_base = smem_u32(q_s);
-    const int qpos[2] = {q0 + warp * 16 + g, q0 + warp * 16 + g + 8};
+    const int qpos[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};
 
     for (int it = 0; it < n_kt; ++it) {
         const int stage = it & 1;
@@ -220,12 +251,42 @@ extern "C" int hos_attn_prefill(const void* q, int q_stride, const void* k, cons
         HOS_REFUSE("attn_prefill: rows must be 16-byte aligned");
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
+        cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
         attr_set = true;
     }
     dim3 grid(n_q_tiles, n_heads);
-    launch_pdl(attn_prefill_kernel, dim3(grid), dim3(128), kPrefillSmem, stream, 
+    launch_pdl(attn_prefill_kernel<false>, dim3(grid), dim3(128), kPrefillSmem, stream,
         (const bf16*)q, q_stride, (const bf16*)k, (const bf16*)v, kv_stride, (bf16*)out, out_stride, cu_seqlens,
-        n_seqs, n_heads, n_kv_heads, scale, cap, window);
+        n_seqs, n_heads, n_kv_heads, scale, cap, window, 0, (const int*)nullptr, (const int*)nullptr, PagedKV{});
     return check_launch("attn_prefill");
+}
+
+// Sequences that go on by many tokens, over the paged cache (which holds the step's keys already).
+// Sequence s of the n_seqs has the rows cu_seqlens[s] - row_base .. cu_seqlens[s + 1] - row_base - 1 of q and
+// out, at the positions token_pos[row] (consecutive within a sequence), and the page table row seq_slot[s];
+// n_q_tiles is at least the sum over sequences of ceil(rows / 64).
+extern "C" int hos_attn_chunk(const void* q, int q_stride, void* out, int out_stride, const int* cu_seqlens,
+                              int row_base, const int* token_pos, const int* seq_slot, int n_seqs, int n_q_tiles,
+                              void* k_pages, void* v_pages, const int* page_table, int table_stride, int ring_pages,
+                              int n_heads, int n_kv_heads, int head_dim, float scale, float cap, int window,
+                              cudaStream_t stream) {
+    if (n_q_tiles <= 0 || n_seqs <= 0) return 0;
+    if (head_dim != PHD) HOS_REFUSE("attn_chunk: built for head_dim %d, asked for %d", PHD, head_dim);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        HOS_REFUSE("attn_chunk: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    if (n_heads > 65535) HOS_REFUSE("attn_chunk: %d heads are more than one launch takes", n_heads);
+    if ((q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) ||
+        ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 4))
+        HOS_REFUSE("attn_chunk: rows and pages must be 16-byte aligned");
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
+        attr_set = true;
+    }
+    dim3 grid(n_q_tiles, n_heads);
+    launch_pdl(attn_prefill_kernel<true>, dim3(grid), dim3(128), kPrefillSmem, stream,
+        (const bf16*)q, q_stride, (const bf16*)nullptr, (const bf16*)nullptr, 0, (bf16*)out, out_stride, cu_seqlens,
+        n_seqs, n_heads, n_kv_heads, scale, cap, window, row_base, token_pos, seq_slot,
+        PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim});
+    return check_launch("attn_chunk");
 }

@@ -7,7 +7,7 @@ import numpy as np
 import torch
 
 from ..errors import HosError
-from ..parts.base import StepInfo
+from ..parts.base import FEW_TOKENS, StepInfo
 
 
 def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slots: Sequence[int],
@@ -25,6 +25,9 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
     if any(s == 0 for s in starts[n_fresh:]):
         raise HosError("the sequences of a step that start at position 0 must be listed first")
     news = [len(t) for t in token_lists]
+    n_tail = 0                        # and the ones that go on by a few tokens only stand last
+    while n_tail < b - n_fresh and news[b - 1 - n_tail] <= FEW_TOKENS:
+        n_tail += 1
     n = sum(news)
     nn = max(n, pad_to)
     cu = np.zeros(b + 1, dtype=np.int64)
@@ -70,7 +73,7 @@ def build_step(token_lists: Sequence[Sequence[int]], starts: Sequence[int], slot
         max_new=max(news) if news else 0,
         max_len_after=max(lens_after) if lens_after else 0,
         slots_host=tuple(slots), cu_host=tuple(int(c) for c in cu), starts_host=tuple(starts),
-        fresh_seqs=n_fresh, fresh_tokens=int(cu[n_fresh]))
+        fresh_seqs=n_fresh, fresh_tokens=int(cu[n_fresh]), tail_seqs=n_tail, tail_tokens=int(cu[b] - cu[b - n_tail]))
     if extra is not None:
         return info, dev[o + 3 * b + 1:]
     return info

@@ -23,7 +23,7 @@ from ..config.base import ModelConfig, read_config_json
 from .. import ops
 from ..errors import ExtensionMissingError, HosError
 from ..model import Model
-from ..parts.base import Runtime
+from ..parts.base import FEW_TOKENS, Runtime
 from ..registry import config_from_dict, plan_for
 from ..weights import RandomSource, SafetensorsFolder, load_tensors
 from .batch import build_step
@@ -163,7 +163,9 @@ class Runner:
         # all or nothing: every sequence gets its pages for the whole step before anything runs
         self.cache.extend_all(slots, [st + len(t) for st, t in zip(starts, token_lists)])
         room = self.cache.chunk_room()
-        order = sorted(range(len(slots)), key=lambda i: starts[i] != 0)     # stable: fresh ones first
+        # stable: the sequences that start come first, the ones that go on by a few tokens last
+        order = sorted(range(len(slots)),
+                       key=lambda i: 0 if starts[i] == 0 else (1 if len(token_lists[i]) > FEW_TOKENS else 2))
         first_row = [0] * len(slots)          # where each sequence's rows begin in the result
         at = 0
         for i, w in enumerate(want):

@@ -127,8 +127,27 @@ class SoftmaxAttention(Mixer):
                             f"keeps a window of {self.window} keys in a ring of "
                             f"{cache.ring_pages * ops.PAGE_TOKENS}: at most {room} fit without overwriting "
                             f"keys that the step still reads")
-                self._attend(qkv[nf:], att[nf:], rest, cache, False)
+                # sequences that bring many tokens: a kernel that takes 64 queries per key tile; the few-token
+                # tail (decoding rows that share the step): the kernel that splits one query's keys over the GPU
+                nt, st = rest.tail_tokens, rest.tail_seqs
+                padded = not rest.cu_host or rest.cu_host[-1] != rest.n_tokens     # padding rows: one kernel takes all
+                many = 0 if padded else rest.n_tokens - nt
+                if many > 0 and self._attend_chunks(qkv[nf:nf + many], att[nf:nf + many],
+                                                    rest.rows(0, many, 0, rest.n_seqs - st), cache):
+                    if nt > 0:
+                        self._attend(qkv[nf + many:], att[nf + many:],
+                                     rest.rows(many, rest.n_tokens, rest.n_seqs - st, rest.n_seqs), cache, False)
+                else:
+                    self._attend(qkv[nf:], att[nf:], rest, cache, False)
         return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
+
+    def _attend_chunks(self, qkv, att, part: StepInfo, cache) -> bool:
+        """Sequences that go on by many tokens, over the cache, 64 queries at a time.  `part`: those
+        rows of the step.  False: no such kernel for this case."""
+        if self.rt.dtype != torch.bfloat16:
+            return False
+        from . import attention_fast
+        return attention_fast.attend_chunks(self, qkv, att, part, cache)
 
     def _attend(self, qkv, att, step: StepInfo, cache, packed: bool) -> None:
         stride = qkv.shape[1]

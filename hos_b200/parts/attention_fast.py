@@ -16,7 +16,7 @@ MAX_HEAD_DIM = 256
 MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
-enabled = {"decode": True, "prefill": True, "prefill_tc": True,
+enabled = {"decode": True, "prefill": True, "prefill_tc": True, "chunk": True,
            "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0",
            "decode_cluster": os.environ.get("HOS_ATTN_CLUSTER", "1") != "0"}
 _pair_state: Dict[int, bool] = {}
@@ -188,6 +188,33 @@ def prefill(q, q_stride, k_rows, v_rows, kv_stride, out, cu_seqlens, n_seqs: int
     lib.call("hos_attn_prefill", ops._ptr(q), q_stride, ops._ptr(k_rows), ops._ptr(v_rows), kv_stride,
              ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens), n_seqs, blocks, n_heads, n_kv_heads, head_dim,
              float(scale), float(cap), int(window) if window else 0, ops._stream())
+
+
+def chunk(q, q_stride, out, cu_seqlens, row_base: int, token_pos, seq_slot, n_seqs: int, blocks: int,
+          cache: ops.PagedKVArgs, n_heads, scale, cap, window) -> None:
+    """Attention of sequences that go on by many tokens over the paged cache (which holds the step's
+    own keys already): sequence s has the rows cu_seqlens[s] - row_base .. of q and out, at consecutive
+    positions from token_pos[its first row], and the page-table row seq_slot[s].  `blocks`: at least the
+    sum over sequences of ceil(rows / 64)."""
+    lib = lib_for(cache.head_dim)
+    lib.call("hos_attn_chunk", ops._ptr(q), q_stride, ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens), int(row_base),
+             ops._ptr(token_pos), ops._ptr(seq_slot), n_seqs, blocks, ops._ptr(cache.k_pages), ops._ptr(cache.v_pages),
+             ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages, n_heads, cache.n_kv_heads,
+             cache.head_dim, float(scale), float(cap), int(window) if window else 0, ops._stream())
+
+
+def attend_chunks(mixer, qkv, att, part, cache) -> bool:
+    """The rows of `part` (sequences of a step that go on by many tokens; see StepInfo.rows) through
+    the chunk kernel; False if it does not take the case."""
+    if cache.k_pages.dtype != torch.bfloat16 or not supports(mixer.head_dim) or not enabled["chunk"]:
+        return False
+    if part.replayed or not part.cu_host:
+        return False
+    cu = part.cu_host
+    blocks = sum((cu[i + 1] - cu[i] + 63) // 64 for i in range(len(cu) - 1))
+    chunk(qkv, qkv.shape[1], att, part.cu_seqlens, part.row_offset, part.token_pos, part.seq_slot[part.seq_offset:],
+          part.n_seqs, blocks, cache, mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
+    return True
 
 
 def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:

@@ -72,6 +72,9 @@ class Runtime:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
 
+FEW_TOKENS = 8      # a sequence that goes on by at most this many tokens counts among the step's "tail"
+
+
 @dataclass
 class StepInfo:
     """One step's batch as the kernels see it.  N tokens (rows) of B sequences, packed
@@ -98,14 +101,20 @@ class StepInfo:
                                      # graph): n_tokens and n_seqs are capacities, the host lists are empty
     fresh_seqs: int = 0              # a step that is not from_zero lists the sequences that start at position 0
     fresh_tokens: int = 0            # first: that many sequences, that many rows (0: every row continues)
+    tail_seqs: int = 0               # and the sequences that go on by a few tokens only (FEW_TOKENS or fewer) last:
+    tail_tokens: int = 0             # that many sequences, that many rows (a mixer may send them to another kernel)
+    row_offset: int = 0              # of a part of a step (see rows()): its first row and its first sequence in the
+    seq_offset: int = 0              # whole step, which cu_seqlens (rows) and token_seq, seq_slot (sequences) still count from
 
     def rows(self, lo: int, hi: int, seq_lo: int, seq_hi: int) -> "StepInfo":
         """The step as seen by rows lo..hi-1 alone, which are the sequences seq_lo..seq_hi-1: what a
         mixer hands to a kernel that takes only a part of a step (the sequences that start at
         position 0 to one kernel, the ones that go on to another).  Row arrays are cut;
         `token_seq` keeps its values, so the per-sequence arrays `seq_slot` and `seq_len_after`
-        stay whole, while `cu_seqlens` and the host lists are cut to the part's sequences (the
-        part must begin at row 0 if a kernel is to use `cu_seqlens` as it is)."""
+        stay whole (the part's first sequence is their entry `seq_offset`), while `cu_seqlens`
+        is cut to the part's sequences and still counts rows from the whole step's first row
+        (`row_offset` rows before the part's first); the host lists are cut and count from the
+        part's first row."""
         import dataclasses
         cu = tuple(c - lo for c in self.cu_host[seq_lo:seq_hi + 1]) if self.cu_host else ()    # counted from the part's first row
         starts = tuple(self.starts_host[seq_lo:seq_hi]) if self.starts_host else ()
@@ -120,7 +129,10 @@ class StepInfo:
             max_new=max(news) if news else self.max_new,
             max_len_after=max((s + k for s, k in zip(starts, news)), default=self.max_len_after),
             slots_host=tuple(self.slots_host[seq_lo:seq_hi]) if self.slots_host else (), cu_host=cu,
-            starts_host=starts, fresh_seqs=seq_hi - seq_lo if fresh else 0, fresh_tokens=hi - lo if fresh else 0)
+            starts_host=starts, fresh_seqs=seq_hi - seq_lo if fresh else 0, fresh_tokens=hi - lo if fresh else 0,
+            tail_seqs=max(0, min(seq_hi, self.n_seqs) - max(seq_lo, self.n_seqs - self.tail_seqs)),
+            tail_tokens=max(0, min(hi, self.n_tokens) - max(lo, self.n_tokens - self.tail_tokens)),
+            row_offset=self.row_offset + lo, seq_offset=self.seq_offset + seq_lo)
 
 
 class CallStore:

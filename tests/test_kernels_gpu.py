@@ -169,6 +169,63 @@ def _ref_attention(q, k, v, pos, scale, cap, window):
     return out
 
 
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=8, cap=50.0, slack=40),
+                                 dict(nh=6, nkv=1, hd=48, window=37, cap=20.0, slack=100),
+                                 dict(nh=3, nkv=1, hd=64, window=None, cap=0.0, slack=0),
+                                 dict(nh=10, nkv=5, hd=80, window=130, cap=9.0, slack=70),
+                                 dict(nh=4, nkv=2, hd=128, window=70, cap=50.0, slack=130),
+                                 dict(nh=8, nkv=4, hd=256, window=200, cap=50.0, slack=120),
+                                 dict(nh=2, nkv=1, hd=256, window=None, cap=50.0, slack=0)])
+def test_attention_chunk_kernel(cfg):
+    """Sequences that go on by many tokens, over a scattered paged cache that holds their keys
+    already: pieces of 1, 64, 65 and 100-odd tokens that begin inside a page, rings that have
+    wrapped and are as long as the window plus the piece needs, a key at the window's edge that
+    stands out (and the one before it, which must not be seen), rows of other sequences before
+    the first piece (the row base)."""
+    from hos_b200.parts import attention_fast as af
+    dt = torch.bfloat16
+    nh, nkv, hd, window, cap, slack = (cfg[k] for k in ("nh", "nkv", "hd", "window", "cap", "slack"))
+    torch.manual_seed(4)
+    seq_lens = [77, 64, 300, 517, 130]                      # lengths after the step
+    news = [1, 64, min(slack, 65) if window else 65, min(slack, 110) if window else 110,
+            min(slack, 100) if window else 100]      # a ring has room for `slack` tokens per step
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(l, nh, hd).to(dt).float() for l in seq_lens]
+    g = nh // nkv
+    if window:
+        p = 517 - 3                                         # a query of the long sequence's piece
+        lo = p + 1 - window
+        ks[3][lo] = qs[3][p, 0::g][:nkv] * 3.0
+        ks[3][lo - 1] = qs[3][p, 0::g][:nkv] * 6.0
+    scale = 0.9 / math.sqrt(hd)
+    ring = (window + slack - 1 + 63) // 64 if window else 0
+    cache, slots = _fill_cache([k.to(DEV) for k in ks], [v.to(DEV) for v in vs], seq_lens, nkv, hd, ring, dt,
+                               n_slots=9, scatter_seed=5, fill=0.0)
+    base = 3                                                # rows of other sequences come first
+    rows, pos, cu = [torch.zeros(base, nh * hd)], [torch.zeros(base, dtype=torch.int32)], [base]
+    for i, (l, n) in enumerate(zip(seq_lens, news)):
+        rows.append(qs[i][l - n:].reshape(n, nh * hd))
+        pos.append(torch.arange(l - n, l, dtype=torch.int32))
+        cu.append(cu[-1] + n)
+    q = torch.cat(rows).to(DEV).to(dt).contiguous()
+    out = torch.full_like(q, 7.0)
+    pos_t = torch.cat(pos).to(DEV)
+    seq_slot = torch.tensor([0, 0] + slots, dtype=torch.int32, device=DEV)      # two other sequences before them
+    blocks = sum((n + 63) // 64 for n in news)
+    af.chunk(q[base:], nh * hd, out[base:], torch.tensor(cu, dtype=torch.int32, device=DEV), base, pos_t[base:],
+             seq_slot[2:], len(news), blocks + 2, cache, nh, scale, cap, window)
+    torch.cuda.synchronize()
+    assert float((out[:base] - 7.0).abs().sum()) == 0.0     # rows before the base are not touched
+    at = base
+    for i, (l, n) in enumerate(zip(seq_lens, news)):
+        for j in range(n):
+            p = l - n + j
+            want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
+            close(out[at + j].reshape(nh, hd), want.to(dt), dt)
+        at += n
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=None, cap=0.0),
                                  dict(nh=6, nkv=1, hd=48, window=37, cap=20.0),
