@@ -5,9 +5,10 @@
 
 A "step" is one decode step of the whole batch.  The timed region is K decode steps that end
 at context length C (default 8192, the benchmark context of the 2B configuration), timed on
-the device with CUDA events; `value` is decoded tokens per second.  `e2e` is the same loop
-through the public entry point (`Engine.step` and the sampler), host token ids in and out
-every step.  `prefill` is one prompt of 2,048 tokens.  `roofline` relates the bytes a decode
+the device with CUDA events; `value` is decoded tokens per second.  `e2e` is the same steps
+through the public entry point (`Engine.generate_from_ids` on conversations that hold the
+context): every step uploads which slots run from pinned memory and brings the sampled ids
+back to the host, where the loop reads them one step late.  `prefill` is one prompt of 2,048 tokens.  `roofline` relates the bytes a decode
 step must read (every weight once, and the cache of the live sequences) to its time.
 `points` holds decoding at batch 1 and 64.  One JSON line is printed.
 
@@ -162,15 +163,13 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
     step, kernel launches in the timed region, h2d bytes per step, d2h bytes per step, mean length)."""
     import torch
     from hos_b200 import ops
-    from hos_b200.sampling import Sampler, SamplingParams
     r = eng.runner
     vocab = r.vocab_size
 
     def prepare():
         slots = r.admit(batch)
         start = ctx - (warmup + steps)
-        for s in slots:
-            r.cache.extend(s, start)
+        r.cache.extend_all(slots, [start] * batch)
         return slots, start
 
     # ---- device-timed: steps issued back to back, tokens stay on the device ----
@@ -180,25 +179,27 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
     for s in slots:
         r.release(s)
 
-    # ---- end to end: the public step and the sampler, host ids in and out every step ----
-    slots, start = prepare()
-    sampler = Sampler(SamplingParams.pure(), r.device)
-    for i, s in enumerate(slots):
-        sampler.open(s, i)
-    toks = [[rng.randrange(vocab)] for _ in range(batch)]
-    for _ in range(warmup):
-        toks = [[t] for t in sampler.sample(eng.step(slots, toks, copy=False), slots)]
+    # ---- end to end: the public entry point (Engine.generate_from_ids on conversations that hold the
+    # context), token ids back on the host; every step uploads which slots run and brings its tokens back ----
+    convs = eng.open(batch)
+    start = ctx - (warmup + steps)
+    r.cache.extend_all([c.slot for c in convs], [start] * batch)
+    r.write_records([c.slot for c in convs], pos=[start] * batch)
+    for c in convs:
+        c.position = start
+    kw = dict(temp=0.0, top_k=0, top_p=1.0, rep_penalty=1.0, stop_ids=[])
+    eng.generate_from_ids(convs, [[rng.randrange(vocab)] for _ in range(batch)], max_tokens=warmup, **kw)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for _ in range(steps):
-        toks = [[t] for t in sampler.sample(eng.step(slots, toks, copy=False), slots)]
+    outs = eng.generate_from_ids(convs, [[] for _ in range(batch)], max_tokens=steps, **kw)
     torch.cuda.synchronize()
     ms_e2e = (time.perf_counter() - t0) * 1e3 / steps
-    for s in slots:
-        sampler.close(s)
-        r.release(s)
-    h2d = (3 * batch + (batch + 1) + 2 * batch) * 4 + batch * 4     # step arrays + wanted rows
-    d2h = batch * 4
+    assert all(len(o) == steps for o in outs), "every sequence decodes every step"
+    for c in convs:
+        c.close()
+    from hos_b200.engine.decode import META, bucket_for
+    h2d = (META + bucket_for(batch)) * 4       # live rows, stop ids, the slots that run
+    d2h = bucket_for(batch) * 4                # the sampled ids
     mean_len = ctx - steps / 2.0
     return ms_dev, ms_e2e, launches, h2d, d2h, mean_len
 
@@ -312,11 +313,13 @@ def main() -> int:
         if args.prefill_tokens % 4 == 0:       # the same prompt as four steps that continue one another
             line["prefill"]["ms_in_4_pieces"] = measure_prefill(eng, args.prefill_tokens, rng, pieces=4)
     if not args.no_points:
-        pts = {}
+        pts, pts_e2e = {}, {f"decode_b{args.batch}": line["e2e"]["value"]}
         for b in (1, 64):
-            m, _, _, _, _, _ = measure_decode(eng, b, args.ctx, max(8, args.steps // 2), args.warmup, rng)
+            m, me, _, _, _, _ = measure_decode(eng, b, args.ctx, args.steps, args.warmup, rng)
             pts[f"decode_b{b}"] = b * 1e3 / m
+            pts_e2e[f"decode_b{b}"] = b * 1e3 / me
         line["points"] = pts
+        line["points_e2e"] = pts_e2e
     print(json.dumps(line))
     return 0
 

@@ -11,9 +11,15 @@ group.
     cache.extend(slot, new_len)          # before a step that lengthens the sequence
     cache.release(slot)                  # the sequence has ended: slot and pages go back
 
-Per-sequence state (`StateNeed`): a tensor [n_slots, *shape] per entry and name,
-zeroed for a slot when a sequence is admitted to it.  Gemma-2 has none; the
-sequences' lengths are the only per-sequence numbers it keeps.
+Per-sequence state of fixed size lives beside the keys and values, a row per slot,
+zeroed when a sequence is admitted to the slot: the record (`record`, int32
+[n_slots, 8]: position, last sampled token, finished flag, count of sampled
+tokens, generator state, limit; `recent`, the ring of the tokens sampled last),
+which single-token steps read and write on the device (csrc/slot_state.cu), and
+whatever a mixer asks for (`StateNeed`: a tensor [n_slots, *shape] per entry and
+name; Gemma-2's mixers ask for none).  The host keeps the lengths too (`lengths`),
+because it hands out the pages; the kernels of a single-token step take positions
+from the record.
 """
 from __future__ import annotations
 
@@ -25,6 +31,8 @@ from ..errors import CacheError
 from ..parts.base import CallStore, KVNeed, StateNeed
 from .kv import KVGroup, PAGE
 from .pool import IdPool
+
+RECORD_WORDS, RECENT_TOKENS = 8, 256       # as csrc/slot_state.cu lays a record out
 
 
 class CacheManager:
@@ -73,6 +81,8 @@ class CacheManager:
             state = {s.name: torch.zeros((self.n_slots,) + tuple(s.shape), dtype=s.dtype,
                                          device=self.device) for s in state_needs[i]}
             self.stores.append(CallStore(kv, owns, state))
+        self.record = torch.zeros((self.n_slots, RECORD_WORDS), dtype=torch.int32, device=self.device)
+        self.recent = torch.zeros((self.n_slots, RECENT_TOKENS), dtype=torch.int32, device=self.device)
 
     # ---- sequences ------------------------------------------------------------------
     def admit(self, lengths: Sequence[int]) -> List[int]:
@@ -94,10 +104,19 @@ class CacheManager:
             self.lengths[slot] = 0
             for g in self.groups:
                 g.open_slot(slot)
+            out.append(slot)
+        at = 0
+        ordered = sorted(out)
+        while at < len(ordered):                       # runs of neighbouring slots are cleared together
+            end = at + 1
+            while end < len(ordered) and ordered[end] == ordered[end - 1] + 1:
+                end += 1
+            lo, hi = ordered[at], ordered[end - 1] + 1
+            self.record[lo:hi].zero_()
             for st in self.stores:
                 for t in st.state.values():
-                    t[slot].zero_()
-            out.append(slot)
+                    t[lo:hi].zero_()
+            at = end
         return out
 
     def extend(self, slot: int, new_len: int) -> None:

@@ -11,7 +11,8 @@ every file and then every few seconds.  A library that cannot be built raises
 
 Libraries and what needs them:
   core        every model: embedding, norms, rotary + cache write, plain matrix
-              product and plain attention (32-bit and bfloat16), sampling
+              product and plain attention (32-bit and bfloat16), sampling, the
+              per-slot record
   attn_hdN    bfloat16 models with head_dim N: tensor-core attention for prompts
               and for decoding over the paged cache
   gemm_tc     bfloat16 models: the tcgen05/TMA matrix product
@@ -39,7 +40,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 
 # library name -> (sources, extra flags)
 _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
-    "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu"], []),
+    "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "slot_state.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
 }

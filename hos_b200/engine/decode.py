@@ -1,29 +1,39 @@
 """Single-token steps with static device buffers, so that a whole step (all layers, the head,
-and optionally the token choice and the move to the next position) is captured once in a
-CUDA graph and replayed: decoding is then bound by the kernels, not by the host.
+and optionally the token choice) is captured once in a CUDA graph and replayed: decoding is
+then bound by the kernels, not by the host.
 
 A session serves every batch of up to `bucket` sequences: which slots take part is data (a
 device array), not structure, and unused rows are padding (token_seq = -1), which every
-kernel skips.  `feed(...)` + `run()` is one step with host token ids (what the step function
-and the generation loop use); `run_greedy_on_device()` is one step whose arg max stays on
-the device and becomes the next input (what measurements of the device time use).  The
-cache's pages for the positions a step writes must exist before it runs: `Runner` extends
-the sequences first.
+kernel skips.  What the host sends per step is the list of slots (and, for a step whose
+tokens the caller brings, the tokens): positions are read from the slots' records on the
+device and moved on there (csrc/slot_state.cu).
+
+  upload(slots, tokens) + run_step()      one step on host token ids -> logits (the step function)
+  upload(slots) + run_generate(params)    one step whose input is the token sampled last (kept in the
+                                          record), followed by sampling on the device; the new token
+                                          goes into the record and is fetched asynchronously
+                                          (fetch_start / fetch_read): the generation loop and the
+                                          measurements
+
+The cache's pages for the positions a step writes must exist before it runs: the caller
+extends the sequences first.
 """
 from __future__ import annotations
 
 import gc
 import os
 import weakref
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from .. import ops
 from ..parts.base import StepInfo
+from ..sampling.sampler import SamplingParams
 
 BUCKETS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+META = 2 + ops.MAX_STOPS        # live rows, number of stop ids, the stop ids
 
 
 def bucket_for(n: int) -> int:
@@ -47,14 +57,14 @@ class DecodeSession:
         if use_graph is None:
             use_graph = os.environ.get("HOS_NO_GRAPH", "") == ""
         self.use_graph = use_graph
-        # one int32 device buffer; two pinned host mirrors used in turn, each guarded by an event,
-        # so that the host may run a step ahead of the device without overwriting a copy's source
-        self._hosts = [torch.zeros(6 * b + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        # What the host sends: meta | slots | tokens.  Two pinned mirrors used in turn, each guarded by
+        # an event, so that the host may run a step ahead of the device without overwriting a copy's source.
+        n_up = META + 2 * b
+        self._hosts = [torch.zeros(n_up, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._hosts_np = [h.numpy() for h in self._hosts]
-        self._laid_out = [-1, -1]               # live rows each mirror's constant fields were written for
         self._copied = [None, None]
         self._turn = 0
-        self._dev = torch.zeros(6 * b + 1, dtype=torch.int32, device=dev)
+        self._dev = torch.zeros(n_up + 4 * b + 1, dtype=torch.int32, device=dev)
         o = 0
 
         def take(n):
@@ -62,15 +72,18 @@ class DecodeSession:
             v = self._dev[o:o + n]
             o += n
             return v
-        self.tokens, self.pos, self.seq, self.cu = take(b), take(b), take(b), take(b + 1)
-        self.slot, self.after = take(b), take(b)
+        self.meta, self.slot, self.tokens = take(META), take(b), take(b)
+        self.pos, self.seq, self.after, self.cu = take(b), take(b), take(b), take(b + 1)     # written on the device
         self.rows = torch.arange(b, dtype=torch.int32, device=dev)
         self.sampled = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.uniforms = torch.zeros(b, dtype=torch.float32, device=dev)
+        self.recent_len = torch.zeros(b, dtype=torch.int32, device=dev)
+        self._recent = {}                       # repeat_last_n -> static [b, n] buffer
+        # sampled tokens on their way to the host: pinned buffers used in turn
+        self._fetch_hosts = [torch.zeros(b, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._fetch_turn = 0
         self.logits: Optional[torch.Tensor] = None
-        self._graph = None
-        self._graph_greedy = None
-        self._ready = False
-        self._greedy_ready = False
+        self._programs = {}                     # key -> (graph or None, logits buffer)
         self.launches_per_step = 0
         self._max_len = runner.cache.max_seq_len
         self.n_live = 0
@@ -87,55 +100,80 @@ class DecodeSession:
                         starts_host=(), token_slot=self.slot,      # row n is sequence n here
                         min_live=smaller_bucket(self.b) + 1, replayed=True)
 
-    def feed(self, slots: Sequence[int], tokens: Sequence[int], lengths_before: Sequence[int]) -> None:
-        """Host token ids, slots and each sequence's length before the step -> the static
-        buffers (one host-to-device copy).  Rows beyond len(slots) are padding."""
+    def upload(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
+               stop_ids: Sequence[int] = ()) -> None:
+        """Which slots the next step runs (rows beyond them are padding), the tokens if the caller
+        brings them, and the stop ids that mark a sequence finished on the device (the first
+        ops.MAX_STOPS of them; the host checks all of them anyway): one host-to-device copy."""
         n = len(slots)
         self.n_live = n
-        pad = self.b - n
         turn = self._turn
         self._turn ^= 1
         if self._copied[turn] is not None:
             self._copied[turn].synchronize()       # the copy that last read this mirror is done
-        h = self._hosts[turn]
-        hn = self._hosts_np[turn]              # the same memory as a numpy array: no tensor per field
-        b = self.b
-        hn[0:n] = tokens
-        hn[b:b + n] = lengths_before
-        hn[4 * b + 1:4 * b + 1 + n] = slots
-        np.add(hn[b:b + n], 1, out=hn[5 * b + 1:5 * b + 1 + n])
-        if self._laid_out[turn] != n:          # what depends on the number of live rows only
-            hn[n:b] = -1
-            hn[b + n:2 * b] = 0
-            hn[2 * b:2 * b + n] = np.arange(n, dtype=np.int32)
-            hn[2 * b + n:3 * b] = -1
-            hn[3 * b:4 * b + 1] = np.minimum(np.arange(b + 1, dtype=np.int32), n)
-            hn[4 * b + 1 + n:5 * b + 1] = 0
-            hn[5 * b + 1 + n:6 * b + 1] = 1
-            self._laid_out[turn] = n
-        self._dev.copy_(h, non_blocking=True)
+        hn, b = self._hosts_np[turn], self.b
+        stops = list(stop_ids)[: ops.MAX_STOPS]
+        hn[0], hn[1] = n, len(stops)
+        hn[2:2 + len(stops)] = stops
+        hn[META:META + n] = slots
+        hn[META + n:META + b] = 0
+        size = META + b
+        if tokens is not None:
+            hn[META + b:META + b + n] = tokens
+            hn[META + b + n:META + 2 * b] = -1
+            size = META + 2 * b
+        self._dev[:size].copy_(self._hosts[turn][:size], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._copied[turn] = ev
 
-    def _forward(self) -> torch.Tensor:
+    # ---- what a step launches ---------------------------------------------------------------
+    def _begin(self, flags: int, recent=None) -> None:
+        c = self.runner.cache
+        ops.slot_begin(c.record, c.recent, self.slot, self.meta, self.b, flags, self.tokens, self.pos, self.after,
+                       self.seq, self.cu, self.uniforms if flags & ops.BEGIN_UNIFORM else None, recent,
+                       self.recent_len if recent is not None else None)
+
+    def _forward_step(self) -> torch.Tensor:
         r = self.runner
+        self._begin(ops.BEGIN_ADVANCE)
         x = r.model.hidden(self._info(), r.cache)
         return r.model.logits(x, self.rows)
 
-    def _forward_greedy(self) -> torch.Tensor:
-        logits = self._forward()
-        ops.argmax(logits, self.sampled)
-        ops.decode_advance(self.tokens, self.pos, self.after, self.seq, self.sampled)
+    def _forward_generate(self, p: SamplingParams) -> torch.Tensor:
+        r = self.runner
+        penal = p.rep_penalty != 1.0 and p.repeat_last_n > 0
+        recent = None
+        if penal:
+            recent = self._recent.get(p.repeat_last_n)
+            if recent is None:
+                recent = self._recent[p.repeat_last_n] = torch.zeros((self.b, p.repeat_last_n), dtype=torch.int32,
+                                                                     device=r.device)
+        flags = ops.BEGIN_ADVANCE | ops.BEGIN_TOKEN_FROM_RECORD | ops.BEGIN_SKIP_FINISHED
+        flags |= ops.BEGIN_UNIFORM if p.temp > 0.0 else 0
+        flags |= ops.BEGIN_RECENT if penal else 0
+        self._begin(flags, recent)
+        x = r.model.hidden(self._info(), r.cache)
+        logits = r.model.logits(x, self.rows)
+        sample_into(logits, self.sampled, p, self.uniforms, recent, self.recent_len)
+        c = r.cache
+        ops.slot_end(c.record, c.recent, self.slot, self.meta, self.b, self.sampled)
         return logits
 
-    def _capture(self, fn):
-        # run once eagerly (first-use set-up of kernels must not happen inside a capture)
+    def _program(self, key, fn):
+        """The launches of `fn` as a replayable program: run once as they are (first-use set-up of
+        kernels must not happen inside a capture; what that run changed in the slots' records is
+        put back), then captured."""
+        prog = self._programs.get(key)
+        if prog is not None:
+            return prog
+        c = self.runner.cache
+        keep = (c.record.clone(), c.recent.clone())
         before = ops.launch_count
         out = fn()
         self.launches_per_step = ops.launch_count - before
-        if not self.use_graph:
-            return None, out
+        c.record.copy_(keep[0])
+        c.recent.copy_(keep[1])
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         # nothing but this thread's own launches may touch the capture: no collection of old
@@ -148,35 +186,76 @@ class DecodeSession:
         finally:
             if gc_was_on:
                 gc.enable()
-        return g, out
+        prog = self._programs[key] = (g, out)
+        return prog
 
-    def run(self) -> torch.Tensor:
-        """One step on what `feed` put in.  Returns float32 logits [live sequences, vocab] (a
-        view of a static buffer when graphs are on: use it before the next run)."""
+    def _run(self, key, fn) -> torch.Tensor:
         self.runner.cache.flush()
-        if not self._ready:
-            self._graph, self.logits = self._capture(self._forward)
-            self._ready = True
-            if self._graph is None:
-                return self.logits[: self.n_live]
-        if self._graph is not None:
-            self._graph.replay()
-        else:
-            self.logits = self._forward()
-        return self.logits[: self.n_live]
+        if not self.use_graph:
+            before = ops.launch_count
+            self.logits = fn()
+            self.launches_per_step = ops.launch_count - before
+            return self.logits
+        g, self.logits = self._program(key, fn)
+        g.replay()
+        return self.logits
 
-    def run_greedy_on_device(self) -> None:
-        """One step; the arg max becomes the next input and positions move on, all on the device."""
-        self.runner.cache.flush()
-        if not self._greedy_ready:
-            keep = self._dev.clone()
-            self._graph_greedy, _ = self._capture(self._forward_greedy)
-            self._dev.copy_(keep)            # undo the warm-up run's move to the next position
-            self._greedy_ready = True
-        if self._graph_greedy is not None:
-            self._graph_greedy.replay()
-        else:
-            self._forward_greedy()
+    def run_step(self) -> torch.Tensor:
+        """One step on the tokens that `upload` brought.  Returns float32 logits [live sequences,
+        vocab] (a view of a static buffer when graphs are on: use it before the next run)."""
+        return self._run(("step",), self._forward_step)[: self.n_live]
+
+    def run_generate(self, params: SamplingParams) -> None:
+        """One step whose input tokens are the ones sampled last; the new ones are sampled on the
+        device (`self.sampled`) and go into the slots' records."""
+        key = ("generate", params.temp, params.top_k, params.top_p, params.rep_penalty, params.repeat_last_n)
+        self._run(key, lambda: self._forward_generate(params))
+
+    def sample_logits(self, logits: torch.Tensor, params: SamplingParams) -> None:
+        """Sample from logits [live rows, vocab] of a step that ran elsewhere (the sequences' first
+        step), with the records' generators and recent tokens, as run_generate does after its own step."""
+        n = logits.shape[0]
+        penal = params.rep_penalty != 1.0 and params.repeat_last_n > 0
+        recent = None
+        if penal:
+            recent = torch.empty((self.b, params.repeat_last_n), dtype=torch.int32, device=logits.device)
+        flags = (ops.BEGIN_UNIFORM if params.temp > 0.0 else 0) | (ops.BEGIN_RECENT if penal else 0)
+        c = self.runner.cache
+        if flags:
+            ops.slot_begin(c.record, c.recent, self.slot, self.meta, self.b, flags, self.tokens, self.pos, self.after,
+                           self.seq, self.cu, self.uniforms if flags & ops.BEGIN_UNIFORM else None, recent,
+                           self.recent_len if recent is not None else None)
+        sample_into(logits, self.sampled[:n], params, self.uniforms[:n], recent[:n] if penal else None,
+                    self.recent_len[:n])
+        ops.slot_end(c.record, c.recent, self.slot, self.meta, self.b, self.sampled)
+
+    # ---- sampled tokens to the host, without waiting --------------------------------------------
+    def fetch_start(self):
+        """Start copying the tokens just sampled to the host; hand the result to fetch_read later."""
+        turn = self._fetch_turn
+        self._fetch_turn = (turn + 1) % len(self._fetch_hosts)
+        host = self._fetch_hosts[turn]
+        host[: self.b].copy_(self.sampled, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return host, ev, self.n_live
+
+    @staticmethod
+    def fetch_read(handle) -> List[int]:
+        host, ev, n = handle
+        ev.synchronize()
+        return host[:n].tolist()
+
+
+def sample_into(logits: torch.Tensor, out: torch.Tensor, p: SamplingParams, uniforms, recent, recent_len) -> None:
+    """The sampler's rule (src/lib.rs:91-172) on device data: arg max when temp <= 0, else
+    temperature, top-k, top-p and the draw `uniforms`; the repetition penalty over `recent` if given."""
+    pen = p.rep_penalty if recent is not None else 1.0
+    if p.temp <= 0.0:
+        ops.argmax(logits, out, pen, recent, recent_len if recent is not None else None)
+    else:
+        ops.sample(logits, uniforms, out, p.temp, p.top_k, p.top_p, pen, recent,
+                   recent_len if recent is not None else None)
 
 
 # ---- short prompts ---------------------------------------------------------------------------
@@ -266,19 +345,28 @@ class PromptSession:
     def _forward(self) -> torch.Tensor:
         r = self.runner
         x = r.model.hidden(self._info(), r.cache)
+        ops.slot_set_pos(r.cache.record, self.slot, self.after, self.cu, self.q)    # the records learn the new lengths
         return r.model.logits(x, self.rows)
 
     def run(self) -> torch.Tensor:
         """The step on what `feed` put in: float32 logits [real sequences, vocab] at each one's last
         token (a view of a static buffer when graphs are on: use it before the next run)."""
         self.runner.cache.flush()
-        if not self._ready:
-            self._graph, self.logits = DecodeSession._capture(self, self._forward)
-            self._ready = True
-            if self._graph is None:
-                return self.logits[: self.n_live]
-        if self._graph is not None:
-            self._graph.replay()
-        else:
+        if not self.use_graph:
             self.logits = self._forward()
+            return self.logits[: self.n_live]
+        if not self._ready:
+            self.logits = self._forward()       # first-use set-up of kernels must not happen inside a capture
+            torch.cuda.synchronize()
+            self._graph = torch.cuda.CUDAGraph()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(self._graph, capture_error_mode="thread_local"):
+                    self.logits = self._forward()
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            self._ready = True
+        self._graph.replay()
         return self.logits[: self.n_live]

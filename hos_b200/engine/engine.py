@@ -9,33 +9,61 @@ from __future__ import annotations
 
 import math
 import time
-from typing import Optional, Sequence, Tuple, Union
+from typing import List, Optional, Sequence, Tuple, Union
 
 import torch
 
 from ..config.base import ModelConfig
 from ..errors import HosError
-from ..sampling import Sampler, SamplingParams
+from ..sampling import SamplingParams, stream_seed
 from . import generate as gen
 from .runner import Runner
 
 Prompt = Union[Sequence[int], Sequence[Sequence[int]]]
 
 
-class _LoopBackend:
-    """What the generation loop drives: the runner, with logits handed over without a copy
-    (the loop samples from them before the next step overwrites them)."""
+class _DeviceBackend:
+    """What the generation loop drives: the runner's step function for each sequence's first
+    step, then record-driven single-token steps with sampling on the device.  Tokens come back
+    through pinned buffers, fetched in the order in which they were sampled."""
 
-    def __init__(self, runner: Runner):
+    def __init__(self, runner: Runner, params: SamplingParams):
         self.runner = runner
-        self.admit, self.release = runner.admit, runner.release
+        self.params = params
+        self.admit, self.release, self.length = runner.admit, runner.release, runner.length
+        self._queue: List[object] = []
+        self._stops: Sequence[int] = ()
 
     @property
     def max_seq_len(self) -> int:
         return self.runner.max_seq_len
 
-    def step(self, slots, token_lists):
-        return self.runner.step(slots, token_lists, copy=False)
+    def begin(self, slots, token_lists, indices, max_new, stop_ids) -> None:
+        r, p = self.runner, self.params
+        self._stops = tuple(stop_ids)
+        logits = r.step(slots, token_lists, copy=False)
+        # each sequence's generator starts from seed + index (src/lib.rs:404-407), the recent tokens are none
+        r.write_records(slots, rng=[stream_seed(p.seed, i) for i in indices], limit=[max_new] * len(slots),
+                        restart=True)
+        sess = r.decode_session(len(slots))
+        sess.upload(slots, stop_ids=self._stops)
+        sess.sample_logits(logits, p)
+        self._queue.append(sess.fetch_start())
+
+    def advance(self, slots) -> None:
+        r = self.runner
+        r.cache.extend_all(slots, [r.cache.lengths[s] + 1 for s in slots])
+        sess = r.decode_session(len(slots))
+        sess.upload(slots, stop_ids=self._stops)
+        sess.run_generate(self.params)
+        self._queue.append(sess.fetch_start())
+
+    def fetch(self) -> List[int]:
+        from .decode import DecodeSession
+        return DecodeSession.fetch_read(self._queue.pop(0))
+
+    def settle(self, slots, lengths) -> None:
+        self.runner.write_records(slots, pos=lengths)
 
 
 def _is_batch(prompt) -> bool:
@@ -108,10 +136,46 @@ class Engine:
         batch = _is_batch(prompt)
         prompts = [list(p) for p in prompt] if batch else [list(prompt)]
         stops = self.stop_ids if stop_ids is None else tuple(stop_ids)
-        outs = gen.generate(_LoopBackend(self.runner), lambda: Sampler(params, self.runner.device), prompts,
-                            max_tokens, stops, self.runner.cache.tokens_capacity(), self.max_batch,
-                            on_token)
+        outs = gen.generate(_DeviceBackend(self.runner, params), prompts, max_tokens, stops,
+                            self.runner.cache.tokens_capacity(), self.max_batch, on_token)
         return outs if batch else outs[0]
+
+    # ---- sequences that stay: a second turn continues where the first ended --------------------
+    def open(self, n: int = 1) -> List["Conversation"]:
+        """n sequences that keep their slots between calls (`generate_from_ids` continues them,
+        `Conversation.reset` starts one afresh, `Conversation.close` gives its slot back)."""
+        return [Conversation(self, s) for s in self.runner.admit(n)]
+
+    def generate_from_ids(self, conversations: Sequence["Conversation"], ids: Sequence[Sequence[int]],
+                          max_tokens: int = 128, temp: float = 0.0, top_k: int = 40, top_p: float = 0.95,
+                          rep_penalty: float = 1.1, repeat_last_n: int = 64, seed: int = 42,
+                          stop_ids: Optional[Sequence[int]] = None, on_token=None) -> List[List[int]]:
+        """Feed `ids[i]` to conversation i on top of what it holds and generate, all conversations
+        side by side (src/lib.rs:499-503: continues from the current position, does not reset; the
+        caller owns the prompt).  Long prompts are fed in pieces by the step function.  A token that
+        the last call returned last is fed first (it was sampled but never run)."""
+        params = SamplingParams(temp, top_k, top_p, rep_penalty, repeat_last_n, seed)
+        stops = self.stop_ids if stop_ids is None else tuple(stop_ids)
+        if len(conversations) != len(ids):
+            raise HosError("generate_from_ids: one list of ids per conversation is needed")
+        prompts = []
+        for c, new in zip(conversations, ids):
+            c._check_open()
+            p = ([c.pending] if c.pending is not None else []) + [int(t) for t in new]
+            if not p:
+                raise HosError("generate_from_ids: a conversation brings no token")
+            if self.runner.length(c.slot) + len(p) > self.runner.max_seq_len:
+                raise HosError(f"generate_from_ids: {self.runner.length(c.slot)} tokens held and {len(p)} more are "
+                               f"more than the context holds ({self.runner.max_seq_len})")
+            prompts.append(p)
+        outs = gen.run_batch(_DeviceBackend(self.runner, params), prompts, list(range(len(prompts))), max_tokens,
+                             stops, on_token, slots=[c.slot for c in conversations])
+        for c, p, o in zip(conversations, prompts, outs):
+            # the last returned token has been sampled but not run, unless the context is full
+            fed = self.runner.length(c.slot) - c.position - len(p)
+            c.position = self.runner.length(c.slot)
+            c.pending = o[-1] if o and fed < len(o) else None
+        return outs
 
     # ---- the step function, for callers that drive it themselves ------------------------
     def step(self, slots, token_lists, want=None, copy: bool = True) -> torch.Tensor:
@@ -152,40 +216,64 @@ class Engine:
         r = self.runner
         prompts = [list(p) for p in prompt] if _is_batch(prompt) else [list(prompt)]
         n_prompt = sum(len(p) for p in prompts)
-        sampler = Sampler(SamplingParams.pure(), r.device)
         slots = r.admit(len(prompts))
-        r.step(slots, prompts)
+        r.step(slots, prompts)                      # the warm-up
         for s in slots:
             r.release(s)
-        slots = r.admit(len(prompts))
-        for i, s in enumerate(slots):
-            sampler.open(s, i)
-        live = list(slots)
-        try:
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            logits = r.step(live, prompts)
-            torch.cuda.synchronize()
-            prefill_secs = time.perf_counter() - t0
-            produced = 0
-            t1 = time.perf_counter()
-            for _ in range(decode_tokens):
-                toks = sampler.sample(logits, live)
-                keep = [i for i, (s, t) in enumerate(zip(live, toks))
-                        if t not in self.stop_ids and r.length(s) < r.max_seq_len]
-                if not keep:
-                    break
-                live, toks = [live[i] for i in keep], [toks[i] for i in keep]
-                logits = r.step(live, [[t] for t in toks])
-                produced += len(live)
-            torch.cuda.synchronize()
-            decode_secs = time.perf_counter() - t1
-        finally:
-            for s in slots:
-                sampler.close(s)
-                r.release(s)
+        backend = _DeviceBackend(r, SamplingParams.pure())
+        times = {}
+
+        class Timed:                                # the loop's backend, with a clock around the first step
+            max_seq_len = r.max_seq_len
+            admit, release, length, advance, fetch, settle = (backend.admit, backend.release, backend.length,
+                                                              backend.advance, backend.fetch, backend.settle)
+
+            @staticmethod
+            def begin(*a):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                backend.begin(*a)
+                torch.cuda.synchronize()
+                times["prefill"] = time.perf_counter() - t0
+                times["t1"] = time.perf_counter()
+
+        # one more token than asked for: the first one belongs to the prompt step
+        outs = gen.run_batch(Timed, prompts, list(range(len(prompts))), decode_tokens + 1, self.stop_ids)
+        torch.cuda.synchronize()
+        decode_secs = time.perf_counter() - times["t1"]
+        produced = sum(max(0, len(o) - 1) for o in outs)
+        prefill_secs = times["prefill"]
         return (n_prompt, prefill_secs, n_prompt / max(prefill_secs, 1e-9),
                 produced, decode_secs, produced / max(decode_secs, 1e-9))
 
     def vocab_size(self) -> int:
         return self.runner.vocab_size
+
+
+class Conversation:
+    """One sequence that keeps its slot, its keys and values and its position between calls of
+    `Engine.generate_from_ids` (the reference's engine is one such sequence: src/lib.rs:175-184,
+    `reset` :489-492)."""
+
+    def __init__(self, engine: Engine, slot: int):
+        self.engine = engine
+        self.slot: Optional[int] = slot
+        self.position = 0                       # tokens in the cache
+        self.pending: Optional[int] = None      # a returned token that has not been run yet
+
+    def _check_open(self) -> None:
+        if self.slot is None:
+            raise HosError("this conversation is closed")
+
+    def reset(self) -> None:
+        """Forget everything: the next call starts at position 0 (pages go back, the slot stays)."""
+        self._check_open()
+        r = self.engine.runner
+        r.release(self.slot)
+        new = r.admit(1)[0]
+        self.slot, self.position, self.pending = new, 0, None
+
+    def close(self) -> None:
+        if self.slot is not None:
+            self.engine.runner.release(self.slot)
+            self.slot = None

@@ -9,11 +9,20 @@ it then leaves the batch, and its slot goes back to the cache, where a later
 batch uses it again.  Unlike the reference's loop (src/lib.rs:443-445) no forward
 pass is run for a token after which nothing is sampled.
 
-The loop talks to a `backend` with four methods, so that its decisions can be
-tested without a GPU:
-    admit(n) -> slots;  step(slots, token_lists) -> logits handle;
-    release(slot);      max_seq_len (attribute)
-and to a sampler with open(key, index), sample(logits, keys) -> tokens, close(key).
+The loop never waits for a token before it launches the next step: sampled tokens
+stay on the device (the next step reads them from the slots' records) and reach
+the host one step late.  So a sequence that samples a stop token takes part in
+one more step, whose token is dropped, as the reference drops its last forward.
+What the host can tell without the tokens (a sequence has all the tokens it may
+have, its context is full) it tells at once.
+
+The loop talks to a `backend`, so that its decisions can be tested without a GPU:
+    admit(n) -> slots;  release(slot);  length(slot);  max_seq_len (attribute)
+    begin(slots, token_lists, indices, max_new, stop_ids)   the first step of each sequence (its prompt,
+                       on top of whatever the slot holds) and the first sampling, not waited for
+    advance(slots)     one more step, fed with the tokens sampled last, and its sampling
+    fetch() -> tokens  of the oldest sampling not yet fetched, in the order of its slots
+    settle(slots, ns)  the sequences hold ns tokens (a step that ran for nothing is forgotten)
 """
 from __future__ import annotations
 
@@ -54,66 +63,78 @@ def plan_batches(prompt_lens: Sequence[int], max_new: int, capacity_tokens: int,
     return batches
 
 
-def run_batch(backend, sampler, prompts: Sequence[Sequence[int]], indices: Sequence[int],
+def run_batch(backend, prompts: Sequence[Sequence[int]], indices: Sequence[int],
               max_new: int, stop_ids: Sequence[int],
-              on_token: Optional[Callable[[int, int], None]] = None) -> List[List[int]]:
-    """Generate for one batch.  Returns the new tokens of each request of `indices`."""
+              on_token: Optional[Callable[[int, int], None]] = None,
+              slots: Optional[Sequence[int]] = None) -> List[List[int]]:
+    """Generate for one batch.  Returns the new tokens of each request of `indices`.  With `slots`
+    the sequences live in those slots already (their prompts continue what the slots hold) and
+    keep them afterwards; otherwise slots are taken and given back here."""
     stop = set(int(s) for s in stop_ids)
     n = len(indices)
     out: List[List[int]] = [[] for _ in range(n)]
     if max_new <= 0:
         return out
-    slots = backend.admit(n)
-    live = list(range(n))                      # positions in `indices` still generating
-    lengths = [len(prompts[i]) for i in indices]
-    for j, i in enumerate(indices):
-        sampler.open(slots[j], i)
+    own = slots is None
+    slots = list(backend.admit(n)) if own else list(slots)
+    held = [True] * n
+
+    def finish(j: int) -> None:
+        if own and held[j]:
+            backend.release(slots[j])
+        held[j] = False
+
     try:
-        logits = backend.step([slots[j] for j in live], [list(prompts[indices[j]]) for j in live])
-        while live:
-            toks = sampler.sample(logits, [slots[j] for j in live])
-            still, feed = [], []
-            for j, t in zip(live, toks):
+        lengths = [backend.length(slots[j]) + len(prompts[indices[j]]) for j in range(n)]
+        backend.begin(slots, [list(prompts[i]) for i in indices], list(indices), max_new, sorted(stop))
+        launched = list(range(n))          # the sequences of the sampling that is fetched next
+        alive = set(launched)
+        k = 0                              # how many samplings have been fetched
+        while launched:
+            # who goes on, as far as that can be told without the tokens of sampling k
+            cand = [j for j in launched if j in alive and k + 1 < max_new and lengths[j] < backend.max_seq_len]
+            if cand:
+                backend.advance([slots[j] for j in cand])
+                for j in cand:
+                    lengths[j] += 1
+            going = set(cand)
+            toks = backend.fetch()
+            for j, t in zip(launched, toks):
+                if j not in alive:
+                    continue                               # it had ended: this token came from a step run for nothing
                 if t in stop:
-                    continue                               # ends; the stop token is not returned
+                    alive.discard(j)                       # ends; the stop token is not returned
+                    if j in going:
+                        lengths[j] -= 1                    # the step that is under way feeds it for nothing
+                    finish(j)
+                    continue
                 out[j].append(t)
                 if on_token is not None:
                     on_token(indices[j], t)
-                if len(out[j]) >= max_new:
-                    continue                               # has all it may have
-                if lengths[j] >= backend.max_seq_len:
-                    continue                               # the context is full
-                still.append(j)
-                feed.append([t])
-            for j in live:
-                if j not in still:
-                    sampler.close(slots[j])
-                    backend.release(slots[j])
-                    slots[j] = -1
-            live = still
-            if not live:
-                break
-            logits = backend.step([slots[j] for j in live], feed)
-            for j in live:
-                lengths[j] += 1
+                if j not in going:                         # has all it may have, or the context is full
+                    alive.discard(j)
+                    finish(j)
+            launched = cand
+            k += 1
+        if not own:
+            backend.settle(slots, lengths)
     finally:
-        for j in range(n):
-            if slots[j] >= 0:
-                sampler.close(slots[j])
-                backend.release(slots[j])
+        if own:
+            for j in range(n):
+                if held[j]:
+                    backend.release(slots[j])
     return out
 
 
-def generate(backend, make_sampler: Callable[[], object], prompts: Sequence[Sequence[int]],
+def generate(backend, prompts: Sequence[Sequence[int]],
              max_new: int, stop_ids: Sequence[int], capacity_tokens: int, max_batch: int,
              on_token: Optional[Callable[[int, int], None]] = None) -> List[List[int]]:
     """As many batches one after another as the requests need."""
     batches = plan_batches([len(p) for p in prompts], max_new, capacity_tokens, max_batch,
                            backend.max_seq_len)
     results: List[List[int]] = [[] for _ in prompts]
-    sampler = make_sampler()
     for batch in batches:
-        outs = run_batch(backend, sampler, prompts, batch, max_new, stop_ids, on_token)
+        outs = run_batch(backend, prompts, batch, max_new, stop_ids, on_token)
         for i, o in zip(batch, outs):
             results[i] = o
     return results

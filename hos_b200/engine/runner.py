@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager
@@ -122,15 +123,11 @@ class Runner:
         last_only = all(len(w) == 1 and w[0] == len(t) - 1 for w, t in zip(want, token_lists))
         if single and not from_zero and last_only and self.use_sessions:
             # decoding: static buffers and a captured graph, one per batch-size bucket
-            from .decode import DecodeSession, bucket_for
             self._check_ids(token_lists)
             self.cache.extend_all(slots, [st + 1 for st in starts])
-            bucket = bucket_for(len(slots))
-            sess = self._sessions.get(bucket)
-            if sess is None:
-                sess = self._sessions[bucket] = DecodeSession(self, bucket)
-            sess.feed(slots, [t[0] for t in token_lists], starts)
-            out = sess.run()
+            sess = self.decode_session(len(slots))
+            sess.upload(slots, [t[0] for t in token_lists])
+            out = sess.run_step()
             return out.clone() if copy else out
         if from_zero and last_only and self.use_sessions and self.prompt_sessions:
             # a short prompt step: static buffers and a captured graph per capacity, as for decoding
@@ -146,6 +143,53 @@ class Runner:
                 out = sess.run()
                 return out.clone() if copy else out
         return self._general(slots, starts, token_lists, want)
+
+    def decode_session(self, n: int):
+        """The session that runs single-token steps of n sequences (one per batch-size bucket)."""
+        from .decode import DecodeSession, bucket_for
+        bucket = bucket_for(n)
+        sess = self._sessions.get(bucket)
+        if sess is None:
+            sess = self._sessions[bucket] = DecodeSession(self, bucket)
+        return sess
+
+    def write_records(self, slots: Sequence[int], pos=None, last=None, rng=None, limit=None,
+                      restart: bool = False) -> None:
+        """Words of the slots' device records (csrc/slot_state.cu) set from the host: `pos` (with it the
+        host's own count of the sequence's tokens; pages are the caller's business), `last` (the token a
+        record-driven step feeds next), `rng` (generator states, 64-bit), `limit` (most tokens to sample);
+        `restart` clears the finished flag and the count of sampled tokens, and with it the recent tokens."""
+        n = len(slots)
+        vals = np.zeros((n, ops.SLOT_WORDS), dtype=np.int64)
+        mask = 0
+        if pos is not None:
+            vals[:, ops.SLOT_POS] = pos
+            mask |= 1 << ops.SLOT_POS
+            for s, p in zip(slots, pos):
+                if s not in self.cache.lengths:
+                    self._no_slot(s)
+                self.cache.lengths[s] = int(p)
+        if last is not None:
+            vals[:, ops.SLOT_LAST] = last
+            mask |= 1 << ops.SLOT_LAST
+        if rng is not None:
+            r = np.asarray([int(x) & ((1 << 64) - 1) for x in rng], dtype=np.uint64)
+            vals[:, ops.SLOT_RNG_LO] = (r & np.uint64(0xffffffff)).astype(np.int64)
+            vals[:, ops.SLOT_RNG_HI] = (r >> np.uint64(32)).astype(np.int64)
+            mask |= (1 << ops.SLOT_RNG_LO) | (1 << ops.SLOT_RNG_HI)
+        if limit is not None:
+            vals[:, ops.SLOT_LIMIT] = limit
+            mask |= 1 << ops.SLOT_LIMIT
+        if restart:
+            mask |= (1 << ops.SLOT_FLAGS) | (1 << ops.SLOT_COUNT)
+        if not mask or n == 0:
+            return
+        host = np.concatenate([(vals & 0xffffffff).astype(np.uint32).view(np.int32).reshape(-1),
+                               np.asarray(slots, dtype=np.int32)])
+        staged = torch.empty(host.shape[0], dtype=torch.int32, pin_memory=True)
+        staged.copy_(torch.from_numpy(host))
+        dev = staged.to(self.device, non_blocking=True)
+        ops.slot_write(self.cache.record, dev[n * ops.SLOT_WORDS:], dev[:n * ops.SLOT_WORDS].view(n, ops.SLOT_WORDS), mask)
 
     def _check_ids(self, token_lists) -> None:
         for toks in token_lists:
@@ -218,34 +262,41 @@ class Runner:
         # a step of many tokens: its kernels are long enough for the next one's set-up to hide under them
         ops.set_launch_ahead(info.n_tokens >= LAUNCH_AHEAD_MIN_TOKENS)
         try:
-            return self.model.hidden(info, self.cache), rows_t
+            x = self.model.hidden(info, self.cache)
+            # the slots' records learn the new lengths (single-token steps take positions from them)
+            ops.slot_set_pos(self.cache.record, info.seq_slot, info.seq_len_after, info.cu_seqlens, info.n_seqs)
+            return x, rows_t
         finally:
             ops.set_launch_ahead(False)
 
     def decode_steps_timed(self, slots, first_tokens, warmup: int, steps: int, clocks=None):
         """`warmup` untimed and `steps` timed greedy decode steps, issued back to back with
-        the chosen tokens staying on the device; timed with CUDA events.  Returns
+        the chosen tokens staying on the device (the records); timed with CUDA events.  Returns
         (milliseconds per step, kernel-launching calls in the timed region)."""
-        from .decode import DecodeSession
+        from ..sampling.sampler import SamplingParams
         lengths = [self.cache.lengths[s] for s in slots]
+        self.cache.extend_all(slots, [n + warmup + steps for n in lengths])     # pages for every position written
         for s, n in zip(slots, lengths):
-            self.cache.extend(s, n + warmup + steps)        # pages for every position written
-        from .decode import bucket_for
-        sess = DecodeSession(self, bucket_for(len(slots)))
-        sess.feed(slots, [t[0] for t in first_tokens], lengths)
+            self.cache.lengths[s] = n
+        self.write_records(slots, pos=lengths, last=[t[0] for t in first_tokens], limit=[0] * len(slots), restart=True)
+        sess = self.decode_session(len(slots))
+        sess.upload(slots)
+        greedy = SamplingParams.pure()
         for _ in range(warmup):
-            sess.run_greedy_on_device()
+            sess.run_generate(greedy)
         torch.cuda.synchronize()
         if clocks is not None:
             clocks.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            sess.run_greedy_on_device()
+            sess.run_generate(greedy)
         e1.record()
         torch.cuda.synchronize()
         if clocks is not None:
             clocks.result = clocks.stop()
+        for s, n in zip(slots, lengths):
+            self.cache.lengths[s] = n + warmup + steps
         return e0.elapsed_time(e1) / steps, sess.launches_per_step * steps
 
     @property

@@ -382,6 +382,39 @@ def sample(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor, temp
                 int(top_k), float(top_p), float(rep_penalty), _ptr(out), _stream())
 
 
+# ---- the per-slot record (csrc/slot_state.cu) ----------------------------------------------
+SLOT_WORDS, RECENT_MAX, MAX_STOPS = 8, 256, 16
+SLOT_POS, SLOT_LAST, SLOT_FLAGS, SLOT_COUNT, SLOT_RNG_LO, SLOT_RNG_HI, SLOT_LIMIT = range(7)
+BEGIN_ADVANCE, BEGIN_TOKEN_FROM_RECORD, BEGIN_UNIFORM, BEGIN_RECENT, BEGIN_SKIP_FINISHED = 1, 2, 4, 8, 16
+
+
+def slot_begin(record, ring, slots, meta, b: int, flags: int, tokens, pos, after, seq, cu, uniforms=None,
+               recent=None, recent_len=None) -> None:
+    """The start of a single-token step of up to b rows (meta[0] of them live): row i belongs to slot
+    slots[i]; positions come from the record and move on by one; the input token comes from the
+    record (or stays the caller's); for sampling, the next draw of each sequence's generator and its
+    recent tokens."""
+    core().call("hos_slot_begin", _ptr(record), _ptr(ring), _ptr(slots), _ptr(meta), int(b), int(flags), _ptr(tokens),
+                _ptr(pos), _ptr(after), _ptr(seq), _ptr(cu), _ptr(uniforms), _ptr(recent), _ptr(recent_len),
+                recent.shape[1] if recent is not None else 0, _stream())
+
+
+def slot_end(record, ring, slots, meta, b: int, sampled) -> None:
+    """After sampling: the tokens go into the records (last token, recent tokens, count, finished)."""
+    core().call("hos_slot_end", _ptr(record), _ptr(ring), _ptr(slots), _ptr(meta), int(b), _ptr(sampled), _stream())
+
+
+def slot_set_pos(record, seq_slot, seq_len_after, cu_seqlens, n_seqs: int) -> None:
+    core().call("hos_slot_set_pos", _ptr(record), _ptr(seq_slot), _ptr(seq_len_after), _ptr(cu_seqlens), int(n_seqs),
+                _stream())
+
+
+def slot_write(record, slots, values, word_mask: int) -> None:
+    """record[slots[i]][w] = values[i][w] for the words w whose bit is set in word_mask."""
+    _check(values, "record values", torch.int32, 2)
+    core().call("hos_slot_write", _ptr(record), _ptr(slots), _ptr(values), int(word_mask), values.shape[0], _stream())
+
+
 def decode_advance(tokens, token_pos, seq_len_after, token_seq, sampled) -> None:
     core().call("hos_decode_advance", _ptr(tokens), _ptr(token_pos), _ptr(seq_len_after), _ptr(token_seq),
                 _ptr(sampled), tokens.shape[0], _stream())

@@ -15,6 +15,7 @@ from typing import Dict, List, Sequence
 import torch
 
 from .. import ops
+from ..errors import HosError
 
 _MASK64 = (1 << 64) - 1
 
@@ -28,6 +29,12 @@ class SamplingParams:
     rep_penalty: float = 1.1      # 1: off
     repeat_last_n: int = 64
     seed: int = 42
+
+    def __post_init__(self):
+        # the penalty looks at the last repeat_last_n sampled tokens; a sequence's record keeps 256 of them
+        if self.rep_penalty != 1.0 and self.repeat_last_n > ops.RECENT_MAX:
+            raise HosError(f"repeat_last_n = {self.repeat_last_n} is more than the {ops.RECENT_MAX} recent tokens "
+                           f"that are kept per sequence; use at most {ops.RECENT_MAX} (or rep_penalty = 1)")
 
     @staticmethod
     def pure(temp: float = 0.0, seed: int = 42) -> "SamplingParams":
@@ -81,7 +88,7 @@ class Sampler:
         penal = p.rep_penalty != 1.0 and p.repeat_last_n > 0
         recent_t = recent_len = None
         if penal:
-            n = min(p.repeat_last_n, 256)
+            n = p.repeat_last_n
             rows, lens = [], []
             for k in keys:
                 r = self._recent[k][-n:]

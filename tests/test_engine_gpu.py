@@ -185,6 +185,82 @@ def test_sampling_through_the_entry_point_follows_the_reference_rule(tmp_path):
     assert len({tuple(o) for o in outs}) == 2
 
 
+def test_single_token_steps_take_their_position_from_the_device_record(tmp_path):
+    """The host's count of a sequence's tokens hands out pages; the position a single-token step
+    runs at is the one in the slot's record on the device.  Set the record back by five tokens
+    behind the host's back: the next step's logits are those of the shorter sequence."""
+    from hos_b200 import ops
+    folder = make_folder(tmp_path, "B")
+    w, cfg = plain_model(folder)
+    r = runner_for(folder, "float32")
+    ids = random_tokens(random.Random(3), 30, 512)
+    a, b = r.admit(2)
+    r.step([a, b], [ids[:24], ids[:9]])
+    dev = r.device
+    vals = torch.zeros((1, ops.SLOT_WORDS), dtype=torch.int32, device=dev)
+    vals[0, ops.SLOT_POS] = 19
+    ops.slot_write(r.cache.record, torch.tensor([a], dtype=torch.int32, device=dev), vals, 1 << ops.SLOT_POS)
+    assert r.length(a) == 24                                    # the host still counts 24
+    got = r.step([a, b], [[ids[25]], [ids[9]]])
+    want_a = P.forward_logits(w, cfg, ids[:19] + [ids[25]])[-1]
+    want_b = P.forward_logits(w, cfg, ids[:10])[-1]
+    assert_close(got, torch.stack([want_a, want_b]), "float32", "record-driven step")
+    rec = r.cache.record.cpu()
+    assert int(rec[a, ops.SLOT_POS]) == 20 and int(rec[b, ops.SLOT_POS]) == 10
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_conversations_continue_where_they_ended(tmp_path, dtype):
+    """Turns on sequences that keep their slots (Engine.generate_from_ids): a turn that ends with
+    all its tokens, a turn that ends at a stop token (one step had run for nothing by then), a long
+    second prompt that the step function feeds in pieces; against the plain implementation run on
+    the whole history each time."""
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, "D")
+    w, cfg = plain_model(folder)
+    eng = Engine(folder, dtype=dtype, max_batch=4)
+    rng = random.Random(8)
+    c1, c2 = eng.open(2)
+    hist = [random_tokens(rng, 20, 1000), random_tokens(rng, 3, 1000)]
+    first = eng.generate_from_ids([c1, c2], hist, max_tokens=6, temp=0.0, rep_penalty=1.0, stop_ids=[])
+    want = [P.greedy_generate(w, cfg, h, 6) for h in hist]
+    if dtype == "float32":
+        assert first == want
+    hist = [h + o for h, o in zip(hist, first)]
+    assert c1.pending == first[0][-1] and c1.position == 20 + 5
+    # second turn: a long prompt for one (more than a ring of the window layers has room for in one
+    # pass: 70 keys of window in 2 + 8 pages... the step function decides), a short one for the other;
+    # the second conversation stops at a token it would sample third
+    turn = [random_tokens(rng, 700, 1000), random_tokens(rng, 2, 1000)]
+    probe = P.greedy_generate(w, cfg, hist[1] + turn[1], 5)
+    stop = probe[2]
+    second = eng.generate_from_ids([c1, c2], turn, max_tokens=5, temp=0.0, rep_penalty=1.0, stop_ids=[stop])
+    want = [P.greedy_generate(w, cfg, h + t, 5, stop_ids=[stop]) for h, t in zip(hist, turn)]
+    if dtype == "float32":
+        assert second == want and len(second[1]) == probe.index(stop)
+    hist = [h + t + o for h, t, o in zip(hist, turn, second)]
+    # after a stop token the conversation holds its history and nothing else
+    if len(second[1]) < 5 and dtype == "float32":
+        assert c2.pending is None and c2.position == len(hist[1])
+    # third turn on the second conversation alone; the first is reset and starts afresh
+    third = eng.generate_from_ids([c2], [[7, 8, 9]], max_tokens=4, temp=0.0, rep_penalty=1.0, stop_ids=[])
+    if dtype == "float32":
+        assert third == [P.greedy_generate(w, cfg, hist[1] + [7, 8, 9], 4)]
+    else:
+        seq = hist[1] + [7, 8, 9]
+        for t in third[0]:                                       # bfloat16: each choice is (almost) the best one
+            l = P.forward_logits(w, cfg, seq)[-1]
+            assert float(l.max() - l[t]) < 0.1
+            seq.append(t)
+    c1.reset()
+    again = eng.generate_from_ids([c1], [hist[0][:20]], max_tokens=6, temp=0.0, rep_penalty=1.0, stop_ids=[])
+    assert again == [first[0]]
+    c1.close()
+    c2.close()
+    eng.runner.cache.check()
+    assert eng.runner.cache.slots.n_held == 0
+
+
 def test_perplexity_and_bench(tmp_path):
     from hos_b200 import Engine
     folder = make_folder(tmp_path, "B")

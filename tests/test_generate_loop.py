@@ -7,14 +7,19 @@ from hos_b200.sampling import SamplingParams, next_rand, stream_seed
 
 
 class FakeBackend:
-    """`step` returns, per sequence, the list of tokens it has seen so far."""
+    """The loop's backend without a GPU.  The next token of a sequence is (sum of the tokens it has
+    been fed) % 50.  Like the device backend, it samples at once but hands the tokens over only
+    when asked (`fetch`), so the loop must decide who goes on before it knows them."""
 
     def __init__(self, n_slots=8, max_seq_len=1000):
         self.free = list(range(n_slots))
         self.seen = {}
+        self.last = {}
         self.max_seq_len = max_seq_len
-        self.steps = []
+        self.steps = []                    # (slots, token lists) of every step
         self.taken_log = []
+        self.queue = []
+        self.settled = {}
 
     def admit(self, n):
         assert n <= len(self.free)
@@ -24,36 +29,39 @@ class FakeBackend:
         self.taken_log.append(list(out))
         return out
 
-    def step(self, slots, token_lists):
+    def length(self, slot):
+        return len(self.seen[slot])
+
+    def _step(self, slots, token_lists):
         self.steps.append((list(slots), [list(t) for t in token_lists]))
-        if len(self.steps) > 1 and any(len(self.seen[s]) for s in slots):
-            assert all(len(t) == 1 for t in token_lists)          # decode steps bring one token
+        toks = []
         for s, t in zip(slots, token_lists):
+            assert len(self.seen[s]) + len(t) <= self.max_seq_len, "a step past the context's end"
             self.seen[s].extend(t)
-        return [list(self.seen[s]) for s in slots]
+            self.last[s] = sum(self.seen[s]) % 50
+            toks.append(self.last[s])
+        self.queue.append(toks)
+
+    def begin(self, slots, token_lists, indices, max_new, stop_ids):
+        assert len(slots) == len(token_lists) == len(indices)
+        self._step(slots, token_lists)
+
+    def advance(self, slots):
+        assert self.queue, "a step is launched one sampling ahead at most... but never with nothing pending"
+        assert len(self.queue) <= 1, "at most one sampling may be waiting when the next step is launched"
+        self._step(slots, [[self.last[s]] for s in slots])
+
+    def fetch(self):
+        return self.queue.pop(0)
+
+    def settle(self, slots, lengths):
+        self.settled.update(zip(slots, lengths))
 
     def release(self, slot):
         assert slot in self.seen, "released twice"
         del self.seen[slot]
         self.free.append(slot)
         self.free.sort()
-
-
-class ScriptSampler:
-    """Next token = (sum of the sequence so far) % 50; deterministic, no GPU."""
-
-    def __init__(self):
-        self.open_keys = set()
-
-    def open(self, key, index):
-        self.open_keys.add(key)
-
-    def close(self, key):
-        self.open_keys.discard(key)
-
-    def sample(self, logits, keys):
-        assert len(logits) == len(keys)
-        return [sum(seq) % 50 for seq in logits]
 
 
 def reference(prompt, max_new, stop, max_len=1000):
@@ -87,7 +95,7 @@ def test_unequal_prompts_end_at_different_times_and_match_single_runs():
     prompts = [[3, 4, 5], [1], [9, 9, 9, 9, 9, 9, 2], [11, 13]]
     stop = set(range(0, 50, 4))
     b = FakeBackend()
-    outs = gen.generate(b, ScriptSampler, prompts, 12, stop, 10_000, 8)
+    outs = gen.generate(b, prompts, 12, stop, 10_000, 8)
     assert outs == [reference(p, 12, stop) for p in prompts]
     assert len({len(o) for o in outs}) > 1                 # they did end at different times
     assert b.seen == {} and b.free == list(range(8))       # every slot came back
@@ -99,21 +107,22 @@ def test_unequal_prompts_end_at_different_times_and_match_single_runs():
 
 def test_stop_token_is_not_returned_and_first_token_can_stop():
     b = FakeBackend()
-    outs = gen.generate(b, ScriptSampler, [[7]], 5, {7}, 1000, 8)      # first sampled token is 7
-    assert outs == [[]] and len(b.steps) == 1 and b.seen == {}
+    outs = gen.generate(b, [[7]], 5, {7}, 1000, 8)      # first sampled token is 7
+    # the step launched before the stop token was seen ran for nothing; no other follows
+    assert outs == [[]] and len(b.steps) == 2 and b.seen == {}
 
 
 def test_max_new_bounds_the_output_and_no_step_follows_the_last_token():
     b = FakeBackend()
-    outs = gen.generate(b, ScriptSampler, [[2, 3]], 4, set(), 1000, 8)
+    outs = gen.generate(b, [[2, 3]], 4, set(), 1000, 8)
     assert len(outs[0]) == 4
     assert len(b.steps) == 4                 # prompt + 3 single tokens; the 4th token is not fed
-    assert gen.generate(FakeBackend(), ScriptSampler, [[2, 3]], 0, set(), 1000, 8) == [[]]
+    assert gen.generate(FakeBackend(), [[2, 3]], 0, set(), 1000, 8) == [[]]
 
 
 def test_context_limit_ends_a_sequence():
     b = FakeBackend(max_seq_len=6)
-    outs = gen.generate(b, ScriptSampler, [[1, 2, 3, 4]], 50, set(), 1000, 8)
+    outs = gen.generate(b, [[1, 2, 3, 4]], 50, set(), 1000, 8)
     assert outs == [reference([1, 2, 3, 4], 50, set(), max_len=6)]
     assert len(outs[0]) == 3                 # positions 4 and 5 are fed, a third token is sampled
     assert max(len(t) for _, toks in b.steps for t in toks) == 4
@@ -122,7 +131,7 @@ def test_context_limit_ends_a_sequence():
 def test_batches_follow_one_another_and_reuse_slots():
     prompts = [[i + 1] * (i + 1) for i in range(7)]
     b = FakeBackend(n_slots=3)
-    outs = gen.generate(b, ScriptSampler, prompts, 5, {0}, 10_000, 3)
+    outs = gen.generate(b, prompts, 5, {0}, 10_000, 3)
     assert outs == [reference(p, 5, {0}) for p in prompts]
     assert b.taken_log == [[0, 1, 2], [0, 1, 2], [0]]
     assert b.seen == {}
@@ -130,14 +139,39 @@ def test_batches_follow_one_another_and_reuse_slots():
 
 def test_slots_come_back_when_a_step_fails():
     class Boom(FakeBackend):
-        def step(self, slots, token_lists):
+        def _step(self, slots, token_lists):
             if len(self.steps) == 2:
                 raise RuntimeError("boom")
-            return super().step(slots, token_lists)
+            return super()._step(slots, token_lists)
     b = Boom()
     with pytest.raises(RuntimeError):
-        gen.generate(b, ScriptSampler, [[1, 2], [3]], 9, set(), 1000, 8)
+        gen.generate(b, [[1, 2], [3]], 9, set(), 1000, 8)
     assert b.seen == {} and b.free == list(range(8))
+
+
+def test_a_stopped_sequence_runs_one_step_for_nothing_and_no_more():
+    # prompt [3]: 3, then (3+3)=6, 12, 24, 48, 96%50=46 ...; stop at 24
+    b = FakeBackend()
+    outs = gen.generate(b, [[3], [1, 1]], 10, {24}, 1000, 8)
+    assert outs[0] == [3, 6, 12] and outs[0] == reference([3], 10, {24})
+    assert outs[1] == reference([1, 1], 10, {24})
+    fed_to_first = [t for slots, toks in b.steps for s, t in zip(slots, toks) if s == 0]
+    # the prompt, the three returned tokens, and the stop token once (a step that was under way)
+    assert fed_to_first == [[3], [3], [6], [12], [24]]
+
+
+def test_sequences_that_keep_their_slots_are_settled_at_their_true_length():
+    b = FakeBackend()
+    slots = b.admit(2)
+    outs = gen.run_batch(b, [[3], [1, 1]], [0, 1], 4, {24}, slots=slots)
+    assert outs == [reference([3], 4, {24}), reference([1, 1], 4, {24})]
+    assert sorted(b.seen) == slots                       # nothing was released
+    # first: prompt + 3 tokens fed, the stop token fed for nothing is not counted;
+    # second: prompt + 3 of its 4 tokens fed (the last one was sampled but never run)
+    assert b.settled == {slots[0]: 1 + 3, slots[1]: 2 + 3}
+    # a second turn continues them
+    outs2 = gen.run_batch(b, [[5], [outs[1][-1], 7]], [0, 1], 2, set(), slots=slots)
+    assert len(outs2[0]) == 2 and len(outs2[1]) == 2
 
 
 def test_host_random_stream_matches_the_reference_generator():
