@@ -43,6 +43,16 @@ constexpr int kConsumers = 128, kDecodeThreads = 160;
 constexpr long long kWaitCycles = 1ll << 31;                        // about a second
 
 __device__ int g_decode_error = 0;     // set when a bounded wait gave up
+__device__ int* g_decode_error_host = nullptr;     // a word in pinned host memory, if the host gave one
+
+__device__ __forceinline__ void record_give_up() {
+    atomicExch(&g_decode_error, 1);
+    int* w = g_decode_error_host;
+    if (w != nullptr) {
+        atomicExch_system(w, kGiveUpAttnDecode);
+        __threadfence_system();
+    }
+}
 
 struct DecodeArgs {
     const bf16* q;
@@ -177,7 +187,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
                     bulk_g2s(dst + kTileBytes / 2, v_pages + off, kTileBytes, &full[s]);
                 }
             }
-            if (!ok) atomicExch(&g_decode_error, 1);
+            if (!ok) record_give_up();
         }
         if (a.cluster_merge) {
             // one item per CTA; the whole cluster meets twice around the merge unless its token is padding
@@ -443,7 +453,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             a.out[(size_t)n * a.out_stride + (size_t)head * HD + d] = __float2bfloat16(acc);
         }
     }
-    if (gave_up && lane == 0) atomicExch(&g_decode_error, 1);
+    if (gave_up && lane == 0) record_give_up();
 }
 
 static int sm_count() {
@@ -493,6 +503,13 @@ extern "C" int hos_attn_decode_error() {
     cudaMemcpyFromSymbol(&v, g_decode_error, sizeof(int));
     if (v) cudaMemcpyToSymbol(g_decode_error, &zero, sizeof(int));
     return v;
+}
+
+// The host's word for waits that ran out; null takes it away.
+extern "C" int hos_attn_decode_set_error_word(int* word) {
+    if (cudaMemcpyToSymbol(g_decode_error_host, &word, sizeof(word)) != cudaSuccess)
+        HOS_REFUSE("attn_decode: cannot set the error word: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
 }
 
 // How many clusters of `size` CTAs with `smem` bytes each run on the GPU at once (0: such clusters cannot be had).

@@ -58,6 +58,16 @@ constexpr long long kTcWaitCycles = 1ll << 31;
 constexpr float kRescaleSlack = 8.0f;
 
 __device__ int g_prefill_tc_error = 0;
+__device__ int* g_prefill_tc_error_host = nullptr;     // a word in pinned host memory, if the host gave one
+
+__device__ __forceinline__ void record_give_up() {
+    atomicExch(&g_prefill_tc_error, 1);
+    int* w = g_prefill_tc_error_host;
+    if (w != nullptr) {
+        atomicExch_system(w, kGiveUpAttnPrefill);
+        __threadfence_system();
+    }
+}
 
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -284,7 +294,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 for (int c = 0; c < CBLK; ++c)
                     tc_tma_2d(vd + c * kKVBlockBytes, &map_kv, a.v_col0 + kvh * THD + 64 * c, krow, &v_full[s]);
             }
-            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -328,7 +338,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 tc_commit(&v_empty[s]);       // the values of this stage have been read
                 tc_commit(&pv_done[pb]);      // this P buffer has been read, O holds tile j
             }
-            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else {
@@ -462,7 +472,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 }
             }
         }
-        if (!ok && lane == 0) atomicExch(&g_prefill_tc_error, 1);
+        if (!ok && lane == 0) record_give_up();
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -598,7 +608,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
                     tma_load_2d_pair(vd + c * kPairVBlockBytes, &map_q, a.v_col0 + kvh * THD + (THD / 2) * (int)rank + 64 * c, krow,
                                      &v_full[s]);
             }
-            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -642,7 +652,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
                 umma_commit_pair(&v_empty[s]);      // the values of this stage have been read
                 umma_commit_pair(&pv_done[pb]);     // this P buffer has been read, O holds tile j
             }
-            if (!ok) atomicExch(&g_prefill_tc_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else {
@@ -774,7 +784,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
                 }
             }
         }
-        if (!ok && lane == 0) atomicExch(&g_prefill_tc_error, 1);
+        if (!ok && lane == 0) record_give_up();
     }
     // ---- teardown: nobody of either CTA touches tensor memory or the other's barriers any more ----
     tc_fence_before_sync();
@@ -830,6 +840,15 @@ extern "C" int hos_attn_prefill_pair(int on) {
 
 // 1 if this library has the tensor-core prompt kernel (head sizes 64, 128, 256).
 extern "C" int hos_attn_prefill_tc_available() { return kHasTcPrefill ? 1 : 0; }
+
+// The host's word for waits that ran out; null takes it away.
+extern "C" int hos_attn_prefill_tc_set_error_word(int* word) {
+#if (HOS_HEAD_DIM == 64) || (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+    if (cudaMemcpyToSymbol(g_prefill_tc_error_host, &word, sizeof(word)) != cudaSuccess)
+        HOS_REFUSE("attn_prefill_tc: cannot set the error word: %s", cudaGetErrorString(cudaGetLastError()));
+#endif
+    return 0;
+}
 
 // 1 if an earlier launch gave up a bounded wait (and clears the flag).  Synchronises.
 extern "C" int hos_attn_prefill_tc_error() {

@@ -38,6 +38,13 @@ inline int check_launch(const char* what) {
     return 0;
 }
 
+// ---- bounded waits -------------------------------------------------------------------
+// Every spin on an mbarrier has a limit.  A kernel whose wait runs out sets a flag on the device,
+// writes one of these codes into a word of pinned host memory (if the host gave one: the
+// hos_*_set_error_word functions), leaves and frees what it holds.  The host looks at the word
+// after any synchronisation, at no cost, and raises an error instead of handing out the step's result.
+enum GiveUpCode : int { kGiveUpGemmTc = 1, kGiveUpAttnDecode = 2, kGiveUpAttnPrefill = 3 };
+
 // ---- programmatic dependent launch -----------------------------------------------------
 // Kernels that follow one another on a stream are launched so that the next one may be set
 // up (its CTAs placed, its prologue run) while the one before is still finishing.  Every such

@@ -40,13 +40,25 @@ constexpr long long kWaitCycles = 1ll << 31;     // about a second
 enum { kGEpiNone = 0, kGEpiSoftcap = 1, kGEpiGated = 2, kGEpiRope = 3 };
 
 __device__ int g_gemm_error = 0;
+__device__ int* g_gemm_error_host = nullptr;     // a word in pinned host memory, if the host gave one
+
+// A wait ran out: the device flag for hos_gemm_tc_error(), and the host's word, which it can look at
+// after any synchronisation without asking the device.
+__device__ __forceinline__ void record_give_up() {
+    atomicExch(&g_gemm_error, 1);
+    int* w = g_gemm_error_host;
+    if (w != nullptr) {
+        atomicExch_system(w, kGiveUpGemmTc);
+        __threadfence_system();
+    }
+}
 
 // ---- PTX wrappers ------------------------------------------------------------------------
-__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity))
-        if (clock64() - t0 > kWaitCycles) return false;
+        if (clock64() - t0 > limit) return false;
     return true;
 }
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -242,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                     }
                 }
             }
-            if (!ok) atomicExch(&g_gemm_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -273,7 +285,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                 }
                 if (ok) umma_commit(&acc_full[acc]);      // the accumulator is complete
             }
-            if (!ok) atomicExch(&g_gemm_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else {
@@ -390,7 +402,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
-        if (!ok && lane == 0) atomicExch(&g_gemm_error, 1);
+        if (!ok && lane == 0) record_give_up();
     }
     // ---- teardown: everyone is done with tensor memory ----
     tc_fence_before();
@@ -499,7 +511,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                     tma_load_2d_pair(a_dst + Cfg::kABytes, &map_w, kb * GK, w_row, &full[s]);
                 }
             }
-            if (!ok) atomicExch(&g_gemm_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -529,7 +541,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                 }
                 if (ok) umma_commit_pair(&acc_full[acc]);
             }
-            if (!ok) atomicExch(&g_gemm_error, 1);
+            if (!ok) record_give_up();
         }
         __syncwarp();
     } else {
@@ -665,7 +677,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(&acc_empty[acc]);
         }
-        if (!ok && lane == 0) atomicExch(&g_gemm_error, 1);
+        if (!ok && lane == 0) record_give_up();
     }
     // ---- teardown: nobody of either CTA touches tensor memory or the other's barriers any more ----
     tc_fence_before();
@@ -781,6 +793,35 @@ extern "C" int hos_gemm_tc_error() {
     cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
     if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
     return v;
+}
+
+// The host's word for waits that ran out (see record_give_up); null takes it away.
+extern "C" int hos_gemm_tc_set_error_word(int* word) {
+    if (cudaMemcpyToSymbol(g_gemm_error_host, &word, sizeof(word)) != cudaSuccess)
+        HOS_REFUSE("gemm_tc: cannot set the error word: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
+namespace hos {
+// One thread waits, with a limit of `limit_cycles` clock cycles, on a barrier at which nothing ever
+// arrives, gives up, records it as the product kernels do, and the kernel ends as usual.
+__global__ void wait_probe_kernel(long long limit_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        if (!mbar_wait_timed(&bar, 0, limit_cycles)) record_give_up();
+    }
+}
+}  // namespace hos
+
+// For tests of the give-up path: what a product kernel does when a wait runs out, without a product and
+// with a short limit (at most 2^24 cycles, a few milliseconds).
+extern "C" int hos_gemm_tc_wait_probe(long long limit_cycles, cudaStream_t stream) {
+    if (limit_cycles < 1 || limit_cycles > (1ll << 24))
+        HOS_REFUSE("gemm_tc_wait_probe: a limit of %lld cycles (1..2^24)", limit_cycles);
+    hos::wait_probe_kernel<<<1, 32, 0, stream>>>(limit_cycles);
+    return check_launch("gemm_tc_wait_probe");
 }
 
 // Floats of workspace for the K-split partial sums of a swapped product (0: no split).

@@ -244,6 +244,7 @@ class DecodeSession:
     def fetch_read(handle) -> List[int]:
         host, ev, n = handle
         ev.synchronize()
+        ops.check_errors()            # a kernel that gave up a wait: these tokens are not to be trusted
         return host[:n].tolist()
 
 

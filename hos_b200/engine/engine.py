@@ -204,6 +204,8 @@ class Engine:
                 nll += float((lse - logits.gather(1, target[:, None])[:, 0]).sum())
         finally:
             r.release(slot)
+        from .. import ops
+        ops.check_errors()
         mean = nll / len(feed)
         return len(feed), mean, math.exp(mean)
 

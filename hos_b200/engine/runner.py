@@ -299,6 +299,13 @@ class Runner:
             self.cache.lengths[s] = n + warmup + steps
         return e0.elapsed_time(e1) / steps, sess.launches_per_step * steps
 
+    def wait(self) -> None:
+        """Wait for the steps launched so far, and raise KernelError if one of their kernels gave up a
+        bounded wait (a caller that reads `step`'s logits by other means calls `ops.check_errors()`
+        after its own synchronisation)."""
+        torch.cuda.synchronize(self.device)
+        ops.check_errors()
+
     @property
     def max_seq_len(self) -> int:
         return self.cache.max_seq_len

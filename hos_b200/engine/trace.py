@@ -39,6 +39,7 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
 
     print("[hos] loading the model (kernels are compiled at their first use)", file=sys.stderr, flush=True)
+    from .. import ops
     from .runner import Runner
     # the cache alone bounds a request's length here: replay is not cut at the model's
     # max_position_embeddings, which generation takes as its context limit
@@ -63,6 +64,7 @@ def main(argv=None) -> int:
                                  [e.get("want", []) for e in entries])
             if logits.shape[0] > 0:
                 arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
+                ops.check_errors()        # the copy waited for the step: a kernel that gave up a wait shows now
                 arr.tofile(os.path.join(args.out, f"{step}.f32"))
         for rid in obj.get("end", []):
             runner.release(slots.pop(str(rid)))

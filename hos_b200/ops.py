@@ -97,6 +97,12 @@ class Library:
             self._last_error = self.lib.hos_last_error
             self._last_error.restype = ctypes.c_char_p
             self._last_error.argtypes = []
+        # kernels whose bounded waits run out say so in one word of pinned host memory (check_errors)
+        for setter in _ERROR_WORD_SETTERS:
+            f = getattr(self.lib, setter, None)
+            if f is not None and torch.cuda.is_available():
+                f.restype, f.argtypes = ctypes.c_int, [ctypes.c_void_p]
+                f(ctypes.c_void_p(_error_word().data_ptr()))
         self._set_pdl = getattr(self.lib, "hos_set_pdl", None)
         if self._set_pdl is not None:
             self._set_pdl.restype, self._set_pdl.argtypes = None, [ctypes.c_int]
@@ -127,6 +133,43 @@ class Library:
 
 _libraries: List["Library"] = []
 _launch_ahead = False
+
+_ERROR_WORD_SETTERS = ("hos_gemm_tc_set_error_word", "hos_attn_decode_set_error_word",
+                       "hos_attn_prefill_tc_set_error_word")
+GIVE_UP_CODES = {1: "the tcgen05 matrix product", 2: "the decode attention", 3: "the tcgen05 prompt attention"}
+_error_word_tensor: Optional[torch.Tensor] = None
+_after_give_up = []        # callables that put shared scratch state right after a kernel gave up
+
+
+def _error_word() -> torch.Tensor:
+    """One int32 in pinned host memory (the same address on the device): 0, or the code of the
+    kernel whose bounded wait ran out last."""
+    global _error_word_tensor
+    if _error_word_tensor is None:
+        _error_word_tensor = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _error_word_tensor
+
+
+def on_give_up(fn) -> None:
+    """Register what has to be put right when a kernel gave up (counters it left behind)."""
+    _after_give_up.append(fn)
+
+
+def check_errors() -> None:
+    """Call after a synchronisation, before a step's result is used: raises KernelError if a kernel of
+    the steps that are complete by now gave up a bounded wait (its results are then not to be trusted).
+    Costs a read of host memory."""
+    w = _error_word_tensor
+    if w is None:
+        return
+    code = int(w[0])
+    if code == 0:
+        return
+    w[0] = 0
+    for fn in _after_give_up:
+        fn()
+    raise KernelError(f"{GIVE_UP_CODES.get(code, 'a kernel')} gave up a wait that should have ended (about a second); "
+                      f"the results of the steps since the last check are not valid")
 
 
 def set_launch_ahead(on: bool) -> None:

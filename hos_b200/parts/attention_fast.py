@@ -90,15 +90,28 @@ def clusters_fit(head_dim: int, n_heads: int, n_kv_heads: int, n_splits: int) ->
     return n
 
 
-_ticket_store: Dict[object, torch.Tensor] = {}
+_ticket_store: Dict[object, list] = {}
+_TICKETS_AT_LEAST = 1 << 16
 
 
 def _tickets(device, n: int) -> torch.Tensor:
-    """Zeroed counters that the kernel leaves zeroed: one allocation per device, grown on demand."""
-    t = _ticket_store.get(device)
-    if t is None or t.numel() < n:
-        t = _ticket_store[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
-    return t
+    """Zeroed counters that the kernel leaves zeroed, shared by all launches on a device.  Captured
+    graphs keep the address they were given, so a buffer is never given up: if a launch needs more
+    than the last one holds, another is made and the old ones stay."""
+    held = _ticket_store.setdefault(device, [])
+    if not held or held[-1].numel() < n:
+        held.append(torch.zeros(max(n, _TICKETS_AT_LEAST), dtype=torch.int32, device=device))
+    return held[-1]
+
+
+def _clear_tickets() -> None:
+    """After a kernel gave up: a share that left early took no ticket, so its counter is not at zero."""
+    for held in _ticket_store.values():
+        for t in held:
+            t.zero_()
+
+
+ops.on_give_up(_clear_tickets)
 
 
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,

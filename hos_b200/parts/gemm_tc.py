@@ -89,6 +89,13 @@ def matmul_partials(x, w, k_splits: Optional[int] = None) -> Optional[torch.Tens
     return ws[: used.value]
 
 
+def wait_probe(limit_cycles: int = 1 << 20) -> None:
+    """A tiny kernel that waits on a barrier nothing arrives at, gives up after `limit_cycles` (well
+    under a millisecond by default) and records it as the product kernels do: for tests of what
+    happens next."""
+    lib().call("hos_gemm_tc_wait_probe", int(limit_cycles), ops._stream())
+
+
 def gave_up() -> bool:
     """True if a launch since the last call left a bounded wait unfinished (synchronises)."""
     f = lib().lib.hos_gemm_tc_error

@@ -108,6 +108,7 @@ class Sampler:
             ops.sample(logits, uniforms, out, p.temp, p.top_k, p.top_p,
                        p.rep_penalty if penal else 1.0, recent_t, recent_len)
         toks = out.tolist()
+        ops.check_errors()            # the copy waited for the step that made the logits
         for k, t in zip(keys, toks):
             self._recent[k].append(int(t))
         return [int(t) for t in toks]

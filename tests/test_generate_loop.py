@@ -190,3 +190,12 @@ def test_sampling_defaults_are_the_references():
     assert (p.temp, p.top_k, p.top_p, p.rep_penalty, p.repeat_last_n, p.seed) == (0.0, 40, 0.95, 1.1, 64, 42)
     q = SamplingParams.pure()
     assert (q.top_k, q.top_p, q.rep_penalty) == (0, 1.0, 1.0)
+
+
+def test_a_penalty_window_longer_than_the_record_keeps_is_refused():
+    # the reference penalises recent[len - repeat_last_n..] whatever its length (src/lib.rs:102-118);
+    # here a sequence's record keeps its last 256 sampled tokens, so a longer window is refused, not cut
+    SamplingParams(rep_penalty=1.3, repeat_last_n=256)
+    SamplingParams(rep_penalty=1.0, repeat_last_n=100000)          # no penalty: the window does not matter
+    with pytest.raises(HosError, match="256 recent tokens"):
+        SamplingParams(rep_penalty=1.3, repeat_last_n=257)

@@ -479,6 +479,35 @@ def _plain_sample_with_u(P, logits, params, recent, u):
         P.next_rand = orig
 
 
+def test_a_wait_that_runs_out_is_reported_to_the_host():
+    """The give-up path in its harmless form: one thread waits half a millisecond on a barrier that
+    nothing arrives at, gives up and records it exactly as the product kernels do; the kernel ends
+    normally.  The host sees it without asking the device (a word in pinned memory), raises, puts
+    the shared counters right, and the next launches work."""
+    from hos_b200 import ops
+    from hos_b200.errors import KernelError
+    from hos_b200.parts import attention_fast as af, gemm_tc
+    ops.check_errors()                                   # nothing pending
+    tickets = af._tickets(torch.device(DEV, torch.cuda.current_device()), 16)
+    tickets[3] = 2                                       # as a share that left early would leave it
+    gemm_tc.wait_probe()
+    torch.cuda.synchronize()
+    assert gemm_tc.gave_up()                             # the device flag (reading it clears it)
+    assert not gemm_tc.gave_up()
+    with pytest.raises(KernelError, match="gave up a wait"):
+        ops.check_errors()
+    assert int(tickets.abs().sum()) == 0                 # the counters are clean again
+    ops.check_errors()                                   # and the word is cleared
+    x = torch.randn(70, 64, device=DEV).to(torch.bfloat16)
+    w = torch.randn(128, 64, device=DEV).to(torch.bfloat16)
+    out = torch.empty(70, 128, device=DEV, dtype=torch.bfloat16)
+    gemm_tc.matmul(x, w, out)
+    torch.cuda.synchronize()
+    ops.check_errors()
+    assert not gemm_tc.gave_up()
+    close(out, x.float() @ w.float().T, torch.bfloat16)
+
+
 def test_gather_rows():
     from hos_b200 import ops
     x = torch.randn(50, 331, device=DEV)
