@@ -127,3 +127,27 @@ def test_sampler_rules():
     a = [P.sample(logits, 0.8, 0, 1.0, 1.0, [], s)[0] for s in seeds]
     b = [P.sample(logits, 0.8, 0, 1.0, 1.0, [], s)[0] for s in seeds]
     assert a == b and len(set(a)) > 2
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_two_restatements_agree(tmp_path, name):
+    """The prompt driver restated with matrices on whole sequences (gemma2_plain.py, from
+    src/forward.rs:247-438) and the one-token driver restated with loops on top of a cache
+    (gemma2_steps.py, from src/forward.rs:443-616): two shapes of the same arithmetic, written
+    apart, must give the same logits at every position (the reference's own invariant,
+    src/forward.rs:242-245).  Lengths cross the windows (8 and 16 keys)."""
+    import json
+    import os
+    from plain import gemma2_steps as S
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    with open(os.path.join(folder, "config.json")) as f:
+        raw = json.load(f)
+    vocab = raw["vocab_size"]
+    tokens = random_tokens(random.Random(31), 27, vocab)
+    whole = P.forward_logits(w, cfg, tokens)
+    steps = S.logits_token_by_token({k: v.numpy() for k, v in w.items()}, raw, tokens)
+    assert steps.shape == tuple(whole.shape)
+    err = (torch.from_numpy(steps) - whole).abs().max()
+    assert float(err) < 2e-5, f"the two restatements differ by {float(err):.2e}"
+    assert float(whole.abs().max()) > 0.3            # and they are not trivially small
