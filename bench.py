@@ -228,6 +228,55 @@ def measure_prefill(eng, tokens, rng, reps=3, pieces=1):
     return best
 
 
+def run_baseline_workload(args) -> int:
+    """The workloads that go with the 9B and 27B layer sizes: 9B, 16 prompts of seeded lengths
+    U[64, 2048] in one ragged prompt step, then 256 greedy tokens each, context 4096; 27B, 8 prompts of
+    1,024 tokens, then 256 each; 2B, 8 prompts of 512 and decoding as far as --decode-tokens says.
+    Method of the reference's own bench (src/lib.rs:683-727): one warm-up prompt step, then the prompt
+    step and the greedy decoding timed apart, through `Engine.bench`, the public entry point."""
+    import random
+    import torch
+    from hos_b200 import Engine
+    from hos_b200 import models  # noqa: F401
+    from hos_b200.registry import config_from_dict
+    full_layers = MODELS[args.model]["num_hidden_layers"]
+    layers = args.layers or full_layers
+    ctx = 4096 if args.model != "2b" else 8192
+    cfg = config_from_dict(dict(MODELS[args.model], num_hidden_layers=layers, max_position_embeddings=ctx))
+    rng = random.Random(0)
+    if args.model == "9b":
+        lens = [rng.randint(64, 2048) for _ in range(16)]
+    elif args.model == "27b":
+        lens = [1024] * 8
+    else:
+        lens = [512] * 8
+    decode = args.decode_tokens
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
+    pk, pk_src = peaks()
+    eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_batch=len(lens),
+                             max_tokens=sum((n + decode + 63) // 64 * 64 for n in lens), max_seq_len=ctx)
+    clocks = ClockSampler(torch.cuda.current_device())
+    clocks.start()
+    n_prompt, pre_s, pre_tps, produced, dec_s, dec_tps = eng.bench(prompts, decode)
+    clock_rec = clocks.stop()
+    fl = sum(prefill_flops(cfg, layers, n) for n in lens)
+    steps = produced / len(lens)
+    wbytes = weight_bytes(cfg, layers)
+    step_bytes = wbytes + sum(kv_bytes_at(cfg, layers, n + int(steps / 2)) for n in lens)
+    ms_step = dec_s * 1e3 / max(steps, 1e-9)
+    print(json.dumps({
+        "workload": "baseline", "model": f"gemma-2-{args.model} sizes, random weights", "layers": layers,
+        "layers_full": full_layers, "batch": len(lens), "prompt_tokens": n_prompt, "prompt_lengths": "U[64,2048] seeded"
+        if args.model == "9b" else str(lens[0]), "context": ctx, "dtype": "bf16", "peaks": pk_src, "clocks": clock_rec,
+        "prefill": {"tokens": n_prompt, "ms": pre_s * 1e3, "value": pre_tps, "unit": "tok/s", "tflop": fl / 1e12,
+                    "frac": fl / pre_s / (pk["bf16_tflops_sustained"] * 1e12), "peak_tflops": pk["bf16_tflops_sustained"],
+                    "of": pk_src + " (sustained)"},
+        "decode": {"tokens": produced, "steps": steps, "ms_per_step": ms_step, "value": dec_tps, "unit": "tok/s",
+                   "bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                   "frac": step_bytes / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], "peak_gbs": pk["hbm_gbs"], "of": pk_src}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -241,6 +290,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--workload", default="step", choices=["step", "baseline"],
+                    help="step: the decode step at the context's end (the default line); baseline: prompts then 256 "
+                         "greedy tokens, the workload that goes with the model's sizes")
+    ap.add_argument("--decode-tokens", type=int, default=256, help="tokens decoded per sequence by --workload baseline")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the contract's 2,048)")
     args = ap.parse_args()
@@ -255,6 +308,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "baseline":
+        return run_baseline_workload(args)
 
     import random
     import torch

@@ -252,7 +252,19 @@ class Runner:
             out = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         return out
 
-    def _hidden(self, slots, starts, token_lists, rows=(), extend: bool = True):
+    def hidden_states(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]]) -> List[torch.Tensor]:
+        """Run the tokens as `step` does (one pass, kernel by kernel) and return the residual stream
+        after the embedding and after every entry of the run order, float32 [tokens, width] each, rows in
+        the order of the sequences given (which must list the ones that start at position 0 first).  For
+        finding the layer at which two paths (bfloat16 and 32-bit, or this library and another
+        implementation) part ways."""
+        starts = [self.cache.lengths[s] if s in self.cache.lengths else self._no_slot(s) for s in slots]
+        self._check_ids(token_lists)
+        tap: List[torch.Tensor] = []
+        self._hidden(slots, starts, token_lists, tap=tap)
+        return tap
+
+    def _hidden(self, slots, starts, token_lists, rows=(), extend: bool = True, tap=None):
         """The hidden rows of one pass, and `rows` (indices into them) as a device tensor.  The
         sequences that start at position 0 must come first."""
         info, rows_t = build_step(token_lists, starts, slots, self.device, self.vocab_size, extra=rows)
@@ -262,7 +274,7 @@ class Runner:
         # a step of many tokens: its kernels are long enough for the next one's set-up to hide under them
         ops.set_launch_ahead(info.n_tokens >= LAUNCH_AHEAD_MIN_TOKENS)
         try:
-            x = self.model.hidden(info, self.cache)
+            x = self.model.hidden(info, self.cache, tap)
             # the slots' records learn the new lengths (single-token steps take positions from them)
             ops.slot_set_pos(self.cache.record, info.seq_slot, info.seq_len_after, info.cu_seqlens, info.n_seqs)
             return x, rows_t

@@ -62,19 +62,26 @@ class Model:
                             max_seq_len or self.plan.max_positions, self.rt.dtype, self.rt.device,
                             max_slots, chunk_tokens)
 
-    def hidden(self, step: StepInfo, cache: CacheManager) -> torch.Tensor:
-        """The residual stream after the last entry of the run order, float32 [N, width]."""
+    def hidden(self, step: StepInfo, cache: CacheManager, tap: Optional[list] = None) -> torch.Tensor:
+        """The residual stream after the last entry of the run order, float32 [N, width].  With `tap`
+        (a list) a copy of the residual stream is appended after the embedding and after every entry
+        of the run order: what tells where two paths begin to differ (the reference keeps such a tap
+        per layer, src/forward.rs:45-103)."""
         x = self.embedding.forward(step.tokens, step)
+        if tap is not None:
+            tap.append(x.clone())
         h = None
         for i, call in enumerate(self.schedule):
             layer = self.layers[call.layer]
             if not layer.chains:
                 layer.forward(x, step, cache.stores[i])
                 h = None
-                continue
-            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
-            next_norm = nxt.entry_norm() if nxt is not None and nxt.chains else None
-            h = layer.forward(x, step, cache.stores[i], h_in=h, next_norm=next_norm)
+            else:
+                nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+                next_norm = nxt.entry_norm() if nxt is not None and nxt.chains else None
+                h = layer.forward(x, step, cache.stores[i], h_in=h, next_norm=next_norm)
+            if tap is not None:
+                tap.append(x.clone())
         return x
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -185,6 +185,19 @@ def set_launch_ahead(on: bool) -> None:
             lib._set_pdl(1 if on else 0)
 
 
+_sm_count: Optional[int] = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once).  Without a device, as the
+    host-side choices are also exercised where there is none, the B200's 148."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = (torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+                     if torch.cuda.is_available() else 148)
+    return _sm_count
+
+
 _core: Optional[Library] = None
 launch_count = 0        # calls into the CUDA libraries so far (each launches one kernel or more)
 

@@ -11,7 +11,6 @@ import torch
 
 from .. import ops
 
-SM_COUNT = 148
 MAX_HEAD_DIM = 256
 MAX_SPLITS = 64
 
@@ -54,13 +53,13 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
         if s == 1:
             merge = 0.0
-        elif clusters_fit is not None and s <= CLUSTER_SHARES and hi * per_token * s <= SM_COUNT \
+        elif clusters_fit is not None and s <= CLUSTER_SHARES and hi * per_token * s <= ops.sm_count() \
                 and clusters_fit(s) >= hi * per_token:
             merge = _CLUSTER_MERGE_US + _CLUSTER_MERGE_PER_SHARE_US * s      # the shares are one cluster
         else:
             merge = _MERGE_US + _MERGE_PER_SHARE_US * s
         per_item = _ITEM_US + _PAGE_US * -(-pages // s) + merge
-        cost = sum(-(-live * per_token * s // SM_COUNT) * per_item for live in lives)
+        cost = sum(-(-live * per_token * s // ops.sm_count()) * per_item for live in lives)
         if best_cost is None or cost < 0.97 * best_cost:          # more shares only for a clear gain
             best, best_cost = s, cost
     return best

@@ -43,7 +43,6 @@ def matmul(x, w, out, epilogue: int = ops.EPI_NONE, act: int = 0) -> None:
                x.stride(0), w.stride(0), out.stride(0), epilogue, act, 1, ops._stream())
 
 
-SM_COUNT = 148
 _MIN_K_PER_CTA = 4096      # below this a CTA's 8 warps have too few loads each to be worth another CTA
 
 
@@ -51,7 +50,7 @@ def k_splits_for(n: int, k: int) -> int:
     """CTAs own 16 output features each; with fewer of them than two per SM, K is split over
     more CTAs while each keeps enough of K to fill its loads."""
     ctas = (n + 15) // 16
-    return max(1, min(2 * SM_COUNT // ctas, k // _MIN_K_PER_CTA, 8))
+    return max(1, min(2 * ops.sm_count() // ctas, k // _MIN_K_PER_CTA, 8))
 
 
 def matmul_partials(x, w, k_splits: Optional[int] = None) -> Optional[torch.Tensor]:

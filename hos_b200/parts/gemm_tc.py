@@ -11,7 +11,6 @@ import torch
 
 from .. import ops
 
-SM_COUNT = 148
 PAIR_MIN_ROWS = 512      # from here on the product runs on pairs of SMs
 _lib: Optional[ops.Library] = None
 enabled = True          # tests switch it off to compare with the plain kernel
@@ -49,14 +48,14 @@ def k_splits_for(m: int, n: int, k: int, epilogue: int) -> int:
         # pairs of SMs with tiles of 256 x 256: a prompt of some hundred tokens gives the o and down products
         # fewer tiles than there are pairs; K is then split so that most pairs have one, 8 blocks of 64 or more each
         tiles = ((m + 255) // 256) * ((n + 255) // 256)
-        return max(1, min((SM_COUNT // 2) // tiles, ((k + 63) // 64) // 8))
+        return max(1, min((ops.sm_count() // 2) // tiles, ((k + 63) // 64) // 8))
     if m > 64:
         return 1
     tiles = (n + 127) // 128
-    if tiles >= SM_COUNT // 2:
+    if tiles >= ops.sm_count() // 2:
         return 1
     k_blocks = (k + 63) // 64
-    return max(1, min(SM_COUNT // tiles, k_blocks // 4))      # tiles x splits stays within one wave
+    return max(1, min(ops.sm_count() // tiles, k_blocks // 4))      # tiles x splits stays within one wave
 
 
 def matmul(x, w, out, epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,

@@ -261,6 +261,23 @@ def test_conversations_continue_where_they_ended(tmp_path, dtype):
     assert eng.runner.cache.slots.n_held == 0
 
 
+def test_the_per_layer_tap_follows_the_plain_residual_stream(tmp_path):
+    """`Runner.hidden_states`: the residual stream after the embedding and after every layer, against
+    the plain implementation cut off after as many layers."""
+    import dataclasses
+    folder = make_folder(tmp_path, "B")
+    w, cfg = plain_model(folder)
+    r = runner_for(folder, "float32")
+    ids = random_tokens(random.Random(12), 21, 512)
+    slot = r.admit(1)[0]
+    taps = r.hidden_states([slot], [ids])
+    assert len(taps) == cfg.num_hidden_layers + 1
+    for n, got in enumerate(taps):
+        want = P.forward_hidden(w, dataclasses.replace(cfg, num_hidden_layers=n), ids)
+        assert_close(got, want, "float32", f"residual stream after {n} layers")
+    assert r.length(slot) == 21
+
+
 def test_perplexity_and_bench(tmp_path):
     from hos_b200 import Engine
     folder = make_folder(tmp_path, "B")
