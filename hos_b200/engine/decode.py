@@ -49,6 +49,22 @@ def smaller_bucket(b: int) -> int:
     return below[-1] if below else max(0, b - 64)
 
 
+MIN_LENGTH_CLASS = 512
+
+
+def length_class(longest: Optional[int], max_seq_len: int) -> int:
+    """The sequence length a replayed step is planned for: the power of two at or above the longest live
+    sequence (at least MIN_LENGTH_CLASS, at most what the cache holds).  How the attention kernel splits the
+    keys over the GPU depends on it, and is part of what is captured: a step is captured once per class, so a
+    batch of short sequences is not run with the split that the longest possible one would want."""
+    if longest is None or longest >= max_seq_len:
+        return max_seq_len
+    c = MIN_LENGTH_CLASS
+    while c < longest:
+        c *= 2
+    return min(c, max_seq_len)
+
+
 class DecodeSession:
     def __init__(self, runner, bucket: int, use_graph: Optional[bool] = None):
         self._runner = weakref.ref(runner)      # the runner owns its sessions: no reference cycle
@@ -86,6 +102,7 @@ class DecodeSession:
         self._programs = {}                     # key -> (graph or None, logits buffer)
         self.launches_per_step = 0
         self._max_len = runner.cache.max_seq_len
+        self._planned_len = self._max_len       # the lengths the replayed launches are planned for (see length_class)
         self.n_live = 0
 
     @property
@@ -96,17 +113,20 @@ class DecodeSession:
         return StepInfo(n_tokens=self.b, n_seqs=self.b, tokens=self.tokens, token_pos=self.pos,
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot,
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
-                        max_len_after=self._max_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
+                        max_len_after=self._planned_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
                         starts_host=(), token_slot=self.slot,      # row n is sequence n here
                         min_live=smaller_bucket(self.b) + 1, replayed=True)
 
     def upload(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
-               stop_ids: Sequence[int] = ()) -> None:
+               stop_ids: Sequence[int] = (), longest: Optional[int] = None) -> None:
         """Which slots the next step runs (rows beyond them are padding), the tokens if the caller
         brings them, and the stop ids that mark a sequence finished on the device (the first
-        ops.MAX_STOPS of them; the host checks all of them anyway): one host-to-device copy."""
+        ops.MAX_STOPS of them; the host checks all of them anyway): one host-to-device copy.
+        `longest`: the length of the longest of these sequences after the step, if the caller knows it
+        (the attention kernel's split of the keys is planned for the power of two above it)."""
         n = len(slots)
         self.n_live = n
+        self._planned_len = length_class(longest, self._max_len)
         turn = self._turn
         self._turn ^= 1
         if self._copied[turn] is not None:
@@ -196,7 +216,7 @@ class DecodeSession:
             self.logits = fn()
             self.launches_per_step = ops.launch_count - before
             return self.logits
-        g, self.logits = self._program(key, fn)
+        g, self.logits = self._program(key + (self._planned_len,), fn)
         g.replay()
         return self.logits
 

@@ -54,7 +54,7 @@ class _DeviceBackend:
         r = self.runner
         r.cache.extend_all(slots, [r.cache.lengths[s] + 1 for s in slots])
         sess = r.decode_session(len(slots))
-        sess.upload(slots, stop_ids=self._stops)
+        sess.upload(slots, stop_ids=self._stops, longest=max(r.cache.lengths[s] for s in slots))
         sess.run_generate(self.params)
         self._queue.append(sess.fetch_start())
 
@@ -210,19 +210,17 @@ class Engine:
         return len(feed), mean, math.exp(mean)
 
     def bench(self, prompt: Prompt, decode_tokens: int = 64):
-        """Time the prompt step and greedy decoding separately, after one warm-up prompt
-        step (src/lib.rs:683-727).  `prompt` is one prompt or a batch of them (decoded
+        """Time the prompt step and greedy decoding separately, after a warm-up of one prompt
+        step and two decode steps (src/lib.rs:683-727).  `prompt` is one prompt or a batch of them (decoded
         together; a sequence that meets a stop token or the context's end leaves the batch).
         Returns (prefill_tokens, prefill_secs, prefill_tps, decode_tokens, decode_secs,
         decode_tps), tokens counted over the batch."""
         r = self.runner
         prompts = [list(p) for p in prompt] if _is_batch(prompt) else [list(prompt)]
         n_prompt = sum(len(p) for p in prompts)
-        slots = r.admit(len(prompts))
-        r.step(slots, prompts)                      # the warm-up
-        for s in slots:
-            r.release(s)
         backend = _DeviceBackend(r, SamplingParams.pure())
+        # the warm-up: the prompt step and two decode steps (kernels built, graphs captured)
+        gen.run_batch(backend, prompts, list(range(len(prompts))), 3, ())
         times = {}
 
         class Timed:                                # the loop's backend, with a clock around the first step

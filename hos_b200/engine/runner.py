@@ -126,7 +126,7 @@ class Runner:
             self._check_ids(token_lists)
             self.cache.extend_all(slots, [st + 1 for st in starts])
             sess = self.decode_session(len(slots))
-            sess.upload(slots, [t[0] for t in token_lists])
+            sess.upload(slots, [t[0] for t in token_lists], longest=max(starts) + 1)
             out = sess.run_step()
             return out.clone() if copy else out
         if from_zero and last_only and self.use_sessions and self.prompt_sessions:
@@ -292,7 +292,7 @@ class Runner:
             self.cache.lengths[s] = n
         self.write_records(slots, pos=lengths, last=[t[0] for t in first_tokens], limit=[0] * len(slots), restart=True)
         sess = self.decode_session(len(slots))
-        sess.upload(slots)
+        sess.upload(slots, longest=max(lengths) + warmup + steps)
         greedy = SamplingParams.pure()
         for _ in range(warmup):
             sess.run_generate(greedy)

@@ -75,3 +75,15 @@ def test_k_splits_of_the_products():
             tiles = ((m + 255) // 256) * ((n + 255) // 256)
             assert 1 <= s and tiles * s <= 74 or s == 1                 # at most one tile per pair of SMs
             assert s == 1 or (k + 63) // 64 // s >= 8
+
+
+def test_replayed_steps_are_planned_for_the_power_of_two_above_the_longest_sequence():
+    from hos_b200.engine.decode import MIN_LENGTH_CLASS, length_class
+    assert length_class(None, 8192) == 8192                  # not known: the longest the cache holds
+    assert length_class(1, 8192) == MIN_LENGTH_CLASS
+    assert length_class(512, 8192) == 512 and length_class(513, 8192) == 1024
+    assert length_class(1025, 8192) == 2048 and length_class(5000, 8192) == 8192
+    assert length_class(9000, 8192) == 8192 and length_class(3000, 3500) == 3500
+    # the class never lies below the sequence: a share of the keys is never planned away
+    for n in range(1, 9000, 37):
+        assert length_class(n, 8192) >= min(n, 8192)
