@@ -182,6 +182,23 @@ def test_toy_architecture_with_a_stateful_mixer_steps_like_whole_prompts(dtype):
             r.release(slots[i])
         live = [i for i in live if pos[i] < len(seqs[i])]
     r.cache.check()
+    # prompts fed in pieces of unequal sizes, in steps that others share: one sequence starts while another
+    # goes on by 9 tokens and a third by one (the mixer's state is resumed from where the last piece left it;
+    # the second attention entry reads the first one's cache over the pieces)
+    slots = r.admit(3)
+    at = [0, 0, 0]
+    plan = [[(0, 11), (2, 40)], [(0, 9), (1, 3), (2, 1)], [(0, 10), (1, 4), (2, 34)]]
+    for stepn, entries in enumerate(plan):
+        feeds = [seqs[i][at[i]:at[i] + k] for i, k in entries]
+        got = r.step([slots[i] for i, _ in entries], feeds, [list(range(len(f))) for f in feeds]).cpu()
+        exp = torch.cat([want[i][at[i]:at[i] + k] for i, k in entries])
+        torch.testing.assert_close(got, exp, **tol)
+        for i, k in entries:
+            at[i] += k
+    assert at == [30, 7, 75]
+    for s in slots:
+        r.release(s)
+    r.cache.check()
 
 
 # ---- a second toy: a feed-forward with routing, a position encoding, a norm and an embedding of its
