@@ -43,7 +43,7 @@ def _device() -> torch.device:
 class Runner:
     def __init__(self, config: ModelConfig, source, dtype: str = "bfloat16", max_tokens: int = 8192,
                  max_seq_len: Optional[int] = None, max_slots: Optional[int] = None,
-                 device: Optional[torch.device] = None, chunk_tokens: int = 512):
+                 device: Optional[torch.device] = None, chunk_tokens: int = 2048):
         """`chunk_tokens`: the most tokens a step adds in one pass to a sequence that is under way
         (layers that keep a window of keys make their ring of pages that much longer; a step
         that brings more is run as several passes)."""

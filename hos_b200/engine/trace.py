@@ -32,7 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to 64")
-    ap.add_argument("--chunk-tokens", type=int, default=512,
+    ap.add_argument("--chunk-tokens", type=int, default=2048,
                     help="most tokens one pass adds to a request that is under way (more are run as several "
                          "passes); layers with a window keep a ring of window + this many keys")
     args = ap.parse_args(argv)

@@ -75,13 +75,13 @@ def build_pieces(name):
     return reqs, t
 
 
-@pytest.mark.parametrize("chunk_tokens", [24, 512])
+@pytest.mark.parametrize("chunk_tokens", [24, 2048])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_in_pieces_matches_the_plain_implementation(tmp_path, name, dtype, chunk_tokens):
     """With --chunk-tokens 24 the rings of the window layers hold one or two pages, wrap all the
     time, and pieces of 64 and 100 tokens are more than they have room for (the step function
-    feeds them in several passes); with 512 every piece runs in one pass."""
+    feeds them in several passes); with 2048 (the default) every piece runs in one pass."""
     folder = make_folder(tmp_path, name)
     w, cfg = plain_model(folder)
     reqs, trace = build_pieces(name)
