@@ -24,9 +24,16 @@
 //
 // A second kernel further down runs the same walk on pairs of SMs for head sizes 128 and 256.
 //
+// The one-SM kernel has a second form (PAGED) for sequences that go on by many tokens: queries are the
+// step's rows, at the positions the step gives them; a key tile is a page of the cache.  In the cache the
+// 16-byte groups of row r of a [64][head_dim] tile are XOR-permuted by (r & 7), which within every 128-byte
+// column block is exactly the 128-byte swizzle that the tensor core's operand descriptors expect: a page's
+// tile is brought in by TMA boxes of [64 rows x 64 columns] WITHOUT swizzle and used as it lands.
+//
 // Compiled per head size: -DHOS_HEAD_DIM=N; the kernel exists for N in {64, 128, 256}.
 #include <cuda.h>
 #include "common.cuh"
+#include "kv_layout.cuh"
 #include "mma_utils.cuh"
 #include "tcgen05_pair.cuh"
 
@@ -203,11 +210,22 @@ struct PrefillTcArgs {
     int q_col0, k_col0, v_col0;     // first column of the q, k and v heads in a projection row
     float scale, cap;
     int window;
+    // the paged form: sequence s has the rows cu_seqlens[s] - row_base .. of the query rows and of out, the first of
+    // them at position token_pos[that row]; its keys and values are the pages of the table row seq_slot[s]
+    int row_base;
+    const int* token_pos;
+    const int* seq_slot;
+    const int* page_table;
+    int table_stride, ring_pages;
 };
 
+// PAGED: map_kv covers the key pages and map_v the value pages, both as [pages x kv heads x 64 rows][head_dim]
+// without swizzle; otherwise map_kv covers the projection rows (keys and values) and map_v is not used.
+template <bool PAGED>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
                        const __grid_constant__ CUtensorMap map_kv,     // boxes of [64 rows x 64 columns]
+                       const __grid_constant__ CUtensorMap map_v,
                        PrefillTcArgs a) {
     pdl_enter();      // the kernels before this one are complete from here on
     extern __shared__ unsigned char smem_unaligned[];
@@ -235,23 +253,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
     // that share keys run side by side.
     int seq = 0, tile = blockIdx.y, row0 = 0, len = 0, nt = 0;
     for (; seq < a.n_seqs; ++seq) {
-        row0 = a.cu_seqlens[seq];
-        len = a.cu_seqlens[seq + 1] - row0;
+        row0 = a.cu_seqlens[seq] - (PAGED ? a.row_base : 0);
+        len = a.cu_seqlens[seq + 1] - (PAGED ? a.row_base : 0) - row0;
         nt = (len + TQ - 1) / TQ;
         if (tile < nt) break;
         tile -= nt;
     }
     if (seq >= a.n_seqs) return;
-    const int q0 = (nt - 1 - tile) * TQ;
+    const int q0 = (nt - 1 - tile) * TQ;                    // first query row of the block within its sequence's rows
+    const int p0 = q0 + (PAGED ? a.token_pos[row0] : 0);    // and its position
     const int head = blockIdx.x, kvh = head / (a.n_heads / a.n_kv_heads);
-    const int last_q = min(len - 1, q0 + TQ - 1);
-    const int first_key = a.window > 0 ? max(0, q0 + 1 - a.window) : 0;
+    const int last_q = p0 + min(len - 1 - q0, TQ - 1);
+    const int first_key = a.window > 0 ? max(0, p0 + 1 - a.window) : 0;
     const int kt_lo = first_key / TK, kt_hi = last_q / TK;
     const int n_tiles = kt_hi - kt_lo + 1;
 
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+        if (PAGED) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
@@ -280,19 +300,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                 tc_tma_2d(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
             // keys and values travel separately: a stage's keys are free again as soon as its S is
             // computed, long before its values are, so the next keys are fetched that much earlier
+            PagedKV geo{nullptr, nullptr, a.page_table, a.table_stride, a.ring_pages, a.n_kv_heads, THD};
+            const int* table = PAGED ? a.page_table + (size_t)a.seq_slot[seq] * a.table_stride : nullptr;
+            int next_page = PAGED ? table[kv_table_entry(geo, kt_lo)] : 0;      // looked up one tile ahead of its use
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % kKVStages;
                 unsigned char* kd = kv_s + (size_t)s * 2 * kKVTileBytes;
                 unsigned char* vd = kd + kKVTileBytes;
-                const int krow = row0 + (kt_lo + j) * TK;
+                const int page = next_page;
+                if (PAGED && j + 1 < n_tiles) next_page = table[kv_table_entry(geo, kt_lo + j + 1)];
+                // the tile's first row in its tensor map, and the first column of its keys and of its values
+                const int krow = PAGED ? (page * a.n_kv_heads + kvh) * kPageTokens : row0 + (kt_lo + j) * TK;
+                const int kcol = PAGED ? 0 : a.k_col0 + kvh * THD, vcol = PAGED ? 0 : a.v_col0 + kvh * THD;
                 if (j >= kKVStages && !tc_wait(&k_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
                 mbar_expect_tx(&k_full[s], kKVTileBytes);
                 for (int c = 0; c < CBLK; ++c)
-                    tc_tma_2d(kd + c * kKVBlockBytes, &map_kv, a.k_col0 + kvh * THD + 64 * c, krow, &k_full[s]);
+                    tc_tma_2d(kd + c * kKVBlockBytes, &map_kv, kcol + 64 * c, krow, &k_full[s]);
                 if (j >= kKVStages && !tc_wait(&v_empty[s], ((j / kKVStages) - 1) & 1)) { ok = false; break; }
                 mbar_expect_tx(&v_full[s], kKVTileBytes);
                 for (int c = 0; c < CBLK; ++c)
-                    tc_tma_2d(vd + c * kKVBlockBytes, &map_kv, a.v_col0 + kvh * THD + 64 * c, krow, &v_full[s]);
+                    tc_tma_2d(vd + c * kKVBlockBytes, PAGED ? &map_v : &map_kv, vcol + 64 * c, krow, &v_full[s]);
             }
             if (!ok) record_give_up();
         }
@@ -347,7 +374,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         const int half = (warp - 2) >> 2;                        // which 32 of the tile's 64 keys
         const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
         const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const int qpos = q0 + r;
+        const int qpos = p0 + r;
         // The walk works on t = tanh(s * scale / cap) (or t = s without a cap): the logit is c * t with c = cap
         // (or scale), so the maximum is taken over t and a probability is exp2(t * c log2e - m * c log2e):
         // per score one multiply, tanh, maximum; one fused multiply-add, exp2, add.
@@ -379,7 +406,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             if (capped) tanh_scores<32>(sc, pre);
             // a tile that every query of the block sees whole needs no mask (all but the last one or two of a walk,
             // and the first ones under a window)
-            const bool whole = kt0 + TK - 1 <= q0 && (a.window <= 0 || kt0 > q0 + TQ - 1 - a.window);
+            const bool whole = kt0 + TK - 1 <= p0 && (a.window <= 0 || kt0 > p0 + TQ - 1 - a.window);
             if (whole) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, sc[i]);
@@ -454,13 +481,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const float l_row = l_run + xchg[(half ^ 1) * TQ + r];
             const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-            bf16* orow = a.out + (size_t)(row0 + qpos) * a.out_stride + (size_t)head * THD;
+            bf16* orow = a.out + (size_t)(row0 + q0 + r) * a.out_stride + (size_t)head * THD;
 #pragma unroll 1
             for (int c = half * (THD / 2); c < (half + 1) * (THD / 2); c += 32) {
                 uint32_t o[32];
                 tc_ld32(t_lane + kColO + c, o);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (qpos < len) {
+                if (q0 + r < len) {
                     uint4* dst = reinterpret_cast<uint4*>(orow + c);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
@@ -808,7 +835,10 @@ static TcEncodeFn tc_encode_fn() {
     }
     return fn;
 }
-static int tc_make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int ld, int box_rows) {
+// swizzle: the 128-byte swizzle for rows as the projection wrote them; none for the cache's tiles, which lie
+// permuted in memory the way the swizzle would place them
+static int tc_make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int ld, int box_rows,
+                       bool swizzle = true) {
     TcEncodeFn fn = tc_encode_fn();
     if (!fn) HOS_REFUSE("attn_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -816,8 +846,8 @@ static int tc_make_map(CUtensorMap* map, const void* ptr, long long rows, int co
     cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) HOS_REFUSE("attn_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
     return 0;
 }
@@ -884,11 +914,11 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
     if ((rc = tc_make_map(&mkv, rows, n_rows, row_stride, row_stride, TK))) return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
             HOS_REFUSE("attn_prefill_tc: cannot get %d bytes of shared memory", kTcSmem);
         attr_set = true;
     }
-    PrefillTcArgs a;
+    PrefillTcArgs a = {};
     a.out = (bf16*)out; a.out_stride = out_stride; a.cu_seqlens = cu_seqlens; a.n_seqs = n_seqs;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
     a.q_col0 = 0; a.k_col0 = n_heads * THD; a.v_col0 = (n_heads + n_kv_heads) * THD;
@@ -907,9 +937,55 @@ extern "C" int hos_attn_prefill_tc(const void* rows, long long n_rows, int row_s
         return check_launch("attn_prefill_tc (pairs of SMs)");
     }
 #endif
-    launch_pdl(attn_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, stream, mq, mkv, a);
+    launch_pdl(attn_prefill_tc_kernel<false>, dim3(grid), dim3(kTcThreads), kTcSmem, stream, mq, mkv, mkv, a);
     return check_launch("attn_prefill_tc");
 #else
     HOS_REFUSE("attn_prefill_tc: no tensor-core prompt kernel for head_dim %d (64, 128 and 256 have one)", HOS_HEAD_DIM);
+#endif
+}
+
+// Sequences that go on by many tokens, over the paged cache (which holds the step's keys already), on the tensor
+// cores.  q: the step's projection rows of these sequences [n_rows, row_stride] (the q heads stand first in a row);
+// sequence s has the rows cu_seqlens[s] - row_base .. of q and out, at the consecutive positions token_pos[row], and
+// the page-table row seq_slot[s]; n_q_tiles is at least the sum over sequences of ceil(rows / 128).  The pages are
+// [n_pages][n_kv_heads][64][head_dim] arrays in the cache's permuted layout.
+extern "C" int hos_attn_chunk_tc(const void* q, long long n_rows, int row_stride, void* out, int out_stride,
+                                 const int* cu_seqlens, int row_base, const int* token_pos, const int* seq_slot,
+                                 int n_seqs, int n_q_tiles, void* k_pages, void* v_pages, long long n_pages,
+                                 const int* page_table, int table_stride, int ring_pages, int n_heads, int n_kv_heads,
+                                 int head_dim, float scale, float cap, int window, cudaStream_t stream) {
+#if (HOS_HEAD_DIM == 64) || (HOS_HEAD_DIM == 128) || (HOS_HEAD_DIM == 256)
+    if (n_q_tiles <= 0 || n_seqs <= 0) return 0;
+    if (head_dim != THD) HOS_REFUSE("attn_chunk_tc: built for head_dim %d, asked for %d", THD, head_dim);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        HOS_REFUSE("attn_chunk_tc: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    if (n_q_tiles > 65535) HOS_REFUSE("attn_chunk_tc: %d blocks of queries are more than one launch takes", n_q_tiles);
+    if (row_stride < n_heads * THD || (row_stride % 8) || ((uintptr_t)q % 16) || (out_stride % 8) || ((uintptr_t)out % 16))
+        HOS_REFUSE("attn_chunk_tc: rows must hold the q heads and be 16-byte aligned");
+    if (((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || n_pages <= 0)
+        HOS_REFUSE("attn_chunk_tc: the pages must be 16-byte aligned");
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = tc_make_map(&mq, q, n_rows, row_stride, row_stride, TQ))) return rc;
+    const long long page_rows = n_pages * n_kv_heads * kPageTokens;
+    if ((rc = tc_make_map(&mk, k_pages, page_rows, THD, THD, TK, false))) return rc;
+    if ((rc = tc_make_map(&mv, v_pages, page_rows, THD, THD, TK, false))) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+            HOS_REFUSE("attn_chunk_tc: cannot get %d bytes of shared memory", kTcSmem);
+        attr_set = true;
+    }
+    PrefillTcArgs a = {};
+    a.out = (bf16*)out; a.out_stride = out_stride; a.cu_seqlens = cu_seqlens; a.n_seqs = n_seqs;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
+    a.q_col0 = 0; a.k_col0 = 0; a.v_col0 = 0;
+    a.scale = scale; a.cap = cap; a.window = window;
+    a.row_base = row_base; a.token_pos = token_pos; a.seq_slot = seq_slot;
+    a.page_table = page_table; a.table_stride = table_stride; a.ring_pages = ring_pages;
+    launch_pdl(attn_prefill_tc_kernel<true>, dim3(n_heads, n_q_tiles), dim3(kTcThreads), kTcSmem, stream, mq, mk, mv, a);
+    return check_launch("attn_chunk_tc");
+#else
+    HOS_REFUSE("attn_chunk_tc: no tensor-core kernel for head_dim %d (64, 128 and 256 have one)", HOS_HEAD_DIM);
 #endif
 }

@@ -15,7 +15,7 @@ MAX_HEAD_DIM = 256
 MAX_SPLITS = 64
 
 _libs: Dict[int, ops.Library] = {}
-enabled = {"decode": True, "prefill": True, "prefill_tc": True, "chunk": True,
+enabled = {"decode": True, "prefill": True, "prefill_tc": True, "chunk": True, "chunk_tc": True,
            "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0",
            "decode_cluster": os.environ.get("HOS_ATTN_CLUSTER", "1") != "0"}
 _pair_state: Dict[int, bool] = {}
@@ -215,17 +215,35 @@ def chunk(q, q_stride, out, cu_seqlens, row_base: int, token_pos, seq_slot, n_se
              cache.head_dim, float(scale), float(cap), int(window) if window else 0, ops._stream())
 
 
+def chunk_tc(q, out, cu_seqlens, row_base: int, token_pos, seq_slot, n_seqs: int, blocks: int,
+             cache: ops.PagedKVArgs, n_heads, scale, cap, window) -> None:
+    """As `chunk`, on the tcgen05 tensor cores (head sizes 64, 128, 256): q is [rows, stride] with the q heads
+    first in a row; `blocks`: at least the sum over sequences of ceil(rows / 128)."""
+    lib = lib_for(cache.head_dim)
+    lib.call("hos_attn_chunk_tc", ops._ptr(q), q.shape[0], q.shape[1], ops._ptr(out), out.shape[1], ops._ptr(cu_seqlens),
+             int(row_base), ops._ptr(token_pos), ops._ptr(seq_slot), n_seqs, blocks, ops._ptr(cache.k_pages),
+             ops._ptr(cache.v_pages), cache.k_pages.shape[0], ops._ptr(cache.page_table), cache.table_stride,
+             cache.ring_pages, n_heads, cache.n_kv_heads, cache.head_dim, float(scale), float(cap),
+             int(window) if window else 0, ops._stream())
+
+
 def attend_chunks(mixer, qkv, att, part, cache) -> bool:
     """The rows of `part` (sequences of a step that go on by many tokens; see StepInfo.rows) through
-    the chunk kernel; False if it does not take the case."""
+    a chunk kernel (the tcgen05 one where the head size has it); False if none takes the case."""
     if cache.k_pages.dtype != torch.bfloat16 or not supports(mixer.head_dim) or not enabled["chunk"]:
         return False
     if part.replayed or not part.cu_host:
         return False
     cu = part.cu_host
+    slots = part.seq_slot[part.seq_offset:]
+    if enabled["chunk_tc"] and qkv.is_contiguous() and has_tc_prefill(mixer.head_dim):
+        blocks = sum((cu[i + 1] - cu[i] + 127) // 128 for i in range(len(cu) - 1))
+        chunk_tc(qkv, att, part.cu_seqlens, part.row_offset, part.token_pos, slots, part.n_seqs, blocks, cache,
+                 mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
+        return True
     blocks = sum((cu[i + 1] - cu[i] + 63) // 64 for i in range(len(cu) - 1))
-    chunk(qkv, qkv.shape[1], att, part.cu_seqlens, part.row_offset, part.token_pos, part.seq_slot[part.seq_offset:],
-          part.n_seqs, blocks, cache, mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
+    chunk(qkv, qkv.shape[1], att, part.cu_seqlens, part.row_offset, part.token_pos, slots, part.n_seqs, blocks, cache,
+          mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
     return True
 
 

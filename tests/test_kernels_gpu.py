@@ -178,7 +178,8 @@ def _ref_attention(q, k, v, pos, scale, cap, window):
                                  dict(nh=2, nkv=1, hd=256, window=None, cap=50.0, slack=0)])
 def test_attention_chunk_kernel(cfg):
     """Sequences that go on by many tokens, over a scattered paged cache that holds their keys
-    already: pieces of 1, 64, 65 and 100-odd tokens that begin inside a page, rings that have
+    already, through the mma.sync kernel and (head sizes 64, 128, 256) the tcgen05 kernel, which takes
+    the cache's tiles as they lie: pieces of 1, 64, 65 and 100-odd tokens that begin inside a page, rings that have
     wrapped and are as long as the window plus the piece needs, a key at the window's edge that
     stands out (and the one before it, which must not be seen), rows of other sequences before
     the first piece (the row base)."""
@@ -212,18 +213,26 @@ def test_attention_chunk_kernel(cfg):
     out = torch.full_like(q, 7.0)
     pos_t = torch.cat(pos).to(DEV)
     seq_slot = torch.tensor([0, 0] + slots, dtype=torch.int32, device=DEV)      # two other sequences before them
-    blocks = sum((n + 63) // 64 for n in news)
-    af.chunk(q[base:], nh * hd, out[base:], torch.tensor(cu, dtype=torch.int32, device=DEV), base, pos_t[base:],
-             seq_slot[2:], len(news), blocks + 2, cache, nh, scale, cap, window)
-    torch.cuda.synchronize()
-    assert float((out[:base] - 7.0).abs().sum()) == 0.0     # rows before the base are not touched
-    at = base
-    for i, (l, n) in enumerate(zip(seq_lens, news)):
-        for j in range(n):
-            p = l - n + j
-            want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
-            close(out[at + j].reshape(nh, hd), want.to(dt), dt)
-        at += n
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    kernels = ["mma.sync"] + (["tcgen05"] if af.has_tc_prefill(hd) else [])
+    for kernel in kernels:
+        out = torch.full_like(q, 7.0)
+        if kernel == "mma.sync":
+            af.chunk(q[base:], nh * hd, out[base:], cu_t, base, pos_t[base:], seq_slot[2:], len(news),
+                     sum((n + 63) // 64 for n in news) + 2, cache, nh, scale, cap, window)
+        else:
+            af.chunk_tc(q[base:], out[base:], cu_t, base, pos_t[base:], seq_slot[2:], len(news),
+                        sum((n + 127) // 128 for n in news) + 2, cache, nh, scale, cap, window)
+            assert not af.prefill_tc_gave_up(hd)
+        torch.cuda.synchronize()
+        assert float((out[:base] - 7.0).abs().sum()) == 0.0     # rows before the base are not touched
+        at = base
+        for i, (l, n) in enumerate(zip(seq_lens, news)):
+            for j in range(n):
+                p = l - n + j
+                want = _ref_attention(qs[i][p], ks[i], vs[i], p, scale, cap, window)
+                close(out[at + j].reshape(nh, hd), want.to(dt), dt)
+            at += n
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
