@@ -37,6 +37,8 @@ static int unroll_for(int blocks_per_warp, int token_tiles) {
     return need <= 7 ? 7 : (need <= 8 ? 8 : (need <= 9 ? 9 : (need <= 10 ? 10 : 12)));
 }
 constexpr int kMaxTokenTiles = 4;       // token tiles of 8: up to 32 rows
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 // streaming load for the weights: read once, do not keep in L1
@@ -52,7 +54,9 @@ template <int MT, int kUnroll, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
-    pdl_enter();      // the kernels before this one are complete from here on
+    // The kernel may be launched ahead of the end of the kernel before it: its CTAs are placed and a warp's first
+    // round of weights, which no kernel writes, is on its way before the activations exist.
+    pdl_launch_dependents();
     __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -86,7 +90,9 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
-    for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+    // One round: the loads of kUnroll k-blocks are all written before any is used.  In the first round the
+    // weights go out before the wait for the kernel before this one, the activations after it.
+    auto round = [&](int kb, auto first) {
         uint4 wa[kUnroll], wb[kUnroll], x[MT][kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -94,8 +100,20 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             const bool in = (kb + u) < kb_end && k < K;          // K is a multiple of 8: a 16-byte load is whole
             wa[u] = (in && ok0) ? ldg16_stream(w0 + (size_t)(kb + u) * 32) : zero;
             wb[u] = (in && ok1) ? ldg16_stream(w1 + (size_t)(kb + u) * 32) : zero;
+            if (!decltype(first)::value) {
 #pragma unroll
-            for (int m = 0; m < MT; ++m) x[m][u] = (in && tok[m]) ? ldg16(a[m] + (size_t)(kb + u) * 32) : zero;
+                for (int m = 0; m < MT; ++m) x[m][u] = (in && tok[m]) ? ldg16(a[m] + (size_t)(kb + u) * 32) : zero;
+            }
+        }
+        if (decltype(first)::value) {
+            pdl_wait();       // the kernels before this one are complete from here on: the activations may be read
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int k = (kb + u) * 32 + 8 * t4;
+                const bool in = (kb + u) < kb_end && k < K;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) x[m][u] = (in && tok[m]) ? ldg16(a[m] + (size_t)(kb + u) * 32) : zero;
+            }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -108,6 +126,15 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
                 mma_bf16(acc[m], fb, x[m][u].z, x[m][u].w);
             }
         }
+    };
+    if (MT == 1) {
+        round(kb_begin, TrueTag{});          // (a warp without a share of K still waits here)
+        for (int kb = kb_begin + kUnroll; kb < kb_end; kb += kUnroll) round(kb, FalseTag{});
+    } else {
+        // more token tiles: the first round is not set apart (its second copy of the loop body costs registers
+        // that these shapes do not have: 24 rows 4.06 -> 4.13 ms per step, 32 rows 4.57 -> 4.71 when it was)
+        pdl_wait();
+        for (int kb = kb_begin; kb < kb_end; kb += kUnroll) round(kb, FalseTag{});
     }
     // C fragment: c0 (row g, token 2t), c1 (row g, token 2t+1), c2 (row g+8, token 2t), c3 (row g+8, token 2t+1)
 #pragma unroll
@@ -169,7 +196,6 @@ qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, b
     // The attention kernel after this one may start now: it fetches old keys and values, which this
     // kernel does not touch, and waits for this kernel's end before it reads q or the newest page.
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
     __shared__ int tok_page[MT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
@@ -186,27 +212,12 @@ qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, b
     else if (rotated) { f_lo = head * hd + 16 * t; f_hi = f_lo + 1; step = 2; }
     else { f_lo = head * hd + 16 * t; f_hi = f_lo + 8; step = 1; }
 
-    // where each token's key/value goes (looked up while the product runs)
-    if (threadIdx.x < MT * 8) {
-        int page = -1;
-        const int tok = threadIdx.x;
-        if (tok < M && q.write_cache) {
-            const int seq = q.token_seq[tok];
-            if (seq >= 0) {
-                const int pos = q.token_pos[tok];
-                if (!(q.cache.ring_pages > 0 && pos + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq]))
-                    page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
-                                              kv_table_entry(q.cache, pos / kPageTokens)];
-            }
-        }
-        tok_page[tok] = page;
-    }
-
     const int k_blocks = (K + 31) / 32;
     const int per_way = (k_blocks + kSkinnyWarps - 1) / kSkinnyWarps;
     const int kb_begin = warp * per_way, kb_end = min(k_blocks, kb_begin + per_way);
     const bf16* w0 = W + (size_t)(f_lo + step * g) * ldw + 8 * t4;
     const bf16* w1 = W + (size_t)(f_hi + step * g) * ldw + 8 * t4;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
     const bf16* a[MT];
     bool tok[MT];
 #pragma unroll
@@ -217,8 +228,24 @@ qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, b
     float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int kb = kb_begin; kb < kb_end; kb += kUnroll) {
+    // where each token's key/value goes (looked up while the product runs)
+    auto setup_pages = [&]() {
+        if (threadIdx.x < MT * 8) {
+            int page = -1;
+            const int t_ = threadIdx.x;
+            if (t_ < M && q.write_cache) {
+                const int seq = q.token_seq[t_];
+                if (seq >= 0) {
+                    const int pos = q.token_pos[t_];
+                    if (!(q.cache.ring_pages > 0 && pos + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq]))
+                        page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
+                                                  kv_table_entry(q.cache, pos / kPageTokens)];
+                }
+            }
+            tok_page[t_] = page;
+        }
+    };
+    auto round = [&](int kb) {
         uint4 wa[kUnroll], wb[kUnroll], x[MT][kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -239,7 +266,10 @@ qkv_rope_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, b
                 mma_bf16(acc[m], fb, x[m][u].z, x[m][u].w);
             }
         }
-    }
+    };
+    pdl_wait();               // the kernels before this one are complete from here on
+    setup_pages();
+    for (int kb = kb_begin; kb < kb_end; kb += kUnroll) round(kb);
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
         part[warp][m][g][2 * t4] = acc[m][0];
@@ -287,6 +317,25 @@ using namespace hos;
 
 extern "C" const char* hos_last_error() { return error_buffer(); }
 
+// Whether the few-rows products are launched ahead of the end of the kernel before them (their first weights
+// are then fetched while that kernel finishes): HOS_SKINNY_AHEAD=0 or 1 in the environment.
+static int skinny_ahead_mode() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("HOS_SKINNY_AHEAD");
+        on = (e && e[0]) ? (e[0] - '0') : 2;        // 2: the gated product of up to 8 rows only; 0: none; 1: all
+    }
+    return on;
+}
+static bool skinny_ahead(bool gated = false) {
+    const int m = skinny_ahead_mode();
+    return m == 1 || (m == 2 && gated) || pdl_enabled();
+}
+// The gate/up product of a step of up to 8 rows follows a norm kernel of 8 CTAs: launched ahead of that kernel's end,
+// its CTAs are placed and their first weights on their way while the norm runs (a batch-8 step 2.123 -> 2.118 ms, one
+// sequence 1.502 -> 1.499 ms).  The other few-rows products follow kernels that fill the SMs; launched ahead they
+// take those kernels' places too early (all of them ahead: 2.12 -> 2.80 ms).
+
 // out[M, N] = A[M, K] . W[N, K]^T for M <= 32.  epilogue 0: none (out bf16 or f32); 2: gated (W has
 // 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
 // multiples of 8 elements, A and W 16-byte aligned.
@@ -308,7 +357,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
     const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
 #define HOS_SK(MT, U, G, T)                                                                                     \
-    launch_pdl(gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+    launch_ahead(skinny_ahead(G && MT == 1), gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
 #define HOS_SK_U(MT, G, T)                              \
     do {                                                \
