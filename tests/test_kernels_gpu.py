@@ -517,6 +517,91 @@ def test_a_wait_that_runs_out_is_reported_to_the_host():
     close(out, x.float() @ w.float().T, torch.bfloat16)
 
 
+def test_slot_record_kernels():
+    """The per-slot record on the device against a few lines of Python: positions handed out and moved on,
+    the input token from the record or from the caller, the xorshift64 draws (the host's `next_rand`), the
+    recent tokens in order, also after the ring of 256 has wrapped, the finished flag on a stop id and at the
+    limit, finished rows turned into padding, rows beyond the live ones left as padding."""
+    from hos_b200 import ops
+    from hos_b200.sampling import next_rand
+    n_slots, B = 7, 6
+    dev = torch.device(DEV)
+    record = torch.zeros((n_slots, ops.SLOT_WORDS), dtype=torch.int32, device=dev)
+    ring = torch.zeros((n_slots, ops.RECENT_MAX), dtype=torch.int32, device=dev)
+    slots = [5, 2, 6, 0]                                        # four live rows of a step of up to six
+    seeds = [42, 0x9E3779B97F4A7C15, 7, (1 << 63) + 12345]
+    starts = [10, 0, 300, 77]
+    vals = torch.zeros((4, ops.SLOT_WORDS), dtype=torch.int32)
+    for i in range(4):
+        vals[i, ops.SLOT_POS] = starts[i]
+        vals[i, ops.SLOT_LAST] = 1000 + i
+        lo, hi = seeds[i] & 0xffffffff, seeds[i] >> 32
+        vals[i, ops.SLOT_RNG_LO] = lo - (1 << 32) if lo >= 1 << 31 else lo
+        vals[i, ops.SLOT_RNG_HI] = hi - (1 << 32) if hi >= 1 << 31 else hi
+        vals[i, ops.SLOT_LIMIT] = [0, 3, 0, 0][i]
+    slots_t = torch.tensor(slots + [0, 0], dtype=torch.int32, device=dev)
+    ops.slot_write(record, slots_t[:4].contiguous(), vals.to(dev), 0xff)
+    meta = torch.zeros(2 + ops.MAX_STOPS, dtype=torch.int32, device=dev)
+    meta[0], meta[1], meta[2], meta[3] = 4, 2, 555, 777           # live rows; two stop ids
+    out = {k: torch.full((B,), -9, dtype=torch.int32, device=dev) for k in ("tokens", "pos", "after", "seq")}
+    cu = torch.full((B + 1,), -9, dtype=torch.int32, device=dev)
+    uniforms = torch.full((B,), -1.0, device=dev)
+    n_rec = 5
+    recent = torch.full((B, n_rec), -9, dtype=torch.int32, device=dev)
+    recent_len = torch.full((B,), -9, dtype=torch.int32, device=dev)
+    flags = (ops.BEGIN_ADVANCE | ops.BEGIN_TOKEN_FROM_RECORD | ops.BEGIN_UNIFORM | ops.BEGIN_RECENT |
+             ops.BEGIN_SKIP_FINISHED)
+    rng = list(seeds)
+    sampled_history = [[] for _ in range(4)]
+    finished = [False] * 4
+    pos = list(starts)
+    last = [1000 + i for i in range(4)]
+    for step in range(270):                                      # the ring of 256 wraps
+        ops.slot_begin(record, ring, slots_t, meta, B, flags, out["tokens"], out["pos"], out["after"], out["seq"], cu,
+                       uniforms, recent, recent_len)
+        tk, ps, af_, sq, cu_h, un, rc, rl = (t.cpu() for t in (out["tokens"], out["pos"], out["after"], out["seq"], cu,
+                                                               uniforms, recent, recent_len))
+        assert cu_h.tolist() == [0, 1, 2, 3, 4, 4, 4]
+        assert sq[4:].tolist() == [-1, -1] and tk[4:].tolist() == [-1, -1]          # padding rows
+        for i in range(4):
+            assert int(ps[i]) == pos[i] and int(af_[i]) == pos[i] + 1 and int(tk[i]) == last[i]
+            assert int(sq[i]) == (-1 if finished[i] else i)
+            new_state, u = next_rand(rng[i])
+            assert abs(float(un[i]) - u) < 1e-9, (step, i)
+            h = sampled_history[i][-n_rec:]
+            assert int(rl[i]) == len(h) and rc[i, :len(h)].tolist() == h
+            if not finished[i]:
+                pos[i] += 1
+                rng[i] = new_state
+        # what the step "samples": stop ids now and then; slot 2 (limit 3) ends after three tokens
+        toks = [(step * 7 + i) % 1000 + 2000 for i in range(4)]
+        if step == 20:
+            toks[0] = 777                                        # a stop id for the first row
+        sampled = torch.tensor(toks + [0, 0], dtype=torch.int32, device=dev)
+        ops.slot_end(record, ring, slots_t, meta, B, sampled)
+        for i in range(4):
+            if finished[i]:
+                continue
+            last[i] = toks[i]
+            sampled_history[i].append(toks[i])
+            if toks[i] in (555, 777) or (i == 1 and len(sampled_history[i]) >= 3):
+                finished[i] = True
+    rec = record.cpu()
+    assert finished == [True, True, False, False]
+    for i, s in enumerate(slots):
+        assert int(rec[s, ops.SLOT_POS]) == pos[i] and int(rec[s, ops.SLOT_COUNT]) == len(sampled_history[i])
+        assert (int(rec[s, ops.SLOT_FLAGS]) & 1) == int(finished[i]) and int(rec[s, ops.SLOT_LAST]) == last[i]
+    assert len(sampled_history[2]) == 270 and pos[0] == starts[0] + 21 and pos[1] == 3
+    assert int(rec[1].abs().sum()) == 0 and int(rec[3].abs().sum()) == 0      # slots that took no part are untouched
+    # a step of many tokens tells the records the new lengths; sequences that brought nothing are left alone
+    seq_slot = torch.tensor([5, 2, 6], dtype=torch.int32, device=dev)
+    after = torch.tensor([40, 9, 999], dtype=torch.int32, device=dev)
+    cu3 = torch.tensor([0, 30, 30, 31], dtype=torch.int32, device=dev)       # the second one brought no token
+    ops.slot_set_pos(record, seq_slot, after, cu3, 3)
+    rec = record.cpu()
+    assert int(rec[5, ops.SLOT_POS]) == 40 and int(rec[2, ops.SLOT_POS]) == pos[1] and int(rec[6, ops.SLOT_POS]) == 999
+
+
 def test_gather_rows():
     from hos_b200 import ops
     x = torch.randn(50, 331, device=DEV)
