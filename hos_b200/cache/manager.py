@@ -33,6 +33,7 @@ from .kv import KVGroup, PAGE
 from .pool import IdPool
 
 RECORD_WORDS, RECENT_TOKENS = 8, 256       # as csrc/slot_state.cu lays a record out
+STATE_ONLY_SLOTS = 256                     # slots of a model that keeps no keys, unless max_slots says otherwise
 
 
 class CacheManager:
@@ -47,8 +48,12 @@ class CacheManager:
             raise CacheError("the cache must hold at least one token")
         self.device = torch.device(device)
         self.n_pages = (max_tokens + PAGE - 1) // PAGE
-        self.max_seq_len = min(max_seq_len, self.n_pages * PAGE)
-        self.n_slots = max(1, min(self.n_pages, max_slots or 4096))
+        keeps_keys = any(need is not None for need in kv_needs)
+        # What bounds a sequence and the number of slots: the pages, where keys and values are kept (a sequence
+        # cannot be longer than all pages hold, and every live sequence holds a page at least); a model whose
+        # mixers keep state of fixed size only is bounded by neither, so its slots are simply counted.
+        self.max_seq_len = min(max_seq_len, self.n_pages * PAGE) if keeps_keys else max_seq_len
+        self.n_slots = max(1, min(self.n_pages, max_slots or 4096)) if keeps_keys else max(1, max_slots or STATE_ONLY_SLOTS)
         self.slots = IdPool(self.n_slots, "slot")
         self.lengths: Dict[int, int] = {}
         # group entries by need
@@ -185,7 +190,14 @@ class CacheManager:
                 raise CacheError("held pages and the sequences' pages differ")
 
     def tokens_capacity(self) -> int:
-        return self.n_pages * PAGE
+        """Tokens the live sequences may hold in all (each rounded up to `page_tokens`); without keys and values
+        to keep, no bound."""
+        return self.n_pages * PAGE if self.groups else 1 << 62
+
+    @property
+    def page_tokens(self) -> int:
+        """The unit in which a sequence takes room (1 where nothing grows with a sequence's length)."""
+        return PAGE if self.groups else 1
 
     def bytes_per_token(self) -> int:
         return sum(g.bytes_per_token() for g in self.groups)

@@ -137,7 +137,8 @@ class Engine:
         prompts = [list(p) for p in prompt] if batch else [list(prompt)]
         stops = self.stop_ids if stop_ids is None else tuple(stop_ids)
         outs = gen.generate(_DeviceBackend(self.runner, params), prompts, max_tokens, stops,
-                            self.runner.cache.tokens_capacity(), self.max_batch, on_token)
+                            self.runner.cache.tokens_capacity(), self.max_batch, on_token,
+                            page=self.runner.cache.page_tokens)
         return outs if batch else outs[0]
 
     # ---- sequences that stay: a second turn continues where the first ended --------------------

@@ -30,7 +30,7 @@ from typing import Callable, List, Optional, Sequence
 
 from ..errors import HosError
 
-PAGE = 64
+PAGE = 64          # the unit a sequence takes room in unless the caller says otherwise (the cache's page)
 
 
 def rounded(n: int, page: int = PAGE) -> int:
@@ -128,10 +128,11 @@ def run_batch(backend, prompts: Sequence[Sequence[int]], indices: Sequence[int],
 
 def generate(backend, prompts: Sequence[Sequence[int]],
              max_new: int, stop_ids: Sequence[int], capacity_tokens: int, max_batch: int,
-             on_token: Optional[Callable[[int, int], None]] = None) -> List[List[int]]:
-    """As many batches one after another as the requests need."""
+             on_token: Optional[Callable[[int, int], None]] = None, page: int = PAGE) -> List[List[int]]:
+    """As many batches one after another as the requests need.  `capacity_tokens`, `page`: what the cache
+    holds and the unit in which a sequence takes room there."""
     batches = plan_batches([len(p) for p in prompts], max_new, capacity_tokens, max_batch,
-                           backend.max_seq_len)
+                           backend.max_seq_len, page)
     results: List[List[int]] = [[] for _ in prompts]
     for batch in batches:
         outs = run_batch(backend, prompts, batch, max_new, stop_ids, on_token)

@@ -222,3 +222,20 @@ def test_extending_the_sequences_of_a_step_is_all_or_nothing():
     c.extend_all([a, d], [20, 64])
     assert c.lengths[a] == 20 and c.lengths[d] == 64
     c.check()
+
+
+def test_a_model_that_keeps_no_keys_is_not_sized_by_pages():
+    # mixers with state of fixed size only: slots are counted, not derived from pages; no bound on tokens
+    c = CacheManager([None, None], [None, None], [[StateNeed("s", (4,))], []], 64, 100000, torch.float32, CPU)
+    assert c.n_slots == 256 and c.max_seq_len == 100000 and not c.groups
+    assert c.page_tokens == 1 and c.tokens_capacity() > 10 ** 15 and c.chunk_room() is None
+    slots = c.admit([0] * 200)
+    c.extend_all(slots, [50000] * 200)
+    assert c.stores[0].state["s"].shape == (256, 4)
+    for s in slots:
+        c.release(s)
+    c.check()
+    c = CacheManager([None], [None], [[]], 64, 1000, torch.float32, CPU, max_slots=3)
+    assert c.n_slots == 3
+    # with keys to keep, as before
+    assert make().page_tokens == 64 and make().tokens_capacity() == 1024
