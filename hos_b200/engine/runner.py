@@ -14,6 +14,7 @@ are simply absent from later steps; their slots go back with `release`.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -125,9 +126,10 @@ class Runner:
             # decoding: static buffers and a captured graph, one per batch-size bucket
             self._check_ids(token_lists)
             self.cache.extend_all(slots, [st + 1 for st in starts])
-            sess = self.decode_session(len(slots))
-            sess.upload(slots, [t[0] for t in token_lists], longest=max(starts) + 1)
-            out = sess.run_step()
+            with self._lengths_back_on_error(slots, starts):
+                sess = self.decode_session(len(slots))
+                sess.upload(slots, [t[0] for t in token_lists], longest=max(starts) + 1)
+                out = sess.run_step()
             return out.clone() if copy else out
         if from_zero and last_only and self.use_sessions and self.prompt_sessions:
             # a short prompt step: static buffers and a captured graph per capacity, as for decoding
@@ -136,13 +138,31 @@ class Runner:
             if bucket is not None:
                 self._check_ids(token_lists)
                 self.cache.extend_all(slots, [len(t) for t in token_lists])
-                sess = self._sessions.get(("prompt",) + bucket)
-                if sess is None:
-                    sess = self._sessions[("prompt",) + bucket] = PromptSession(self, *bucket)
-                sess.feed(slots, token_lists)
-                out = sess.run()
+                with self._lengths_back_on_error(slots, starts):
+                    sess = self._sessions.get(("prompt",) + bucket)
+                    if sess is None:
+                        sess = self._sessions[("prompt",) + bucket] = PromptSession(self, *bucket)
+                    sess.feed(slots, token_lists)
+                    out = sess.run()
                 return out.clone() if copy else out
         return self._general(slots, starts, token_lists, want)
+
+    @contextlib.contextmanager
+    def _lengths_back_on_error(self, slots, starts):
+        """A step that fails after its sequences were given their pages leaves them as long as they were (the
+        pages stay theirs; what the failed step may have stored lies beyond their lengths and is never read)."""
+        try:
+            yield
+        except Exception:
+            for s, st in zip(slots, starts):
+                if s in self.cache.lengths:
+                    self.cache.lengths[s] = st
+            try:                     # the records on the device too, if the device still takes work
+                live = [(s, st) for s, st in zip(slots, starts) if s in self.cache.lengths]
+                self.write_records([s for s, _ in live], pos=[st for _, st in live])
+            except Exception:
+                pass
+            raise
 
     def decode_session(self, n: int):
         """The session that runs single-token steps of n sequences (one per batch-size bucket)."""
@@ -206,6 +226,10 @@ class Runner:
         self._check_ids(token_lists)
         # all or nothing: every sequence gets its pages for the whole step before anything runs
         self.cache.extend_all(slots, [st + len(t) for st, t in zip(starts, token_lists)])
+        with self._lengths_back_on_error(slots, starts):
+            return self._passes(slots, starts, token_lists, want)
+
+    def _passes(self, slots, starts, token_lists, want) -> torch.Tensor:
         room = self.cache.chunk_room()
         # stable: the sequences that start come first, the ones that go on by a few tokens last
         order = sorted(range(len(slots)),

@@ -437,3 +437,35 @@ def test_real_layer_sizes_whole_prompt_against_prompt_and_decode(sizes):
     r.release(a)
     r.release(b)
     r.cache.check()
+
+
+def test_a_step_that_fails_leaves_its_sequences_as_long_as_they_were(tmp_path, monkeypatch):
+    """A kernel that refuses in the middle of a step (here: made to, on the host side): the step raises, and the
+    sequences are as long as before on the host and in their records; the same step then runs."""
+    from hos_b200 import ops
+    from hos_b200.errors import KernelError
+    folder = make_folder(tmp_path, "A")
+    w, cfg = plain_model(folder)
+    r = runner_for(folder, "float32")
+    a, b = r.admit(2)
+    r.step([a, b], [[1, 2, 3], [4, 5]])
+    real = ops.norm_add_norm
+    calls = {"n": 0}
+
+    def failing(*args, **kw):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise KernelError("made to fail")
+        return real(*args, **kw)
+    monkeypatch.setattr(ops, "norm_add_norm", failing)
+    r.use_sessions = False                                  # kernel by kernel, so that the failure falls inside the step
+    with pytest.raises(KernelError, match="made to fail"):
+        r.step([a, b], [[6, 7, 8, 9], [10]])
+    monkeypatch.setattr(ops, "norm_add_norm", real)
+    assert r.length(a) == 3 and r.length(b) == 2
+    rec = r.cache.record.cpu()
+    assert int(rec[a, ops.SLOT_POS]) == 3 and int(rec[b, ops.SLOT_POS]) == 2
+    got = r.step([a, b], [[6, 7, 8, 9], [10]])
+    want = torch.stack([P.forward_logits(w, cfg, [1, 2, 3, 6, 7, 8, 9])[-1], P.forward_logits(w, cfg, [4, 5, 10])[-1]])
+    assert_close(got, want, "float32", "the step after the failed one")
+    r.cache.check()
