@@ -469,3 +469,24 @@ def test_a_step_that_fails_leaves_its_sequences_as_long_as_they_were(tmp_path, m
     want = torch.stack([P.forward_logits(w, cfg, [1, 2, 3, 6, 7, 8, 9])[-1], P.forward_logits(w, cfg, [4, 5, 10])[-1]])
     assert_close(got, want, "float32", "the step after the failed one")
     r.cache.check()
+
+
+def test_stop_ids_beyond_the_ones_the_device_knows(tmp_path):
+    """The device marks a sequence finished for the first 16 stop ids; the host checks all of them.  A stop id that
+    is the 20th of the list ends its sequence all the same, the token after it is dropped, and a sequence beside it
+    goes on; so does a stop id among the first 16."""
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, "B")
+    w, cfg = plain_model(folder)
+    eng = Engine(folder, dtype="float32", max_batch=4)
+    prompts = [[9, 8, 7, 6], [100, 200, 300]]
+    free = [P.greedy_generate(w, cfg, p, 12) for p in prompts]
+    k = next(i for i in range(2, 12) if free[0][i] not in free[0][:i])      # a token the first sequence samples then for the first time
+    stop = free[0][k]
+    others = [t for t in range(400, 440) if t not in free[0] and t not in free[1]]
+    for stops in (others[:19] + [stop], [stop] + others[:5]):
+        outs = eng.generate_ids(prompts, 12, stop_ids=stops)
+        assert outs == [P.greedy_generate(w, cfg, p, 12, stop_ids=stops) for p in prompts]
+        assert outs[0] == free[0][:k]
+    eng.runner.cache.check()
+    assert eng.runner.cache.slots.n_held == 0
