@@ -299,9 +299,15 @@ def prompt_bucket(n_tokens: int, n_seqs: int):
 
 
 class PromptSession:
-    def __init__(self, runner, tokens_cap: int, seqs_cap: int, use_graph: Optional[bool] = None):
+    """`continuing`: the sequences do not start at position 0 but go on from where the cache left them (a
+    second turn of a few dozen tokens): the same capture, with positions that begin at each sequence's length and
+    attention over the cache, planned for sequences of up to `planned_len` tokens."""
+
+    def __init__(self, runner, tokens_cap: int, seqs_cap: int, use_graph: Optional[bool] = None,
+                 continuing: bool = False, planned_len: int = 0):
         self._runner = weakref.ref(runner)
         self.t, self.q = tokens_cap, seqs_cap
+        self.continuing, self.planned_len = continuing, planned_len
         if use_graph is None:
             use_graph = os.environ.get("HOS_NO_GRAPH", "") == ""
         self.use_graph = use_graph
@@ -328,10 +334,12 @@ class PromptSession:
     def _info(self) -> StepInfo:
         return StepInfo(n_tokens=self.t, n_seqs=self.q, tokens=self.tokens, token_pos=self.pos,
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot, seq_len_after=self.after,
-                        from_zero=True, single_token=False, max_new=self.t, max_len_after=self.t,
-                        slots_host=(), cu_host=(), starts_host=(), replayed=True)
+                        from_zero=not self.continuing, single_token=False, max_new=self.t,
+                        max_len_after=self.planned_len if self.continuing else self.t,
+                        slots_host=(), cu_host=(), starts_host=(), replayed=True, min_live=1)
 
-    def feed(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]]) -> None:
+    def feed(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+             starts: Optional[Sequence[int]] = None) -> None:
         live = len(slots)
         self.n_live = live
         turn = self._turn
@@ -345,7 +353,7 @@ class PromptSession:
         for i, toks in enumerate(token_lists):
             k = len(toks)
             hn[at:at + k] = toks
-            hn[t + at:t + at + k] = np.arange(k, dtype=np.int32)
+            hn[t + at:t + at + k] = np.arange(k, dtype=np.int32) + (starts[i] if starts is not None else 0)
             hn[2 * t + at:2 * t + at + k] = i
             cu[i] = at
             at += k
@@ -357,6 +365,8 @@ class PromptSession:
         hn[o + q + 1 + live:o + 2 * q + 1] = 0
         lens = np.diff(cu)
         hn[o + 2 * q + 1:o + 3 * q + 1] = lens
+        if starts is not None:
+            hn[o + 2 * q + 1:o + 2 * q + 1 + live] += np.asarray(starts, dtype=np.int32)
         hn[o + 3 * q + 1:o + 4 * q + 1] = np.maximum(cu[1:] - 1, 0)     # the last row of each sequence
         self._dev.copy_(self._hosts[turn], non_blocking=True)
         ev = torch.cuda.Event()

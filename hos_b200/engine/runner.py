@@ -145,6 +145,23 @@ class Runner:
                     sess.feed(slots, token_lists)
                     out = sess.run()
                 return out.clone() if copy else out
+        if not single and last_only and self.use_sessions and self.prompt_sessions and all(st > 0 for st in starts):
+            # a short step of sequences that go on by several tokens (a second turn): replayed too
+            from .decode import PromptSession, length_class, prompt_bucket
+            bucket = prompt_bucket(sum(len(t) for t in token_lists), len(slots))
+            room = self.cache.chunk_room()
+            if bucket is not None and (room is None or bucket[0] <= room):
+                self._check_ids(token_lists)
+                self.cache.extend_all(slots, [st + len(t) for st, t in zip(starts, token_lists)])
+                with self._lengths_back_on_error(slots, starts):
+                    planned = length_class(max(st + len(t) for st, t in zip(starts, token_lists)), self.cache.max_seq_len)
+                    key = ("turn",) + bucket + (planned,)
+                    sess = self._sessions.get(key)
+                    if sess is None:
+                        sess = self._sessions[key] = PromptSession(self, *bucket, continuing=True, planned_len=planned)
+                    sess.feed(slots, token_lists, starts)
+                    out = sess.run()
+                return out.clone() if copy else out
         return self._general(slots, starts, token_lists, want)
 
     @contextlib.contextmanager

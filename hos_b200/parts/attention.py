@@ -130,8 +130,14 @@ class SoftmaxAttention(Mixer):
                 # sequences that bring many tokens: a kernel that takes 64 queries per key tile; the few-token
                 # tail (decoding rows that share the step): the kernel that splits one query's keys over the GPU
                 nt, st = rest.tail_tokens, rest.tail_seqs
-                padded = not rest.cu_host or rest.cu_host[-1] != rest.n_tokens     # padding rows: one kernel takes all
-                many = 0 if padded else rest.n_tokens - nt
+                if rest.replayed:
+                    # a captured step (a short second turn): which rows are which is known on the device only; from
+                    # 32 rows on all of them go to the kernel that takes many queries per key tile
+                    nt, st = 0, 0
+                    many = rest.n_tokens if rest.n_tokens >= 32 else 0
+                else:
+                    padded = not rest.cu_host or rest.cu_host[-1] != rest.n_tokens     # padding rows: one kernel takes all
+                    many = 0 if padded else rest.n_tokens - nt
                 if many > 0 and self._attend_chunks(qkv[nf:nf + many], att[nf:nf + many],
                                                     rest.rows(0, many, 0, rest.n_seqs - st), cache):
                     if nt > 0:

@@ -232,16 +232,17 @@ def attend_chunks(mixer, qkv, att, part, cache) -> bool:
     a chunk kernel (the tcgen05 one where the head size has it); False if none takes the case."""
     if cache.k_pages.dtype != torch.bfloat16 or not supports(mixer.head_dim) or not enabled["chunk"]:
         return False
-    if part.replayed or not part.cu_host:
+    if part.replayed:
+        att.zero_()                          # which rows are padding is known on the device only: a defined output
+    elif not part.cu_host:
         return False
-    cu = part.cu_host
     slots = part.seq_slot[part.seq_offset:]
     if enabled["chunk_tc"] and qkv.is_contiguous() and has_tc_prefill(mixer.head_dim):
-        blocks = sum((cu[i + 1] - cu[i] + 127) // 128 for i in range(len(cu) - 1))
+        _, blocks = prompt_blocks(part, 128)
         chunk_tc(qkv, att, part.cu_seqlens, part.row_offset, part.token_pos, slots, part.n_seqs, blocks, cache,
                  mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
         return True
-    blocks = sum((cu[i + 1] - cu[i] + 63) // 64 for i in range(len(cu) - 1))
+    _, blocks = prompt_blocks(part, 64)
     chunk(qkv, qkv.shape[1], att, part.cu_seqlens, part.row_offset, part.token_pos, slots, part.n_seqs, blocks, cache,
           mixer.n_heads, mixer.scale, mixer.softcap, mixer.window)
     return True

@@ -490,3 +490,43 @@ def test_stop_ids_beyond_the_ones_the_device_knows(tmp_path):
         assert outs[0] == free[0][:k]
     eng.runner.cache.check()
     assert eng.runner.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_short_turns_on_live_sequences_are_replayed_and_match_whole_prompts(tmp_path, name, dtype):
+    """Sequences that go on by a few dozen tokens (a second turn) in a step that wants their last logits: the step
+    is captured once per capacity and replayed with other sequences, lengths and slots; against the plain
+    implementation on the whole history, and against the same step launched kernel by kernel."""
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(21)
+    r = runner_for(folder, dtype, chunk_tokens=300)
+    eager = runner_for(folder, dtype, chunk_tokens=300)
+    eager.prompt_sessions = False
+    hist = [random_tokens(rng, n, vocab) for n in (30, 77, 5)]
+    turns = [[random_tokens(rng, n, vocab) for n in ns] for ns in ((17, 5, 40), (3, 50, 2), (33, 2, 9))]
+    slots, slots_e = r.admit(3), eager.admit(3)
+    r.step(slots, hist)
+    eager.step(slots_e, hist)
+    for turn in turns:
+        got = r.step(slots, turn)
+        same = eager.step(slots_e, turn)
+        hist = [h + t for h, t in zip(hist, turn)]
+        want = torch.stack([P.forward_logits(w, cfg, h)[-1] for h in hist])
+        assert_close(got, want, dtype, "a replayed turn")
+        assert_close(same, want, dtype, "the same turn kernel by kernel")
+        # and single tokens in between, as generation would bring them
+        nxt = [[rng.randrange(vocab)] for _ in hist]
+        got = r.step(slots, nxt)
+        hist = [h + t for h, t in zip(hist, nxt)]
+        eager.step(slots_e, nxt)
+        assert_close(got, torch.stack([P.forward_logits(w, cfg, h)[-1] for h in hist]), dtype, "a token after the turn")
+    assert any(k[0] == "turn" for k in r._sessions if isinstance(k, tuple))       # the turns did run as replayed steps
+    assert not any(isinstance(k, tuple) and k[0] == "turn" for k in eager._sessions)
+    # fewer sequences than the capture's capacity, in another order of slots
+    got = r.step([slots[2], slots[0]], [[1, 2, 3], [4, 5]])
+    want = torch.stack([P.forward_logits(w, cfg, hist[2] + [1, 2, 3])[-1], P.forward_logits(w, cfg, hist[0] + [4, 5])[-1]])
+    assert_close(got, want, dtype, "two of the three")
+    r.cache.check()
