@@ -319,14 +319,15 @@ extern "C" const char* hos_last_error() { return error_buffer(); }
 
 // Whether the few-rows products are launched ahead of the end of the kernel before them (their first weights
 // are then fetched while that kernel finishes): HOS_SKINNY_AHEAD=0 or 1 in the environment.
-// Which few-rows products (of up to 8 rows) are launched ahead of the end of the kernel before them: bits 1 gate/up,
-// 2 products with bfloat16 output (o), 4 products that write partial sums (down), 8 the q/k/v projection;
-// HOS_SKINNY_AHEAD in the environment, default 9 (see below).
+// Which few-rows products are launched ahead of the end of the kernel before them.  Of up to 8 rows: bits 1 gate/up,
+// 2 products with bfloat16 output (o), 4 products that write partial sums (down), 8 the q/k/v projection; of 9 to 32
+// rows (without weights fetched early): 16 gate/up, 32 the q/k/v projection.  HOS_SKINNY_AHEAD in the environment,
+// default 57 (see below).
 static int skinny_ahead_mode() {
     static int on = -1;
     if (on < 0) {
         const char* e = getenv("HOS_SKINNY_AHEAD");
-        on = (e && e[0]) ? atoi(e) : 9;
+        on = (e && e[0]) ? atoi(e) : 57;
     }
     return on;
 }
@@ -337,6 +338,8 @@ static bool skinny_ahead(int kind) { return (skinny_ahead_mode() & kind) != 0 ||
 // ahead 2.123 (1.502), gate/up 2.118 (1.500), gate/up and q/k/v 2.111 (1.495), gate/up and down 2.125 (1.497),
 // gate/up and o 2.414 (1.598), all four 2.697 (1.790).  The o and down products follow kernels that fill the SMs
 // (and the attention before o is itself launched ahead of q/k/v): launched ahead they take places too early.
+// With 9 to 32 rows the two products behind a norm are launched ahead as well, only to have their CTAs placed (12 rows
+// 2.652 -> 2.625 ms, 16 rows 2.958 -> 2.936, 32 rows 4.564 -> 4.558).
 
 // out[M, N] = A[M, K] . W[N, K]^T for M <= 32.  epilogue 0: none (out bf16 or f32); 2: gated (W has
 // 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
@@ -359,7 +362,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
     const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
 #define HOS_SK(MT, U, G, T)                                                                                     \
-    launch_ahead(skinny_ahead(MT != 1 ? 0 : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+    launch_ahead(skinny_ahead(MT != 1 ? (G ? 16 : 0) : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
 #define HOS_SK_U(MT, G, T)                              \
     do {                                                \
@@ -417,7 +420,7 @@ extern "C" int hos_qkv_rope_skinny(const void* A, const void* W, void* out, int 
     const unsigned grid = (unsigned)((n_heads + 2 * n_kv_heads) * (head_dim / 16));
     const int unroll = unroll_for(((K + 31) / 32 + kSkinnyWarps - 1) / kSkinnyWarps, (M + 7) / 8);
 #define HOS_QR(MT, U)                                                                                                      \
-    launch_ahead(skinny_ahead(MT == 1 ? 8 : 0), qkv_rope_skinny_kernel<MT, U>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, \
+    launch_ahead(skinny_ahead(MT == 1 ? 8 : 32), qkv_rope_skinny_kernel<MT, U>, dim3(grid), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, \
                (bf16*)out, M, K, lda, ldw, ldo, q)
 #define HOS_QR_U(MT)                     \
     do {                                 \

@@ -130,9 +130,12 @@ class SoftmaxAttention(Mixer):
                 # sequences that bring many tokens: a kernel that takes 64 queries per key tile; the few-token
                 # tail (decoding rows that share the step): the kernel that splits one query's keys over the GPU
                 nt, st = rest.tail_tokens, rest.tail_seqs
-                if rest.replayed:
-                    # a captured step (a short second turn): which rows are which is known on the device only; from
-                    # 32 rows on all of them go to the kernel that takes many queries per key tile
+                if rest.replayed and rest.single_token:
+                    many = 0                 # a captured single-token step: the kernel that splits one query's keys
+                elif rest.replayed:
+                    # a captured step of several tokens per sequence (a short second turn): which rows are which is
+                    # known on the device only; from 32 rows on all of them go to the kernel that takes many queries
+                    # per key tile
                     nt, st = 0, 0
                     many = rest.n_tokens if rest.n_tokens >= 32 else 0
                 else:

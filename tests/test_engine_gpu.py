@@ -530,3 +530,22 @@ def test_short_turns_on_live_sequences_are_replayed_and_match_whole_prompts(tmp_
     want = torch.stack([P.forward_logits(w, cfg, hist[2] + [1, 2, 3])[-1], P.forward_logits(w, cfg, hist[0] + [4, 5])[-1]])
     assert_close(got, want, dtype, "two of the three")
     r.cache.check()
+
+
+def test_single_token_steps_of_many_sequences_keep_the_decode_kernel(tmp_path, monkeypatch):
+    """A replayed single-token step of 40 sequences must not be taken for a step of many tokens per sequence: the
+    kernel that takes 64 or 128 queries per key tile would give the right logits and take twice the time."""
+    from hos_b200.parts import attention_fast as af
+    folder = make_folder(tmp_path, "D")
+    r = runner_for(folder, "bfloat16", max_tokens=64 * 64)
+    slots = r.admit(40)
+    rng = random.Random(2)
+    r.step(slots, [random_tokens(rng, 3 + i % 5, 1000) for i in range(40)])
+    calls = []
+    real = af.attend_chunks
+    monkeypatch.setattr(af, "attend_chunks", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    r.step(slots, [[rng.randrange(1000)] for _ in slots])
+    r.step(slots, [[rng.randrange(1000)] for _ in slots])
+    assert not calls
+    r.step(slots[:2], [random_tokens(rng, 40, 1000), random_tokens(rng, 9, 1000)])     # a turn of 49 tokens does take it
+    assert calls
