@@ -640,9 +640,9 @@ extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const 
     if (chunks == 0 && n_parts > 1) HOS_REFUSE("norm_add_norm: partial sums need a width that is a multiple of 4 (%d)", D);
     // A few rows (decoding): the kernel is launched ahead of the end of the product before it, so that its CTAs are
     // placed and the norms' weights fetched while that one finishes (a batch-8 step 2.154 -> 2.129 ms, one sequence
-    // 1.533 -> 1.503 ms); HOS_NORM_AHEAD=0 switches it off.
+    // 1.533 -> 1.503 ms, 64 sequences 8.098 -> 8.090 ms); HOS_NORM_AHEAD=0 switches it off.
     static const bool few_rows_ahead = !(getenv("HOS_NORM_AHEAD") && getenv("HOS_NORM_AHEAD")[0] == '0');
-    const bool ahead = pdl_enabled() || (few_rows_ahead && N <= 32);
+    const bool ahead = pdl_enabled() || (few_rows_ahead && N < kRowsKernelMinRows);
 #define HOS_VEC(TY, TH, CH) launch_ahead(ahead, norm_add_norm_vec_kernel<TY, TH, CH>, dim3(N), dim3(threads), 0, stream,         \
         (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D)
 #define HOS_LAUNCH(TY, TH)                                                                                  \
