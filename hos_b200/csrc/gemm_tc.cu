@@ -752,7 +752,11 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
         attr_set = true;
     }
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
-    launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), Cfg::kSmem, stream, mm, mn, p);
+    // The gated product of a single-token step (weights as the M operand) follows a norm kernel of a few CTAs:
+    // launched ahead of that kernel's end, its barriers and tensor memory are set up meanwhile.
+    static const bool gated_ahead = !(getenv("HOS_GEMM_TC_AHEAD") && getenv("HOS_GEMM_TC_AHEAD")[0] == '0');
+    launch_ahead(pdl_enabled() || (gated_ahead && SWAP && EPI == kGEpiGated), kernel, dim3(grid), dim3(kGemmThreads),
+                 Cfg::kSmem, stream, mm, mn, p);
     return check_launch("gemm_tc");
 }
 
