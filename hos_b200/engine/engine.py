@@ -182,6 +182,29 @@ class Engine:
     def step(self, slots, token_lists, want=None, copy: bool = True) -> torch.Tensor:
         return self.runner.step(slots, token_lists, want, copy)
 
+    # ---- embeddings ----------------------------------------------------------------------
+    def embed(self, ids: Sequence[int], pooling: str = "mean") -> torch.Tensor:
+        """The final hidden state (after the last norm, before the head) of a token sequence, pooled: "mean" over
+        all its tokens, or "last" (py/src/lib.rs:50-63, src/lib.rs:285-326).  Runs on a slot of its own, so
+        sequences that are under way are untouched.  float32 [width], on the device."""
+        if pooling not in ("mean", "last"):
+            raise HosError("pooling must be 'mean' or 'last'")
+        ids = list(ids)
+        if not ids:
+            raise HosError("embed: no tokens")
+        if len(ids) > self.runner.max_seq_len:
+            raise HosError(f"embed: {len(ids)} tokens are more than the context holds ({self.runner.max_seq_len})")
+        r = self.runner
+        slot = r.admit(1)[0]
+        try:
+            x, _ = r._hidden([slot], [0], [ids])
+            if pooling == "last":
+                x = x[-1:].contiguous()
+            h = r.model.final_norm.forward(x).float()
+        finally:
+            r.release(slot)
+        return h.mean(dim=0) if pooling == "mean" else h[0]
+
     # ---- measurements -------------------------------------------------------------------
     def perplexity(self, ids: Sequence[int]) -> Tuple[int, float, float]:
         """(scored tokens, mean negative log-likelihood in nats, perplexity) of a token

@@ -549,3 +549,25 @@ def test_single_token_steps_of_many_sequences_keep_the_decode_kernel(tmp_path, m
     assert not calls
     r.step(slots[:2], [random_tokens(rng, 40, 1000), random_tokens(rng, 9, 1000)])     # a turn of 49 tokens does take it
     assert calls
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embeddings_are_the_pooled_final_hidden_state(tmp_path, dtype):
+    """Engine.embed: the hidden state after the last norm, mean over the tokens or the last token's
+    (py/src/lib.rs:50-63), against the plain implementation; sequences under way are not disturbed."""
+    from hos_b200 import Engine
+    folder = make_folder(tmp_path, "B")
+    w, cfg = plain_model(folder)
+    eng = Engine(folder, dtype=dtype, max_batch=2)
+    ids = random_tokens(random.Random(6), 37, 512)
+    h = P.rmsnorm(P.forward_hidden(w, cfg, ids), w["model.norm.weight"], cfg.rms_norm_eps)
+    conv, = eng.open(1)
+    eng.generate_from_ids([conv], [[5, 6, 7]], max_tokens=2, temp=0.0, rep_penalty=1.0, stop_ids=[])
+    held = eng.runner.length(conv.slot)
+    tol = dict(atol=1e-4, rtol=1e-4) if dtype == "float32" else dict(atol=6e-2, rtol=6e-2)
+    torch.testing.assert_close(eng.embed(ids, "mean").cpu(), h.mean(0), **tol)
+    torch.testing.assert_close(eng.embed(ids, "last").cpu(), h[-1], **tol)
+    with pytest.raises(ValueError, match="pooling"):
+        eng.embed(ids, "max")
+    assert eng.runner.length(conv.slot) == held and eng.runner.cache.slots.n_held == 1
+    conv.close()
