@@ -37,18 +37,23 @@ def close(got, want, dtype, what):
     return float(err.max())
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_sequences_through_the_window_ring_and_in_pieces(dtype):
+# head sizes and groups: 256 and 128 with two query heads per kv head (the prompt kernel on pairs of SMs), 64 with
+# three (the one-SM kernel); the 32-bit path once
+@pytest.mark.parametrize("dtype,heads", [("float32", (2, 1, 256)), ("bfloat16", (2, 1, 256)), ("bfloat16", (4, 2, 128)),
+                                         ("bfloat16", (3, 1, 64))])
+def test_long_sequences_through_the_window_ring_and_in_pieces(dtype, heads):
     from hos_b200.engine import Runner
     from hos_b200.registry import config_from_dict
     from hos_b200 import models  # noqa: F401
-    config = config_from_dict(RAW)
+    raw = dict(RAW, num_attention_heads=heads[0], num_key_value_heads=heads[1], head_dim=heads[2],
+               query_pre_attn_scalar=heads[2])
+    config = config_from_dict(raw)
     weights = make_weights(config, 3)
     # attention that is not diffuse: larger q and k projections, so that single keys matter
     for name in list(weights):
         if name.endswith("q_proj.weight") or name.endswith("k_proj.weight"):
             weights[name] = (weights[name].float() * 6.0).to(torch.bfloat16)
-    pcfg = P.PlainConfig.from_json(RAW)
+    pcfg = P.PlainConfig.from_json(raw)
     pw = {k: v.float().cpu() for k, v in weights.items()}
     rng = random.Random(9)
     seq_a = [rng.randrange(500) for _ in range(9300)]
@@ -75,4 +80,4 @@ def test_long_sequences_through_the_window_ring_and_in_pieces(dtype):
     r.wait()
     assert r.length(a) == 9300 and r.length(b) == 4300
     r.cache.check()
-    print(f"[long context {dtype}] largest error {worst:.6f}")
+    print(f"[long context {dtype} heads {heads}] largest error {worst:.6f}")
