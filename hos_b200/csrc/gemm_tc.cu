@@ -315,15 +315,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                     const int n0 = nt * COLS + c0;
                     if (m < p.M) {
                         float f[32];
+                        if (EPI == kGEpiGated) {
+                            if (p.act == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            float x = __uint_as_float(v[j]);
-                            if (EPI == kGEpiSoftcap) x = softcap_precise(x, p.cap);
-                            if (EPI == kGEpiGated) {
-                                const float a = p.act == 0 ? gelu_tanh(x) : x / (1.f + __expf(-x));
-                                x = a * __uint_as_float(u[j]);
+                                for (int j = 0; j < 32; ++j) f[j] = gelu_tanh_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) f[j] = silu_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
                             }
-                            f[j] = x;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float x = __uint_as_float(v[j]);
+                                f[j] = EPI == kGEpiSoftcap ? softcap_precise(x, p.cap) : x;
+                            }
                         }
                         if (n0 + 32 <= p.N && (p.ldo % 8) == 0) {
                             if (sizeof(OutT) == 2) {
@@ -376,10 +381,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                         }
                         asm volatile("bar.sync 1, 128;" ::: "memory");
                         if (r < 64) {
+                            if (p.act == 0) {
 #pragma unroll
-                            for (int j = 0; j < CH; ++j) {
-                                const float a = p.act == 0 ? gelu_tanh(f[j]) : f[j] / (1.f + __expf(-f[j]));
-                                f[j] = a * exchange[r * BN + c0 + j];
+                                for (int j = 0; j < CH; ++j) f[j] = gelu_tanh_fast(f[j]) * exchange[r * BN + c0 + j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j) f[j] = silu_fast(f[j]) * exchange[r * BN + c0 + j];
                             }
                         }
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -432,7 +439,8 @@ struct PairCfg {
     static constexpr int kBBytes = 128 * GK * 2;            // this CTA's half of the tile's 256 rows of W
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = 6;
-    static constexpr int kSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kStagingBytes = 8 * 4096;          // [32 rows][128 bytes] per epilogue warp
+    static constexpr int kSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStagingBytes;
     static constexpr int kTmemCols = 512;                   // two accumulators of 256 columns
 };
 
@@ -452,6 +460,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
     uint64_t* acc_full = empty + Cfg::kStages;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    unsigned char* staging = reinterpret_cast<unsigned char*>(bars) + 256;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();               // 0: the leader of the pair
@@ -555,122 +564,207 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
             int mt, nt, ks;
             tile_coords(tile, mt, nt, ks);
             const int acc = local_tile & 1;
-            if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
-            tc_fence_after();
             const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-            const int r = quarter * 32 + lane;
-            const int m = mt * 2 * GM + (int)rank * GM + r;
-            OutT* orow = reinterpret_cast<OutT*>(p.out) + (p.k_splits > 1 ? (size_t)ks * p.M * p.ldo : 0) + (size_t)m * p.ldo;
             constexpr int COLS = (EPI == kGEpiGated) ? BN / 2 : BN;
             if constexpr (EPI == kGEpiRope) {
-                // A tile holds whole heads (head_dim divides 256).  A thread has one token's row: it rotates the
-                // pairs (i, i + head_dim/2) of q and k heads, writes the row, and puts keys and values into the cache.
+                // A tile holds whole heads (head_dim divides 256).  A thread has one token's row of the accumulator;
+                // stored, rotated and looked up from there, every access of a warp would touch 32 lines (the table of
+                // angles above all: 16 loads of 16 bytes per thread and 32 pairs).  So the warp stages 16 pairs
+                // (i, i + head_dim/2) of its 32 rows in shared memory as 32-bit values and finishes them the other
+                // way round: eight lanes per row, each with two pairs, read the angles as whole lines, rotate, and
+                // store the row to the step's output and, for keys and values, to the cache.
+                // While other CTAs stream their operands a load from L2 takes 2 to 3 us, more than a pass's work: what
+                // does not depend on the accumulator (the rows' sequences, pages and the angles of the first two
+                // passes) is fetched BEFORE the wait for the accumulator, the angles of pass t + 2 right after pass t.
                 const RopeEpi& q = p.rope;
                 const int hd = q.cache.head_dim, half = hd >> 1;
-                const bool in_rows = m < p.M;
-                const int seq = in_rows ? q.token_seq[m] : -1;
-                const int pos = in_rows ? q.token_pos[m] : 0;
+                unsigned char* stg = staging + (size_t)(warp - 2) * 4096;
+                const int m_warp0 = mt * 2 * GM + (int)rank * GM + quarter * 32;
                 const int first_head = nt * BN / hd;
-                int page = -1;
-                if (seq >= 0 && q.write_cache && first_head + BN / hd > q.n_heads &&
-                    !(q.cache.ring_pages > 0 && pos + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq]))
-                    page = q.cache.page_table[(size_t)q.seq_slot[seq] * q.cache.table_stride +
-                                              kv_table_entry(q.cache, pos / kPageTokens)];
-                const int rr = pos % kPageTokens;
+                const int heads_in_tile = BN / hd;
+                const int sub = lane >> 3, piece = lane & 7;
                 // the two warps of a lane quarter share the work: whole heads if the tile holds several, else halves
                 // of the one head's pairs
-                const int heads_in_tile = BN / hd;
                 const int col_begin = heads_in_tile > 1 ? col_half * (BN / 2) : 0, col_end = heads_in_tile > 1 ? col_begin + BN / 2 : BN;
                 const int pair_begin = heads_in_tile > 1 ? 0 : col_half * (half / 2), pair_end = heads_in_tile > 1 ? half : pair_begin + half / 2;
+                // This lane's eight rows of the second phase: row 4 k + sub.  Per row: is it a row of the step, is it
+                // rotated (a live sequence), and where its row of the page lies in the cache (kv head 0).
+                uint32_t row_mask = 0, rot_mask = 0, cache_mask = 0, rr_low = 0;     // rr_low: (position % 8), four bits a row
+                uint32_t cache_row[8];                       // in units of 8 elements (16 bytes): a layer's pages stay far below 2^32 of them
+                {
+                    int seq8[8], pos8[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int mm = m_warp0 + 4 * k + sub;
+                        const bool in_rows = mm < p.M;
+                        seq8[k] = in_rows ? q.token_seq[mm] : -1;
+                        pos8[k] = in_rows ? q.token_pos[mm] : 0;
+                        if (in_rows) row_mask |= 1u << k;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        if (seq8[k] >= 0) rot_mask |= 1u << k;
+                        cache_row[k] = 0;
+                        if (seq8[k] >= 0 && q.write_cache && first_head + heads_in_tile > q.n_heads &&
+                            !(q.cache.ring_pages > 0 && pos8[k] + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq8[k]])) {
+                            const int page = q.cache.page_table[(size_t)q.seq_slot[seq8[k]] * q.cache.table_stride +
+                                                                kv_table_entry(q.cache, pos8[k] / kPageTokens)];
+                            cache_row[k] = (uint32_t)((kv_tile_offset(q.cache, page, 0) + (size_t)(pos8[k] % kPageTokens) * hd) >> 3);
+                            cache_mask |= 1u << k;
+                            rr_low |= (uint32_t)(pos8[k] & 7) << (4 * k);
+                        }
+                    }
+                }
+                const bool swizzled = kv_is_swizzled(hd);
+                const float2* ang_lane = q.angles + (size_t)(m_warp0 + sub) * half + 2 * piece;     // row k: + 4 k half
+                auto load_angles = [&](int c0, bool rotated, float4 (&a)[8]) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        a[k] = make_float4(1.f, 0.f, 1.f, 0.f);      // values and padding rows are not rotated
+                        if (rotated && ((rot_mask >> k) & 1u))
+                            a[k] = __ldg(reinterpret_cast<const float4*>(ang_lane + (size_t)(4 * k) * half + c0));
+                    }
+                };
+                // the passes of this warp in order: heads outside, 16 pairs inside; (col0, c0) of a pass and of the one
+                // two passes on are carried along, not divided out
+                int col0 = col_begin, c0 = pair_begin;               // this pass
+                int col0_n = col_begin, c0_n = pair_begin;           // the pass whose angles are fetched next
+                auto advance = [&](int& cc, int& pc) {
+                    pc += 16;
+                    if (pc >= pair_end) { pc = pair_begin; cc += hd; }
+                };
+                auto live = [&](int cc) { return cc < col_end && nt * BN + cc < p.N; };
+                auto rotated_head = [&](int cc) { return first_head + cc / hd < q.n_heads + q.n_kv_heads; };
+                float4 ang_a[8], ang_b[8];
+                if (live(col0_n)) { load_angles(c0_n, rotated_head(col0_n), ang_a); advance(col0_n, c0_n); }
+                if (live(col0_n)) { load_angles(c0_n, rotated_head(col0_n), ang_b); advance(col0_n, c0_n); }
+
+                if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                bf16* out_lane = reinterpret_cast<bf16*>(p.out) + (size_t)(m_warp0 + sub) * p.ldo + nt * BN;   // row k: + 4 k ldo
+                const size_t out_step = (size_t)4 * p.ldo;
+                // where this lane reads the staged rows: row 4 k + sub, piece XOR (row & 7); (row & 7) = 4 (k & 1) + sub
+                const unsigned char* stg_lane = stg + sub * 128;
+                const int even_off = (piece ^ sub) << 4, odd_off = (piece ^ (4 + sub)) << 4;
+                bool odd = false;
 #pragma unroll 1
-                for (int col0 = col_begin; col0 < col_end && nt * BN + col0 < p.N; col0 += hd) {
+                for (; live(col0); advance(col0, c0), odd = !odd) {
                     const int head = first_head + col0 / hd;
                     const bool is_v = head >= q.n_heads + q.n_kv_heads;
-                    bf16* tile = nullptr;
-                    if (head >= q.n_heads && page >= 0)
-                        tile = (bf16*)(is_v ? q.cache.v_pages : q.cache.k_pages) +
-                               kv_tile_offset(q.cache, page, is_v ? head - q.n_heads - q.n_kv_heads : head - q.n_heads);
-#pragma unroll 1
-                    for (int c0 = pair_begin; c0 < pair_end; c0 += 32) {
-                        uint32_t lo[32], hi[32];
-                        tmem_ld_32x32(t_lane + col0 + c0, lo);
-                        tmem_ld_32x32(t_lane + col0 + half + c0, hi);
+                    bf16* pages = nullptr;
+                    if (head >= q.n_heads)
+                        pages = (bf16*)(is_v ? q.cache.v_pages : q.cache.k_pages) +
+                                (size_t)(is_v ? head - q.n_heads - q.n_kv_heads : head - q.n_heads) * kPageTokens * hd;
+                    {
+                        uint32_t lo[16], hi[16];
+                        tmem_ld_32x16(t_lane + col0 + c0, lo);
+                        tmem_ld_32x16(t_lane + col0 + half + c0, hi);
                         tmem_ld_wait();
-                        if (in_rows) {
-                        if (!is_v && seq >= 0) {
-                            const float4* ang = reinterpret_cast<const float4*>(q.angles + (size_t)m * half + c0);
+                        unsigned char* srow = stg + lane * 128;
 #pragma unroll
-                            for (int j = 0; j < 32; j += 2) {
-                                const float4 a2 = __ldg(ang + j / 2);          // (cos, sin) of two pairs
-                                const float x0 = __uint_as_float(lo[j]), x1 = __uint_as_float(hi[j]);
-                                lo[j] = __float_as_uint(x0 * a2.x - x1 * a2.y);
-                                hi[j] = __float_as_uint(x0 * a2.y + x1 * a2.x);
-                                const float y0 = __uint_as_float(lo[j + 1]), y1 = __uint_as_float(hi[j + 1]);
-                                lo[j + 1] = __float_as_uint(y0 * a2.z - y1 * a2.w);
-                                hi[j + 1] = __float_as_uint(y0 * a2.w + y1 * a2.z);
-                            }
-                        }
-                        bf16* dst = reinterpret_cast<bf16*>(orow) + nt * BN + col0 + c0;
+                        for (int g = 0; g < 8; ++g)        // piece g: pairs 2g and 2g + 1 as (lo, lo, hi, hi)
+                            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) =
+                                make_uint4(lo[2 * g], lo[2 * g + 1], hi[2 * g], hi[2 * g + 1]);
+                    }
+                    __syncwarp();
+                    // lanes in twos: the even one stores four low columns, the odd one the four high ones
+                    const int col = c0 + 2 * (piece & ~1) + ((piece & 1) ? half : 0);
+                    bf16* out_p = out_lane + col0 + col;
+                    const uint32_t cache_mask_here = pages != nullptr ? cache_mask : 0u;
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const uint4 a = make_uint4(
-                                pack_bf16(__uint_as_float(lo[8 * q4]), __uint_as_float(lo[8 * q4 + 1])),
-                                pack_bf16(__uint_as_float(lo[8 * q4 + 2]), __uint_as_float(lo[8 * q4 + 3])),
-                                pack_bf16(__uint_as_float(lo[8 * q4 + 4]), __uint_as_float(lo[8 * q4 + 5])),
-                                pack_bf16(__uint_as_float(lo[8 * q4 + 6]), __uint_as_float(lo[8 * q4 + 7])));
-                            const uint4 b = make_uint4(
-                                pack_bf16(__uint_as_float(hi[8 * q4]), __uint_as_float(hi[8 * q4 + 1])),
-                                pack_bf16(__uint_as_float(hi[8 * q4 + 2]), __uint_as_float(hi[8 * q4 + 3])),
-                                pack_bf16(__uint_as_float(hi[8 * q4 + 4]), __uint_as_float(hi[8 * q4 + 5])),
-                                pack_bf16(__uint_as_float(hi[8 * q4 + 6]), __uint_as_float(hi[8 * q4 + 7])));
-                            *reinterpret_cast<uint4*>(dst + 8 * q4) = a;
-                            *reinterpret_cast<uint4*>(dst + half + 8 * q4) = b;
-                            if (tile != nullptr) {
-                                *reinterpret_cast<uint4*>(tile + kv_elem_offset(rr, c0 + 8 * q4, hd)) = a;
-                                *reinterpret_cast<uint4*>(tile + kv_elem_offset(rr, half + c0 + 8 * q4, hd)) = b;
-                            }
+                    for (int k = 0; k < 8; ++k) {
+                        const float4 x = *reinterpret_cast<const float4*>(stg_lane + ((k & 1) ? odd_off : even_off) + k * 512);
+                        const float4 a2 = odd ? ang_b[k] : ang_a[k];
+                        const uint32_t lo2 = pack_bf16(x.x * a2.x - x.z * a2.y, x.y * a2.z - x.w * a2.w);
+                        const uint32_t hi2 = pack_bf16(x.x * a2.y + x.z * a2.x, x.y * a2.w + x.w * a2.z);
+                        // an even lane needs its neighbour's low pair, an odd lane its neighbour's high pair
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, (piece & 1) ? lo2 : hi2, 1);
+                        const uint2 val = (piece & 1) ? make_uint2(other, hi2) : make_uint2(lo2, other);
+                        if ((row_mask >> k) & 1u) *reinterpret_cast<uint2*>(out_p + k * out_step) = val;
+                        if ((cache_mask_here >> k) & 1u) {
+                            const int chunk = swizzled ? ((col >> 3) ^ (int)((rr_low >> (4 * k)) & 7u)) : (col >> 3);
+                            *reinterpret_cast<uint2*>(pages + (((size_t)cache_row[k] + chunk) << 3) + (col & 7)) = val;
                         }
-                        }
+                    }
+                    __syncwarp();
+                    if (live(col0_n)) {
+                        if (odd) load_angles(c0_n, rotated_head(col0_n), ang_b);
+                        else load_angles(c0_n, rotated_head(col0_n), ang_a);
+                        advance(col0_n, c0_n);
                     }
                 }
             } else {
+            if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            // A thread has one token's row of the accumulator, but rows are far apart in memory: stored from here,
+            // each 16-byte store of a warp would touch 32 lines.  The warp stages [32 rows][128 bytes] in shared
+            // memory (16-byte pieces XOR-permuted by the row, so that neither side conflicts) and copies whole lines
+            // out: eight lanes per row, four rows per store.
+            constexpr int CW = 128 / (int)sizeof(OutT);            // columns of a staged row
+            constexpr int EPP = 16 / (int)sizeof(OutT);            // elements of a 16-byte piece
+            unsigned char* stg = staging + (size_t)(warp - 2) * 4096;
+            OutT* out_base = reinterpret_cast<OutT*>(p.out) + (p.k_splits > 1 ? (size_t)ks * p.M * p.ldo : 0);
+            const int m_warp0 = mt * 2 * GM + (int)rank * GM + quarter * 32;
+            const bool vec_ok = (p.ldo % EPP) == 0;
 #pragma unroll 1
-            for (int c0 = col_half * (COLS / 2); c0 < (col_half + 1) * (COLS / 2); c0 += 32) {
-                uint32_t v[32], u[32];
-                tmem_ld_32x32(t_lane + c0, v);
-                if (EPI == kGEpiGated) tmem_ld_32x32(t_lane + BN / 2 + c0, u);
-                tmem_ld_wait();
-                const int n0 = nt * COLS + c0;
-                if (m < p.M) {
+            for (int c0 = col_half * (COLS / 2); c0 < (col_half + 1) * (COLS / 2); c0 += CW) {
+#pragma unroll
+                for (int h = 0; h < CW / 32; ++h) {
+                    uint32_t v[32], u[32];
+                    tmem_ld_32x32(t_lane + c0 + 32 * h, v);
+                    if (EPI == kGEpiGated) tmem_ld_32x32(t_lane + BN / 2 + c0 + 32 * h, u);
+                    tmem_ld_wait();
                     float f[32];
+                    if (EPI == kGEpiGated) {
+                        // the kind of activation is tested once, not per element: a select would evaluate both
+                        if (p.act == 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(v[j]);
-                        if (EPI == kGEpiSoftcap) x = softcap_precise(x, p.cap);
-                        if (EPI == kGEpiGated) {
-                            const float a = p.act == 0 ? gelu_tanh(x) : x / (1.f + __expf(-x));
-                            x = a * __uint_as_float(u[j]);
-                        }
-                        f[j] = x;
-                    }
-                    if (n0 + 32 <= p.N && (p.ldo % 8) == 0) {
-                        if (sizeof(OutT) == 2) {
-                            uint4* dst = reinterpret_cast<uint4*>(orow + n0);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                dst[q] = make_uint4(pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
-                                                    pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+                            for (int j = 0; j < 32; ++j) f[j] = gelu_tanh_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
                         } else {
-                            float4* dst = reinterpret_cast<float4*>(orow + n0);
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) dst[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+                            for (int j = 0; j < 32; ++j) f[j] = silu_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + j < p.N) orow[n0 + j] = from_float<OutT>(f[j]);
+                        for (int j = 0; j < 32; ++j) {
+                            const float x = __uint_as_float(v[j]);
+                            f[j] = EPI == kGEpiSoftcap ? softcap_precise(x, p.cap) : x;
+                        }
+                    }
+                    unsigned char* srow = stg + lane * 128;
+                    if (sizeof(OutT) == 2) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            *reinterpret_cast<uint4*>(srow + (((4 * h + q) ^ (lane & 7)) << 4)) =
+                                make_uint4(pack_bf16(f[8 * q], f[8 * q + 1]), pack_bf16(f[8 * q + 2], f[8 * q + 3]),
+                                           pack_bf16(f[8 * q + 4], f[8 * q + 5]), pack_bf16(f[8 * q + 6], f[8 * q + 7]));
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<float4*>(srow + ((q ^ (lane & 7)) << 4)) =
+                                make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
                     }
                 }
+                __syncwarp();
+                const int n0 = nt * COLS + c0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int row = 4 * k + (lane >> 3), piece = lane & 7;
+                    const int mm = m_warp0 + row, n = n0 + piece * EPP;
+                    const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 128 + ((piece ^ (row & 7)) << 4));
+                    if (mm < p.M && n < p.N) {
+                        OutT* dst = out_base + (size_t)mm * p.ldo + n;
+                        if (vec_ok && n + EPP <= p.N) {
+                            *reinterpret_cast<uint4*>(dst) = val;
+                        } else {
+                            const OutT* e = reinterpret_cast<const OutT*>(&val);
+#pragma unroll
+                            for (int j = 0; j < EPP; ++j)
+                                if (n + j < p.N) dst[j] = e[j];
+                        }
+                    }
+                }
+                __syncwarp();
             }
             }
             tc_fence_before();
