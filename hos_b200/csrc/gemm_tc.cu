@@ -571,7 +571,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                 // stored, rotated and looked up from there, every access of a warp would touch 32 lines (the table of
                 // angles above all: 16 loads of 16 bytes per thread and 32 pairs).  So the warp stages 16 pairs
                 // (i, i + head_dim/2) of its 32 rows in shared memory as 32-bit values and finishes them the other
-                // way round: eight lanes per row, each with two pairs, read the angles as whole lines, rotate, and
+                // way round: four lanes per row, each with four pairs, read the rows' angles line by line, rotate, and
                 // store the row to the step's output and, for keys and values, to the cache.
                 // While other CTAs stream their operands a load from L2 takes 2 to 3 us, more than a pass's work: what
                 // does not depend on the accumulator (the rows' sequences, pages and the angles of the first two
@@ -582,47 +582,50 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                 const int m_warp0 = mt * 2 * GM + (int)rank * GM + quarter * 32;
                 const int first_head = nt * BN / hd;
                 const int heads_in_tile = BN / hd;
-                const int sub = lane >> 3, piece = lane & 7;
+                const int sub = lane >> 2, quad = lane & 3;          // second phase: row 8 k + sub, pairs 4 quad .. 4 quad + 3
                 // the two warps of a lane quarter share the work: whole heads if the tile holds several, else halves
                 // of the one head's pairs
                 const int col_begin = heads_in_tile > 1 ? col_half * (BN / 2) : 0, col_end = heads_in_tile > 1 ? col_begin + BN / 2 : BN;
                 const int pair_begin = heads_in_tile > 1 ? 0 : col_half * (half / 2), pair_end = heads_in_tile > 1 ? half : pair_begin + half / 2;
-                // This lane's eight rows of the second phase: row 4 k + sub.  Per row: is it a row of the step, is it
-                // rotated (a live sequence), and where its row of the page lies in the cache (kv head 0).
+                // This lane's four rows of the second phase.  Per row: is it a row of the step, is it rotated (a live
+                // sequence), and where its row of the page lies in the cache (kv head 0).
                 uint32_t row_mask = 0, rot_mask = 0, cache_mask = 0, rr_low = 0;     // rr_low: (position % 8), four bits a row
-                uint32_t cache_row[8];                       // in units of 8 elements (16 bytes): a layer's pages stay far below 2^32 of them
+                uint32_t cache_row[4];                       // in units of 8 elements (16 bytes): a layer's pages stay far below 2^32 of them
                 {
-                    int seq8[8], pos8[8];
+                    int seq4[4], pos4[4];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const int mm = m_warp0 + 4 * k + sub;
+                    for (int k = 0; k < 4; ++k) {
+                        const int mm = m_warp0 + 8 * k + sub;
                         const bool in_rows = mm < p.M;
-                        seq8[k] = in_rows ? q.token_seq[mm] : -1;
-                        pos8[k] = in_rows ? q.token_pos[mm] : 0;
+                        seq4[k] = in_rows ? q.token_seq[mm] : -1;
+                        pos4[k] = in_rows ? q.token_pos[mm] : 0;
                         if (in_rows) row_mask |= 1u << k;
                     }
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        if (seq8[k] >= 0) rot_mask |= 1u << k;
+                    for (int k = 0; k < 4; ++k) {
+                        if (seq4[k] >= 0) rot_mask |= 1u << k;
                         cache_row[k] = 0;
-                        if (seq8[k] >= 0 && q.write_cache && first_head + heads_in_tile > q.n_heads &&
-                            !(q.cache.ring_pages > 0 && pos8[k] + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq8[k]])) {
-                            const int page = q.cache.page_table[(size_t)q.seq_slot[seq8[k]] * q.cache.table_stride +
-                                                                kv_table_entry(q.cache, pos8[k] / kPageTokens)];
-                            cache_row[k] = (uint32_t)((kv_tile_offset(q.cache, page, 0) + (size_t)(pos8[k] % kPageTokens) * hd) >> 3);
+                        if (seq4[k] >= 0 && q.write_cache && first_head + heads_in_tile > q.n_heads &&
+                            !(q.cache.ring_pages > 0 && pos4[k] + q.cache.ring_pages * kPageTokens < q.seq_len_after[seq4[k]])) {
+                            const int page = q.cache.page_table[(size_t)q.seq_slot[seq4[k]] * q.cache.table_stride +
+                                                                kv_table_entry(q.cache, pos4[k] / kPageTokens)];
+                            cache_row[k] = (uint32_t)((kv_tile_offset(q.cache, page, 0) + (size_t)(pos4[k] % kPageTokens) * hd) >> 3);
                             cache_mask |= 1u << k;
-                            rr_low |= (uint32_t)(pos8[k] & 7) << (4 * k);
+                            rr_low |= (uint32_t)(pos4[k] & 7) << (4 * k);
                         }
                     }
                 }
                 const bool swizzled = kv_is_swizzled(hd);
-                const float2* ang_lane = q.angles + (size_t)(m_warp0 + sub) * half + 2 * piece;     // row k: + 4 k half
+                const float2* ang_lane = q.angles + (size_t)(m_warp0 + sub) * half + 4 * quad;     // row k: + 8 k half
                 auto load_angles = [&](int c0, bool rotated, float4 (&a)[8]) {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        a[k] = make_float4(1.f, 0.f, 1.f, 0.f);      // values and padding rows are not rotated
-                        if (rotated && ((rot_mask >> k) & 1u))
-                            a[k] = __ldg(reinterpret_cast<const float4*>(ang_lane + (size_t)(4 * k) * half + c0));
+                    for (int k = 0; k < 4; ++k) {
+                        a[2 * k] = a[2 * k + 1] = make_float4(1.f, 0.f, 1.f, 0.f);      // values and padding rows are not rotated
+                        if (rotated && ((rot_mask >> k) & 1u)) {
+                            const float4* src = reinterpret_cast<const float4*>(ang_lane + (size_t)(8 * k) * half + c0);
+                            a[2 * k] = __ldg(src);
+                            a[2 * k + 1] = __ldg(src + 1);
+                        }
                     }
                 };
                 // the passes of this warp in order: heads outside, 16 pairs inside; (col0, c0) of a pass and of the one
@@ -641,11 +644,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
 
                 if (!mbar_wait_timed(&acc_full[acc], (local_tile >> 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                bf16* out_lane = reinterpret_cast<bf16*>(p.out) + (size_t)(m_warp0 + sub) * p.ldo + nt * BN;   // row k: + 4 k ldo
-                const size_t out_step = (size_t)4 * p.ldo;
-                // where this lane reads the staged rows: row 4 k + sub, piece XOR (row & 7); (row & 7) = 4 (k & 1) + sub
+                bf16* out_lane = reinterpret_cast<bf16*>(p.out) + (size_t)(m_warp0 + sub) * p.ldo + nt * BN;   // row k: + 8 k ldo
+                const size_t out_step = (size_t)8 * p.ldo;
+                // where this lane reads the staged rows: row 8 k + sub has (row & 7) = sub; pieces 2 quad and 2 quad + 1
                 const unsigned char* stg_lane = stg + sub * 128;
-                const int even_off = (piece ^ sub) << 4, odd_off = (piece ^ (4 + sub)) << 4;
+                const int off0 = ((2 * quad) ^ sub) << 4, off1 = ((2 * quad + 1) ^ sub) << 4;
                 bool odd = false;
 #pragma unroll 1
                 for (; live(col0); advance(col0, c0), odd = !odd) {
@@ -667,23 +670,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                                 make_uint4(lo[2 * g], lo[2 * g + 1], hi[2 * g], hi[2 * g + 1]);
                     }
                     __syncwarp();
-                    // lanes in twos: the even one stores four low columns, the odd one the four high ones
-                    const int col = c0 + 2 * (piece & ~1) + ((piece & 1) ? half : 0);
+                    const int col = c0 + 4 * quad;                   // the lane's four low columns; the high ones: + half
                     bf16* out_p = out_lane + col0 + col;
                     const uint32_t cache_mask_here = pages != nullptr ? cache_mask : 0u;
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const float4 x = *reinterpret_cast<const float4*>(stg_lane + ((k & 1) ? odd_off : even_off) + k * 512);
-                        const float4 a2 = odd ? ang_b[k] : ang_a[k];
-                        const uint32_t lo2 = pack_bf16(x.x * a2.x - x.z * a2.y, x.y * a2.z - x.w * a2.w);
-                        const uint32_t hi2 = pack_bf16(x.x * a2.y + x.z * a2.x, x.y * a2.w + x.w * a2.z);
-                        // an even lane needs its neighbour's low pair, an odd lane its neighbour's high pair
-                        const uint32_t other = __shfl_xor_sync(0xffffffffu, (piece & 1) ? lo2 : hi2, 1);
-                        const uint2 val = (piece & 1) ? make_uint2(other, hi2) : make_uint2(lo2, other);
-                        if ((row_mask >> k) & 1u) *reinterpret_cast<uint2*>(out_p + k * out_step) = val;
+                    for (int k = 0; k < 4; ++k) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(stg_lane + k * 1024 + off0);
+                        const float4 x1 = *reinterpret_cast<const float4*>(stg_lane + k * 1024 + off1);
+                        const float4 a0 = odd ? ang_b[2 * k] : ang_a[2 * k], a1 = odd ? ang_b[2 * k + 1] : ang_a[2 * k + 1];
+                        const uint2 lo4 = make_uint2(pack_bf16(x0.x * a0.x - x0.z * a0.y, x0.y * a0.z - x0.w * a0.w),
+                                                     pack_bf16(x1.x * a1.x - x1.z * a1.y, x1.y * a1.z - x1.w * a1.w));
+                        const uint2 hi4 = make_uint2(pack_bf16(x0.x * a0.y + x0.z * a0.x, x0.y * a0.w + x0.w * a0.z),
+                                                     pack_bf16(x1.x * a1.y + x1.z * a1.x, x1.y * a1.w + x1.w * a1.z));
+                        if ((row_mask >> k) & 1u) {
+                            *reinterpret_cast<uint2*>(out_p + k * out_step) = lo4;
+                            *reinterpret_cast<uint2*>(out_p + k * out_step + half) = hi4;
+                        }
                         if ((cache_mask_here >> k) & 1u) {
-                            const int chunk = swizzled ? ((col >> 3) ^ (int)((rr_low >> (4 * k)) & 7u)) : (col >> 3);
-                            *reinterpret_cast<uint2*>(pages + (((size_t)cache_row[k] + chunk) << 3) + (col & 7)) = val;
+                            const int rx = swizzled ? (int)((rr_low >> (4 * k)) & 7u) : 0;
+                            bf16* crow = pages + ((size_t)cache_row[k] << 3) + (col & 7);
+                            *reinterpret_cast<uint2*>(crow + (((col >> 3) ^ rx) << 3)) = lo4;
+                            *reinterpret_cast<uint2*>(crow + ((((col + half) >> 3) ^ rx) << 3)) = hi4;
                         }
                     }
                     __syncwarp();
