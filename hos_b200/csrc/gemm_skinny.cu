@@ -50,21 +50,23 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
 }
 
 // MT: token tiles of 8 (M <= 8 MT).  GATED: rows come in gate/up pairs.
-template <int MT, int kUnroll, bool GATED, typename OutT>
-__global__ void __launch_bounds__(kSkinnyThreads, 2)
+// WARPS: 8, or 4 for a CTA that keeps half the registers: four such CTAs fit an SM, so a product of up to
+// 4 x SMs CTAs runs as ONE wave where CTAs of 8 warps would come in two, with a ramp between them.
+template <int MT, int kUnroll, bool GATED, typename OutT, int WARPS = kSkinnyWarps>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
     // The kernel may be launched ahead of the end of the kernel before it: its CTAs are placed and a warp's first
     // round of weights, which no kernel writes, is on its way before the activations exist.
     pdl_launch_dependents();
-    __shared__ float part[kSkinnyWarps][MT][16][8 + 1];
+    __shared__ float part[WARPS][MT][16][8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * 16;
     // which rows of W this warp reads, and which share of K
-    const int k_ways = GATED ? kSkinnyWarps / 2 : kSkinnyWarps;
-    const int k_way = GATED ? (warp & 3) : warp;
-    const int row_base = (GATED && warp >= 4) ? gate_rows + n0 : n0;
-    const int row_limit = (GATED && warp >= 4) ? gate_rows + N : N;
+    const int k_ways = GATED ? WARPS / 2 : WARPS;
+    const int k_way = GATED ? warp % (WARPS / 2) : warp;
+    const int row_base = (GATED && warp >= WARPS / 2) ? gate_rows + n0 : n0;
+    const int row_limit = (GATED && warp >= WARPS / 2) ? gate_rows + N : N;
     // gridDim.y > 1: K is split over CTAs too; CTA (x, y) writes its 32-bit partial sums to out + y * M * ldo
     const int k_blocks = (K + 31) / 32;
     const int per_cta = (k_blocks + gridDim.y - 1) / gridDim.y;
@@ -145,7 +147,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
         part[warp][m][g + 8][2 * t4 + 1] = acc[m][3];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += kSkinnyThreads) {
+    for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += WARPS * 32) {
         const int tok = idx / 16, r = idx % 16;            // consecutive threads: consecutive features of one token
         const int m = tok >> 3, t = tok & 7;
         const int n = n0 + r;
@@ -154,13 +156,13 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
         if (GATED) {
             float gsum = 0.f, usum = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) { gsum += part[w][m][r][t]; usum += part[4 + w][m][r][t]; }
+            for (int w = 0; w < WARPS / 2; ++w) { gsum += part[w][m][r][t]; usum += part[WARPS / 2 + w][m][r][t]; }
             const float a = act == 0 ? gelu_tanh(gsum) : gsum / (1.f + __expf(-gsum));
             v = a * usum;
         } else {
             v = 0.f;
 #pragma unroll
-            for (int w = 0; w < kSkinnyWarps; ++w) v += part[w][m][r][t];
+            for (int w = 0; w < WARPS; ++w) v += part[w][m][r][t];
         }
         out[(size_t)tok * ldo + n] = from_float<OutT>(v);
     }
@@ -358,12 +360,21 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     if (k_splits > 1 && (epilogue != 0 || out_dtype != kF32))
         HOS_REFUSE("gemm_skinny: partial sums over a split K are 32-bit and take no epilogue");
     const unsigned grid = (unsigned)((N + 15) / 16);
-    const int k_ways = epilogue == 2 ? kSkinnyWarps / 2 : kSkinnyWarps;
+    // The gated product has the most CTAs (gate/up of a feed-forward): with 4 warps each, four of them fit an SM
+    // and the waves are half as many (Gemma-2 2B sizes: 576 CTAs are one wave instead of two).
+    static const int gated_warps = (getenv("HOS_SKINNY_GATED_WARPS") && atoi(getenv("HOS_SKINNY_GATED_WARPS")) == 8) ? 8 : 4;
+    const int warps = (epilogue == 2 && k_splits == 1) ? gated_warps : kSkinnyWarps;
+    const int k_ways = epilogue == 2 ? warps / 2 : warps;
     const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
     const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
-#define HOS_SK(MT, U, G, T)                                                                                     \
-    launch_ahead(skinny_ahead(MT != 1 ? (G ? 16 : 0) : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T>, dim3(grid, k_splits), dim3(kSkinnyThreads), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+#define HOS_SK_W(MT, U, G, T, WP)                                                                                \
+    launch_ahead(skinny_ahead(MT != 1 ? (G ? 16 : 0) : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T, WP>, dim3(grid, k_splits), dim3(WP * 32), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act)
+#define HOS_SK(MT, U, G, T)                                                                                     \
+    do {                                                                                                        \
+        if (G && warps == 4) HOS_SK_W(MT, U, G, T, (G ? 4 : kSkinnyWarps));                                     \
+        else HOS_SK_W(MT, U, G, T, kSkinnyWarps);                                                               \
+    } while (0)
 #define HOS_SK_U(MT, G, T)                              \
     do {                                                \
         if (unroll == 8) HOS_SK(MT, 8, G, T);           \
@@ -393,6 +404,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
 #undef HOS_SK_U
 #undef HOS_SK_M
 #undef HOS_SK
+#undef HOS_SK_W
     return check_launch("gemm_skinny");
 }
 
