@@ -732,7 +732,8 @@ def test_attention_prefill_kernel(cfg):
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (200, 300, 136), (257, 520, 2304), (1, 128, 64), (8, 1000, 200),
                                    (16, 512, 72), (17, 264, 640), (33, 2304, 96), (64, 384, 192), (65, 136, 80),
-                                   (512, 256, 64), (700, 520, 136), (1100, 2304, 200), (2048, 1000, 2304)])
+                                   (512, 256, 64), (700, 520, 136), (1100, 2304, 200), (2048, 1000, 2304),
+                                   (600, 1001, 72), (513, 260, 64)])     # rows of a width that no 16-byte store fits
 @pytest.mark.parametrize("variant", ["plain_out", "f32_out", "softcap", "gated_gelu", "gated_silu", "split_k"])
 def test_gemm_tensor_core(shape, variant):
     """The tcgen05/TMA product against float64, in both orientations (more than 64 rows: the
