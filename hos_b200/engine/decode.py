@@ -49,6 +49,19 @@ def smaller_bucket(b: int) -> int:
     return below[-1] if below else max(0, b - 64)
 
 
+def live_class(n_live: int, bucket: int):
+    """(fewest, most) live rows that a replayed step of `bucket` rows is planned for when `n_live` of them are
+    live: the rows above the next smaller bucket, cut into up to four classes.  How the attention kernel splits
+    the keys depends on how many rows take part (17 rows of 4 kv heads in two shares fill the SMs once; 24 do
+    not), so a step is captured per class, as it is per length class."""
+    lo = smaller_bucket(bucket) + 1
+    if n_live < lo:
+        return (1, lo - 1) if n_live > 0 else (lo, bucket)     # fewer rows than the bucket is meant for: one class
+    width = max(1, (bucket - lo + 1 + 3) // 4)
+    first = lo + (n_live - lo) // width * width
+    return first, min(bucket, first + width - 1)
+
+
 MIN_LENGTH_CLASS = 512
 
 
@@ -103,6 +116,7 @@ class DecodeSession:
         self.launches_per_step = 0
         self._max_len = runner.cache.max_seq_len
         self._planned_len = self._max_len       # the lengths the replayed launches are planned for (see length_class)
+        self._planned_live = (smaller_bucket(b) + 1, b)      # and the numbers of live rows (see live_class)
         self.n_live = 0
 
     @property
@@ -115,7 +129,7 @@ class DecodeSession:
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
                         max_len_after=self._planned_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
                         starts_host=(), token_slot=self.slot,      # row n is sequence n here
-                        min_live=smaller_bucket(self.b) + 1, replayed=True)
+                        min_live=self._planned_live[0], max_live=self._planned_live[1], replayed=True)
 
     def upload(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
                stop_ids: Sequence[int] = (), longest: Optional[int] = None) -> None:
@@ -127,6 +141,7 @@ class DecodeSession:
         n = len(slots)
         self.n_live = n
         self._planned_len = length_class(longest, self._max_len)
+        self._planned_live = live_class(n, self.b)
         turn = self._turn
         self._turn ^= 1
         if self._copied[turn] is not None:
@@ -216,7 +231,7 @@ class DecodeSession:
             self.logits = fn()
             self.launches_per_step = ops.launch_count - before
             return self.logits
-        g, self.logits = self._program(key + (self._planned_len,), fn)
+        g, self.logits = self._program(key + (self._planned_len, self._planned_live), fn)
         g.replay()
         return self.logits
 

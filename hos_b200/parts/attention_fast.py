@@ -34,19 +34,23 @@ def lib_for(head_dim: int) -> ops.Library:
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int],
-                  min_live: int = 0, clusters_fit=None) -> int:
+                  min_live: int = 0, clusters_fit=None, max_live: int = 0) -> int:
     """How many shares the keys of one (token, kv head) are cut into.  The kernel's CTAs (one per
     SM) take items one after another; an item costs a fixed part (look-ups, first loads, the merge)
     and a part per page.  The number of shares is the one that makes the step shortest by that
     model (constants measured at head size 256), for all `n_tokens` rows live and, if the step is
-    a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well.
+    a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well
+    (`max_live`: no more than that many of the rows are live; 0: all may be).
     `clusters_fit(s)`: how many clusters of s CTAs of the kernel run at once (None: no cluster merge); with
     all of a step's clusters on the GPU at once the shares merge through shared memory, which is cheaper."""
+    if os.environ.get("HOS_ATTN_SPLITS"):
+        forced = os.environ["HOS_ATTN_SPLITS"].split(",")
+        return int(forced[1] if window and len(forced) > 1 else forced[0])
     chunks = (group + 15) // 16
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
     per_token = max(1, n_kv_heads * chunks)
-    hi = max(1, n_tokens)
+    hi = max(1, min(n_tokens, max_live) if max_live else n_tokens)
     lo = min(max(1, min_live), hi) if min_live else hi
     lives = (lo, (lo + hi) // 2, hi, hi) if lo < hi else (hi,)      # fewest, middle and most live rows (a full batch counts twice)
     best, best_cost = 1, None
@@ -116,7 +120,8 @@ ops.on_give_up(_clear_tickets)
 def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_seq, seq_slot,
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
            window: Optional[int], max_len: int, n_splits: Optional[int] = None,
-           max_new: Optional[int] = None, min_live: int = 0, token_slot=None, cluster: bool = True) -> None:
+           max_new: Optional[int] = None, min_live: int = 0, token_slot=None, cluster: bool = True,
+           max_live: int = 0) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
     position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
     the kernel may fetch keys that lie below them while the kernel before it (which writes the
@@ -132,7 +137,7 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
         _cluster_state[hd] = want
     if n_splits is None:
         fit = (lambda s: clusters_fit(hd, n_heads, nkv, s)) if want else None
-        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit)
+        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit, max_live)
     ws = tickets = None
     if n_splits > 1:
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
@@ -273,5 +278,6 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
         return False
     decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
            mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new,
-           min_live=getattr(step, "min_live", 0), token_slot=getattr(step, "token_slot", None))
+           min_live=getattr(step, "min_live", 0), token_slot=getattr(step, "token_slot", None),
+           max_live=getattr(step, "max_live", 0))
     return True

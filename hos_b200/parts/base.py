@@ -97,6 +97,7 @@ class StepInfo:
     starts_host: Sequence[int] = ()  # each sequence's length before the step
     token_slot: Optional[torch.Tensor] = None   # int32 [N] seq_slot[token_seq] for every row (anything for padding), if at hand
     min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
+    max_live: int = 0                # ... and at most this many of its rows are live (0: all may be)
     replayed: bool = False           # the device arrays are refilled and the same launches replayed (a CUDA
                                      # graph): n_tokens and n_seqs are capacities, the host lists are empty
     fresh_seqs: int = 0              # a step that is not from_zero lists the sequences that start at position 0
