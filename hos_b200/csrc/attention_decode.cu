@@ -98,37 +98,109 @@ __device__ __forceinline__ float ld_cluster(const float* p, int rank) {
 
 // What an item is and which pages it covers: the same arithmetic on both sides of the pipe.
 struct Item {
-    int n, y, kvh, head0, n_rows, split;     // y: (kv head, chunk of 16 query heads) of the token
+    int n, y, kvh, head0, n_rows;            // y: (kv head, chunk of 16 query heads) of the token
     int seq, pos, slot, lo, lp_begin, n_tiles;
+    int part, n_parts, first_cta;            // which of the (token, y)'s shares this is; with even shares: the CTA of share 0
 };
-__device__ __forceinline__ Item make_item(const DecodeArgs& a, int index, int group, int chunks) {
-    Item it;
-    const int per_token = a.cache.n_kv_heads * chunks * a.n_splits;
-    it.n = index / per_token;
-    const int r = index % per_token;
-    const int y = it.y = r / a.n_splits;
-    it.split = r % a.n_splits;
+// everything but the share: the heads, the sequence, its slot and the lowest visible key
+__device__ __forceinline__ void item_base(const DecodeArgs& a, Item& it, int n, int y, int group, int chunks) {
+    it.n = n;
+    it.y = y;
     it.kvh = y / chunks;
     const int chunk = y % chunks;
     it.head0 = it.kvh * group + chunk * kMaxHeadsPerCta;
     it.n_rows = min(kMaxHeadsPerCta, group - chunk * kMaxHeadsPerCta);
     // the three look-ups go out together; only the slot of a step that gives none waits for the sequence
-    it.seq = a.token_seq[it.n];
-    it.pos = a.token_pos[it.n];
-    it.slot = a.token_slot != nullptr ? a.token_slot[it.n] : -1;
+    it.seq = a.token_seq[n];
+    it.pos = a.token_pos[n];
+    it.slot = a.token_slot != nullptr ? a.token_slot[n] : -1;
     it.lo = 0; it.lp_begin = 0; it.n_tiles = 0;
-    if (it.seq < 0) { it.pos = 0; return it; }
+    it.part = 0; it.n_parts = 1; it.first_cta = 0;
+    if (it.seq < 0) { it.pos = 0; return; }
     if (a.token_slot == nullptr) it.slot = a.seq_slot[it.seq];
     it.lo = a.window > 0 ? max(0, it.pos + 1 - a.window) : 0;
+}
+// Equal shares: every (token, y) is cut into n_splits shares of its own pages; item `index` is one share.
+__device__ __forceinline__ Item make_item(const DecodeArgs& a, int index, int group, int chunks) {
+    Item it;
+    const int per_token = a.cache.n_kv_heads * chunks * a.n_splits;
+    const int r = index % per_token;
+    item_base(a, it, index / per_token, r / a.n_splits, group, chunks);
+    it.part = r % a.n_splits;
+    it.n_parts = a.n_splits;
+    if (it.seq < 0) return it;
     const int lp_lo = it.lo / kPageTokens, lp_hi = it.pos / kPageTokens;
     const int n_lp = lp_hi - lp_lo + 1;
     const int per_split = (n_lp + a.n_splits - 1) / a.n_splits;
-    it.lp_begin = lp_lo + it.split * per_split;
+    it.lp_begin = lp_lo + it.part * per_split;
     const int lp_end = min(it.lp_begin + per_split, lp_hi + 1);
     it.n_tiles = max(0, lp_end - it.lp_begin);
     return it;
 }
 
+// Even shares: the pages of all (token, y) in one row (tokens in order, within a token y in order, within that
+// the pages in order), and every CTA takes the same number of consecutive pages of that row, wherever the borders
+// of the (token, y) fall.  With items of equal size a number of items that is no multiple of the SMs leaves SMs
+// idle for a whole item's time (160 items on 148 SMs: twice the time of 148); cut like this, no CTA has more than
+// one page more than another.  A (token, y) that lies in several CTAs is merged by the CTA that finishes last
+// (tickets), from two places per CTA in the workspace: the share of a (token, y) that began in an earlier CTA is
+// a CTA's first piece of work (place 0), the share of one that goes on in the next CTA its last (place 1).
+struct EvenPlan {
+    const int* pre;        // shared memory [n_tokens + 1]: pages of one y of the tokens before token n
+    int per_token;         // (kv head, chunk) pairs per token
+    int per_cta;           // pages per CTA
+    long long total;       // pages in the row
+};
+struct EvenWalk {
+    int n, y, off;         // the next piece: token, y, pages of that (token, y) already given out
+    long long at, end;     // where this CTA stands in the row, and where it stops
+};
+__device__ __forceinline__ EvenWalk even_begin(const EvenPlan& e, int n_tokens) {
+    EvenWalk w;
+    w.at = (long long)blockIdx.x * e.per_cta;
+    w.end = min(e.total, w.at + e.per_cta);
+    w.n = 0; w.y = 0; w.off = 0;
+    if (w.at >= w.end) return w;
+    int lo = 0, hi = n_tokens - 1;              // the last token whose pages begin at or before `at` and that has pages
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if ((long long)e.pre[mid] * e.per_token <= w.at) lo = mid; else hi = mid - 1;
+    }
+    while (e.pre[lo + 1] == e.pre[lo]) --lo;    // (a token without pages begins where the next one does)
+    const int pages = e.pre[lo + 1] - e.pre[lo];
+    const long long rem = w.at - (long long)e.pre[lo] * e.per_token;
+    w.n = lo;
+    w.y = (int)(rem / pages);
+    w.off = (int)(rem % pages);
+    return w;
+}
+// The next piece of this CTA's walk: false when there is none.
+__device__ __forceinline__ bool even_next(const DecodeArgs& a, const EvenPlan& e, EvenWalk& w, Item& it, int group, int chunks) {
+    if (w.at >= w.end) return false;
+    const int pages = e.pre[w.n + 1] - e.pre[w.n];
+    const int take = (int)min((long long)(pages - w.off), w.end - w.at);
+    item_base(a, it, w.n, w.y, group, chunks);
+    it.lp_begin = it.lo / kPageTokens + w.off;
+    it.n_tiles = take;
+    const long long start = (long long)e.pre[w.n] * e.per_token + (long long)w.y * pages;
+    it.first_cta = (int)(start / e.per_cta);
+    it.n_parts = (int)((start + pages - 1) / e.per_cta) - it.first_cta + 1;
+    it.part = (int)blockIdx.x - it.first_cta;
+    w.at += take;
+    w.off += take;
+    if (w.off == pages) {
+        w.off = 0;
+        if (++w.y == e.per_token) {
+            w.y = 0;
+            do { ++w.n; } while (w.n < a.n_tokens && e.pre[w.n + 1] == e.pre[w.n]);
+        }
+    }
+    return true;
+}
+constexpr int kEvenMaxTokens = 2048;   // rows of a step with even shares (their running sums live in shared memory)
+constexpr int kEvenMaxParts = 32;      // a (token, y) lies in at most this many CTAs (the CTAs' shares grow if need be)
+
+template <bool EVEN>
 __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int stages = a.stages;
@@ -141,18 +213,59 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
     float* res = wl + a.merge_rows * kMaxSplits;                                // [merge_rows][HD + 2]: this share's result, for the cluster
     uint64_t* full = reinterpret_cast<uint64_t*>(res + a.merge_rows * (HD + 2));   // [stages]
     uint64_t* empty = full + kMaxStages;                                        // [stages]
+    int* pre = reinterpret_cast<int*>(empty + kMaxStages);                      // even shares: [n_tokens + 1]
     __shared__ int last_flag;
+    __shared__ int even_most;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = a.n_heads / a.cache.n_kv_heads;
     const int chunks = (group + kMaxHeadsPerCta - 1) / kMaxHeadsPerCta;
-    const int total_items = a.n_tokens * a.cache.n_kv_heads * chunks * a.n_splits;
+    const int total_items = EVEN ? 0 : a.n_tokens * a.cache.n_kv_heads * chunks * a.n_splits;
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
         mbar_fence_init();
+        even_most = 1;
     }
     __syncthreads();
+    EvenPlan plan{pre, a.cache.n_kv_heads * chunks, 1, 0};
+    if (EVEN) {
+        // pages per token (positions and sequences were written at the head of the step, long before this kernel),
+        // their running sum, and the most pages of one token; padding rows have none
+        int most = 0;
+        for (int n = tid; n < a.n_tokens; n += kDecodeThreads) {
+            int pages = 0;
+            if (a.token_seq[n] >= 0) {
+                const int pos = a.token_pos[n];
+                const int lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+                pages = pos / kPageTokens - lo / kPageTokens + 1;
+            }
+            pre[n + 1] = pages;
+            most = max(most, pages);
+        }
+        if (most > 1) atomicMax(&even_most, most);
+        __syncthreads();
+        if (warp == 0) {                       // running sum, 32 tokens at a time
+            int carry = 0;
+            for (int n0 = 0; n0 < a.n_tokens; n0 += 32) {
+                const int n = n0 + lane;
+                int v = n < a.n_tokens ? pre[n + 1] : 0;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += u;
+                }
+                if (n < a.n_tokens) pre[n + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+            if (lane == 0) pre[0] = 0;
+        }
+        __syncthreads();
+        plan.total = (long long)pre[a.n_tokens] * plan.per_token;
+        const long long even = (plan.total + gridDim.x - 1) / gridDim.x;
+        const int least = (even_most + kEvenMaxParts - 2) / (kEvenMaxParts - 1);     // so that no (token, y) lies in too many CTAs
+        plan.per_cta = (int)max(even, (long long)max(1, least));
+    }
     pdl_launch_dependents();
     // This kernel is launched so that it may start while the projection before it still runs.  That
     // kernel writes q and the step's new keys and values, nothing else that is read here: the
@@ -168,8 +281,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             const bf16* v_pages = reinterpret_cast<const bf16*>(a.cache.v_pages);
             int t = 0;            // tiles issued so far by this CTA
             bool ok = true, waited = false;
-            for (int index = blockIdx.x; index < total_items && ok; index += gridDim.x) {
-                const Item it = make_item(a, index, group, chunks);
+            EvenWalk walk = even_begin(plan, a.n_tokens);
+            for (int index = blockIdx.x; ok; index += gridDim.x) {
+                Item it;
+                if (EVEN) {
+                    if (!even_next(a, plan, walk, it, group, chunks)) break;
+                } else {
+                    if (index >= total_items) break;
+                    it = make_item(a, index, group, chunks);
+                }
                 if (it.n_tiles == 0) continue;
                 const int* table = a.cache.page_table + (size_t)it.slot * a.cache.table_stride;
                 for (int tile = 0; tile < it.n_tiles; ++tile, ++t) {
@@ -202,18 +322,37 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
 
     // ---------------- consumers: warps 0..3 ----------------
     pdl_wait();                   // q and the newest keys are complete from here on
+    if (EVEN) {                   // padding rows are nobody's work here: a defined output for them
+        for (int n = blockIdx.x; n < a.n_tokens; n += gridDim.x)
+            if (pre[n + 1] == pre[n])
+                for (int i = tid; i < a.n_heads * HD; i += kConsumers)
+                    a.out[(size_t)n * a.out_stride + i] = __float2bfloat16(0.f);
+    }
     const int g = lane >> 2, t4 = lane & 3;
     const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
     const uint32_t q_base = smem_u32(q_s);
     int t = 0;                    // tiles consumed so far by this CTA
     bool gave_up = false;
 
-    for (int index = blockIdx.x; index < total_items; index += gridDim.x) {
-        const Item it = make_item(a, index, group, chunks);
+    EvenWalk walk = even_begin(plan, a.n_tokens);
+    for (int index = blockIdx.x;; index += gridDim.x) {
+        Item it;
+        if (EVEN) {
+            if (!even_next(a, plan, walk, it, group, chunks)) break;
+        } else {
+            if (index >= total_items) break;
+            it = make_item(a, index, group, chunks);
+        }
         const int n = it.n;
-        auto part_index = [&](int head) { return ((size_t)n * a.n_heads + head) * a.n_splits + it.split; };
+        const int mr = a.merge_rows;
+        // Where share s of this (token, y) leaves row r of its result.  Equal shares: [token][head][share].  Even
+        // shares: [CTA][place][row], place 1 for the share that begins the (token, y), place 0 for the others.
+        auto part_row = [&](int r, int s) -> size_t {
+            if (EVEN) return ((size_t)(it.first_cta + s) * 2 + (s == 0 ? 1 : 0)) * mr + r;
+            return ((size_t)n * a.n_heads + it.head0 + r) * a.n_splits + s;
+        };
         if (it.seq < 0) {                      // padding row: a defined output, nothing read
-            if (it.split == 0)
+            if (it.part == 0)
                 for (int i = tid; i < it.n_rows * HD; i += kConsumers)
                     a.out[(size_t)n * a.out_stride + (size_t)it.head0 * HD + i] = __float2bfloat16(0.f);
             continue;
@@ -326,7 +465,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
             l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
             l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
         }
-        const int mr = a.merge_rows;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = g + 8 * h;
@@ -358,29 +496,30 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
                 acc += mo[((size_t)w * mr + r) * HD + d] * f;
             }
             const int head = it.head0 + r;
-            if (a.n_splits == 1) {
+            if (it.n_parts == 1) {
                 a.out[(size_t)n * a.out_stride + (size_t)head * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
-            } else if (a.cluster_merge) {
+            } else if (!EVEN && a.cluster_merge) {
                 res[r * (HD + 2) + d] = acc;
                 if (d == 0) {
                     res[r * (HD + 2) + HD] = M;
                     res[r * (HD + 2) + HD + 1] = L;
                 }
             } else {
-                a.part_o[part_index(head) * HD + d] = acc;
+                const size_t at = part_row(r, it.part);
+                a.part_o[at * HD + d] = acc;
                 if (d == 0) {
-                    a.part_ml[part_index(head) * 2 + 0] = M;
-                    a.part_ml[part_index(head) * 2 + 1] = L;
+                    a.part_ml[at * 2 + 0] = M;
+                    a.part_ml[at * 2 + 1] = L;
                 }
             }
         }
-        if (a.n_splits == 1) continue;
-        if (a.cluster_merge) {
+        if (it.n_parts == 1) continue;
+        if (!EVEN && a.cluster_merge) {
             // ---- the shares of this (token, kv head) are the CTAs of this cluster: every one of them merges a
             // slice of the columns, reading the others' results from their shared memory ----
             cluster_barrier();
             const int per_rank = (HD + a.n_splits - 1) / a.n_splits;
-            const int d0 = it.split * per_rank, d1 = min(HD, d0 + per_rank);
+            const int d0 = it.part * per_rank, d1 = min(HD, d0 + per_rank);
             for (int idx = tid; idx < it.n_rows * (d1 - d0); idx += kConsumers) {
                 const int r = idx / (d1 - d0), d = d0 + idx % (d1 - d0);
                 float M = -INFINITY;
@@ -404,51 +543,51 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) attn_decode_kernel(DecodeAr
         consumer_sync();
         int* ticket = a.tickets + (size_t)n * a.cache.n_kv_heads * chunks + it.y;
         if (tid == 0) {
-            last_flag = atomicAdd(ticket, 1) == a.n_splits - 1;
+            last_flag = atomicAdd(ticket, 1) == it.n_parts - 1;
             if (last_flag) *ticket = 0;        // left at zero for the next launch
         }
         consumer_sync();
         if (!last_flag) continue;
         __threadfence();
         // weights of the shares, once per row: w_s = e^{M_s - M} / sum_s L_s e^{M_s - M} (0 for a share without keys)
-        for (int i = tid; i < it.n_rows * a.n_splits; i += kConsumers) {
-            const int r = i / a.n_splits, s = i % a.n_splits;
-            const size_t base = ((size_t)n * a.n_heads + it.head0 + r) * a.n_splits;
-            wm[r * kMaxSplits + s] = __ldcg(&a.part_ml[(base + s) * 2]);
-            wl[r * kMaxSplits + s] = __ldcg(&a.part_ml[(base + s) * 2 + 1]);
+        for (int i = tid; i < it.n_rows * it.n_parts; i += kConsumers) {
+            const int r = i / it.n_parts, s = i % it.n_parts;
+            const size_t at = part_row(r, s);
+            wm[r * kMaxSplits + s] = __ldcg(&a.part_ml[at * 2]);
+            wl[r * kMaxSplits + s] = __ldcg(&a.part_ml[at * 2 + 1]);
         }
         consumer_sync();
         if (tid < it.n_rows) {
             float M = -INFINITY, L = 0.f;
-            for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, wm[tid * kMaxSplits + s]);
-            for (int s = 0; s < a.n_splits; ++s) {
+            for (int s = 0; s < it.n_parts; ++s) M = fmaxf(M, wm[tid * kMaxSplits + s]);
+            for (int s = 0; s < it.n_parts; ++s) {
                 const float ms = wm[tid * kMaxSplits + s];
                 const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
                 L += wl[tid * kMaxSplits + s] * f;
                 wm[tid * kMaxSplits + s] = f;
             }
             const float inv = L > 0.f ? 1.f / L : 0.f;
-            for (int s = 0; s < a.n_splits; ++s) wm[tid * kMaxSplits + s] *= inv;
+            for (int s = 0; s < it.n_parts; ++s) wm[tid * kMaxSplits + s] *= inv;
         }
         consumer_sync();
         for (int idx = tid; idx < it.n_rows * HD; idx += kConsumers) {
             const int r = idx / HD, d = idx % HD;
             const int head = it.head0 + r;
-            const float* po = a.part_o + ((size_t)n * a.n_heads + head) * a.n_splits * HD + d;
+            const float* po = a.part_o + d;
             float acc = 0.f;
             int s = 0;
-            for (; s + 8 <= a.n_splits; s += 8) {          // eight loads in flight; a share without keys wrote nothing
+            for (; s + 8 <= it.n_parts; s += 8) {          // eight loads in flight; a share without keys wrote nothing
                 float w[8], v[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) w[j] = wm[r * kMaxSplits + s + j];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = w[j] != 0.f ? __ldcg(po + (size_t)(s + j) * HD) : 0.f;
+                for (int j = 0; j < 8; ++j) v[j] = w[j] != 0.f ? __ldcg(po + part_row(r, s + j) * HD) : 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc += w[j] * v[j];
             }
-            for (; s < a.n_splits; ++s) {
+            for (; s < it.n_parts; ++s) {
                 const float w = wm[r * kMaxSplits + s];
-                if (w != 0.f) acc += w * __ldcg(po + (size_t)s * HD);
+                if (w != 0.f) acc += w * __ldcg(po + part_row(r, s) * HD);
             }
             a.out[(size_t)n * a.out_stride + (size_t)head * HD + d] = __float2bfloat16(acc);
         }
@@ -492,6 +631,12 @@ extern "C" long long hos_attn_decode_workspace(int n_tokens, int n_heads, int n_
     if (n_splits <= 1) return 0;
     return (long long)n_tokens * n_heads * n_splits * (HD + 2);
 }
+// The same for even shares: two places per CTA.
+extern "C" long long hos_attn_decode_even_workspace(int n_heads, int n_kv_heads) {
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return 0;
+    const int group = n_heads / n_kv_heads;
+    return (long long)sm_count() * 2 * (group < kMaxHeadsPerCta ? group : kMaxHeadsPerCta) * (HD + 2);
+}
 extern "C" long long hos_attn_decode_tickets(int n_tokens, int n_heads, int n_kv_heads) {
     const int group = n_heads / n_kv_heads;
     return (long long)n_tokens * n_kv_heads * ((group + kMaxHeadsPerCta - 1) / kMaxHeadsPerCta);
@@ -519,12 +664,12 @@ static int clusters_that_fit(int size, int smem) {
     if (known[size][0] == smem) return known[size][1];
     static bool wide = false;
     if (size > 8 && !wide) {
-        wide = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        wide = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         cudaGetLastError();
     }
     static int attr_smem = 0;
     if (smem > attr_smem &&
-        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess)
+        cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess)
         attr_smem = smem;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)size);
@@ -536,15 +681,16 @@ static int clusters_that_fit(int size, int smem) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if ((size > 8 && !wide) || cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel, &cfg) != cudaSuccess) n = 0;
+    if ((size > 8 && !wide) || cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<false>, &cfg) != cudaSuccess) n = 0;
     cudaGetLastError();
     known[size][0] = smem;
     known[size][1] = n;
     return n;
 }
-static int decode_smem(int group, int* stages_out) {
+static int decode_smem(int group, int* stages_out, int even_tokens = 0) {
     const int merge_rows = group < kMaxHeadsPerCta ? group : kMaxHeadsPerCta;
-    const int fixed = kQBytes + 5 * merge_rows * (HD + 2) * 4 + 2 * merge_rows * kMaxSplits * 4 + 2 * kMaxStages * 8 + 128;
+    const int fixed = kQBytes + 5 * merge_rows * (HD + 2) * 4 + 2 * merge_rows * kMaxSplits * 4 + 2 * kMaxStages * 8 + 128 +
+                      (even_tokens > 0 ? ((even_tokens + 1) * 4 + 15) / 16 * 16 : 0);
     int stages = (kSmemBudget - fixed) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages_out) *stages_out = stages;
@@ -569,31 +715,35 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
     if (head_dim != HD) HOS_REFUSE("attn_decode: built for head_dim %d, asked for %d", HD, head_dim);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         HOS_REFUSE("attn_decode: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
-    if (n_splits < 1 || n_splits > kMaxSplits) HOS_REFUSE("attn_decode: %d splits (1..%d)", n_splits, kMaxSplits);
-    if (n_splits > 1 && (workspace == nullptr || tickets == nullptr))
+    const bool even = n_splits == 0;            // 0: even shares, every CTA the same number of pages
+    if (n_splits < 0 || n_splits > kMaxSplits) HOS_REFUSE("attn_decode: %d splits (0: even shares, 1..%d)", n_splits, kMaxSplits);
+    if (n_splits != 1 && (workspace == nullptr || tickets == nullptr))
         HOS_REFUSE("attn_decode: splits need a workspace and tickets");
+    if (even && n_tokens > kEvenMaxTokens) HOS_REFUSE("attn_decode: even shares take up to %d rows, not %d", kEvenMaxTokens, n_tokens);
     if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0)
         HOS_REFUSE("attn_decode: query rows must be 16-byte aligned");
     const int group = n_heads / n_kv_heads;
     const int chunks = (group + kMaxHeadsPerCta - 1) / kMaxHeadsPerCta;
-    const long long items = (long long)n_tokens * n_kv_heads * chunks * n_splits;
+    const long long items = (long long)n_tokens * n_kv_heads * chunks * (even ? 1 : n_splits);
     if (items > (1ll << 30)) HOS_REFUSE("attn_decode: too many work items");
     DecodeArgs a;
     a.merge_rows = group < kMaxHeadsPerCta ? group : kMaxHeadsPerCta;
     int stages = 0;
-    const int smem = decode_smem(group, &stages);
+    const int smem = decode_smem(group, &stages, even ? n_tokens : 0);
     if (stages < 2) HOS_REFUSE("attn_decode: shared memory holds fewer than two stages for head_dim %d", HD);
     a.stages = stages;
-    static int attr_smem = 0;
-    if (smem > attr_smem) {
-        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            HOS_REFUSE("attn_decode: cannot get %d bytes of shared memory", smem);
-        attr_smem = smem;
+    static int attr_smem[2] = {0, 0};
+    if (smem > attr_smem[even]) {
+        const cudaError_t e = even
+            ? cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+            : cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) HOS_REFUSE("attn_decode: cannot get %d bytes of shared memory", smem);
+        attr_smem[even] = smem;
     }
     a.q = (const bf16*)q; a.q_stride = q_stride;
     a.out = (bf16*)out; a.out_stride = out_stride;
     a.part_o = workspace;
-    a.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * n_splits * HD : nullptr;
+    a.part_ml = workspace ? workspace + (even ? (size_t)sm_count() * 2 * a.merge_rows : (size_t)n_tokens * n_heads * n_splits) * HD : nullptr;
     a.tickets = tickets;
     a.token_pos = token_pos; a.token_seq = token_seq; a.seq_slot = seq_slot; a.token_slot = token_slot;
     a.cache = PagedKV{k_pages, v_pages, page_table, table_stride, ring_pages, n_kv_heads, head_dim};
@@ -618,12 +768,16 @@ extern "C" int hos_attn_decode(const void* q, int q_stride, void* out, int out_s
         if ((long long)fit * n_splits >= items) {
             a.cluster_merge = 1;
             cfg.numAttrs = 2;
-            cudaLaunchKernelEx(&cfg, attn_decode_kernel, a);
+            cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, a);
             return check_launch("attn_decode (clusters)");
         }
     }
+    if (even) {
+        launch_ahead(true, attn_decode_kernel<true>, dim3(sm_count()), dim3(kDecodeThreads), smem, stream, a);
+        return check_launch("attn_decode (even shares)");
+    }
     const int grid = items < sm_count() ? (int)items : sm_count();
-    launch_ahead(true, attn_decode_kernel, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
+    launch_ahead(true, attn_decode_kernel<false>, dim3(grid), dim3(kDecodeThreads), smem, stream, a);
     return check_launch("attn_decode");
 }
 

@@ -17,7 +17,8 @@ MAX_SPLITS = 64
 _libs: Dict[int, ops.Library] = {}
 enabled = {"decode": True, "prefill": True, "prefill_tc": True, "chunk": True, "chunk_tc": True,
            "prefill_pair": os.environ.get("HOS_ATTN_PAIR", "1") != "0",
-           "decode_cluster": os.environ.get("HOS_ATTN_CLUSTER", "1") != "0"}
+           "decode_cluster": os.environ.get("HOS_ATTN_CLUSTER", "1") != "0",
+           "decode_even": os.environ.get("HOS_ATTN_EVEN", "1") != "0"}
 _pair_state: Dict[int, bool] = {}
 _cluster_state: Dict[int, bool] = {}     # tests switch a kernel off to compare with the plain one
 
@@ -43,9 +44,6 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     (`max_live`: no more than that many of the rows are live; 0: all may be).
     `clusters_fit(s)`: how many clusters of s CTAs of the kernel run at once (None: no cluster merge); with
     all of a step's clusters on the GPU at once the shares merge through shared memory, which is cheaper."""
-    if os.environ.get("HOS_ATTN_SPLITS"):
-        forced = os.environ["HOS_ATTN_SPLITS"].split(",")
-        return int(forced[1] if window and len(forced) > 1 else forced[0])
     chunks = (group + 15) // 16
     span = min(max_len, window) if window else max_len
     pages = (span + ops.PAGE_TOKENS - 1) // ops.PAGE_TOKENS + (1 if window else 0)
@@ -54,18 +52,40 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     lo = min(max(1, min_live), hi) if min_live else hi
     lives = (lo, (lo + hi) // 2, hi, hi) if lo < hi else (hi,)      # fewest, middle and most live rows (a full batch counts twice)
     best, best_cost = 1, None
-    for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
+    sms = ops.sm_count()
+
+    def merge_us(s: int) -> float:
         if s == 1:
-            merge = 0.0
-        elif clusters_fit is not None and s <= CLUSTER_SHARES and hi * per_token * s <= ops.sm_count() \
+            return 0.0
+        if clusters_fit is not None and s <= CLUSTER_SHARES and hi * per_token * s <= sms \
                 and clusters_fit(s) >= hi * per_token:
-            merge = _CLUSTER_MERGE_US + _CLUSTER_MERGE_PER_SHARE_US * s      # the shares are one cluster
-        else:
-            merge = _MERGE_US + _MERGE_PER_SHARE_US * s
-        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + merge
-        cost = sum(-(-live * per_token * s // ops.sm_count()) * per_item for live in lives)
+            return _CLUSTER_MERGE_US + _CLUSTER_MERGE_PER_SHARE_US * s      # the shares are one cluster
+        return _MERGE_US + _MERGE_PER_SHARE_US * s
+
+    for s in range(1, min(MAX_SPLITS, max(1, (pages + 1) // 2)) + 1):
+        per_item = _ITEM_US + _PAGE_US * -(-pages // s) + merge_us(s)
+        cost = sum(-(-live * per_token * s // sms) * per_item for live in lives)
         if best_cost is None or cost < 0.97 * best_cost:          # more shares only for a clear gain
             best, best_cost = s, cost
+    # Even shares (0): every CTA the same number of pages, wherever the borders of the (token, kv head) fall.  They
+    # cost a fixed part more (the running sums of the pages, a second piece of work per CTA, a merge of almost
+    # every (token, kv head) through the workspace) and save the last round that equal items leave mostly empty.
+    # Weighed with a model that knows that many CTAs at once share the memory's speed: a round of all SMs is
+    # slower per page than a last round of a few.
+    # Only with at least half as many (token, kv head) as SMs: fewer lie in many CTAs each, and the last CTA of
+    # each merges all of its parts (one sequence at 32,768 keys: 1.90 ms a step against 1.75 ms in clusters).
+    if enabled["decode_even"] and n_tokens <= EVEN_MAX_ROWS and 2 * lo * per_token >= sms:
+        def page_us(active: int) -> float:
+            return max(_PAGE_US, active * _PAGE_SHARED_US)
+        share, equal, even = -(-pages // best), 0.0, 0.0
+        for live in lives:
+            full, rest = divmod(live * per_token * best, sms)      # rounds of all SMs, and what is left for a last one
+            equal += full * (_ITEM_US + share * page_us(sms) + merge_us(best))
+            if rest:
+                equal += _ITEM_US + share * page_us(rest) + merge_us(best)
+            even += _EVEN_US + -(-live * per_token * pages // sms) * page_us(sms)
+        if even < 0.95 * equal:
+            return 0
     return best
 
 
@@ -77,6 +97,13 @@ _ITEM_US, _PAGE_US, _MERGE_US, _MERGE_PER_SHARE_US = 6.0, 0.9, 1.0, 0.275
 # than through the workspace (one sequence, 8,192 keys, 16 shares: 17.4 -> 14.6 us; a window of 4,096: 13.5 -> 10.7).
 CLUSTER_SHARES = 16
 _CLUSTER_MERGE_US, _CLUSTER_MERGE_PER_SHARE_US = 0.3, 0.03
+# Even shares against the best equal shares, a step of Gemma-2 2B sizes at 8,192 keys (ms): 20 sequences 3.63 / 3.81,
+# 40: 5.80 / 6.92, 56: 7.28 / 8.15, 64: 8.04 / 8.02; but 8: 2.41 / 2.11, 16: 3.16 / 2.94, 32: 4.82 / 4.58.
+# The model that fits these: 12 us more per launch, and a page costs a CTA 0.9 us alone but 0.0085 us times the
+# number of CTAs that stream at once (64 KB per page at head size 256: 7.7 TB/s between them).
+_EVEN_US = 12.0
+_PAGE_SHARED_US = 0.0085
+EVEN_MAX_ROWS = 2048
 
 
 _fit_known: Dict[tuple, int] = {}
@@ -139,8 +166,13 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
         fit = (lambda s: clusters_fit(hd, n_heads, nkv, s)) if want else None
         n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit, max_live)
     ws = tickets = None
-    if n_splits > 1:
+    if n_splits == 0:            # even shares: every CTA the same number of pages, two places per CTA for what is cut
+        f = lib.lib.hos_attn_decode_even_workspace
+        f.restype, f.argtypes = ctypes.c_longlong, [ctypes.c_int, ctypes.c_int]
+        ws = torch.empty(int(f(n_heads, nkv)), dtype=torch.float32, device=q.device)
+    elif n_splits > 1:
         ws = torch.empty(n_tokens * n_heads * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+    if n_splits != 1:
         tickets = _tickets(q.device, n_tokens * nkv * ((n_heads // nkv + 15) // 16))
     lib.call("hos_attn_decode", ops._ptr(q), q_stride, ops._ptr(out), out.shape[1], ops._ptr(ws),
              ops._ptr(tickets), ops._ptr(token_pos), ops._ptr(token_seq), ops._ptr(seq_slot), ops._ptr(token_slot),

@@ -13,7 +13,7 @@ def test_shares_are_within_bounds(n_tokens, max_len, window):
         s = af.decode_splits(n_tokens, 4, 2, max_len, window, 0, fit)
         span = min(max_len, window) if window else max_len
         pages = (span + 63) // 64 + (1 if window else 0)
-        assert 1 <= s <= af.MAX_SPLITS
+        assert 0 <= s <= af.MAX_SPLITS                # 0: even shares
         assert s <= max(1, (pages + 1) // 2)          # a share holds two pages or more (or there is one share)
 
 
@@ -28,6 +28,22 @@ def test_few_sequences_are_cut_finely_and_many_not_at_all():
     assert 2 <= af.decode_splits(8, 4, 2, 8192, None) <= 8
     assert af.decode_splits(32, 4, 2, 8192, None) == 1         # 128 items: one wave as they are
     assert af.decode_splits(64, 4, 2, 8192, None) == 1
+
+
+def test_even_shares_where_equal_ones_leave_a_round_mostly_empty():
+    assert af.decode_splits(40, 4, 2, 8192, None) == 0         # 160 items on 148 SMs
+    assert af.decode_splits(40, 4, 2, 8192, 4096) == 0
+    assert af.decode_splits(56, 4, 2, 8192, None) == 0
+    assert af.decode_splits(48, 4, 2, 8192, None, 37, None, 40) == 0       # a bucket of 48 rows, 37 to 40 of them live
+    for n in (1, 2, 4, 8, 16, 32):                              # whole rounds (or clusters): nothing to gain
+        assert af.decode_splits(n, 4, 2, 8192, None, 0, lambda s: 1000) >= 1
+    was = af.enabled["decode_even"]
+    af.enabled["decode_even"] = False
+    try:
+        assert af.decode_splits(40, 4, 2, 8192, None) >= 1
+    finally:
+        af.enabled["decode_even"] = was
+    assert af.decode_splits(af.EVEN_MAX_ROWS + 1, 4, 2, 8192, None) >= 1   # more rows than the kernel's running sums hold
 
 
 def test_clusters_that_do_not_fit_change_nothing():

@@ -395,6 +395,43 @@ def test_many_sequences_decode_together(tmp_path, n_seqs, dtype):
     r.cache.check()
 
 
+@pytest.mark.parametrize("name", ["C", "D", "F"])
+def test_decoding_with_even_shares_of_the_keys(tmp_path, name, monkeypatch):
+    """The other way to cut the decode attention's work: every CTA the same number of pages, wherever the borders
+    of the (token, kv head) fall, merged by the last arrival.  Forced here for every launch (the planner asks for
+    it only from dozens of sequences on): 23 sequences of 1 to 7 pages, whose window rings have wrapped (C, D),
+    in a session of 24 rows (one padding row), decoded until the shortest have left.  Every logit against the
+    plain implementation."""
+    from hos_b200.parts import attention_fast as af
+    calls = []
+    monkeypatch.setattr(af, "decode_splits", lambda *a, **k: (calls.append(1), 0)[1])
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(11)
+    lens = [rng.randrange(1, 440) for _ in range(23)]
+    lens[0], lens[1], lens[2] = 1, 64, 65                       # a page's borders
+    total = [n + rng.randrange(2, 9) for n in lens]
+    seqs = [random_tokens(rng, t, vocab) for t in total]
+    want = [P.forward_logits(w, cfg, s) for s in seqs]
+    r = runner_for(folder, "bfloat16", max_tokens=64 * 256)
+    slots = r.admit(len(seqs))
+    r.step(slots, [s[:n] for s, n in zip(seqs, lens)])
+    pos, live = list(lens), list(range(len(seqs)))
+    while live:
+        got = r.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live])
+        assert_close(got, torch.stack([want[i][pos[i]] for i in live]), "bfloat16", f"decode with {len(live)} live")
+        for i in live:
+            pos[i] += 1
+        for i in [i for i in live if pos[i] == total[i]]:
+            r.release(slots[i])
+        live = [i for i in live if pos[i] < total[i]]
+    r.wait()
+    assert calls, "the decode kernel was never asked how to cut its work"
+    assert not af.decode_gave_up(TINY[name][0]["head_dim"])
+    r.cache.check()
+
+
 @pytest.mark.parametrize("sizes", [dict(num_hidden_layers=4),
                                    dict(num_hidden_layers=2, hidden_size=4608, num_attention_heads=32,
                                         num_key_value_heads=16, head_dim=128, intermediate_size=36864,

@@ -619,7 +619,7 @@ def test_gather_rows():
                                  dict(nh=4, nkv=2, hd=128, window=None, cap=50.0),
                                  dict(nh=8, nkv=4, hd=256, window=200, cap=50.0),
                                  dict(nh=2, nkv=1, hd=256, window=None, cap=50.0)])
-@pytest.mark.parametrize("n_splits", [1, 3, 8, 64])
+@pytest.mark.parametrize("n_splits", [0, 1, 3, 8, 64])      # 0: even shares
 def test_attention_decode_kernel(cfg, n_splits):
     """The tensor-core decode kernel over a scattered paged cache: rings that have wrapped,
     a key at the window's edge that stands out, sequences of 1 token and of several pages,
