@@ -861,14 +861,25 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
     return check_launch("gemm_tc");
 }
 
-// Whether products of many tokens run on pairs of SMs (HOS_GEMM_PAIR=0 keeps them on single SMs).
-static bool pair_enabled() {
-    static int on = -1;
-    if (on < 0) {
+// From how many rows on a product runs on pairs of SMs: everything above the swapped orientation's 64 rows
+// (HOS_GEMM_PAIR=0, or hos_gemm_tc_pair_min_rows(0): never; single SMs with tiles of 128 x 256 run instead).
+// It was 512 while the pair kernel's epilogues stored row by row; since they store whole lines a prompt of 70
+// to 128 tokens takes 2.7 ms instead of 3.9 (Gemma-2 2B sizes), 129 to 256 tokens 2.9 instead of 4.1, 257 to 384
+// 3.4 instead of 4.4, and a decode step of 128 sequences 15.0 ms instead of 15.9.
+static int& pair_min_state() {
+    static int n = -1;
+    if (n < 0) {
         const char* e = getenv("HOS_GEMM_PAIR");
-        on = (e && e[0] == '0') ? 0 : 1;
+        n = (e && e[0] == '0') ? 0 : 65;
     }
-    return on == 1;
+    return n;
+}
+static int pair_min_rows() { return pair_min_state(); }
+static bool pair_enabled() { return pair_min_state() > 0; }
+extern "C" int hos_gemm_tc_pair_min_rows(int rows) {
+    if (rows != 0 && rows <= 64) HOS_REFUSE("gemm_tc: up to 64 rows run in the swapped orientation: %d", rows);
+    pair_min_state() = rows;
+    return 0;
 }
 
 template <int EPI, typename OutT>
@@ -953,9 +964,9 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     if (epilogue == kGEpiGated && out_dtype != kBF16) HOS_REFUSE("gemm_tc: the gated epilogue writes bfloat16");
     if (k_splits < 1) k_splits = 1;
     const bool swap = M <= 64;
-    const bool pairs = !swap && M >= 512 && pair_enabled();
+    const bool pairs = !swap && M >= pair_min_rows() && pair_enabled();
     if (k_splits > 1 && (!(swap || pairs) || epilogue != kGEpiNone || workspace == nullptr))
-        HOS_REFUSE("gemm_tc: K splits need up to 64 or at least 512 rows, no epilogue and a workspace");
+        HOS_REFUSE("gemm_tc: K splits need up to 64 rows or the kernel on pairs of SMs, no epilogue and a workspace");
     const int w_rows = epilogue == kGEpiGated ? 2 * N : N;
     GemmParams p;
     p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.k_splits = k_splits; p.gate_rows = N; p.cap = cap; p.act = act;
@@ -1052,14 +1063,15 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
 // SMs): out[M, N] = A . W^T, N = (n_heads + 2 n_kv_heads) * head_dim (n_kv_heads = 0: q heads only), q and k heads
 // rotated over the whole head (rotate-half) by the angles[M][head_dim / 2] (cos, sin) of hos_rope_table, keys and
 // values stored at the tokens' places if write_cache.
-// head_dim 64, 128 or 256; at least 512 rows; bfloat16 output whose rows are 16-byte aligned.
+// head_dim 64, 128 or 256; rows enough for the kernel on pairs of SMs; bfloat16 output whose rows are 16-byte aligned.
 extern "C" int hos_gemm_tc_qkv_rope(const void* A, const void* W, void* out, int M, int N, int K, int lda, int ldw, int ldo,
                                     int n_heads, int n_kv_heads, int head_dim, const int* token_pos, const int* token_seq,
                                     const int* seq_slot, const int* seq_len_after, const float* angles, void* k_pages,
                                     void* v_pages, const int* page_table, int table_stride, int ring_pages,
                                     int write_cache, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M < 512) HOS_REFUSE("gemm_tc_qkv_rope: %d rows are fewer than the 512 this kernel is for", M);
+    if (!pair_enabled() || M < pair_min_rows())
+        HOS_REFUSE("gemm_tc_qkv_rope: %d rows do not run on pairs of SMs (from %d rows on; 0: never)", M, pair_min_rows());
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
         HOS_REFUSE("gemm_tc_qkv_rope: K and the leading dimensions must be multiples of 8 elements and the operands "
                    "16-byte aligned (K %d lda %d ldw %d)", K, lda, ldw);

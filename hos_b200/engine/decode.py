@@ -300,8 +300,8 @@ def sample_into(logits: torch.Tensor, out: torch.Tensor, p: SamplingParams, unif
 # start at position 0 and want the logits of their last token, are therefore captured too: one
 # graph per (token capacity, sequence capacity), the real token count, lengths and slots being
 # data.  Rows beyond the real tokens are padding; sequences beyond the real ones have length 0.
-PROMPT_TOKENS = 256
-PROMPT_TOKEN_BUCKETS = (16, 32, 64, 128, 256)
+PROMPT_TOKENS = 512
+PROMPT_TOKEN_BUCKETS = (16, 32, 64, 128, 256, 384, 512)
 PROMPT_SEQ_BUCKETS = (1, 2, 4, 8)
 
 

@@ -5,13 +5,17 @@ CTAs when the output alone gives too few tiles to fill the GPU."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
 
 from .. import ops
 
-PAIR_MIN_ROWS = 512      # from here on the product runs on pairs of SMs
+# From here on the product runs on pairs of SMs (everything above the swapped orientation's 64 rows); a number no
+# product reaches when HOS_GEMM_PAIR=0 keeps them on single SMs.
+NEVER = 1 << 30
+PAIR_MIN_ROWS = NEVER if os.environ.get("HOS_GEMM_PAIR", "1") == "0" else 65
 _lib: Optional[ops.Library] = None
 enabled = True          # tests switch it off to compare with the plain kernel
 
@@ -21,6 +25,13 @@ def lib() -> ops.Library:
     if _lib is None:
         _lib = ops.Library("gemm_tc")
     return _lib
+
+
+def set_pair_min_rows(rows: int) -> None:
+    """From how many rows on products run on pairs of SMs (0: never); tests compare the two kernels with it."""
+    global PAIR_MIN_ROWS
+    lib().call("hos_gemm_tc_pair_min_rows", int(rows))
+    PAIR_MIN_ROWS = rows if rows > 0 else NEVER
 
 
 def can_take(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
@@ -106,7 +117,7 @@ def gave_up() -> bool:
 
 def can_fuse_qkv_rope(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int, style: int, inv_freq) -> bool:
     """Whether the q/k/v projection of many tokens can rotate q and k and store keys and values in its own
-    epilogue: the product's rules, at least 512 rows, the whole head rotated with the rotate-half pairing,
+    epilogue: the product's rules, rows enough for the kernel on pairs of SMs, the whole head rotated with the rotate-half pairing,
     a head size that divides the tile's 256 columns."""
     if not enabled or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] < PAIR_MIN_ROWS:
         return False

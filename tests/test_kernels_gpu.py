@@ -780,6 +780,47 @@ def test_gemm_tensor_core(shape, variant):
     assert not gemm_tc.gave_up()
 
 
+@pytest.mark.parametrize("shape", [(65, 136, 80), (200, 300, 136), (700, 520, 136), (1100, 2304, 200)])
+@pytest.mark.parametrize("variant", ["plain_out", "f32_out", "softcap", "gated_gelu", "gated_silu"])
+def test_gemm_tensor_core_on_single_sms(shape, variant):
+    """The kernel that runs when products are kept off the pairs of SMs (HOS_GEMM_PAIR=0): tiles of 128 x 256 on
+    one SM each, every epilogue, against float64."""
+    from hos_b200 import ops
+    from hos_b200.parts import gemm_tc
+    M, N, K = shape
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gated = variant.startswith("gated")
+    w = (torch.randn(2 * N if gated else N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double() @ w[:N].double().T
+    was = gemm_tc.PAIR_MIN_ROWS
+    gemm_tc.set_pair_min_rows(0)
+    try:
+        assert gemm_tc.k_splits_for(M, N, K, ops.EPI_NONE) == 1
+        if variant == "plain_out":
+            out = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+            gemm_tc.matmul(a, w, out)
+            close(out, ref.to(torch.bfloat16), torch.bfloat16)
+        elif variant == "f32_out":
+            out = torch.empty((M, N), device=DEV)
+            gemm_tc.matmul(a, w, out)
+            close(out, ref, torch.float32, scale=3)
+        elif variant == "softcap":
+            out = torch.empty((M, N), device=DEV)
+            gemm_tc.matmul(a, w, out, ops.EPI_SOFTCAP, cap=0.6)
+            close(out, 0.6 * torch.tanh(ref / 0.6), torch.float32, scale=3)
+        else:
+            act = "gelu_tanh" if variant == "gated_gelu" else "silu"
+            out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+            gemm_tc.matmul(a, w, out, ops.EPI_GATED, act=ops.ACTIVATIONS[act])
+            g, u = ref, a.double() @ w[N:].double().T
+            af = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
+            close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
+        assert not gemm_tc.gave_up()
+    finally:
+        gemm_tc.set_pair_min_rows(was if was != gemm_tc.NEVER else 0)
+
+
 def test_gemm_tensor_core_refuses_what_it_cannot_take():
     from hos_b200 import ops
     from hos_b200.parts import gemm_tc, linear
