@@ -390,9 +390,16 @@ class PromptSession:
 
     def _forward(self) -> torch.Tensor:
         r = self.runner
-        x = r.model.hidden(self._info(), r.cache)
-        ops.slot_set_pos(r.cache.record, self.slot, self.after, self.cu, self.q)    # the records learn the new lengths
-        return r.model.logits(x, self.rows)
+        # the kernels of a prompt step, short ones too, are launched ahead of one another's end: their set-up
+        # (barriers, tensor memory, the first look-ups) runs under the kernel before (40 tokens 2.15 -> 2.11 ms, 256
+        # tokens 2.90 -> 2.81, 512 tokens 3.66 -> 3.48 at Gemma-2 2B sizes)
+        ops.set_launch_ahead(True)
+        try:
+            x = r.model.hidden(self._info(), r.cache)
+            ops.slot_set_pos(r.cache.record, self.slot, self.after, self.cu, self.q)    # the records learn the new lengths
+            return r.model.logits(x, self.rows)
+        finally:
+            ops.set_launch_ahead(False)
 
     def run(self) -> torch.Tensor:
         """The step on what `feed` put in: float32 logits [real sequences, vocab] at each one's last
