@@ -861,7 +861,12 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
     return check_launch("gemm_tc");
 }
 
-// From how many rows on a product runs on pairs of SMs: everything above the swapped orientation's 64 rows
+// Up to this many rows the weights are the 128-row operand and the tokens the columns (16, 32, 64 or 128 of them).
+// It was 64 until the orientations were measured against each other again: a decode step of 72 sequences 9.45 -> 8.95 ms,
+// of 128 sequences 14.97 -> 14.46 ms, a prompt of 100 tokens 2.62 -> 2.37 ms (Gemma-2 2B sizes); from 33 to 64 rows the
+// kernel on pairs of SMs is 0.7 ms a step slower than this one.
+constexpr int kSwapMaxRows = 128;
+// From how many rows on a product runs on pairs of SMs: everything above the swapped orientation's rows
 // (HOS_GEMM_PAIR=0, or hos_gemm_tc_pair_min_rows(0): never; single SMs with tiles of 128 x 256 run instead).
 // It was 512 while the pair kernel's epilogues stored row by row; since they store whole lines a prompt of 70
 // to 128 tokens takes 2.7 ms instead of 3.9 (Gemma-2 2B sizes), 129 to 256 tokens 2.9 instead of 4.1, 257 to 384
@@ -870,14 +875,14 @@ static int& pair_min_state() {
     static int n = -1;
     if (n < 0) {
         const char* e = getenv("HOS_GEMM_PAIR");
-        n = (e && e[0] == '0') ? 0 : 65;
+        n = (e && e[0] == '0') ? 0 : kSwapMaxRows + 1;
     }
     return n;
 }
 static int pair_min_rows() { return pair_min_state(); }
 static bool pair_enabled() { return pair_min_state() > 0; }
 extern "C" int hos_gemm_tc_pair_min_rows(int rows) {
-    if (rows != 0 && rows <= 64) HOS_REFUSE("gemm_tc: up to 64 rows run in the swapped orientation: %d", rows);
+    if (rows != 0 && rows <= kSwapMaxRows) HOS_REFUSE("gemm_tc: up to %d rows run in the swapped orientation: %d", kSwapMaxRows, rows);
     pair_min_state() = rows;
     return 0;
 }
@@ -947,7 +952,7 @@ extern "C" long long hos_gemm_tc_workspace(int M, int N, int k_splits) {
 
 // out[M, N] = A[M, K] . W[N, K]^T, bf16 operands.  out_dtype: 1 bf16, 0 f32.  epilogue: 0 none,
 // 1 soft-cap (f32 output), 2 gated (W has 2N rows: gate rows, then up rows at row N).
-// M <= 64 runs swapped; k_splits > 1 is allowed only then and only without an epilogue, and
+// M <= 128 runs swapped; k_splits > 1 is allowed only then and only without an epilogue, and
 // needs `workspace` (see hos_gemm_tc_workspace).  With reduce_now == 0 the partial sums are left
 // in the workspace as [k_splits_used][M][N] floats for the consumer to add, `out` is not written,
 // and the number of parts is returned through *parts_used.  lda, ldw, ldo in elements.
@@ -963,10 +968,10 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     if (epilogue == kGEpiSoftcap && out_dtype != kF32) HOS_REFUSE("gemm_tc: the soft-cap epilogue writes 32-bit");
     if (epilogue == kGEpiGated && out_dtype != kBF16) HOS_REFUSE("gemm_tc: the gated epilogue writes bfloat16");
     if (k_splits < 1) k_splits = 1;
-    const bool swap = M <= 64;
+    const bool swap = M <= kSwapMaxRows;
     const bool pairs = !swap && M >= pair_min_rows() && pair_enabled();
     if (k_splits > 1 && (!(swap || pairs) || epilogue != kGEpiNone || workspace == nullptr))
-        HOS_REFUSE("gemm_tc: K splits need up to 64 rows or the kernel on pairs of SMs, no epilogue and a workspace");
+        HOS_REFUSE("gemm_tc: K splits need up to %d rows or the kernel on pairs of SMs, no epilogue and a workspace", kSwapMaxRows);
     const int w_rows = epilogue == kGEpiGated ? 2 * N : N;
     GemmParams p;
     p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.k_splits = k_splits; p.gate_rows = N; p.cap = cap; p.act = act;
@@ -1016,14 +1021,15 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
         if (out_dtype == kBF16) HOS_GO(256, kGEpiNone, false, bf16, tiles);
         HOS_GO(256, kGEpiNone, false, float, tiles);
     }
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((rc = make_map(&mn, A, M, K, lda, bn))) return rc;
     if (epilogue == kGEpiGated) {
         if ((rc = make_map(&mm, W, w_rows, K, ldw, 64))) return rc;
         const int tiles = (N + 63) / 64;
         if (bn == 16) HOS_GO(16, kGEpiGated, true, bf16, tiles);
         if (bn == 32) HOS_GO(32, kGEpiGated, true, bf16, tiles);
-        HOS_GO(64, kGEpiGated, true, bf16, tiles);
+        if (bn == 64) HOS_GO(64, kGEpiGated, true, bf16, tiles);
+        HOS_GO(128, kGEpiGated, true, bf16, tiles);
     }
     if ((rc = make_map(&mm, W, w_rows, K, ldw, GM))) return rc;
     const int tiles = ((N + GM - 1) / GM) * k_splits;
@@ -1032,7 +1038,8 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
         p.ldo = N;
         if (bn == 16) rc = launch<16, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
         else if (bn == 32) rc = launch<32, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
-        else rc = launch<64, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
+        else if (bn == 64) rc = launch<64, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
+        else rc = launch<128, kGEpiNone, true, float>(mm, mn, p, tiles, stream);
         if (rc) return rc;
         if (parts_used) *parts_used = k_splits;
         if (!reduce_now) return 0;
@@ -1046,16 +1053,19 @@ extern "C" int hos_gemm_tc(const void* A, const void* W, void* out, int out_dtyp
     if (epilogue == kGEpiSoftcap) {
         if (bn == 16) HOS_GO(16, kGEpiSoftcap, true, float, tiles);
         if (bn == 32) HOS_GO(32, kGEpiSoftcap, true, float, tiles);
-        HOS_GO(64, kGEpiSoftcap, true, float, tiles);
+        if (bn == 64) HOS_GO(64, kGEpiSoftcap, true, float, tiles);
+        HOS_GO(128, kGEpiSoftcap, true, float, tiles);
     }
     if (out_dtype == kBF16) {
         if (bn == 16) HOS_GO(16, kGEpiNone, true, bf16, tiles);
         if (bn == 32) HOS_GO(32, kGEpiNone, true, bf16, tiles);
-        HOS_GO(64, kGEpiNone, true, bf16, tiles);
+        if (bn == 64) HOS_GO(64, kGEpiNone, true, bf16, tiles);
+        HOS_GO(128, kGEpiNone, true, bf16, tiles);
     }
     if (bn == 16) HOS_GO(16, kGEpiNone, true, float, tiles);
     if (bn == 32) HOS_GO(32, kGEpiNone, true, float, tiles);
-    HOS_GO(64, kGEpiNone, true, float, tiles);
+    if (bn == 64) HOS_GO(64, kGEpiNone, true, float, tiles);
+    HOS_GO(128, kGEpiNone, true, float, tiles);
 #undef HOS_GO
 }
 

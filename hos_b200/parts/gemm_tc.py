@@ -1,5 +1,5 @@
 """Python face of the tcgen05/TMA matrix product (csrc/gemm_tc.cu): bfloat16 operands, both
-K-major, 32-bit accumulation in tensor memory.  Up to 64 rows of activations run in the
+K-major, 32-bit accumulation in tensor memory.  Up to 128 rows of activations run in the
 swapped orientation (the weight tile is the 128-row operand), where K may be split over
 CTAs when the output alone gives too few tiles to fill the GPU."""
 from __future__ import annotations
@@ -12,10 +12,11 @@ import torch
 
 from .. import ops
 
-# From here on the product runs on pairs of SMs (everything above the swapped orientation's 64 rows); a number no
+SWAP_MAX_ROWS = 128      # up to here the weight tile is the 128-row operand (csrc/gemm_tc.cu: kSwapMaxRows)
+# From here on the product runs on pairs of SMs (everything above the swapped orientation's rows); a number no
 # product reaches when HOS_GEMM_PAIR=0 keeps them on single SMs.
 NEVER = 1 << 30
-PAIR_MIN_ROWS = NEVER if os.environ.get("HOS_GEMM_PAIR", "1") == "0" else 65
+PAIR_MIN_ROWS = NEVER if os.environ.get("HOS_GEMM_PAIR", "1") == "0" else SWAP_MAX_ROWS + 1
 _lib: Optional[ops.Library] = None
 enabled = True          # tests switch it off to compare with the plain kernel
 
@@ -60,7 +61,7 @@ def k_splits_for(m: int, n: int, k: int, epilogue: int) -> int:
         # fewer tiles than there are pairs; K is then split so that most pairs have one, 8 blocks of 64 or more each
         tiles = ((m + 255) // 256) * ((n + 255) // 256)
         return max(1, min((ops.sm_count() // 2) // tiles, ((k + 63) // 64) // 8))
-    if m > 64:
+    if m > SWAP_MAX_ROWS:
         return 1
     tiles = (n + 127) // 128
     if tiles >= ops.sm_count() // 2:

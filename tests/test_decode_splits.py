@@ -80,7 +80,8 @@ def test_k_splits_of_the_products():
     assert gemm_tc.k_splits_for(8, 2304, 9216, gated) == 1 and gemm_tc.k_splits_for(600, 2304, 9216, gated) == 1
     assert gemm_tc.k_splits_for(40, 2304, 9216, none) > 1              # 18 tiles of 128 features
     assert gemm_tc.k_splits_for(40, 256000, 2304, none) == 1           # the head: tiles enough
-    assert gemm_tc.k_splits_for(100, 2304, 9216, none) == 8            # from 65 rows on: pairs of SMs, 9 tiles for 74 pairs
+    assert gemm_tc.k_splits_for(100, 2304, 9216, none) == 8            # up to 128 rows: the weights are the M operand, 18 tiles
+    assert gemm_tc.k_splits_for(200, 2304, 9216, none) == 8            # from 129 rows on: pairs of SMs, 9 tiles for 74 pairs
     assert gemm_tc.k_splits_for(512, 2304, 9216, none) == 4 and gemm_tc.k_splits_for(512, 2304, 2048, none) == 4
     assert gemm_tc.k_splits_for(1024, 2304, 9216, none) == 2
     assert gemm_tc.k_splits_for(2048, 2304, 9216, none) == 1 and gemm_tc.k_splits_for(8192, 2304, 2048, none) == 1

@@ -731,15 +731,15 @@ def test_attention_prefill_kernel(cfg):
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (200, 300, 136), (257, 520, 2304), (1, 128, 64), (8, 1000, 200),
-                                   (16, 512, 72), (17, 264, 640), (33, 2304, 96), (64, 384, 192), (65, 136, 80),
+                                   (16, 512, 72), (17, 264, 640), (33, 2304, 96), (64, 384, 192), (65, 136, 80), (100, 2304, 264), (129, 200, 72),
                                    (512, 256, 64), (700, 520, 136), (1100, 2304, 200), (2048, 1000, 2304),
                                    (600, 1001, 72), (513, 260, 64)])     # rows of a width that no 16-byte store fits
 @pytest.mark.parametrize("variant", ["plain_out", "f32_out", "softcap", "gated_gelu", "gated_silu", "split_k"])
 def test_gemm_tensor_core(shape, variant):
-    """The tcgen05/TMA product against float64, in both orientations (more than 64 rows: the
-    activation tile is the 128-row operand; up to 64: the weight tile is) and, from 512 rows on,
-    on pairs of SMs (tiles of 256 x 256, cta_group::2), with row and column counts and a K that
-    fill no tile, and every epilogue; and against the plain kernel."""
+    """The tcgen05/TMA product against float64, in both orientations (up to 128 rows: the weight
+    tile is the 128-row operand and the tokens are 16, 32, 64 or 128 columns; more: pairs of SMs with
+    tiles of 256 x 256, cta_group::2), with row and column counts and a K that fill no tile, and
+    every epilogue; and against the plain kernel."""
     from hos_b200 import ops
     from hos_b200.parts import gemm_tc
     M, N, K = shape
@@ -771,7 +771,7 @@ def test_gemm_tensor_core(shape, variant):
         af = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.silu(g)
         close(out, (af * u).to(torch.bfloat16), torch.bfloat16)
     else:
-        if M > 64:
+        if M > 128:
             pytest.skip("K is split in the swapped orientation only")
         for ks in (2, 3, 100):
             out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
@@ -780,7 +780,7 @@ def test_gemm_tensor_core(shape, variant):
     assert not gemm_tc.gave_up()
 
 
-@pytest.mark.parametrize("shape", [(65, 136, 80), (200, 300, 136), (700, 520, 136), (1100, 2304, 200)])
+@pytest.mark.parametrize("shape", [(129, 136, 80), (200, 300, 136), (700, 520, 136), (1100, 2304, 200)])
 @pytest.mark.parametrize("variant", ["plain_out", "f32_out", "softcap", "gated_gelu", "gated_silu"])
 def test_gemm_tensor_core_on_single_sms(shape, variant):
     """The kernel that runs when products are kept off the pairs of SMs (HOS_GEMM_PAIR=0): tiles of 128 x 256 on
