@@ -678,6 +678,41 @@ def test_attention_decode_kernel(cfg, n_splits):
     close(out3, out, dt)
 
 
+@pytest.mark.parametrize("hd,nh,nkv", [(64, 4, 2), (256, 2, 1)])
+def test_attention_decode_even_shares_one_long_sequence_among_short_ones(hd, nh, nkv):
+    """Even shares where they are hardest: one sequence of 40,000 keys (625 pages: more than 32 CTAs' fair
+    shares, so the CTAs' shares grow until it lies in at most 32 of them) beside sequences of 1 to 3 pages and
+    padding rows at the front, in the middle and at the end; one key far back in the long sequence stands out.
+    Twice in a row (the counters must be back at zero), against float64."""
+    from hos_b200.parts import attention_fast as af
+    dt = torch.bfloat16
+    torch.manual_seed(8)
+    seq_lens = [40000, 3, 70, 129, 64]
+    ks = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    vs = [torch.randn(l, nkv, hd).to(dt).float() for l in seq_lens]
+    qs = [torch.randn(nh, hd).to(dt).float() for _ in seq_lens]
+    g = nh // nkv
+    ks[0][1234] = qs[0][0::g][:nkv] * 4.0                    # a far key that takes most of the weight
+    scale = 1.0 / math.sqrt(hd)
+    cache, slots = _fill_cache([k.to(DEV) for k in ks], [v.to(DEV) for v in vs], seq_lens, nkv, hd, 0, dt,
+                               n_slots=7, scatter_seed=5, fill=0.0)
+    items = [(-1, 0), (0, 39999), (1, 2), (-1, 0), (2, 69), (3, 128), (4, 63), (-1, 0)]
+    q = torch.stack([qs[i] if i >= 0 else torch.zeros(nh, hd) for i, _ in items]).reshape(len(items), nh * hd)
+    q = q.to(DEV).to(dt).contiguous()
+    pos = torch.tensor([p for _, p in items], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([i for i, _ in items], dtype=torch.int32, device=DEV)
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out = torch.full_like(q, 7.0)
+        af.decode(q, nh * hd, out, pos, seq, slot_t, cache, len(items), nh, scale, 0.0, None, 40000, n_splits=0)
+        assert not af.decode_gave_up(hd)
+        for j, (i, p) in enumerate(items):
+            if i < 0:
+                assert float(out[j].abs().sum()) == 0.0
+                continue
+            close(out[j].reshape(nh, hd), _ref_attention(qs[i], ks[i], vs[i], p, scale, 0.0, None).to(dt), dt)
+
+
 @pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=16, window=8, cap=50.0),
                                  dict(nh=6, nkv=1, hd=32, window=16, cap=20.0),
                                  dict(nh=5, nkv=5, hd=48, window=40, cap=30.0),
