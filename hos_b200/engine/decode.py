@@ -62,6 +62,19 @@ def live_class(n_live: int, bucket: int):
     return first, min(bucket, first + width - 1)
 
 
+def fill_class(total: Optional[int], n_live: int, planned_len: int) -> float:
+    """The fraction of (live rows x planned length) that the sequences' lengths add up to, rounded up to 1, 1/2,
+    1/4 or 1/8: sequences of unequal lengths hold fewer keys than as many of the longest length would, and where
+    the attention kernel's work is cut by the sum of the pages (even shares) that decides how it is planned."""
+    if not total or n_live <= 0 or planned_len <= 0:
+        return 1.0
+    ratio = total / float(n_live * planned_len)
+    for f in (0.125, 0.25, 0.5):
+        if ratio <= f:
+            return f
+    return 1.0
+
+
 MIN_LENGTH_CLASS = 512
 
 
@@ -117,6 +130,8 @@ class DecodeSession:
         self._max_len = runner.cache.max_seq_len
         self._planned_len = self._max_len       # the lengths the replayed launches are planned for (see length_class)
         self._planned_live = (smaller_bucket(b) + 1, b)      # and the numbers of live rows (see live_class)
+        self._planned_fill = ()                 # and how full of keys the sequences are, per window (see fill_class)
+        self._windows = sorted({g.need.window or 0 for g in runner.cache.groups})
         self.n_live = 0
 
     @property
@@ -129,19 +144,28 @@ class DecodeSession:
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
                         max_len_after=self._planned_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
                         starts_host=(), token_slot=self.slot,      # row n is sequence n here
-                        min_live=self._planned_live[0], max_live=self._planned_live[1], replayed=True)
+                        min_live=self._planned_live[0], max_live=self._planned_live[1], fills=self._planned_fill,
+                        replayed=True)
 
     def upload(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
-               stop_ids: Sequence[int] = (), longest: Optional[int] = None) -> None:
+               stop_ids: Sequence[int] = (), longest: Optional[int] = None,
+               lengths: Optional[Sequence[int]] = None) -> None:
         """Which slots the next step runs (rows beyond them are padding), the tokens if the caller
         brings them, and the stop ids that mark a sequence finished on the device (the first
         ops.MAX_STOPS of them; the host checks all of them anyway): one host-to-device copy.
         `longest`: the length of the longest of these sequences after the step, if the caller knows it
-        (the attention kernel's split of the keys is planned for the power of two above it)."""
+        (the attention kernel's split of the keys is planned for the power of two above it); `lengths`: all of
+        their lengths after the step, if known (see fill_class)."""
         n = len(slots)
         self.n_live = n
-        self._planned_len = length_class(longest, self._max_len)
+        if lengths is not None and longest is None:
+            longest = max(lengths)
+        planned = self._planned_len = length_class(longest, self._max_len)
         self._planned_live = live_class(n, self.b)
+        # per window of the cache's groups (0: all keys): the keys held, over n x what the planned length holds
+        self._planned_fill = () if lengths is None else tuple(
+            (w, fill_class(sum(min(x, w) if w else x for x in lengths), n, min(planned, w) if w else planned))
+            for w in self._windows)
         turn = self._turn
         self._turn ^= 1
         if self._copied[turn] is not None:
@@ -231,7 +255,7 @@ class DecodeSession:
             self.logits = fn()
             self.launches_per_step = ops.launch_count - before
             return self.logits
-        g, self.logits = self._program(key + (self._planned_len, self._planned_live), fn)
+        g, self.logits = self._program(key + (self._planned_len, self._planned_live, self._planned_fill), fn)
         g.replay()
         return self.logits
 

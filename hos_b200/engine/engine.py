@@ -54,7 +54,7 @@ class _DeviceBackend:
         r = self.runner
         r.cache.extend_all(slots, [r.cache.lengths[s] + 1 for s in slots])
         sess = r.decode_session(len(slots))
-        sess.upload(slots, stop_ids=self._stops, longest=max(r.cache.lengths[s] for s in slots))
+        sess.upload(slots, stop_ids=self._stops, lengths=[r.cache.lengths[s] for s in slots])
         sess.run_generate(self.params)
         self._queue.append(sess.fetch_start())
 

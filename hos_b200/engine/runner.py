@@ -128,7 +128,7 @@ class Runner:
             self.cache.extend_all(slots, [st + 1 for st in starts])
             with self._lengths_back_on_error(slots, starts):
                 sess = self.decode_session(len(slots))
-                sess.upload(slots, [t[0] for t in token_lists], longest=max(starts) + 1)
+                sess.upload(slots, [t[0] for t in token_lists], lengths=[st + 1 for st in starts])
                 out = sess.run_step()
             return out.clone() if copy else out
         if from_zero and last_only and self.use_sessions and self.prompt_sessions:
@@ -333,7 +333,7 @@ class Runner:
             self.cache.lengths[s] = n
         self.write_records(slots, pos=lengths, last=[t[0] for t in first_tokens], limit=[0] * len(slots), restart=True)
         sess = self.decode_session(len(slots))
-        sess.upload(slots, longest=max(lengths) + warmup + steps)
+        sess.upload(slots, lengths=[n + warmup + steps for n in lengths])
         greedy = SamplingParams.pure()
         for _ in range(warmup):
             sess.run_generate(greedy)

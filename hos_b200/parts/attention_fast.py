@@ -35,13 +35,15 @@ def lib_for(head_dim: int) -> ops.Library:
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, window: Optional[int],
-                  min_live: int = 0, clusters_fit=None, max_live: int = 0) -> int:
+                  min_live: int = 0, clusters_fit=None, max_live: int = 0, fill: float = 1.0) -> int:
     """How many shares the keys of one (token, kv head) are cut into.  The kernel's CTAs (one per
     SM) take items one after another; an item costs a fixed part (look-ups, first loads, the merge)
     and a part per page.  The number of shares is the one that makes the step shortest by that
     model (constants measured at head size 256), for all `n_tokens` rows live and, if the step is
     a replayed one whose last rows may be padding, for `min_live` live rows and half-way as well
-    (`max_live`: no more than that many of the rows are live; 0: all may be).
+    (`max_live`: no more than that many of the rows are live; 0: all may be).  `fill`: the sequences' lengths add
+    up to at most this fraction of live rows x what the longest holds (in this layer: of its window, if it has one):
+    equal shares follow the longest sequence whatever the others hold, even shares follow the sum.
     `clusters_fit(s)`: how many clusters of s CTAs of the kernel run at once (None: no cluster merge); with
     all of a step's clusters on the GPU at once the shares merge through shared memory, which is cheaper."""
     chunks = (group + 15) // 16
@@ -72,9 +74,11 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
     # every (token, kv head) through the workspace) and save the last round that equal items leave mostly empty.
     # Weighed with a model that knows that many CTAs at once share the memory's speed: a round of all SMs is
     # slower per page than a last round of a few.
-    # Only with at least half as many (token, kv head) as SMs: fewer lie in many CTAs each, and the last CTA of
-    # each merges all of its parts (one sequence at 32,768 keys: 1.90 ms a step against 1.75 ms in clusters).
-    if enabled["decode_even"] and n_tokens <= EVEN_MAX_ROWS and 2 * lo * per_token >= sms:
+    # Only while the longest (token, kv head) lies in at most EVEN_MOST_PARTS CTAs: the last CTA of each merges all
+    # of its parts (one sequence at 32,768 keys in 37 parts: 1.90 ms a step against 1.75 ms in clusters).
+    held = max(1.0, pages * fill)             # pages an average (token, kv head) holds in this layer
+    if enabled["decode_even"] and n_tokens <= EVEN_MAX_ROWS and \
+            pages <= EVEN_MOST_PARTS * max(1, -(-int(lo * per_token * held) // sms)):
         def page_us(active: int) -> float:
             return max(_PAGE_US, active * _PAGE_SHARED_US)
         share, equal, even = -(-pages // best), 0.0, 0.0
@@ -83,7 +87,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
             equal += full * (_ITEM_US + share * page_us(sms) + merge_us(best))
             if rest:
                 equal += _ITEM_US + share * page_us(rest) + merge_us(best)
-            even += _EVEN_US + -(-live * per_token * pages // sms) * page_us(sms)
+            even += _EVEN_US + -(-int(live * per_token * held) // sms) * page_us(sms)
         if even < 0.95 * equal:
             return 0
     return best
@@ -101,9 +105,13 @@ _CLUSTER_MERGE_US, _CLUSTER_MERGE_PER_SHARE_US = 0.3, 0.03
 # 40: 5.80 / 6.92, 56: 7.28 / 8.15, 64: 8.04 / 8.02; but 8: 2.41 / 2.11, 16: 3.16 / 2.94, 32: 4.82 / 4.58.
 # The model that fits these: 12 us more per launch, and a page costs a CTA 0.9 us alone but 0.0085 us times the
 # number of CTAs that stream at once (64 KB per page at head size 256: 7.7 TB/s between them).
+# Sequences of unequal lengths (8,100 / 4,000 / 2,000 / 1,000 / 500 / 500 / 250 / 250 keys, repeated): equal shares
+# take as long as the longest sequence's share, even shares follow the sum: 8 sequences 1.96 -> 1.86 ms a step, 16
+# sequences 2.69 -> 2.22, 32 sequences 4.05 -> 3.00.
 _EVEN_US = 12.0
 _PAGE_SHARED_US = 0.0085
 EVEN_MAX_ROWS = 2048
+EVEN_MOST_PARTS = 12
 
 
 _fit_known: Dict[tuple, int] = {}
@@ -148,7 +156,7 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
            cache: ops.PagedKVArgs, n_tokens: int, n_heads: int, scale: float, cap: float,
            window: Optional[int], max_len: int, n_splits: Optional[int] = None,
            max_new: Optional[int] = None, min_live: int = 0, token_slot=None, cluster: bool = True,
-           max_live: int = 0) -> None:
+           max_live: int = 0, fill: float = 1.0) -> None:
     """Attention of n_tokens single queries over the paged cache (each token at its own
     position in its own sequence).  `max_new`: the most tokens any sequence brings in this step;
     the kernel may fetch keys that lie below them while the kernel before it (which writes the
@@ -164,7 +172,7 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
         _cluster_state[hd] = want
     if n_splits is None:
         fit = (lambda s: clusters_fit(hd, n_heads, nkv, s)) if want else None
-        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit, max_live)
+        n_splits = decode_splits(n_tokens, nkv, n_heads // nkv, max_len, window, min_live, fit, max_live, fill)
     ws = tickets = None
     if n_splits == 0:            # even shares: every CTA the same number of pages, two places per CTA for what is cut
         f = lib.lib.hos_attn_decode_even_workspace
@@ -311,5 +319,6 @@ def attend(mixer, qkv, att, step, cache, packed: bool) -> bool:
     decode(qkv, qkv.shape[1], att, step.token_pos, step.token_seq, step.seq_slot, cache, step.n_tokens,
            mixer.n_heads, mixer.scale, mixer.softcap, mixer.window, step.max_len_after, max_new=step.max_new,
            min_live=getattr(step, "min_live", 0), token_slot=getattr(step, "token_slot", None),
-           max_live=getattr(step, "max_live", 0))
+           max_live=getattr(step, "max_live", 0),
+           fill=step.fill_for(mixer.window) if hasattr(step, "fill_for") else 1.0)
     return True

@@ -98,6 +98,9 @@ class StepInfo:
     token_slot: Optional[torch.Tensor] = None   # int32 [N] seq_slot[token_seq] for every row (anything for padding), if at hand
     min_live: int = 0                # a replayed step's rows may be padding from this row on (0: none is)
     max_live: int = 0                # ... and at most this many of its rows are live (0: all may be)
+    fill: float = 1.0                # the keys that the sequences hold add up to at most this fraction of (live rows x
+                                     # the keys of the longest), for mixers that see all keys ...
+    fills: tuple = ()                # ... and ((window, fraction), ...) for mixers that see a window of them: see fill_for
     replayed: bool = False           # the device arrays are refilled and the same launches replayed (a CUDA
                                      # graph): n_tokens and n_seqs are capacities, the host lists are empty
     fresh_seqs: int = 0              # a step that is not from_zero lists the sequences that start at position 0
@@ -106,6 +109,20 @@ class StepInfo:
     tail_tokens: int = 0             # that many sequences, that many rows (a mixer may send them to another kernel)
     row_offset: int = 0              # of a part of a step (see rows()): its first row and its first sequence in the
     seq_offset: int = 0              # whole step, which cu_seqlens (rows) and token_seq, seq_slot (sequences) still count from
+
+    def fill_for(self, window: Optional[int]) -> float:
+        """How full of keys the step's sequences are for a mixer with this window (None: all keys): the sum over
+        the sequences of the keys each holds, over (sequences x what the longest holds).  1.0 when they are all
+        as long as the longest, or when nothing is known.  A kernel whose work follows the sum of the keys rather
+        than the longest sequence plans with it."""
+        if self.starts_host and self.cu_host:
+            lens = [s + (self.cu_host[i + 1] - self.cu_host[i]) for i, s in enumerate(self.starts_host)]
+            held = [min(n, window) if window else n for n in lens]
+            return min(1.0, sum(held) / float(len(held) * max(held))) if held and max(held) > 0 else 1.0
+        for w, f in self.fills:
+            if w == (window or 0):
+                return f
+        return self.fill
 
     def rows(self, lo: int, hi: int, seq_lo: int, seq_hi: int) -> "StepInfo":
         """The step as seen by rows lo..hi-1 alone, which are the sequences seq_lo..seq_hi-1: what a

@@ -46,6 +46,31 @@ def test_even_shares_where_equal_ones_leave_a_round_mostly_empty():
     assert af.decode_splits(af.EVEN_MAX_ROWS + 1, 4, 2, 8192, None) >= 1   # more rows than the kernel's running sums hold
 
 
+def test_sequences_of_unequal_lengths_argue_for_even_shares():
+    """Equal shares take as long as the longest sequence's share whatever the others hold; even shares follow the
+    sum of the keys.  `fill`: that sum over (sequences x the longest's keys)."""
+    fit = lambda s: 148 // s
+    assert af.decode_splits(16, 4, 2, 8192, None, 16, fit, 16, 1.0) >= 1       # sixteen sequences, all long: clusters
+    assert af.decode_splits(16, 4, 2, 8192, None, 16, fit, 16, 0.5) == 0       # half as many keys: even shares
+    assert af.decode_splits(32, 4, 2, 8192, 4096, 32, fit, 32, 0.25) == 0
+    assert af.decode_splits(1, 4, 2, 8192, None, 1, fit, 1, 0.125) >= 1        # one sequence is as long as itself
+    assert af.decode_splits(4, 4, 2, 8192, None, 4, fit, 4, 0.5) >= 1          # the longest would lie in too many CTAs
+
+
+def test_how_full_of_keys_a_step_is():
+    from hos_b200.engine.decode import fill_class
+    from hos_b200.parts.base import StepInfo
+    assert fill_class(None, 8, 8192) == 1.0 and fill_class(8 * 8192, 8, 8192) == 1.0
+    assert fill_class(16600, 8, 8192) == 0.5 and fill_class(8 * 1000, 8, 8192) == 0.125 and fill_class(5, 8, 8192) == 0.125
+    kw = dict(n_tokens=3, n_seqs=3, tokens=None, token_pos=None, token_seq=None, cu_seqlens=None, seq_slot=None,
+              seq_len_after=None, from_zero=False, single_token=True, max_new=1, max_len_after=1000)
+    step = StepInfo(**kw, cu_host=(0, 1, 2, 3), starts_host=(999, 499, 99))
+    assert abs(step.fill_for(None) - 1600 / 3000) < 1e-9                    # from the host's lists, exactly
+    assert abs(step.fill_for(200) - 500 / 600) < 1e-9                       # a window of 200 keys: 200 + 200 + 100
+    replayed = StepInfo(**kw, replayed=True, fills=((0, 0.5), (200, 0.25)))
+    assert replayed.fill_for(None) == 0.5 and replayed.fill_for(200) == 0.25 and replayed.fill_for(64) == 1.0
+
+
 def test_clusters_that_do_not_fit_change_nothing():
     for n in (1, 2, 4, 8):
         for window in (None, 4096):

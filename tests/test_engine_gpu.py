@@ -432,6 +432,34 @@ def test_decoding_with_even_shares_of_the_keys(tmp_path, name, monkeypatch):
     r.cache.check()
 
 
+def test_sequences_of_unequal_lengths_get_even_shares_by_the_planner(tmp_path, monkeypatch):
+    """40 sequences of 2 kv heads, most of them short and a few long: the session tells the attention how full of
+    keys the sequences are, and the planner itself asks for even shares (nothing is forced here).  Every logit
+    against the plain implementation."""
+    from hos_b200.parts import attention_fast as af
+    chosen = []
+    real = af.decode_splits
+    monkeypatch.setattr(af, "decode_splits", lambda *a, **k: (chosen.append(real(*a, **k)), chosen[-1])[1])
+    folder = make_folder(tmp_path, "D")
+    w, cfg = plain_model(folder)
+    rng = random.Random(12)
+    lens = [rng.choice((900, 700)) if i % 8 == 0 else rng.randrange(5, 120) for i in range(40)]
+    total = [n + 3 for n in lens]
+    seqs = [random_tokens(rng, t, 1000) for t in total]
+    want = [P.forward_logits(w, cfg, s) for s in seqs]
+    r = runner_for(folder, "bfloat16", max_tokens=64 * 400)
+    slots = r.admit(len(seqs))
+    for lo in range(0, 40, 8):                                  # the prompts, eight sequences a step
+        r.step(slots[lo:lo + 8], [s[:n] for s, n in zip(seqs[lo:lo + 8], lens[lo:lo + 8])])
+    chosen.clear()
+    for t in range(3):
+        got = r.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+        assert_close(got, torch.stack([wl[n + t] for wl, n in zip(want, lens)]), "bfloat16", f"decode step {t}")
+    r.wait()
+    assert chosen and 0 in chosen, f"the planner never asked for even shares: {sorted(set(chosen))}"
+    r.cache.check()
+
+
 @pytest.mark.parametrize("sizes", [dict(num_hidden_layers=4),
                                    dict(num_hidden_layers=2, hidden_size=4608, num_attention_heads=32,
                                         num_key_value_heads=16, head_dim=128, intermediate_size=36864,
