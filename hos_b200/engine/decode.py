@@ -79,15 +79,16 @@ MIN_LENGTH_CLASS = 512
 
 
 def length_class(longest: Optional[int], max_seq_len: int) -> int:
-    """The sequence length a replayed step is planned for: the power of two at or above the longest live
-    sequence (at least MIN_LENGTH_CLASS, at most what the cache holds).  How the attention kernel splits the
-    keys over the GPU depends on it, and is part of what is captured: a step is captured once per class, so a
-    batch of short sequences is not run with the split that the longest possible one would want."""
+    """The sequence length a replayed step is planned for: the next of 512, 768, 1024, 1536, 2048, 3072, ... at or
+    above the longest live sequence (at most what the cache holds).  How the attention kernel cuts the keys over
+    the GPU depends on it, and is part of what is captured: a step is captured once per class, so a batch of short
+    sequences is not run with the cut that the longest possible one would want.  (Powers of two alone left the plan
+    up to a factor of two beside the truth: sixteen sequences of up to 2,300 keys were planned as for 4,096.)"""
     if longest is None or longest >= max_seq_len:
         return max_seq_len
     c = MIN_LENGTH_CLASS
     while c < longest:
-        c *= 2
+        c = c * 3 // 2 if c & (c - 1) == 0 else c * 4 // 3
     return min(c, max_seq_len)
 
 
@@ -131,6 +132,7 @@ class DecodeSession:
         self._planned_len = self._max_len       # the lengths the replayed launches are planned for (see length_class)
         self._planned_live = (smaller_bucket(b) + 1, b)      # and the numbers of live rows (see live_class)
         self._planned_fill = ()                 # and how full of keys the sequences are, per window (see fill_class)
+        self._seen_len, self._seen_fill = self._max_len, ()     # what the step at hand really holds: a new capture plans with it
         self._windows = sorted({g.need.window or 0 for g in runner.cache.groups})
         self.n_live = 0
 
@@ -142,9 +144,9 @@ class DecodeSession:
         return StepInfo(n_tokens=self.b, n_seqs=self.b, tokens=self.tokens, token_pos=self.pos,
                         token_seq=self.seq, cu_seqlens=self.cu, seq_slot=self.slot,
                         seq_len_after=self.after, from_zero=False, single_token=True, max_new=1,
-                        max_len_after=self._planned_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
+                        max_len_after=self._seen_len, slots_host=(), cu_host=tuple(range(self.b + 1)),
                         starts_host=(), token_slot=self.slot,      # row n is sequence n here
-                        min_live=self._planned_live[0], max_live=self._planned_live[1], fills=self._planned_fill,
+                        min_live=self._planned_live[0], max_live=self._planned_live[1], fills=self._seen_fill,
                         replayed=True)
 
     def upload(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
@@ -154,7 +156,7 @@ class DecodeSession:
         brings them, and the stop ids that mark a sequence finished on the device (the first
         ops.MAX_STOPS of them; the host checks all of them anyway): one host-to-device copy.
         `longest`: the length of the longest of these sequences after the step, if the caller knows it
-        (the attention kernel's split of the keys is planned for the power of two above it); `lengths`: all of
+        (the attention kernel's split of the keys is planned for the class of lengths above it); `lengths`: all of
         their lengths after the step, if known (see fill_class)."""
         n = len(slots)
         self.n_live = n
@@ -162,10 +164,16 @@ class DecodeSession:
             longest = max(lengths)
         planned = self._planned_len = length_class(longest, self._max_len)
         self._planned_live = live_class(n, self.b)
-        # per window of the cache's groups (0: all keys): the keys held, over n x what the planned length holds
-        self._planned_fill = () if lengths is None else tuple(
-            (w, fill_class(sum(min(x, w) if w else x for x in lengths), n, min(planned, w) if w else planned))
-            for w in self._windows)
+        # Per window of the cache's groups (0: all keys): the keys held, over n x what the longest holds.  The classes
+        # name the captured program; a capture itself plans with what the step at hand really holds (the first
+        # step of a class decides for the class: the classes are narrow enough for that).
+        self._seen_len = min(longest, self._max_len) if longest is not None else self._max_len
+        self._planned_fill = self._seen_fill = ()
+        if lengths is not None:
+            held = [(w, sum(min(x, w) if w else x for x in lengths), min(self._seen_len, w) if w else self._seen_len)
+                    for w in self._windows]
+            self._seen_fill = tuple((w, min(1.0, total / float(n * most))) for w, total, most in held)
+            self._planned_fill = tuple((w, fill_class(total, n, most)) for w, total, most in held)
         turn = self._turn
         self._turn ^= 1
         if self._copied[turn] is not None:

@@ -87,6 +87,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_len: int, wind
             equal += full * (_ITEM_US + share * page_us(sms) + merge_us(best))
             if rest:
                 equal += _ITEM_US + share * page_us(rest) + merge_us(best)
+            equal += _ROUND_US * max(0, full + (1 if rest else 0) - 1)
             even += _EVEN_US + -(-int(live * per_token * held) // sms) * page_us(sms)
         if even < 0.95 * equal:
             return 0
@@ -103,15 +104,18 @@ CLUSTER_SHARES = 16
 _CLUSTER_MERGE_US, _CLUSTER_MERGE_PER_SHARE_US = 0.3, 0.03
 # Even shares against the best equal shares, a step of Gemma-2 2B sizes at 8,192 keys (ms): 20 sequences 3.63 / 3.81,
 # 40: 5.80 / 6.92, 56: 7.28 / 8.15, 64: 8.04 / 8.02; but 8: 2.41 / 2.11, 16: 3.16 / 2.94, 32: 4.82 / 4.58.
-# The model that fits these: 12 us more per launch, and a page costs a CTA 0.9 us alone but 0.0085 us times the
-# number of CTAs that stream at once (64 KB per page at head size 256: 7.7 TB/s between them).
+# The model that fits these: 22 us more per launch than one round of equal shares, 8 us for every further round of
+# equal shares, and a page costs a CTA 0.9 us alone but 0.0085 us times the number of CTAs that stream at once (64 KB
+# per page at head size 256: 7.7 TB/s between them).  At Gemma-2 9B sizes, 16 sequences of 64 to 2,300 keys (0.64 of
+# what 16 of the longest would hold) lose 0.15 ms a step with even shares: the model has to say no there.
 # Sequences of unequal lengths (8,100 / 4,000 / 2,000 / 1,000 / 500 / 500 / 250 / 250 keys, repeated): equal shares
 # take as long as the longest sequence's share, even shares follow the sum: 8 sequences 1.96 -> 1.86 ms a step, 16
 # sequences 2.69 -> 2.22, 32 sequences 4.05 -> 3.00.
-_EVEN_US = 12.0
+_EVEN_US = 22.0
+_ROUND_US = 8.0
 _PAGE_SHARED_US = 0.0085
 EVEN_MAX_ROWS = 2048
-EVEN_MOST_PARTS = 12
+EVEN_MOST_PARTS = 20
 
 
 _fit_known: Dict[tuple, int] = {}

@@ -54,7 +54,8 @@ def test_sequences_of_unequal_lengths_argue_for_even_shares():
     assert af.decode_splits(16, 4, 2, 8192, None, 16, fit, 16, 0.5) == 0       # half as many keys: even shares
     assert af.decode_splits(32, 4, 2, 8192, 4096, 32, fit, 32, 0.25) == 0
     assert af.decode_splits(1, 4, 2, 8192, None, 1, fit, 1, 0.125) >= 1        # one sequence is as long as itself
-    assert af.decode_splits(4, 4, 2, 8192, None, 4, fit, 4, 0.5) >= 1          # the longest would lie in too many CTAs
+    assert af.decode_splits(4, 4, 2, 8192, None, 4, fit, 4, 0.5) >= 1          # few sequences: clusters are cheaper
+    assert af.decode_splits(16, 8, 2, 2049, None, 16, fit, 16, 0.64) >= 1      # 16 of 64 to 2,049 keys, 8 kv heads: little to gain
 
 
 def test_how_full_of_keys_a_step_is():
@@ -119,13 +120,14 @@ def test_k_splits_of_the_products():
             assert s == 1 or (k + 63) // 64 // s >= 8
 
 
-def test_replayed_steps_are_planned_for_the_power_of_two_above_the_longest_sequence():
+def test_replayed_steps_are_planned_for_the_class_above_the_longest_sequence():
     from hos_b200.engine.decode import MIN_LENGTH_CLASS, length_class
     assert length_class(None, 8192) == 8192                  # not known: the longest the cache holds
     assert length_class(1, 8192) == MIN_LENGTH_CLASS
-    assert length_class(512, 8192) == 512 and length_class(513, 8192) == 1024
-    assert length_class(1025, 8192) == 2048 and length_class(5000, 8192) == 8192
-    assert length_class(9000, 8192) == 8192 and length_class(3000, 3500) == 3500
+    assert length_class(512, 8192) == 512 and length_class(513, 8192) == 768 and length_class(769, 8192) == 1024
+    assert length_class(1025, 8192) == 1536 and length_class(2304, 8192) == 3072 and length_class(5000, 8192) == 6144
+    assert length_class(6145, 8192) == 8192 and length_class(9000, 8192) == 8192 and length_class(3000, 3500) == 3072
+    assert length_class(3100, 3500) == 3500
     # the class never lies below the sequence: a share of the keys is never planned away
     for n in range(1, 9000, 37):
         assert length_class(n, 8192) >= min(n, 8192)

@@ -433,21 +433,26 @@ def test_decoding_with_even_shares_of_the_keys(tmp_path, name, monkeypatch):
 
 
 def test_sequences_of_unequal_lengths_get_even_shares_by_the_planner(tmp_path, monkeypatch):
-    """40 sequences of 2 kv heads, most of them short and a few long: the session tells the attention how full of
-    keys the sequences are, and the planner itself asks for even shares (nothing is forced here).  Every logit
-    against the plain implementation."""
+    """40 sequences of 2 kv heads, most of them short and five of some 3,000 tokens: the session tells the
+    attention how full of keys the sequences are, and the planner itself asks for even shares (nothing is forced
+    here).  Every logit against the plain implementation."""
+    from hos_b200.engine import Runner
     from hos_b200.parts import attention_fast as af
+    from hos_b200.registry import config_from_dict
+    from hos_b200.weights import write_model_folder
     chosen = []
     real = af.decode_splits
     monkeypatch.setattr(af, "decode_splits", lambda *a, **k: (chosen.append(real(*a, **k)), chosen[-1])[1])
-    folder = make_folder(tmp_path, "D")
+    folder = str(tmp_path / "tiny_D_long")
+    write_model_folder(config_from_dict(dict(TINY["D"][0], max_position_embeddings=4096)), 3, folder)
     w, cfg = plain_model(folder)
     rng = random.Random(12)
-    lens = [rng.choice((900, 700)) if i % 8 == 0 else rng.randrange(5, 120) for i in range(40)]
+    lens = [rng.choice((3000, 2600)) if i % 8 == 0 else rng.randrange(5, 120) for i in range(40)]
     total = [n + 3 for n in lens]
     seqs = [random_tokens(rng, t, 1000) for t in total]
-    want = [P.forward_logits(w, cfg, s) for s in seqs]
-    r = runner_for(folder, "bfloat16", max_tokens=64 * 400)
+    with torch.no_grad():
+        want = [P.forward_logits(w, cfg, s) for s in seqs]
+    r = Runner.from_folder(folder, dtype="bfloat16", max_tokens=64 * 400, chunk_tokens=1)
     slots = r.admit(len(seqs))
     for lo in range(0, 40, 8):                                  # the prompts, eight sequences a step
         r.step(slots[lo:lo + 8], [s[:n] for s, n in zip(seqs[lo:lo + 8], lens[lo:lo + 8])])
