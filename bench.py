@@ -158,22 +158,27 @@ def fill_cache_random(runner):
                 flat[lo:lo + (1 << 28)].normal_(0.0, 0.5)
 
 
-def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
-    """K timed decode steps that end at length ctx.  Returns (device ms per step, e2e ms per
-    step, kernel launches in the timed region, h2d bytes per step, d2h bytes per step, mean length)."""
+MIXED = (1.0, 0.5, 0.25, 0.125, 0.0625, 0.0625, 0.03125, 0.03125)     # --mixed-lengths: fractions of the context, in turn
+
+
+def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None, mixed=False):
+    """K timed decode steps that end at length ctx (with `mixed`: at the fractions MIXED of it, in turn).  Returns
+    (device ms per step, e2e ms per step, kernel launches in the timed region, h2d bytes per step, d2h bytes per
+    step, mean length, or with `mixed` the list of the sequences' mean lengths)."""
     import torch
     from hos_b200 import ops
     r = eng.runner
     vocab = r.vocab_size
+    ends = [max(warmup + steps + 1, int(ctx * MIXED[i % len(MIXED)])) if mixed else ctx for i in range(batch)]
+    starts = [e - (warmup + steps) for e in ends]
 
     def prepare():
         slots = r.admit(batch)
-        start = ctx - (warmup + steps)
-        r.cache.extend_all(slots, [start] * batch)
-        return slots, start
+        r.cache.extend_all(slots, starts)
+        return slots
 
     # ---- device-timed: steps issued back to back, tokens stay on the device ----
-    slots, start = prepare()
+    slots = prepare()
     toks = [[rng.randrange(vocab)] for _ in range(batch)]
     ms_dev, launches = r.decode_steps_timed(slots, toks, warmup, steps, clocks)
     for s in slots:
@@ -182,10 +187,9 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
     # ---- end to end: the public entry point (Engine.generate_from_ids on conversations that hold the
     # context), token ids back on the host; every step uploads which slots run and brings its tokens back ----
     convs = eng.open(batch)
-    start = ctx - (warmup + steps)
-    r.cache.extend_all([c.slot for c in convs], [start] * batch)
-    r.write_records([c.slot for c in convs], pos=[start] * batch)
-    for c in convs:
+    r.cache.extend_all([c.slot for c in convs], starts)
+    r.write_records([c.slot for c in convs], pos=starts)
+    for c, start in zip(convs, starts):
         c.position = start
     kw = dict(temp=0.0, top_k=0, top_p=1.0, rep_penalty=1.0, stop_ids=[])
     eng.generate_from_ids(convs, [[rng.randrange(vocab)] for _ in range(batch)], max_tokens=warmup, **kw)
@@ -200,7 +204,7 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None):
     from hos_b200.engine.decode import META, bucket_for
     h2d = (META + bucket_for(batch)) * 4       # live rows, stop ids, the slots that run
     d2h = bucket_for(batch) * 4                # the sampled ids
-    mean_len = ctx - steps / 2.0
+    mean_len = [e - steps / 2.0 for e in ends] if mixed else ctx - steps / 2.0
     return ms_dev, ms_e2e, launches, h2d, d2h, mean_len
 
 
@@ -294,6 +298,9 @@ def main() -> int:
                     help="step: the decode step at the context's end (the default line); baseline: prompts then 256 "
                          "greedy tokens, the workload that goes with the model's sizes")
     ap.add_argument("--decode-tokens", type=int, default=256, help="tokens decoded per sequence by --workload baseline")
+    ap.add_argument("--mixed-lengths", action="store_true",
+                    help="the sequences end at 1, 1/2, 1/4, 1/8, 1/16, 1/16, 1/32, 1/32 of the context, in turn, "
+                         "instead of all at its end (not the driver's line: how a batch of unequal lengths decodes)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the contract's 2,048)")
     args = ap.parse_args()
@@ -333,11 +340,14 @@ def main() -> int:
 
     clocks = ClockSampler(torch.cuda.current_device())
     ms_dev, ms_e2e, launches, h2d, d2h, mean_len = measure_decode(
-        eng, args.batch, args.ctx, args.steps, args.warmup, rng, clocks)
+        eng, args.batch, args.ctx, args.steps, args.warmup, rng, clocks, mixed=args.mixed_lengths)
     clock_rec = clocks.result
 
     wbytes = weight_bytes(cfg, args.layers)
-    step_bytes = wbytes + args.batch * kv_bytes_at(cfg, args.layers, int(mean_len))
+    if args.mixed_lengths:
+        step_bytes = wbytes + sum(kv_bytes_at(cfg, args.layers, int(n)) for n in mean_len)
+    else:
+        step_bytes = wbytes + args.batch * kv_bytes_at(cfg, args.layers, int(mean_len))
     achieved = step_bytes / (ms_dev * 1e-3) / 1e9
     line = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Gemma-2 2B)",
@@ -349,7 +359,8 @@ def main() -> int:
             "parallelism": "single_gpu", "layers": args.layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-            "sliding_window": cfg.sliding_window, "decode_ends_at": args.ctx,
+            "sliding_window": cfg.sliding_window,
+            "decode_ends_at": "1, 1/2, 1/4, 1/8, 1/16, 1/16, 1/32, 1/32 of %d in turn" % args.ctx if args.mixed_lengths else args.ctx,
             "cache_fill": "random keys and values", "l2": "inputs larger than L2 (weights %.1f GB per step)" % (wbytes / 1e9),
             "peaks": pk_src, "prefill_tokens": args.prefill_tokens},
         "clocks": clock_rec,
