@@ -127,6 +127,7 @@ class DecodeSession:
         self._fetch_turn = 0
         self.logits: Optional[torch.Tensor] = None
         self._programs = {}                     # key -> (graph or None, logits buffer)
+        self._pool = None                       # the programs' buffers share one pool: only one of them runs at a time
         self.launches_per_step = 0
         self._max_len = runner.cache.max_seq_len
         self._planned_len = self._max_len       # the lengths the replayed launches are planned for (see length_class)
@@ -248,11 +249,16 @@ class DecodeSession:
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            with torch.cuda.graph(g, pool=self._pool, capture_error_mode="thread_local"):
                 out = fn()
         finally:
             if gc_was_on:
                 gc.enable()
+        if self._pool is None:
+            # Every class of lengths, of live rows and of fill has its own program, and each would keep its own
+            # logits [rows, vocab] and activations; what a program leaves is used before the next one runs, so
+            # they may all live in the same memory.
+            self._pool = g.pool()
         prog = self._programs[key] = (g, out)
         return prog
 
