@@ -18,6 +18,11 @@
 // rows (fewer than 16 heads per kv head) cost nothing that matters: the kernel is bound by
 // the cache's bytes.
 //
+// The kernel has a second way to cut the work (attn_decode_kernel<true>, asked for with 0 shares): not every
+// (token, kv head) into the same number of shares, but the row of all pages of all (token, kv head) into one
+// piece of equal length per CTA, wherever the borders fall (see EvenPlan).  That wins where equal shares would
+// leave a round of SMs mostly empty, and where the sequences are of unequal lengths.
+//
 // Compiled per head size: -DHOS_HEAD_DIM=N, N a multiple of 16 up to 256.
 #include "common.cuh"
 #include "kv_layout.cuh"
