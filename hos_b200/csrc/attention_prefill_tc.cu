@@ -227,7 +227,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
                        const __grid_constant__ CUtensorMap map_kv,     // boxes of [64 rows x 64 columns]
                        const __grid_constant__ CUtensorMap map_v,
                        PrefillTcArgs a) {
-    pdl_enter();      // the kernels before this one are complete from here on
+    // The kernel may start while the projection before it still runs: barriers, tensor memory and the look-ups of
+    // the step's own arrays (written at the head of the step) are set up meanwhile; the producer waits for that
+    // kernel's end before its first copy, and nothing else here touches global memory before data has arrived.
+    pdl_launch_dependents();
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
@@ -295,6 +298,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes 
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             bool ok = true;
+            pdl_wait();       // the projection's rows and the step's keys and values are complete from here on
             mbar_expect_tx(q_full, kQBytesTc);
             for (int c = 0; c < CBLK; ++c)
                 tc_tma_2d(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
@@ -549,7 +553,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxes of [128 rows x 64 columns]
                          const __grid_constant__ CUtensorMap map_k,      // boxes of [64 rows x 64 columns]
                          PrefillTcArgs a) {
-    pdl_enter();      // the kernels before this one are complete from here on
+    pdl_launch_dependents();      // as in the one-CTA kernel: set-up first, the producers wait before their first copy
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
@@ -616,6 +620,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,      // boxe
         // ---------------- TMA producer (both CTAs, each its own halves) ----------------
         if (lane == 0) {
             bool ok = true;
+            pdl_wait();       // the projection's rows are complete from here on
             if (leader) mbar_expect_tx(q_full, 2 * kQBytesTc);
             for (int c = 0; c < CBLK; ++c)
                 tma_load_2d_pair(q_s + c * kQBlockBytes, &map_q, a.q_col0 + head * THD + 64 * c, row0 + q0, q_full);
