@@ -227,7 +227,9 @@ __global__ void norm_add_norm_rows_kernel(const TY* __restrict__ y, int n_parts,
                                           const float* __restrict__ w_post, float eps_post, float add_one_post,
                                           float* __restrict__ x, const float* __restrict__ w_next, float eps_next,
                                           float add_one_next, TH* __restrict__ h, int D, int N) {
-    pdl_enter();      // the kernels before this one are complete from here on
+    // launched ahead of the end of the kernel before it: the CTAs are placed and the norms' weights, which no
+    // kernel writes, are fetched meanwhile
+    pdl_launch_dependents();
     __shared__ float scratch[32];
     const int c0 = threadIdx.x * 8;
     const bool live = c0 < D;                       // the block is rounded up to whole warps
@@ -238,6 +240,7 @@ __global__ void norm_add_norm_rows_kernel(const TY* __restrict__ y, int n_parts,
         wp = load8(w_post + c0);
         if (h != nullptr) wn = load8(w_next + c0);
     }
+    pdl_wait();       // the kernels before this one are complete from here on
     auto fetch_y = [&](int row) {
         Row8 r = load8(y + (size_t)row * D + c0);
         for (int p = 1; p < n_parts; ++p) {
