@@ -176,7 +176,9 @@ def load(name: str) -> ctypes.CDLL:
         return lib
 
 
-def build_all(head_dims: Sequence[int] = (16, 32, 64, 128, 256)) -> List[str]:
-    """Build every library (the attention library once per head size)."""
+def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 80, 128, 256)) -> List[str]:
+    """Build every library (the attention library once per head size: the sizes of the Gemma-2 checkpoints, 128
+    and 256, and the ones that the tests' small configurations have; any other multiple of 16 is built when a
+    model with it is first loaded)."""
     names = list(_STATIC_LIBS) + [f"attn_hd{h}" for h in head_dims]
     return [library_path(n) for n in names]
