@@ -55,10 +55,12 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
 template <int MT, int kUnroll, bool GATED, typename OutT, int WARPS = kSkinnyWarps>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
-                   int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act) {
+                   int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act, int late) {
     // The kernel may be launched ahead of the end of the kernel before it: its CTAs are placed and a warp's first
     // round of weights, which no kernel writes, is on its way before the activations exist.
-    pdl_launch_dependents();
+    // (`late`: the kernel after this one is let go only when the kernel before this one has ended: this kernel was
+    // itself launched ahead, and a chain of kernels that all wait on the SMs costs more than it hides)
+    if (!late) pdl_launch_dependents();
     __shared__ float part[WARPS][MT][16][8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -109,6 +111,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
         }
         if (decltype(first)::value) {
             pdl_wait();       // the kernels before this one are complete from here on: the activations may be read
+            if (late) pdl_launch_dependents();
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 const int k = (kb + u) * 32 + 8 * t4;
@@ -136,6 +139,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
         // more token tiles: the first round is not set apart (its second copy of the loop body costs registers
         // that these shapes do not have: 24 rows 4.06 -> 4.13 ms per step, 32 rows 4.57 -> 4.71 when it was)
         pdl_wait();
+        if (late) pdl_launch_dependents();
         for (int kb = kb_begin; kb < kb_end; kb += kUnroll) round(kb, FalseTag{});
     }
     // C fragment: c0 (row g, token 2t), c1 (row g, token 2t+1), c2 (row g+8, token 2t), c3 (row g+8, token 2t+1)
@@ -329,7 +333,7 @@ static int skinny_ahead_mode() {
     static int on = -1;
     if (on < 0) {
         const char* e = getenv("HOS_SKINNY_AHEAD");
-        on = (e && e[0]) ? atoi(e) : 57;
+        on = (e && e[0]) ? atoi(e) : 61;
     }
     return on;
 }
@@ -342,6 +346,12 @@ static bool skinny_ahead(int kind) { return (skinny_ahead_mode() & kind) != 0 ||
 // (and the attention before o is itself launched ahead of q/k/v): launched ahead they take places too early.
 // With 9 to 32 rows the two products behind a norm are launched ahead as well, only to have their CTAs placed (12 rows
 // 2.652 -> 2.625 ms, 16 rows 2.958 -> 2.936, 32 rows 4.564 -> 4.558).
+// What cost the down product its place in that list was the chain behind it: launched ahead, it let the norm after it
+// go at once, which let the q/k/v projection go, and all of them sat waiting on the SMs.  Launched ahead but letting
+// its own dependents go only when the kernel before it has ended (`late`), it gains: a step of 8 sequences 2.128 ->
+// 2.101 ms, one sequence 1.478 -> 1.464, 2 sequences 1.585 -> 1.562, 8 sequences at 1,024 keys 1.487 -> 1.464.  The o
+// product the same way gains 3% for one sequence up to 8,192 keys (1.478 -> 1.436 ms with both) and loses 7 to 20%
+// everywhere else (2, 4 or 8 sequences; one sequence at 32,768 keys): it stays behind its attention kernel.
 
 // out[M, N] = A[M, K] . W[N, K]^T for M <= 32.  epilogue 0: none (out bf16 or f32); 2: gated (W has
 // 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
@@ -367,9 +377,11 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     const int k_ways = epilogue == 2 ? kGatedWarps / 2 : kSkinnyWarps;
     const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
     const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
+    const int kind = (M > 8) ? (epilogue == 2 ? 16 : 0) : (epilogue == 2 ? 1 : (out_dtype == kBF16 ? 2 : 4));
+    const int late = (kind == 2 || kind == 4) && skinny_ahead(kind) ? 1 : 0;     // o and down, when launched ahead
 #define HOS_SK_W(MT, U, G, T, WP)                                                                                \
     launch_ahead(skinny_ahead(MT != 1 ? (G ? 16 : 0) : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T, WP>, dim3(grid, k_splits), dim3(WP * 32), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
-                                                                       M, N, K, lda, ldw, ldo, N, act)
+                                                                       M, N, K, lda, ldw, ldo, N, act, late)
 #define HOS_SK(MT, U, G, T) HOS_SK_W(MT, U, G, T, (G ? kGatedWarps : kSkinnyWarps))
 #define HOS_SK_U(MT, G, T)                              \
     do {                                                \

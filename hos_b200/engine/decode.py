@@ -431,7 +431,9 @@ class PromptSession:
         # the kernels of a prompt step, short ones too, are launched ahead of one another's end: their set-up
         # (barriers, tensor memory, the first look-ups) runs under the kernel before (40 tokens 2.15 -> 2.11 ms, 256
         # tokens 2.90 -> 2.81, 512 tokens 3.66 -> 3.48 at Gemma-2 2B sizes)
-        ops.set_launch_ahead(True)
+        # (up to 32 rows the few-rows products run, which choose for themselves which of them go ahead: all of them
+        # ahead is what they measured as their worst case, 16 tokens 2.63 ms instead of 2.0)
+        ops.set_launch_ahead(self.t > 32)
         try:
             x = r.model.hidden(self._info(), r.cache)
             ops.slot_set_pos(r.cache.record, self.slot, self.after, self.cu, self.q)    # the records learn the new lengths
