@@ -134,10 +134,13 @@ template <typename TY, typename TH, int CH>
 __global__ void norm_add_norm_vec_kernel(const TY* __restrict__ y, int n_parts, size_t part_stride,
                                          const float* __restrict__ w_post, float eps_post, float add_one_post,
                                          float* __restrict__ x, const float* __restrict__ w_next, float eps_next,
-                                         float add_one_next, TH* __restrict__ h, int D) {
+                                         float add_one_next, TH* __restrict__ h, int D, int late_flag) {
     // This kernel may be launched ahead of the end of the kernel before it (a few rows: decoding): its CTAs
-    // are placed and the norms' weights, which no kernel writes, are fetched meanwhile.
-    pdl_launch_dependents();
+    // are placed and the norms' weights, which no kernel writes, are fetched meanwhile.  Then (`late_flag`) it lets
+    // the kernel after it go only when the kernel before it has ended: a chain of kernels that all wait on the SMs
+    // costs more than it hides.
+    const bool late_x = late_flag != 0;
+    if (!late_x) pdl_launch_dependents();
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * D;
     float4 yv[CH], xv[CH], wp[CH], wn[CH];
@@ -150,6 +153,7 @@ __global__ void norm_add_norm_vec_kernel(const TY* __restrict__ y, int n_parts, 
         }
     }
     pdl_wait();       // the kernels before this one are complete from here on
+    if (late_x) pdl_launch_dependents();
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
@@ -646,8 +650,9 @@ extern "C" int hos_norm_add_norm(const void* y, int y_dtype, int n_parts, const 
     // 1.533 -> 1.503 ms, 64 sequences 8.098 -> 8.090 ms); HOS_NORM_AHEAD=0 switches it off.
     static const bool few_rows_ahead = !(getenv("HOS_NORM_AHEAD") && getenv("HOS_NORM_AHEAD")[0] == '0');
     const bool ahead = pdl_enabled() || (few_rows_ahead && N < kRowsKernelMinRows);
+    const int norm_late = ahead ? 1 : 0;
 #define HOS_VEC(TY, TH, CH) launch_ahead(ahead, norm_add_norm_vec_kernel<TY, TH, CH>, dim3(N), dim3(threads), 0, stream,         \
-        (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D)
+        (const TY*)y, n_parts, ps, w_post, eps_post, a1, x, w_next, eps_next, a2, (TH*)h, D, norm_late)
 #define HOS_LAUNCH(TY, TH)                                                                                  \
     do {                                                                                                    \
         if (chunks == 1) HOS_VEC(TY, TH, 1);                                                                \

@@ -358,7 +358,8 @@ static bool skinny_ahead(int kind) { return (skinny_ahead_mode() & kind) != 0 ||
 // multiples of 8 elements, A and W 16-byte aligned.
 // k_splits > 1: `out` is [k_splits][M][ldo] 32-bit partial sums for a consumer that adds them (no epilogue).
 extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                               int lda, int ldw, int ldo, int epilogue, int act, int k_splits, cudaStream_t stream) {
+                               int lda, int ldw, int ldo, int epilogue, int act, int k_splits, int room_before,
+                               cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 8 * kMaxTokenTiles) HOS_REFUSE("gemm_skinny: %d rows are more than %d", M, 8 * kMaxTokenTiles);
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
@@ -378,9 +379,12 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     const int k_blocks = (K + 31) / 32, per_cta = (k_blocks + k_splits - 1) / k_splits;
     const int unroll = unroll_for((per_cta + k_ways - 1) / k_ways, (M + 7) / 8);
     const int kind = (M > 8) ? (epilogue == 2 ? 16 : 0) : (epilogue == 2 ? 1 : (out_dtype == kBF16 ? 2 : 4));
-    const int late = (kind == 2 || kind == 4) && skinny_ahead(kind) ? 1 : 0;     // o and down, when launched ahead
+    // `room_before` (the caller's word that the kernel before this one leaves at least half of the SMs free, as the
+    // attention of one sequence does): the o product is then launched ahead as well
+    const bool ahead = skinny_ahead(kind) || (kind == 2 && room_before != 0);
+    const int late = (kind == 2 || kind == 4) && ahead ? 1 : 0;     // o and down, when launched ahead
 #define HOS_SK_W(MT, U, G, T, WP)                                                                                \
-    launch_ahead(skinny_ahead(MT != 1 ? (G ? 16 : 0) : (G ? 1 : (sizeof(T) == 2 ? 2 : 4))), gemm_skinny_kernel<MT, U, G, T, WP>, dim3(grid, k_splits), dim3(WP * 32), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
+    launch_ahead(ahead, gemm_skinny_kernel<MT, U, G, T, WP>, dim3(grid, k_splits), dim3(WP * 32), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
                                                                        M, N, K, lda, ldw, ldo, N, act, late)
 #define HOS_SK(MT, U, G, T) HOS_SK_W(MT, U, G, T, (G ? kGatedWarps : kSkinnyWarps))
 #define HOS_SK_U(MT, G, T)                              \

@@ -172,6 +172,24 @@ def check_errors() -> None:
                       f"the results of the steps since the last check are not valid")
 
 
+_room_left = False
+
+
+def note_room_left(left: bool) -> None:
+    """A launcher's word about the kernel it has just launched: it leaves at least half of the SMs free (the decode
+    attention of one sequence does: 64 CTAs).  The launcher of the next kernel may then place that kernel beside it,
+    ahead of its end (`take_room_left`); with the SMs full, kernels that wait on them cost more than they hide."""
+    global _room_left
+    _room_left = bool(left)
+
+
+def take_room_left() -> bool:
+    """What the last launcher said (see note_room_left); the word holds for one launch."""
+    global _room_left
+    left, _room_left = _room_left, False
+    return left
+
+
 def set_launch_ahead(on: bool) -> None:
     """Whether kernels are launched so that they may be set up while the kernel before them still
     runs (programmatic dependent launch).  It pays for steps of many tokens, whose kernels are

@@ -192,6 +192,9 @@ def decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, token_pos, token_s
              ops._ptr(cache.v_pages), ops._ptr(cache.page_table), cache.table_stride, cache.ring_pages,
              n_tokens, n_heads, nkv, hd, float(scale), float(cap), int(window) if window else 0,
              int(n_splits), int(max_new) if max_new else 1 << 30, ops._stream())
+    # one or two sequences' worth of CTAs leave most SMs free: the product after this kernel may be placed beside it
+    ctas = ops.sm_count() if n_splits == 0 else n_tokens * nkv * ((n_heads // nkv + 15) // 16) * n_splits
+    ops.note_room_left(2 * ctas <= ops.sm_count())
 
 
 def decode_gave_up(head_dim: int) -> bool:

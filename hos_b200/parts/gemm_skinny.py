@@ -40,7 +40,7 @@ def matmul(x, w, out, epilogue: int = ops.EPI_NONE, act: int = 0) -> None:
     m, k = x.shape
     n = out.shape[1]
     lib().call("hos_gemm_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(out), ops.dtype_code(out.dtype), m, n, k,
-               x.stride(0), w.stride(0), out.stride(0), epilogue, act, 1, ops._stream())
+               x.stride(0), w.stride(0), out.stride(0), epilogue, act, 1, 1 if ops.take_room_left() else 0, ops._stream())
 
 
 _MIN_K_PER_CTA = 4096      # below this a CTA's 8 warps have too few loads each to be worth another CTA
@@ -64,7 +64,7 @@ def matmul_partials(x, w, k_splits: Optional[int] = None) -> Optional[torch.Tens
         return None
     parts = torch.empty((k_splits, m, n), dtype=torch.float32, device=x.device)
     lib().call("hos_gemm_skinny", ops._ptr(x), ops._ptr(w), ops._ptr(parts), ops.F32, m, n, k,
-               x.stride(0), w.stride(0), n, ops.EPI_NONE, 0, k_splits, ops._stream())
+               x.stride(0), w.stride(0), n, ops.EPI_NONE, 0, k_splits, 1 if ops.take_room_left() else 0, ops._stream())
     return parts
 
 
