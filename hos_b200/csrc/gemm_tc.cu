@@ -854,9 +854,13 @@ static int launch(const CUtensorMap& mm, const CUtensorMap& mn, const GemmParams
     }
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
     // The gated product of a single-token step (weights as the M operand) follows a norm kernel of a few CTAs:
-    // launched ahead of that kernel's end, its barriers and tensor memory are set up meanwhile.
-    static const bool gated_ahead = !(getenv("HOS_GEMM_TC_AHEAD") && getenv("HOS_GEMM_TC_AHEAD")[0] == '0');
-    launch_ahead(pdl_enabled() || (gated_ahead && SWAP && EPI == kGEpiGated), kernel, dim3(grid), dim3(kGemmThreads),
+    // launched ahead of that kernel's end, its barriers and tensor memory are set up meanwhile.  So are the
+    // products that leave 32-bit partial sums (q/k/v, o and down of 33 to 128 rows): every kernel here lets its own
+    // dependents go only after its wait, so nothing piles up behind them (64 sequences 8.04 -> 7.97 ms a step, 40
+    // sequences 5.80 -> 5.75, 128 sequences 14.50 -> 14.44; the head launched ahead changes nothing).
+    static const bool swapped_ahead = !(getenv("HOS_GEMM_TC_AHEAD") && getenv("HOS_GEMM_TC_AHEAD")[0] == '0');
+    const bool ahead = swapped_ahead && SWAP && (EPI == kGEpiGated || (EPI == kGEpiNone && sizeof(OutT) == 4));
+    launch_ahead(pdl_enabled() || ahead, kernel, dim3(grid), dim3(kGemmThreads),
                  Cfg::kSmem, stream, mm, mn, p);
     return check_launch("gemm_tc");
 }
