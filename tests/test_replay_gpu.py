@@ -88,3 +88,54 @@ def test_replay_in_pieces_matches_the_plain_implementation(tmp_path, name, dtype
     expected = {i: P.forward_logits(w, cfg, r) for i, r in enumerate(reqs)}
     got = run_trace(folder, dtype, trace, str(tmp_path / "out"), extra_args=["--chunk-tokens", chunk_tokens])
     check_trace(trace, got, expected, dtype)
+
+
+SPECIAL_LENGTHS = [1, 2, 63, 64, 65, 127, 128, 129, 191, 192, 193, 256, 257]
+
+
+def build_random(name, seed):
+    """A schedule drawn from a seed: batches, requests fed in pieces, steps that starting and continuing requests
+    share, and tails decoded one by one, over requests whose lengths lie on and around the pages' borders."""
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(seed * 1000 + ord(name))
+    n_req = rng.randint(6, 12)
+    lens = [rng.choice(SPECIAL_LENGTHS) if rng.random() < 0.4 else rng.randint(1, 420) for _ in range(n_req)]
+    reqs = [random_tokens(rng, n, vocab) for n in lens]
+    t = Trace()
+    made = [0]
+
+    def rid(prefix):
+        made[0] += 1
+        return f"{prefix}{made[0]}"
+
+    for _ in range(rng.randint(5, 8)):
+        kind = rng.choice(["batch", "batch", "mixed", "mixed", "chunked", "tail"])
+        if kind == "batch":
+            group = rng.sample(range(n_req), rng.randint(1, min(8, n_req)))
+            plens = [max(1, len(reqs[i]) - rng.choice([0, 1, 3, 32, 70, 130])) for i in group]
+            t.batch([(rid("b"), i, reqs[i]) for i in group], plens)
+        elif kind == "mixed":
+            group = rng.sample(range(n_req), rng.randint(2, min(6, n_req)))
+            joins = [0] + [rng.randint(0, 5) for _ in group[1:]]
+            sizes = [[rng.choice([1, 1, 1, 2, 5, 17, 40, 64, 65, 100, 1000]) for _ in range(rng.randint(1, 5))]
+                     for _ in group]
+            t.mixed([(rid("m"), i, reqs[i]) for i in group], joins, sizes)
+        elif kind == "chunked":
+            i = rng.randrange(n_req)
+            t.chunked(rid("c"), i, reqs[i], [rng.choice([1, 3, 7, 33, 64, 100]) for _ in range(rng.randint(1, 4))])
+        else:
+            i = rng.randrange(n_req)
+            t.tail_one_by_one(rid("t"), i, reqs[i], tail=rng.choice([1, 5, 32, 80]))
+    return reqs, t, rng.choice([1, 24, 100, 2048])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+# these seeds draw rings made for 1, 100, 24 and 2,048 more tokens a step
+@pytest.mark.parametrize("name,seed", [("A", 6), ("B", 4), ("C", 13), ("D", 9)])
+def test_replay_of_a_drawn_schedule_matches_the_plain_implementation(tmp_path, name, seed, dtype):
+    folder = make_folder(tmp_path, name)
+    w, cfg = plain_model(folder)
+    reqs, trace, chunk_tokens = build_random(name, seed)
+    expected = {i: P.forward_logits(w, cfg, r) for i, r in enumerate(reqs)}
+    got = run_trace(folder, dtype, trace, str(tmp_path / "out"), extra_args=["--chunk-tokens", chunk_tokens])
+    check_trace(trace, got, expected, dtype)
