@@ -117,7 +117,6 @@ class DecodeSession:
             return v
         self.meta, self.slot, self.tokens = take(META), take(b), take(b)
         self.pos, self.seq, self.after, self.cu = take(b), take(b), take(b), take(b + 1)     # written on the device
-        self.rows = torch.arange(b, dtype=torch.int32, device=dev)
         self.sampled = torch.zeros(b, dtype=torch.int32, device=dev)
         self.uniforms = torch.zeros(b, dtype=torch.float32, device=dev)
         self.recent_len = torch.zeros(b, dtype=torch.int32, device=dev)
@@ -205,8 +204,7 @@ class DecodeSession:
     def _forward_step(self) -> torch.Tensor:
         r = self.runner
         self._begin(ops.BEGIN_ADVANCE)
-        x = r.model.hidden(self._info(), r.cache)
-        return r.model.logits(x, self.rows)
+        return r.model.step_logits(self._info(), r.cache)
 
     def _forward_generate(self, p: SamplingParams) -> torch.Tensor:
         r = self.runner
@@ -221,8 +219,7 @@ class DecodeSession:
         flags |= ops.BEGIN_UNIFORM if p.temp > 0.0 else 0
         flags |= ops.BEGIN_RECENT if penal else 0
         self._begin(flags, recent)
-        x = r.model.hidden(self._info(), r.cache)
-        logits = r.model.logits(x, self.rows)
+        logits = r.model.step_logits(self._info(), r.cache)
         sample_into(logits, self.sampled, p, self.uniforms, recent, self.recent_len)
         c = r.cache
         ops.slot_end(c.record, c.recent, self.slot, self.meta, self.b, self.sampled)

@@ -67,6 +67,11 @@ class Model:
         (a list) a copy of the residual stream is appended after the embedding and after every entry
         of the run order: what tells where two paths begin to differ (the reference keeps such a tap
         per layer, src/forward.rs:45-103)."""
+        return self._run_layers(step, cache, tap, None)[0]
+
+    def _run_layers(self, step: StepInfo, cache: CacheManager, tap: Optional[list], last_norm):
+        """(x, h): the residual stream after the last entry of the run order and, if `last_norm` is given, that
+        norm of it, which comes out of the last layer's last kernel where the arrangement hands norms on."""
         x = self.embedding.forward(step.tokens, step)
         if tap is not None:
             tap.append(x.clone())
@@ -78,11 +83,22 @@ class Model:
                 h = None
             else:
                 nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
-                next_norm = nxt.entry_norm() if nxt is not None and nxt.chains else None
+                if nxt is None:
+                    next_norm = last_norm
+                else:
+                    next_norm = nxt.entry_norm() if nxt.chains else None
                 h = layer.forward(x, step, cache.stores[i], h_in=h, next_norm=next_norm)
             if tap is not None:
                 tap.append(x.clone())
-        return x
+        if last_norm is None:
+            return x, None
+        return x, (h if h is not None else last_norm.forward(x))
+
+    def step_logits(self, step: StepInfo, cache: CacheManager) -> torch.Tensor:
+        """float32 [N, vocab]: the logits of every row of the step (what a decoding step wants): no rows are
+        picked, and the final norm is the last layer's to hand on."""
+        _, h = self._run_layers(step, cache, None, self.final_norm)
+        return self.head.forward(h)
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """float32 [len(rows), vocab] for the given rows of the residual stream."""
