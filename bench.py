@@ -166,7 +166,6 @@ def measure_decode(eng, batch, ctx, steps, warmup, rng, clocks=None, mixed=False
     (device ms per step, e2e ms per step, kernel launches in the timed region, h2d bytes per step, d2h bytes per
     step, mean length, or with `mixed` the list of the sequences' mean lengths)."""
     import torch
-    from hos_b200 import ops
     r = eng.runner
     vocab = r.vocab_size
     ends = [max(warmup + steps + 1, int(ctx * MIXED[i % len(MIXED)])) if mixed else ctx for i in range(batch)]
@@ -320,7 +319,7 @@ def main() -> int:
 
     import random
     import torch
-    from hos_b200 import Engine, ops
+    from hos_b200 import Engine
     from hos_b200 import models  # noqa: F401
     from hos_b200.registry import config_from_dict
 

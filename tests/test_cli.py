@@ -1,9 +1,7 @@
 """The command line: option names, defaults and exit codes of the reference's `hos`
 (src/main.rs:3459-3577); generation through it on the GPU."""
 import os
-import random
 import subprocess
-import sys
 
 import pytest
 

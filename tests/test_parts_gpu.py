@@ -1,7 +1,6 @@
 """Each kind of part alone, built from a PartSpec through the registry, against the plain
 implementation's function for that part."""
 import math
-import random
 
 import pytest
 import torch

@@ -7,7 +7,6 @@ one token, some by many).  In 32-bit and in bfloat16."""
 import random
 
 import pytest
-import torch
 
 from plain import gemma2_plain as P
 from helpers import TINY, Trace, check_trace, make_folder, plain_model, random_tokens, run_trace
