@@ -32,10 +32,25 @@ def register_architecture(name: str, config_cls: Type[ModelConfig],
 
 
 def registered_architectures():
+    _load_builtins()
     return sorted(_architectures)
 
 
+_builtins_loaded = False
+
+
+def _load_builtins() -> None:
+    """The package's own parts and architectures register themselves when their modules are imported; a look-up
+    that finds nothing imports them once, so that the tables do not depend on what the caller imported before."""
+    global _builtins_loaded
+    if _builtins_loaded:
+        return
+    _builtins_loaded = True
+    from . import models, parts  # noqa: F401
+
+
 def resolve_architecture(raw: Mapping[str, Any]) -> str:
+    _load_builtins()
     archs = raw.get("architectures")
     if isinstance(archs, list):
         for a in archs:
@@ -57,6 +72,9 @@ def config_from_dict(raw: Mapping[str, Any]) -> ModelConfig:
 def plan_for(config: ModelConfig) -> ModelPlan:
     entry = _architectures.get(config.architecture)
     if entry is None:
+        _load_builtins()
+        entry = _architectures.get(config.architecture)
+    if entry is None:
         raise UnsupportedArchError(
             f"unsupported architecture: {config.architecture!r} - registered: "
             f"{', '.join(registered_architectures())}")
@@ -76,6 +94,9 @@ def part_impl(category: str, kind: str) -> Any:
     if table is None:
         raise SpecError(f"arch spec error: unknown part category {category!r}")
     impl = table.get(kind)
+    if impl is None:
+        _load_builtins()
+        impl = table.get(kind)
     if impl is None:
         raise SpecError(f"arch spec error: no {category} of kind {kind!r} is registered "
                         f"(known: {', '.join(sorted(table)) or 'none'})")
