@@ -106,3 +106,18 @@ def test_plan_validation_rejects_bad_run_orders():
     bad.schedule = [LayerCall(0), LayerCall(1, cache_from=0), LayerCall(0, cache_from=1)]
     with pytest.raises(SpecError, match="no cache of its own"):
         bad.validate()
+
+
+def test_registry_finds_the_packages_own_parts_whatever_was_imported_first():
+    """In a fresh interpreter that imported nothing but the registry: a built-in part, the built-in architecture and
+    the list of architectures are there (the tables fill themselves on the first look-up)."""
+    import os
+    import subprocess
+    import sys
+    code = ("from hos_b200.registry import part_impl, registered_architectures, config_from_dict\n"
+            "assert part_impl('norm', 'rmsnorm').__name__ == 'RMSNorm'\n"
+            "assert 'Gemma2ForCausalLM' in registered_architectures()\n"
+            "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-c", code], cwd=root, stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=300)
+    assert p.returncode == 0 and p.stdout.decode().strip() == "ok", p.stderr.decode()[-2000:]
