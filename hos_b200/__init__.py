@@ -8,7 +8,7 @@ from .errors import (CacheError, ExtensionMissingError, FormatError, HosError, I
                      KernelError, MissingMetaError, MissingTensorError, SpecError,
                      UnsupportedArchError, WeightMismatchError)
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 
 def version() -> str:
